@@ -1,0 +1,103 @@
+"""Loader of libbpt_b200.so, the C-ABI CUDA library declared in include/bpt_b200.h.
+
+There is no CPU fallback: if the library has not been built, or no CUDA device is present
+when a kernel is requested, the call raises.
+"""
+import ctypes
+import os
+
+import torch
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libbpt_b200.so")
+
+F32, F64, BF16, F16 = 0, 1, 2, 3
+_DTYPE_CODE = {torch.float32: F32, torch.float64: F64, torch.bfloat16: BF16, torch.float16: F16}
+
+_i64, _int, _vp, _sz, _dbl = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_double
+
+# name -> (restype, argtypes); mirrors include/bpt_b200.h declaration by declaration.
+SIGNATURES = {
+    "bpt_last_error": (ctypes.c_char_p, []),
+    "bpt_version": (_int, []),
+    "bpt_bp_levels": (_int, [_i64, _vp, _vp, _vp, _vp]),
+    "bpt_bp_count_workspace_bytes": (_sz, [_i64]),
+    "bpt_bp_count": (_int, [_i64, _int, _int, _int, _vp, _vp, _sz, _vp, _vp]),
+    "bpt_bp_fill": (_int, [_i64, _int, _int, _int, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "bpt_coo_to_csr_workspace_bytes": (_sz, [_i64, _i64]),
+    "bpt_coo_to_csr": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "bpt_partition_csr_workspace_bytes": (_sz, [_i64]),
+    "bpt_partition_csr_count": (_int, [_vp, _i64, _int, _vp, _vp, _sz, _vp, _vp]),
+    "bpt_partition_csr_fill": (_int, [_vp, _i64, _int, _vp, _i64, _vp, _vp, _vp]),
+    "bpt_maskedmm_csr_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _int, _int, _vp]),
+    "bpt_maskedmm_csr_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
+                                         _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp]),
+    "bpt_node_mul_edge_forward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _int, _int, _vp]),
+    "bpt_node_mul_edge_backward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64,
+                                          _int, _int, _int, _vp]),
+    "bpt_sparse_softmax_forward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _int, _int, _vp]),
+    "bpt_sparse_softmax_backward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _int, _vp]),
+    "bpt_vector_spmm_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
+    "bpt_vector_spmm_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
+                                        _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
+    "bpt_attn_plan_bytes": (_sz, [_i64, _i64, _int]),
+    "bpt_attn_plan_workspace_bytes": (_sz, [_i64, _i64, _int]),
+    "bpt_attn_plan_build": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp, _sz, _vp, _vp]),
+    "bpt_attn_workspace_bytes": (_sz, [_i64, _vp, _int, _int, _int]),
+    "bpt_attn_forward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
+                                _int, _int, _int, _vp, _sz, _vp]),
+    "bpt_attn_backward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp,
+                                 _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library. Raises if it was never built (python -m bpt_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "bpt_b200: %s is missing; build it with `python -m bpt_b200.build` "
+                "(nvcc, sm_100a). There is no CPU fallback." % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        msg = lib().bpt_last_error()
+        raise RuntimeError("bpt_b200 error %d: %s" % (rc, msg.decode() if msg else "unknown"))
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("bpt_b200: expected a CUDA tensor (there is no CPU path)")
+        if not t.is_contiguous():
+            raise RuntimeError("bpt_b200: expected a contiguous tensor")
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype):
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise RuntimeError("bpt_b200: unsupported dtype %s" % dtype)
+
+
+def workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)

@@ -1,0 +1,609 @@
+// Fused graph attention, CUDA-core path: one warp per work item (a destination row or a
+// <=128-edge slice of one), any head count, head dim <= 128, fp32 / bf16 / fp16 storage with
+// fp32 arithmetic.
+//
+// Forward = the reference's masked_mm -> node_mul_edge -> scale -> sparse_softmax ->
+// vec_spmm chain (modules/attention.py:66-77) in one pass per destination row: scores live
+// in shared memory, never in HBM; only O and the row log-sum-exp are written.
+// Backward = three segment reductions with one writer per output element:
+//   over the in-CSR   : P, dS (scratch, in-CSR order) and dQ
+//   over the out-CSR  : dK, dV
+//   over type buckets : d embed_ak
+// Rows longer than a work item are reduced in item order by a merge kernel, so every
+// result is bitwise reproducible (the reference's are not: graph_kernel/atomic.cuh).
+#include "plan.cuh"
+
+namespace bpt {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr int kWarpsPerBlock = 4;
+
+// ---- 16-element slice loads/stores: each lane owns 16 consecutive elements of a head ----
+
+template <typename T, bool kVec>
+__device__ __forceinline__ void load16(const T *__restrict__ p, int nvalid, float (&out)[16]);
+
+template <>
+__device__ __forceinline__ void load16<float, true>(const float *__restrict__ p, int, float (&out)[16]) {
+    const float4 *v = reinterpret_cast<const float4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 x = __ldg(v + i);
+        out[4 * i] = x.x; out[4 * i + 1] = x.y; out[4 * i + 2] = x.z; out[4 * i + 3] = x.w;
+    }
+}
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16, true>(const __nv_bfloat16 *__restrict__ p, int,
+                                                            float (&out)[16]) {
+    const uint4 *v = reinterpret_cast<const uint4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint4 x = __ldg(v + i);
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // bf16 -> fp32 is a 16-bit shift
+            out[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+            out[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    }
+}
+template <>
+__device__ __forceinline__ void load16<__half, true>(const __half *__restrict__ p, int, float (&out)[16]) {
+    const uint4 *v = reinterpret_cast<const uint4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint4 x = __ldg(v + i);
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+            out[8 * i + 2 * j] = f.x;
+            out[8 * i + 2 * j + 1] = f.y;
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ void load16_scalar(const T *__restrict__ p, int nvalid, float (&out)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = i < nvalid ? to_acc(p[i]) : 0.f;
+}
+template <> __device__ __forceinline__ void load16<float, false>(const float *__restrict__ p, int n, float (&o)[16]) { load16_scalar(p, n, o); }
+template <> __device__ __forceinline__ void load16<__nv_bfloat16, false>(const __nv_bfloat16 *__restrict__ p, int n, float (&o)[16]) { load16_scalar(p, n, o); }
+template <> __device__ __forceinline__ void load16<__half, false>(const __half *__restrict__ p, int n, float (&o)[16]) { load16_scalar(p, n, o); }
+
+template <typename T>
+__device__ __forceinline__ void store16(T *__restrict__ p, int nvalid, const float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        if (i < nvalid) p[i] = from_acc<T>(v[i]);
+}
+
+template <int LPH>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int off = LPH / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Everything a kernel needs to locate its slice.
+struct Geometry {
+    int H, D;
+};
+
+// ------------------------------------------------------------------ forward
+
+template <typename T, int LPH, bool kVec>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+attn_forward_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ in_src,
+                    const int32_t *__restrict__ in_etype, const T *__restrict__ q,
+                    const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ ak,
+                    float scale, T *__restrict__ o, float *__restrict__ lse,
+                    float *__restrict__ part_o, float *__restrict__ part_ml, Geometry g) {
+    constexpr int HPW = 32 / LPH;
+    __shared__ float s_all[kWarpsPerBlock][kSegEdges * HPW];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= n_items) return;
+    const int4 it = items[item];
+    const int row = it.x, beg = it.y, n = it.z - it.y, slot = it.w;
+    const int hl = lane / LPH, gl = lane % LPH;
+    const int head = blockIdx.y * HPW + hl;
+    const int d0 = gl * 16;
+    int nvalid = g.D - d0;
+    nvalid = nvalid > 16 ? 16 : nvalid;
+    const bool active = head < g.H && nvalid > 0;
+    const int H = g.H, D = g.D;
+    float *sc = s_all[warp];
+
+    float qf[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qf[i] = 0.f;
+    if (active) load16<T, kVec>(q + (static_cast<int64_t>(row) * H + head) * D + d0, nvalid, qf);
+    const float qs = scale * kLog2e;  // scores are kept in the log2 domain
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qf[i] *= qs;
+
+    for (int j = 0; j < n; ++j) {
+        const int src = in_src[beg + j];
+        float part = 0.f;
+        if (active) {
+            float kf[16];
+            load16<T, kVec>(k + (static_cast<int64_t>(src) * H + head) * D + d0, nvalid, kf);
+            if (ak) {
+                float af[16];
+                load16<T, kVec>(ak + static_cast<int64_t>(in_etype[beg + j]) * D + d0, nvalid, af);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) kf[i] += af[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) part = fmaf(qf[i], kf[i], part);
+        }
+        part = group_sum<LPH>(part);
+        if (gl == 0) sc[j * HPW + hl] = part;
+    }
+    __syncwarp();
+
+    // Row statistics: this lane looks at head (lane % HPW), edges lane / HPW, + LPH, ...
+    const int hh = lane % HPW;
+    float m = -INFINITY;
+    for (int j = lane / HPW; j < n; j += LPH) m = fmaxf(m, sc[j * HPW + hh]);
+#pragma unroll
+    for (int off = HPW; off < 32; off <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float l = 0.f;
+    for (int j = lane / HPW; j < n; j += LPH) {
+        const float p = exp2f(sc[j * HPW + hh] - m);
+        sc[j * HPW + hh] = p;
+        l += p;
+    }
+#pragma unroll
+    for (int off = HPW; off < 32; off <<= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    __syncwarp();
+    const float m_h = __shfl_sync(0xffffffffu, m, hl);  // lane hl holds head hl's statistics
+    const float l_h = __shfl_sync(0xffffffffu, l, hl);
+
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    if (active) {
+        for (int j = 0; j < n; ++j) {
+            const int src = in_src[beg + j];
+            const float p = sc[j * HPW + hl];
+            float vf[16];
+            load16<T, kVec>(v + (static_cast<int64_t>(src) * H + head) * D + d0, nvalid, vf);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+        }
+    }
+    if (!active) return;
+    if (slot < 0) {
+        const float inv = n > 0 ? 1.f / l_h : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] *= inv;
+        store16<T>(o + (static_cast<int64_t>(row) * H + head) * D + d0, nvalid, acc);
+        if (gl == 0) lse[static_cast<int64_t>(row) * H + head] = n > 0 ? (m_h + log2f(l_h)) * kLn2 : -INFINITY;
+    } else {
+        store16<float>(part_o + (static_cast<int64_t>(slot) * H + head) * D + d0, nvalid, acc);
+        if (gl == 0) {
+            part_ml[(static_cast<int64_t>(slot) * H + head) * 2] = m_h;
+            part_ml[(static_cast<int64_t>(slot) * H + head) * 2 + 1] = l_h;
+        }
+    }
+}
+
+// Combines the partial (m, l, o) triples of a split row in slot order.
+template <typename T>
+__global__ void attn_forward_merge_kernel(const int4 *__restrict__ split_rows, int n_split,
+                                          const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                                          T *__restrict__ o, float *__restrict__ lse, Geometry g) {
+    const int sr = blockIdx.x;
+    if (sr >= n_split) return;
+    const int4 rec = split_rows[sr];
+    const int row = rec.x, first = rec.y, count = rec.z;
+    const int HD = g.H * g.D;
+    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+        const int head = c / g.D;
+        float m = -INFINITY;
+        for (int s = 0; s < count; ++s) m = fmaxf(m, part_ml[(static_cast<int64_t>(first + s) * g.H + head) * 2]);
+        float l = 0.f, acc = 0.f;
+        for (int s = 0; s < count; ++s) {
+            const int64_t base = static_cast<int64_t>(first + s) * g.H + head;
+            const float w = exp2f(part_ml[base * 2] - m);
+            l = fmaf(part_ml[base * 2 + 1], w, l);
+            acc = fmaf(part_o[static_cast<int64_t>(first + s) * HD + c], w, acc);
+        }
+        o[static_cast<int64_t>(row) * HD + c] = from_acc<T>(acc / l);
+        if (c % g.D == 0) lse[static_cast<int64_t>(row) * g.H + head] = (m + log2f(l)) * kLn2;
+    }
+}
+
+// ------------------------------------------------------------------ backward, pass over destinations
+
+template <typename T, int LPH, bool kVec>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+attn_backward_dq_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ in_src,
+                        const int32_t *__restrict__ in_etype, const T *__restrict__ q,
+                        const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ ak,
+                        float scale, const T *__restrict__ o, const float *__restrict__ lse,
+                        const T *__restrict__ d_o, float *__restrict__ P, float *__restrict__ dS,
+                        T *__restrict__ dq, float *__restrict__ part_dq, Geometry g) {
+    constexpr int HPW = 32 / LPH;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= n_items) return;
+    const int4 it = items[item];
+    const int row = it.x, beg = it.y, end = it.z, slot = it.w;
+    const int hl = lane / LPH, gl = lane % LPH;
+    const int head = blockIdx.y * HPW + hl;
+    const int d0 = gl * 16;
+    int nvalid = g.D - d0;
+    nvalid = nvalid > 16 ? 16 : nvalid;
+    const bool active = head < g.H && nvalid > 0;
+    const int H = g.H, D = g.D;
+    const int64_t row_off = (static_cast<int64_t>(row) * H + head) * D + d0;
+
+    float qf[16], dof[16], acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { qf[i] = 0.f; dof[i] = 0.f; acc[i] = 0.f; }
+    float delta = 0.f, lse2 = 0.f;
+    if (active) {
+        float of[16];
+        load16<T, kVec>(q + row_off, nvalid, qf);
+        load16<T, kVec>(d_o + row_off, nvalid, dof);
+        load16<T, kVec>(o + row_off, nvalid, of);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) delta = fmaf(dof[i], of[i], delta);
+        lse2 = lse[static_cast<int64_t>(row) * H + head] * kLog2e;
+    }
+    delta = group_sum<LPH>(delta);
+    const float qs = scale * kLog2e;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qf[i] *= qs;
+
+    for (int j = beg; j < end; ++j) {
+        const int src = in_src[j];
+        float kf[16];
+        float s = 0.f, dp = 0.f;
+        if (active) {
+            const int64_t src_off = (static_cast<int64_t>(src) * H + head) * D + d0;
+            float vf[16];
+            load16<T, kVec>(k + src_off, nvalid, kf);
+            load16<T, kVec>(v + src_off, nvalid, vf);
+            if (ak) {
+                float af[16];
+                load16<T, kVec>(ak + static_cast<int64_t>(in_etype[j]) * D + d0, nvalid, af);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) kf[i] += af[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                s = fmaf(qf[i], kf[i], s);
+                dp = fmaf(dof[i], vf[i], dp);
+            }
+        }
+        s = group_sum<LPH>(s);
+        dp = group_sum<LPH>(dp);
+        if (active) {
+            const float p = exp2f(s - lse2);
+            const float ds = p * (dp - delta) * scale;
+            if (gl == 0) {
+                P[static_cast<int64_t>(j) * H + head] = p;
+                dS[static_cast<int64_t>(j) * H + head] = ds;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(ds, kf[i], acc[i]);
+        }
+    }
+    if (!active) return;
+    if (slot < 0)
+        store16<T>(dq + row_off, nvalid, acc);
+    else
+        store16<float>(part_dq + (static_cast<int64_t>(slot) * H + head) * D + d0, nvalid, acc);
+}
+
+// ------------------------------------------------------------------ backward, pass over sources
+
+template <typename T, int LPH, bool kVec>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ out_dst,
+                         const int32_t *__restrict__ out_inpos, const T *__restrict__ q,
+                         const T *__restrict__ d_o, const float *__restrict__ P,
+                         const float *__restrict__ dS, T *__restrict__ dk, T *__restrict__ dv,
+                         float *__restrict__ part_dkv, Geometry g) {
+    constexpr int HPW = 32 / LPH;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= n_items) return;
+    const int4 it = items[item];
+    const int row = it.x, beg = it.y, end = it.z, slot = it.w;
+    const int hl = lane / LPH, gl = lane % LPH;
+    const int head = blockIdx.y * HPW + hl;
+    const int d0 = gl * 16;
+    int nvalid = g.D - d0;
+    nvalid = nvalid > 16 ? 16 : nvalid;
+    if (!(head < g.H && nvalid > 0)) return;  // no warp-wide operation below
+    const int H = g.H, D = g.D;
+
+    float dkf[16], dvf[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { dkf[i] = 0.f; dvf[i] = 0.f; }
+    for (int j = beg; j < end; ++j) {
+        const int dst = out_dst[j];
+        const int64_t pos = out_inpos[j];
+        const float ds = dS[pos * H + head], p = P[pos * H + head];
+        const int64_t dst_off = (static_cast<int64_t>(dst) * H + head) * D + d0;
+        float qf[16], dof[16];
+        load16<T, kVec>(q + dst_off, nvalid, qf);
+        load16<T, kVec>(d_o + dst_off, nvalid, dof);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            dkf[i] = fmaf(ds, qf[i], dkf[i]);
+            dvf[i] = fmaf(p, dof[i], dvf[i]);
+        }
+    }
+    const int64_t row_off = (static_cast<int64_t>(row) * H + head) * D + d0;
+    if (slot < 0) {
+        store16<T>(dk + row_off, nvalid, dkf);
+        store16<T>(dv + row_off, nvalid, dvf);
+    } else {
+        const int64_t HD = static_cast<int64_t>(H) * D;
+        float *base = part_dkv + static_cast<int64_t>(slot) * 2 * HD + static_cast<int64_t>(head) * D + d0;
+        store16<float>(base, nvalid, dkf);
+        store16<float>(base + HD, nvalid, dvf);
+    }
+}
+
+// ------------------------------------------------------------------ backward, pass over type buckets
+
+template <typename T, int LPH, bool kVec>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ et_dst,
+                         const int32_t *__restrict__ et_inpos, const T *__restrict__ q,
+                         const float *__restrict__ dS, float *__restrict__ dak,
+                         float *__restrict__ part_dak, Geometry g) {
+    constexpr int HPW = 32 / LPH;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= n_items) return;
+    const int4 it = items[item];
+    const int row = it.x, beg = it.y, end = it.z, slot = it.w;
+    const int hl = lane / LPH, gl = lane % LPH;
+    const int d0 = gl * 16;
+    int nvalid = g.D - d0;
+    nvalid = nvalid > 16 ? 16 : nvalid;
+    const int H = g.H, D = g.D;
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    for (int h0 = 0; h0 < H; h0 += HPW) {
+        const int head = h0 + hl;
+        if (head < H && nvalid > 0) {
+            for (int j = beg; j < end; ++j) {
+                const int dst = et_dst[j];
+                const float ds = dS[static_cast<int64_t>(et_inpos[j]) * H + head];
+                float qf[16];
+                load16<T, kVec>(q + (static_cast<int64_t>(dst) * H + head) * D + d0, nvalid, qf);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] = fmaf(ds, qf[i], acc[i]);
+            }
+        }
+    }
+    // Sum over the heads held by lanes with the same gl, in a fixed butterfly order.
+#pragma unroll
+    for (int off = LPH; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+    }
+    if (hl == 0 && nvalid > 0) {
+        float *out = slot < 0 ? dak + static_cast<int64_t>(row) * D + d0
+                              : part_dak + static_cast<int64_t>(slot) * D + d0;
+        store16<float>(out, nvalid, acc);
+    }
+}
+
+// out[row, c] = sum over the row's slots, in slot order, of part[slot * stride + c], for
+// `n_out` output arrays laid side by side in a slot (dK|dV share a slot).
+template <typename T>
+__global__ void sum_merge_kernel(const int4 *__restrict__ split_rows, int n_split,
+                                 const float *__restrict__ part, int width, int n_out,
+                                 T *__restrict__ out0, T *__restrict__ out1) {
+    const int sr = blockIdx.x;
+    if (sr >= n_split) return;
+    const int4 rec = split_rows[sr];
+    const int row = rec.x, first = rec.y, count = rec.z;
+    const int stride = width * n_out;
+    for (int c = threadIdx.x; c < stride; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < count; ++s) acc += part[static_cast<int64_t>(first + s) * stride + c];
+        if (c < width)
+            out0[static_cast<int64_t>(row) * width + c] = from_acc<T>(acc);
+        else
+            out1[static_cast<int64_t>(row) * width + (c - width)] = from_acc<T>(acc);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+struct Scratch {
+    float *part_o, *part_ml;            // forward
+    float *P, *dS, *part_dq, *part_dkv, *part_dak;  // backward
+};
+
+size_t forward_ws_bytes(const int32_t *counts, int H, int D) {
+    const size_t slots = static_cast<size_t>(counts[1]);
+    return align_up(slots * H * D * 4, 256) + align_up(slots * H * 2 * 4, 256) + 512;
+}
+
+size_t backward_ws_bytes(int64_t n_edges, const int32_t *counts, int H, int D) {
+    const size_t e = static_cast<size_t>(n_edges);
+    return 2 * align_up(e * H * 4, 256) + align_up(static_cast<size_t>(counts[1]) * H * D * 4, 256) +
+           align_up(static_cast<size_t>(counts[4]) * 2 * H * D * 4, 256) +
+           align_up(static_cast<size_t>(counts[7]) * D * 4, 256) + 1024;
+}
+
+int pick_lph(int D) { return D <= 32 ? 2 : (D <= 64 ? 4 : 8); }
+
+template <typename T>
+bool can_vectorise(int D, int lph, const void *a, const void *b, const void *c, const void *d, const void *e,
+                   const void *f) {
+    if (D != 16 * lph) return false;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                           reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d) |
+                           reinterpret_cast<uintptr_t>(e) | reinterpret_cast<uintptr_t>(f);
+    return (bits & 15) == 0;
+}
+
+#define BPT_DISPATCH_LPH_VEC(lph, vec, ...)                                         \
+    do {                                                                            \
+        if (lph == 2) {                                                             \
+            constexpr int LPH = 2;                                                  \
+            if (vec) { constexpr bool VEC = true; __VA_ARGS__; } else { constexpr bool VEC = false; __VA_ARGS__; } \
+        } else if (lph == 4) {                                                      \
+            constexpr int LPH = 4;                                                  \
+            if (vec) { constexpr bool VEC = true; __VA_ARGS__; } else { constexpr bool VEC = false; __VA_ARGS__; } \
+        } else {                                                                    \
+            constexpr int LPH = 8;                                                  \
+            if (vec) { constexpr bool VEC = true; __VA_ARGS__; } else { constexpr bool VEC = false; __VA_ARGS__; } \
+        }                                                                           \
+    } while (0)
+
+template <typename T>
+int forward_impl(const PlanView &p, const int32_t *counts, const void *q_, const void *k_, const void *v_,
+                 const void *ak_, float scale, void *o_, float *lse, int H, int D, void *ws_ptr,
+                 size_t ws_bytes, cudaStream_t stream) {
+    const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
+    const T *ak = static_cast<const T *>(ak_);
+    T *o = static_cast<T *>(o_);
+    Workspace ws(ws_ptr, ws_bytes);
+    const size_t slots = static_cast<size_t>(counts[1]);
+    float *part_o = ws.take<float>(slots * H * D);
+    float *part_ml = ws.take<float>(slots * H * 2);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_forward: workspace of %zu bytes is too small", ws_bytes);
+    const int n_items = counts[0], n_split = counts[2];
+    if (n_items == 0) return BPT_OK;
+    const int lph = pick_lph(D);
+    const bool vec = can_vectorise<T>(D, lph, q, k, v, ak, o, o);
+    const Geometry g{H, D};
+    const int hpw = 32 / lph;
+    const dim3 grid((n_items + kWarpsPerBlock - 1) / kWarpsPerBlock, (H + hpw - 1) / hpw);
+    BPT_DISPATCH_LPH_VEC(lph, vec, (attn_forward_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        p.in_work.items, n_items, p.in_src, p.in_etype, q, k, v, ak, scale, o, lse, part_o, part_ml, g)));
+    BPT_LAUNCH_CHECK();
+    if (n_split > 0) {
+        attn_forward_merge_kernel<T><<<n_split, 256, 0, stream>>>(p.in_work.split_rows, n_split, part_o,
+                                                                  part_ml, o, lse, g);
+        BPT_LAUNCH_CHECK();
+    }
+    return BPT_OK;
+}
+
+template <typename T>
+int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, const void *k_, const void *v_,
+                  const void *ak_, float scale, const void *o_, const float *lse, const void *do_,
+                  void *dq_, void *dk_, void *dv_, float *dak, int H, int D, void *ws_ptr, size_t ws_bytes,
+                  cudaStream_t stream) {
+    const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
+    const T *ak = static_cast<const T *>(ak_), *o = static_cast<const T *>(o_), *d_o = static_cast<const T *>(do_);
+    T *dq = static_cast<T *>(dq_), *dk = static_cast<T *>(dk_), *dv = static_cast<T *>(dv_);
+    Workspace ws(ws_ptr, ws_bytes);
+    const size_t e = static_cast<size_t>(p.n_edges);
+    float *P = ws.take<float>(e * H);
+    float *dS = ws.take<float>(e * H);
+    float *part_dq = ws.take<float>(static_cast<size_t>(counts[1]) * H * D);
+    float *part_dkv = ws.take<float>(static_cast<size_t>(counts[4]) * 2 * H * D);
+    float *part_dak = ws.take<float>(static_cast<size_t>(counts[7]) * D);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward: workspace of %zu bytes is too small", ws_bytes);
+    const int lph = pick_lph(D);
+    const bool vec = can_vectorise<T>(D, lph, q, k, v, ak, o, d_o) && can_vectorise<T>(D, lph, dq, dk, dv, dq, dq, dq);
+    const Geometry g{H, D};
+    const int hpw = 32 / lph;
+    const unsigned gy = (H + hpw - 1) / hpw;
+    if (counts[0] > 0) {
+        const dim3 grid((counts[0] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.in_work.items, counts[0], p.in_src, p.in_etype, q, k, v, ak, scale, o, lse, d_o, P, dS, dq,
+            part_dq, g)));
+        BPT_LAUNCH_CHECK();
+        if (counts[2] > 0) {
+            sum_merge_kernel<T><<<counts[2], 256, 0, stream>>>(p.in_work.split_rows, counts[2], part_dq, H * D, 1,
+                                                              dq, dq);
+            BPT_LAUNCH_CHECK();
+        }
+    }
+    if (counts[3] > 0) {
+        const dim3 grid((counts[3] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dkv_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dS, dk, dv, part_dkv, g)));
+        BPT_LAUNCH_CHECK();
+        if (counts[5] > 0) {
+            sum_merge_kernel<T><<<counts[5], 256, 0, stream>>>(p.out_work.split_rows, counts[5], part_dkv, H * D,
+                                                              2, dk, dv);
+            BPT_LAUNCH_CHECK();
+        }
+    }
+    if (ak != nullptr && dak != nullptr && counts[6] > 0) {
+        const dim3 grid((counts[6] + kWarpsPerBlock - 1) / kWarpsPerBlock, 1);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, dS, dak, part_dak, g)));
+        BPT_LAUNCH_CHECK();
+        if (counts[8] > 0) {
+            sum_merge_kernel<float><<<counts[8], 128, 0, stream>>>(p.et_work.split_rows, counts[8], part_dak, D, 1,
+                                                                  dak, dak);
+            BPT_LAUNCH_CHECK();
+        }
+    }
+    return BPT_OK;
+}
+
+int check_attn_args(const char *name, const void *plan, const int32_t *counts, int64_t n_nodes,
+                    int64_t n_edges, int n_etypes, int H, int D, int dtype) {
+    BPT_CHECK_ARG(plan != nullptr && counts != nullptr, "%s: null plan", name);
+    BPT_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && n_etypes >= 1, "%s: bad sizes", name);
+    BPT_CHECK_ARG(H >= 1 && D >= 1, "%s: h and d must be positive", name);
+    if (D > 128) return fail(BPT_ERR_UNSUPPORTED, "%s: head dim %d > 128 has no kernel", name, D);
+    if (dtype == BPT_F64) return fail(BPT_ERR_UNSUPPORTED, "%s: fp64 has no fused kernel (use the operators)", name);
+    return BPT_OK;
+}
+
+}  // namespace
+}  // namespace bpt
+
+using namespace bpt;
+
+extern "C" size_t bpt_attn_workspace_bytes(int64_t n_edges, const int32_t *counts, int h, int d, int backward) {
+    if (counts == nullptr || n_edges < 0 || h < 1 || d < 1) return 0;
+    return backward ? backward_ws_bytes(n_edges, counts, h, d) : forward_ws_bytes(counts, h, d);
+}
+
+extern "C" int bpt_attn_forward(const void *plan, const int32_t *counts, int64_t n_nodes, int64_t n_edges,
+                                int n_etypes, const void *q, const void *k, const void *v, const void *ak,
+                                double scale, void *o, float *lse, int h, int d, int dtype, void *workspace,
+                                size_t workspace_bytes, bpt_stream_t stream) {
+    if (int rc = check_attn_args("attn_forward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
+    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && o && lse), "attn_forward: null tensor");
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
+    switch (dtype) {
+        case BPT_F32: return forward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_BF16: return forward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_F16: return forward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
+        default: return fail(BPT_ERR_UNSUPPORTED, "attn_forward: unknown dtype code %d", dtype);
+    }
+}
+
+extern "C" int bpt_attn_backward(const void *plan, const int32_t *counts, int64_t n_nodes, int64_t n_edges,
+                                 int n_etypes, const void *q, const void *k, const void *v, const void *ak,
+                                 double scale, const void *o, const float *lse, const void *d_o, void *dq,
+                                 void *dk, void *dv, float *dak, int h, int d, int dtype, void *workspace,
+                                 size_t workspace_bytes, bpt_stream_t stream) {
+    if (int rc = check_attn_args("attn_backward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
+    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && o && lse && d_o && dq && dk && dv), "attn_backward: null tensor");
+    BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward: ak given without dak");
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
+    switch (dtype) {
+        case BPT_F32: return backward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_BF16: return backward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_F16: return backward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        default: return fail(BPT_ERR_UNSUPPORTED, "attn_backward: unknown dtype code %d", dtype);
+    }
+}

@@ -1,0 +1,186 @@
+// Builds the fused-attention plan on the device: the in-CSR the forward walks, the out-CSR
+// and the by-type buckets the backward's segment reductions walk, and warp-sized work lists
+// for each.  All of it is integer work derived from the COO edge list; none of it exists in
+// the reference, which hands int64 CSRs and 32-edge chunk arrays (graph/base.py:71-86) to
+// one kernel per operator.
+#include <cub/device/device_scan.cuh>
+
+#include "plan.cuh"
+
+namespace bpt {
+namespace {
+
+__global__ void permute_in_kernel(const int32_t *__restrict__ in_eid, const int32_t *__restrict__ etype,
+                                  int64_t n_edges, int32_t *__restrict__ in_etype,
+                                  int32_t *__restrict__ inpos_of_eid) {
+    const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (p >= n_edges) return;
+    const int32_t e = in_eid[p];
+    in_etype[p] = etype ? etype[e] : 0;
+    inpos_of_eid[e] = static_cast<int32_t>(p);
+}
+
+__global__ void gather_kernel(const int32_t *__restrict__ idx, const int32_t *__restrict__ table,
+                              int64_t n, int32_t *__restrict__ out) {
+    const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (p < n) out[p] = table[idx[p]];
+}
+
+__global__ void zero_keys_kernel(int64_t n, int32_t *__restrict__ out) {
+    const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (p < n) out[p] = 0;
+}
+
+// Per row: how many items, slots and split-row records it contributes.
+__global__ void work_count_kernel(const int32_t *__restrict__ indptr, int64_t n_rows,
+                                  int32_t *__restrict__ n_items, int32_t *__restrict__ n_slots,
+                                  int32_t *__restrict__ n_split) {
+    const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (r > n_rows) return;
+    int items = 0;
+    if (r < n_rows) {
+        const int deg = indptr[r + 1] - indptr[r];
+        items = deg <= kSegEdges ? 1 : (deg + kSegEdges - 1) / kSegEdges;
+    }
+    n_items[r] = items;
+    n_slots[r] = items > 1 ? items : 0;
+    n_split[r] = items > 1 ? 1 : 0;
+}
+
+__global__ void work_fill_kernel(const int32_t *__restrict__ indptr, int64_t n_rows,
+                                 const int32_t *__restrict__ item_off, const int32_t *__restrict__ slot_off,
+                                 const int32_t *__restrict__ split_off, WorkList w) {
+    const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (r == n_rows) {
+        w.counters[0] = item_off[n_rows];
+        w.counters[1] = slot_off[n_rows];
+        w.counters[2] = split_off[n_rows];
+    }
+    if (r >= n_rows) return;
+    const int beg = indptr[r], end = indptr[r + 1];
+    const int items = item_off[r + 1] - item_off[r];
+    if (items == 1) {
+        w.items[item_off[r]] = make_int4(static_cast<int>(r), beg, end, -1);
+        return;
+    }
+    // Split evenly so no item is nearly empty.
+    const int deg = end - beg;
+    const int per = (deg + items - 1) / items;
+    for (int i = 0; i < items; ++i) {
+        const int b = beg + i * per;
+        int e = b + per;
+        if (e > end) e = end;
+        w.items[item_off[r] + i] = make_int4(static_cast<int>(r), b, e, slot_off[r] + i);
+    }
+    w.split_rows[split_off[r]] = make_int4(static_cast<int>(r), slot_off[r], items, 0);
+}
+
+size_t scan_i32_temp_bytes(int64_t n) {
+    size_t bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, bytes, static_cast<const int32_t *>(nullptr),
+                                  static_cast<int32_t *>(nullptr), n);
+    return bytes;
+}
+
+int build_work(const int32_t *indptr, int64_t n_rows, WorkList w, Workspace &ws, cudaStream_t stream) {
+    const size_t n1 = static_cast<size_t>(n_rows + 1);
+    int32_t *cnt = ws.take<int32_t>(3 * n1);
+    int32_t *off = ws.take<int32_t>(3 * n1);
+    size_t temp_bytes = scan_i32_temp_bytes(n_rows + 1);
+    char *temp = ws.take<char>(temp_bytes > 0 ? temp_bytes : 1);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: workspace too small");
+    const unsigned blocks = static_cast<unsigned>((n_rows + 1 + 255) / 256);
+    work_count_kernel<<<blocks, 256, 0, stream>>>(indptr, n_rows, cnt, cnt + n1, cnt + 2 * n1);
+    BPT_LAUNCH_CHECK();
+    for (int i = 0; i < 3; ++i)
+        BPT_CUDA(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, cnt + i * n1, off + i * n1, n_rows + 1, stream));
+    work_fill_kernel<<<blocks, 256, 0, stream>>>(indptr, n_rows, off, off + n1, off + 2 * n1, w);
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+size_t work_ws_bytes(int64_t n_rows) {
+    const size_t n1 = static_cast<size_t>(n_rows + 1);
+    return 2 * align_up(3 * n1 * 4, 256) + align_up(scan_i32_temp_bytes(n_rows + 1), 256) + 256;
+}
+
+}  // namespace
+}  // namespace bpt
+
+using namespace bpt;
+
+extern "C" size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes) {
+    if (n_nodes < 0 || n_edges < 0 || n_etypes < 1) return 0;
+    return plan_view(nullptr, n_nodes, n_edges, n_etypes).bytes;
+}
+
+extern "C" size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes) {
+    if (n_nodes < 0 || n_edges < 0 || n_etypes < 1) return 0;
+    const int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
+    return 3 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 3 * work_ws_bytes(rows) + 1024;
+}
+
+extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
+                                   int64_t n_edges, int64_t n_nodes, int n_etypes, void *plan,
+                                   size_t plan_bytes, void *workspace, size_t workspace_bytes,
+                                   int32_t *counts_host, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && n_etypes >= 1, "attn_plan_build: bad sizes");
+    if (n_nodes >= (int64_t(1) << 31) - 1 || n_edges >= (int64_t(1) << 31) - 1)
+        return fail(BPT_ERR_OVERFLOW, "attn_plan_build: nodes or edges exceed 32-bit indices");
+    BPT_CHECK_ARG(plan != nullptr && counts_host != nullptr, "attn_plan_build: null output");
+    BPT_CHECK_ARG(n_edges == 0 || (src && dst), "attn_plan_build: null edge arrays");
+    PlanView p = plan_view(plan, n_nodes, n_edges, n_etypes);
+    if (plan_bytes < p.bytes) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: plan buffer too small");
+    cudaStream_t stream = as_stream(stream_);
+    Workspace ws(workspace, workspace_bytes);
+    const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
+    int32_t *tmp_eid = ws.take<int32_t>(e);
+    int32_t *inpos_of_eid = ws.take<int32_t>(e);
+    int32_t *zero_keys = ws.take<int32_t>(e);
+    const int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    const size_t csr_ws_bytes = bpt_coo_to_csr_workspace_bytes(n_edges, rows);
+    char *csr_ws = ws.take<char>(csr_ws_bytes);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: workspace too small");
+    const unsigned eb = static_cast<unsigned>((n_edges + 255) / 256);
+
+    // in-CSR (rows = destinations)
+    if (int rc = bpt_coo_to_csr(dst, src, n_edges, n_nodes, 4, p.in_indptr, p.in_src, tmp_eid, csr_ws,
+                                csr_ws_bytes, stream_))
+        return rc;
+    if (n_edges > 0) {
+        permute_in_kernel<<<eb, 256, 0, stream>>>(tmp_eid, etype, n_edges, p.in_etype, inpos_of_eid);
+        BPT_LAUNCH_CHECK();
+    }
+    // out-CSR (rows = sources)
+    if (int rc = bpt_coo_to_csr(src, dst, n_edges, n_nodes, 4, p.out_indptr, p.out_dst, tmp_eid, csr_ws,
+                                csr_ws_bytes, stream_))
+        return rc;
+    if (n_edges > 0) {
+        gather_kernel<<<eb, 256, 0, stream>>>(tmp_eid, inpos_of_eid, n_edges, p.out_inpos);
+        BPT_LAUNCH_CHECK();
+    }
+    // buckets by edge type
+    const int32_t *keys = etype;
+    if (etype == nullptr && n_edges > 0) {
+        zero_keys_kernel<<<eb, 256, 0, stream>>>(n_edges, zero_keys);
+        BPT_LAUNCH_CHECK();
+        keys = zero_keys;
+    }
+    if (int rc = bpt_coo_to_csr(keys, dst, n_edges, n_etypes, 4, p.et_indptr, p.et_dst, tmp_eid, csr_ws,
+                                csr_ws_bytes, stream_))
+        return rc;
+    if (n_edges > 0) {
+        gather_kernel<<<eb, 256, 0, stream>>>(tmp_eid, inpos_of_eid, n_edges, p.et_inpos);
+        BPT_LAUNCH_CHECK();
+    }
+    // work lists
+    if (int rc = build_work(p.in_indptr, n_nodes, p.in_work, ws, stream)) return rc;
+    if (int rc = build_work(p.out_indptr, n_nodes, p.out_work, ws, stream)) return rc;
+    if (int rc = build_work(p.et_indptr, n_etypes, p.et_work, ws, stream)) return rc;
+    BPT_CUDA(cudaMemcpyAsync(counts_host + 0, p.in_work.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    BPT_CUDA(cudaMemcpyAsync(counts_host + 3, p.out_work.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    BPT_CUDA(cudaMemcpyAsync(counts_host + 6, p.et_work.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    BPT_CUDA(cudaStreamSynchronize(stream));
+    return BPT_OK;
+}

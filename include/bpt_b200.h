@@ -1,0 +1,220 @@
+/*
+ * bpt_b200 — C ABI of the B200 (sm_100a) implementation of BP-Transformer's graph
+ * attention hot path.  Plain pointers and sizes only; every pointer named "device" must
+ * be device memory of the current CUDA device, every launch goes to the given stream and
+ * no entry point synchronises unless it says so.  All functions return 0 on success and a
+ * BPT_ERR_* code otherwise; bpt_last_error() gives the message of the calling thread's
+ * last failure.
+ *
+ * Each entry point names the reference interface it replaces (paths are relative to the
+ * yzh119/BPT source tree).
+ */
+#ifndef BPT_B200_H_
+#define BPT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *bpt_stream_t; /* a cudaStream_t */
+
+enum {
+    BPT_OK = 0,
+    BPT_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, unsupported shape) */
+    BPT_ERR_CUDA = 2,        /* a CUDA runtime call or launch failed */
+    BPT_ERR_WORKSPACE = 3,   /* workspace too small */
+    BPT_ERR_UNSUPPORTED = 4, /* dtype / head-dim combination without a kernel */
+    BPT_ERR_OVERFLOW = 5     /* a size does not fit the 32-bit indices of the fused path */
+};
+
+/* Element types of feature tensors. Accumulation is fp32 (fp64 for BPT_F64). */
+enum { BPT_F32 = 0, BPT_F64 = 1, BPT_BF16 = 2, BPT_F16 = 3 };
+
+const char *bpt_last_error(void);
+int bpt_version(void);
+
+/* ------------------------------------------------------------------------------------
+ * Binary-partition graph construction.
+ * Replaces BinaryPartition.__cinit__/build_graph, graph_builder/builder.pyx:29-116.
+ * Results are bit-identical to that code for the same (length, triu, step, clip_dist).
+ * ---------------------------------------------------------------------------------- */
+
+/* Level table (host only, no GPU work): builder.pyx:41-56.  n_nodes_arr and shift are host
+ * arrays of at least 64 entries; entry j is the size / first node id of level j. */
+int bpt_bp_levels(int64_t length, uint32_t *n_nodes_arr, uint32_t *shift,
+                  int64_t *n_nodes, int *n_levels);
+
+/* Bytes of device workspace bpt_bp_count needs. */
+size_t bpt_bp_count_workspace_bytes(int64_t length);
+
+/* Per-leaf edge counts and their exclusive prefix sum (builder.pyx:64-116 replayed without
+ * writing).  leaf_offsets: device int64[length+1]; leaf_offsets[i] is the edge id of leaf
+ * i's first edge, leaf_offsets[length] the edge count.  If n_edges_host is not NULL the
+ * call waits for the stream and stores the edge count there. */
+int bpt_bp_count(int64_t length, int triu, int step, int clip_dist, int64_t *leaf_offsets,
+                 void *workspace, size_t workspace_bytes, int64_t *n_edges_host,
+                 bpt_stream_t stream);
+
+/* Writes the edge list in the reference's emission order (builder.pyx:64-116) and the
+ * node positions (builder.pyx:46-47,57-62).  src/dst get v_shift added, which is how
+ * get_edges(v_shift) (builder.pyx:137-140) and the block-diagonal batching of
+ * graph/lm.py:59-98 place a sequence inside a batch.  Outputs are device arrays of
+ * n_edges (src, dst, etype) and n_nodes (pos) entries; index_bytes selects int32 (4) or
+ * int64 (8) elements.  Any of the output pointers may be NULL. */
+int bpt_bp_fill(int64_t length, int triu, int step, int clip_dist,
+                const int64_t *leaf_offsets, int64_t v_shift, int index_bytes,
+                void *src, void *dst, void *etype, void *pos, bpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * CSR extraction.  Replaces get_csrs(), graph/base.py:71-86 (two COO->CSR conversions and
+ * two partition_csr calls).  Entries of a row are in ascending edge-id order.
+ * ---------------------------------------------------------------------------------- */
+
+size_t bpt_coo_to_csr_workspace_bytes(int64_t n_edges, int64_t n_rows);
+
+/* key[e] = row of edge e, other[e] = its column; index_bytes = 4 or 8 for every array.
+ * indptr[n_rows+1], indices[n_edges] = other[eid], eid[n_edges]. */
+int bpt_coo_to_csr(const void *key, const void *other, int64_t n_edges, int64_t n_rows,
+                   int index_bytes, void *indptr, void *indices, void *eid,
+                   void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+
+size_t bpt_partition_csr_workspace_bytes(int64_t n_rows);
+
+/* partition_csr(indptr, chunk_size), graph_builder/builder.pyx:305-321, in two steps.
+ * Count: chunk_offsets device int64[n_rows+1] (first chunk id of every row; last entry =
+ * number of chunks).  If n_chunks_host is not NULL the call waits for the stream. */
+int bpt_partition_csr_count(const int64_t *indptr, int64_t n_rows, int chunk_size,
+                            int64_t *chunk_offsets, void *workspace, size_t workspace_bytes,
+                            int64_t *n_chunks_host, bpt_stream_t stream);
+/* Fill: row int64[n_chunks], indptr_out int64[n_chunks+1]. */
+int bpt_partition_csr_fill(const int64_t *indptr, int64_t n_rows, int chunk_size,
+                           const int64_t *chunk_offsets, int64_t n_chunks, int64_t *row,
+                           int64_t *indptr_out, bpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * The eight graph operators.  Replace the functions exported by graph_kernel/graphop.cpp:
+ * 216-225 (kernels in graph_kernel/graphop_kernel.cu).  `row`/`indptr` are the chunk
+ * arrays of partition_csr (n_chunks and n_chunks+1 entries, rows non-decreasing), `eid`
+ * maps CSR position to edge id, `indices` is the other endpoint; all int64, device.
+ * Feature tensors are contiguous (N,h,d) / (E,h); dtype is a BPT_* element type.
+ * Unlike the reference no operator uses floating-point atomics: results are bitwise
+ * reproducible.  Outputs indexed by edge id are written only at edge ids that occur in
+ * `eid`; the caller zero-fills them first if the CSR does not cover every edge (the
+ * reference allocates them with at::zeros, graphop_kernel.cu:248,284).
+ * ---------------------------------------------------------------------------------- */
+
+/* maskedmm_csr_forward, graphop.cpp:16-30 / graphop_kernel.cu:269-304:
+ * y[eid[j],h] = sum_d A[row_of(j),h,d] * B[indices[j],h,d]. */
+int bpt_maskedmm_csr_forward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                             const int64_t *indices, int64_t n_chunks,
+                             const void *A, const void *B, void *y,
+                             int h, int d, int dtype, bpt_stream_t stream);
+
+/* maskedmm_csr_backward, graphop.cpp:104-131 / graphop_kernel.cu:355-409:
+ * dA[r] = sum over the (row,...) CSR of dy * B[indices]; dB[c] = sum over the (col,...)
+ * CSR of dy * A[indices].  n_rows_a / n_rows_b: rows of dA / dB (zero-filled by the call
+ * for rows without edges). */
+int bpt_maskedmm_csr_backward(const int64_t *row, const int64_t *indptr_r, const int64_t *eid_r,
+                              const int64_t *indices_r, int64_t n_chunks_r,
+                              const int64_t *col, const int64_t *indptr_c, const int64_t *eid_c,
+                              const int64_t *indices_c, int64_t n_chunks_c,
+                              const void *A, const void *B, const void *dy,
+                              void *dA, void *dB, int64_t n_rows_a, int64_t n_rows_b,
+                              int h, int d, int dtype, bpt_stream_t stream);
+
+/* node_mul_edge_forward, graphop.cpp:38-51 / graphop_kernel.cu:235-266:
+ * y[eid[j],h] = sum_d A[row_of(j),h,d] * B[eid[j],d]. */
+int bpt_node_mul_edge_forward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                              int64_t n_chunks, const void *A, const void *B, void *y,
+                              int h, int d, int dtype, bpt_stream_t stream);
+
+/* node_mul_edge_backward, graphop.cpp:133-154 / graphop_kernel.cu:306-351:
+ * dA[r,h,:] = sum_j dy[eid[j],h] * B[eid[j],:]; dB[eid[j],:] = sum_h dy[eid[j],h] * A[r,h,:]. */
+int bpt_node_mul_edge_backward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                               int64_t n_chunks, const void *A, const void *B, const void *dy,
+                               void *dA, void *dB, int64_t n_rows_a,
+                               int h, int d, int dtype, bpt_stream_t stream);
+
+/* sparse_softmax_forward, graphop.cpp:59-70 / graphop_kernel.cu:411-463:
+ * softmax of x over the entries of each CSR row, per head. */
+int bpt_sparse_softmax_forward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                               int64_t n_chunks, const void *x, void *y,
+                               int h, int dtype, bpt_stream_t stream);
+
+/* sparse_softmax_backward, graphop.cpp:156-171 / graphop_kernel.cu:465-507:
+ * dx = y * (dy - sum_row(dy*y)). */
+int bpt_sparse_softmax_backward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                                int64_t n_chunks, const void *y, const void *dy, void *dx,
+                                int h, int dtype, bpt_stream_t stream);
+
+/* vector_spmm_forward, graphop.cpp:80-95 / graphop_kernel.cu:509-542:
+ * y[r,h,:] = sum_j edata[eid[j],h] * x[indices[j],h,:]; rows without edges get zero. */
+int bpt_vector_spmm_forward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                            const int64_t *indices, int64_t n_chunks,
+                            const void *edata, const void *x, void *y, int64_t n_rows_y,
+                            int h, int d, int dtype, bpt_stream_t stream);
+
+/* vector_spmm_backward, graphop.cpp:173-214 / graphop_kernel.cu:544-600:
+ * dedata[eid[j],h] = sum_d dy[r,h,d] * x[indices[j],h,d] over the (row,...) CSR;
+ * dx[c,h,:] = sum_j edata[eid_t[j],h] * dy[indices_t[j],h,:] over the transposed CSR.
+ * Every chunk of the transposed CSR is processed (the reference sizes that launch with
+ * the other CSR's chunk count, graphop_kernel.cu:566,588). */
+int bpt_vector_spmm_backward(const int64_t *row, const int64_t *indptr, const int64_t *eid,
+                             const int64_t *indices, int64_t n_chunks,
+                             const int64_t *col, const int64_t *indptr_t, const int64_t *eid_t,
+                             const int64_t *indices_t, int64_t n_chunks_t,
+                             const void *edata, const void *dy, const void *x,
+                             void *dedata, void *dx, int64_t n_rows_x,
+                             int h, int d, int dtype, bpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Fused graph attention.  One call replaces the reference's operator chain
+ *   masked_mm -> node_mul_edge -> (e_rel + e)/sqrt(d_k) -> sparse_softmax -> vec_spmm
+ * of BPTBlock.forward, modules/attention.py:66-77 (dropout off), i.e. per destination i
+ *   o[i,h,:] = sum_e softmax_e(scale * <q[i,h], k[src_e,h] + ak[etype_e]>) * v[src_e,h,:]
+ * over i's incoming edges, and bpt_attn_backward its gradient (what autograd builds from
+ * modules/op.py:10-58).  Edge scores never reach HBM in the forward; no floating-point
+ * atomics anywhere, so results are bitwise reproducible.
+ *
+ * The graph is given as a plan: a device blob built once per graph from the COO edge list
+ * (src, dst, etype: int32, edge id = position), holding the int32 in-CSR, out-CSR, per-type
+ * buckets and the work lists the kernels walk.  counts_host[9] (host memory, filled by
+ * bpt_attn_plan_build, which waits for the stream) must be passed back to the other calls.
+ * etype may be NULL (all edges type 0); every etype must be < n_etypes.
+ * ---------------------------------------------------------------------------------- */
+
+size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes);
+size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes);
+int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
+                        int64_t n_edges, int64_t n_nodes, int n_etypes, void *plan,
+                        size_t plan_bytes, void *workspace, size_t workspace_bytes,
+                        int32_t *counts_host, bpt_stream_t stream);
+
+/* Scratch bytes of bpt_attn_forward (backward == 0) or bpt_attn_backward (backward != 0). */
+size_t bpt_attn_workspace_bytes(int64_t n_edges, const int32_t *counts_host, int h, int d,
+                                int backward);
+
+/* q, k, v, o: (n_nodes, h, d) of `dtype` (BPT_F32, BPT_BF16 or BPT_F16; d <= 128);
+ * ak: (n_etypes, d) of `dtype` or NULL for no relative-position term; lse: fp32
+ * (n_nodes, h), natural-log sum of exponentials of each row's scaled scores (-inf for a
+ * row without incoming edges, whose o is 0). */
+int bpt_attn_forward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
+                     int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
+                     const void *ak, double scale, void *o, float *lse, int h, int d, int dtype,
+                     void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+
+/* o, lse: the forward's outputs; d_o: gradient of o.  dq, dk, dv: (n_nodes, h, d) of
+ * `dtype`; dak: fp32 (n_etypes, d), required when ak is given. */
+int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
+                      int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
+                      const void *ak, double scale, const void *o, const float *lse,
+                      const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
+                      int dtype, void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BPT_B200_H_ */

@@ -1,0 +1,63 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol that
+include/bpt_b200.h declares; the ctypes signature table covers the same set."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "bpt_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bpt_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from bpt_b200 import build
+    return build.build()
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    L = ctypes.CDLL(built_lib)
+    names = declared_symbols()
+    assert len(names) >= 19
+    for name in names:
+        assert hasattr(L, name), name
+
+
+def test_signature_table_matches_header(built_lib):
+    from bpt_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+    assert _lib.lib().bpt_version() >= 1
+
+
+def test_argument_errors_need_no_gpu(built_lib):
+    from bpt_b200 import _lib
+    L = _lib.lib()
+    rc = L.bpt_bp_levels(0, None, None, None, None)
+    assert rc == 1 and b"length" in L.bpt_last_error()
+    with pytest.raises(RuntimeError, match="length"):
+        _lib.check(rc)
+    assert L.bpt_bp_fill(8, 0, 1, 10, None, 0, 4, None, None, None, None, None) == 1
+
+
+def test_host_level_table(built_lib):
+    from bpt_b200 import graphbuilder
+    nn, sh, total = graphbuilder.levels(5)
+    assert nn == [5, 3, 2, 1] and sh == [0, 5, 8, 10] and total == 11
+    nn, sh, total = graphbuilder.levels(8192)
+    assert total == 16383 and len(nn) == 14
+    assert graphbuilder.levels(1) == ([1], [0], 1)
+
+
+def test_product_does_not_import_oracle():
+    pkg = os.path.join(ROOT, "bpt_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower() or f == "build.py", os.path.join(dirpath, f)

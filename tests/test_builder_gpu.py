@@ -1,0 +1,114 @@
+"""GPU graph construction through the C ABI: bit-exact with the oracle and the golden
+digests of the reference's builder."""
+import pickle
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import digest
+
+pytestmark = pytest.mark.gpu
+
+
+def _gb():
+    from bpt_b200 import graphbuilder
+    return graphbuilder
+
+
+def test_gpu_builder_matches_golden_digests(golden):
+    gb = _gb()
+    for rec in golden["cases"]:
+        g = gb.BinaryPartition(rec["length"], rec["triu"], rec["step"], rec["clip_dist"])
+        key = (rec["length"], rec["triu"], rec["step"], rec["clip_dist"])
+        assert g.number_of_nodes == rec["n_nodes"], key
+        assert g.number_of_edges == rec["n_edges"], key
+        assert g.number_of_levels == rec["n_levels"], key
+        s, d, t = g.get_edges()
+        assert s.dtype == np.int64
+        assert digest(s, d, t, g.get_pos()) == rec["sha256"], key
+
+
+def test_gpu_builder_matches_oracle_random(oracle_lib):
+    gb = _gb()
+    rng = np.random.default_rng(5)
+    for _ in range(120):
+        n = int(rng.integers(1, 3000))
+        step = int(rng.choice([1, 2, 3, 4, 5, 8, 16, 64]))
+        triu = bool(rng.integers(0, 2))
+        clip = int(rng.choice([0, 1, 3, 6, 10, 30]))
+        v_shift = int(rng.integers(0, 1000))
+        g = gb.BinaryPartition(n, triu, step, clip)
+        o = oracle_lib.binary_partition(n, triu, step, clip)
+        s, d, t = g.get_edges(v_shift)
+        assert np.array_equal(s, o["src"] + v_shift) and np.array_equal(d, o["dst"] + v_shift)
+        assert np.array_equal(t, o["etype"]) and np.array_equal(g.get_pos(), o["pos"])
+        assert np.array_equal(g.leaf_ids(v_shift), np.arange(v_shift, v_shift + n))
+        assert g.root_id(v_shift) == v_shift + o["n_nodes"] - 1
+        assert [g.number_of_nodes_at_lvl(i) for i in range(g.number_of_levels)] == o["n_nodes_arr"].tolist()
+        assert len(g.internal_ids()) == o["n_nodes"] - n
+
+
+def test_accessors_and_pickle():
+    gb = _gb()
+    g = gb.BinaryPartition(100, True, 2, 5)
+    assert g.is_triu
+    g2 = pickle.loads(pickle.dumps(g))
+    for a, b in zip(g.get_edges(), g2.get_edges()):
+        assert np.array_equal(a, b)
+    with pytest.raises(ValueError):
+        gb.BinaryPartition(0)
+
+
+def test_partition_csr_matches_golden_and_oracle(golden, oracle_lib):
+    gb = _gb()
+    for rec in golden["partition_csr"]:
+        row, ip = gb.partition_csr(np.array(rec["indptr"], np.int64), rec["chunk_size"])
+        assert row.tolist() == rec["row"] and ip.tolist() == rec["indptr_out"]
+    # empty rows only, and a device-resident call
+    row, ip = gb.partition_csr(np.zeros(5, np.int64))
+    assert row.size == 0 and ip.tolist() == [0]
+    indptr = torch.tensor([0, 70, 70, 71, 200], device="cuda")
+    row, ip = gb.partition_csr(indptr, 32)
+    r2, p2 = oracle_lib.partition_csr(indptr.cpu().numpy(), 32)
+    assert row.is_cuda and row.cpu().numpy().tolist() == r2.tolist() and ip.cpu().numpy().tolist() == p2.tolist()
+
+
+def test_get_csrs_and_batching_match_oracle(oracle_lib):
+    from bpt_b200 import csr
+    gb = _gb()
+    specs = [(513, False, 4, 10), (37, False, 2, 3), (513, False, 4, 10), (5, False, 1, 10), (1, False, 4, 10)]
+    cache = {}
+    graphs = []
+    for sp in specs:
+        if sp not in cache:
+            cache[sp] = gb.BinaryPartition(*sp)
+        graphs.append(cache[sp])
+    batch = csr.batch_graphs(graphs, dtype=torch.int64)
+    ob = oracle_lib.batch_graphs([oracle_lib.binary_partition(*sp) for sp in specs])
+    assert batch.n_nodes == ob["n_nodes"] and batch.n_edges == ob["n_edges"]
+    for mine, ref in ((batch.src, ob["src"]), (batch.dst, ob["dst"]), (batch.etype, ob["etype"]),
+                      (batch.pos, ob["pos"])):
+        assert np.array_equal(mine.cpu().numpy(), ref)
+    # n=513 with triu=False has duplicate (src, dst) pairs: the CSR must keep them apart
+    got = csr.get_csrs(batch.src, batch.dst, batch.n_nodes)
+    want = oracle_lib.get_csrs(ob["src"], ob["dst"], ob["n_nodes"])
+    for i in range(2):
+        for j in range(3):
+            assert got[i][j].dtype == torch.int64
+            assert np.array_equal(got[i][j].cpu().numpy(), want[i][j]), (i, j)
+    for j in range(2, 6):
+        assert np.array_equal(got[j].cpu().numpy(), want[j]), j
+    # int32 flavour used by the fused path
+    ip, idx, eid = csr.coo_to_csr(batch.dst.int(), batch.src.int(), batch.n_nodes)
+    assert ip.dtype == torch.int32 and np.array_equal(idx.cpu().numpy(), want[1][1])
+
+
+def test_large_graph_digest(golden):
+    """n = 65536, k = 8: 13.2 M edges, the largest size the sweep uses."""
+    gb = _gb()
+    rec = [r for r in golden["cases"] if r["length"] == 65536 and r["step"] == 8][0]
+    g = gb.BinaryPartition(65536, False, 8, 10)
+    assert g.number_of_edges == rec["n_edges"] == 13239926
+    s, d, t = g.get_edges()
+    assert digest(s, d, t, g.get_pos()) == rec["sha256"]

@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the fused binary-partition graph attention layer (forward + backward).
+
+One "step" is one pass of the hot path over one batch: a block-diagonal batch of `--seqs`
+independent sequences of `--n` tokens with `--k` neighbours per side per level, 8 heads x 64,
+forward and backward.  The metric is attention edges per second (edges of the batch graph
+divided by the step time), the one BASELINE.json quotes at n = 8192, k = 4.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With N > 1 it is launched by torch.distributed.run, one rank per GPU; every rank processes
+its own batch (independent graphs shard by graph, no collective on the data path) and the
+reported value is all ranks' edges over the slowest rank's device time.
+`--impl reference` times the CPU restatement of the reference's math on the host cores.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, D = 8, 64
+MAX_ETYPE = 1000  # rows of the reference's embed_ak table (modules/attention.py:23,42)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--seqs", type=int, default=8)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=4)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(a):
+    return "bpt_attention_fwd_bwd %dx(n=%d,k=%d,%s) h=%dx%d %s" % (
+        a.seqs, a.n, a.k, "causal" if a.causal else "bidirectional", H, D, a.dtype)
+
+
+def algorithmic_bytes(n_nodes, n_edges, elem_bytes):
+    """Bytes a perfect kernel must move: unique Q/K/V/O (and gradient) bytes plus the int32
+    CSR (indptr, indices, etype).  Forward reads Q,K,V and writes O; backward reads Q,K,V,dO
+    and lse/delta-sized rows and writes dQ,dK,dV, walking the CSR and its transpose."""
+    csr = 4 * (n_nodes + 1) + 8 * n_edges
+    fwd = 4 * n_nodes * H * D * elem_bytes + csr
+    bwd = 8 * n_nodes * H * D * elem_bytes + 2 * n_nodes * H * 4 + 2 * csr
+    return fwd, bwd
+
+
+# ----------------------------------------------------------------------------- CPU side
+
+def cpu_reference_run(a, steps, warmup, min_seconds=0.0):
+    """fp32 CPU restatement of the reference math (oracle/bpt_oracle.c) on ONE sequence of the
+    workload, all host threads: forward + backward per step.  Returns (edges/s, info)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    oracle.build_lib()
+    g = oracle.binary_partition(a.n, a.causal, a.k, 10)
+    N, E = g["n_nodes"], g["n_edges"]
+    csr = oracle.get_csrs(g["src"], g["dst"], N)
+    rng = np.random.default_rng(2)
+    q, k, v = [(rng.standard_normal((N, H, D)) * 0.125).astype(np.float32) for _ in range(3)]
+    ak = (rng.standard_normal((MAX_ETYPE, D)) * 0.125).astype(np.float32)
+    d_o = rng.standard_normal((N, H, D)).astype(np.float32)
+    scale = 1.0 / math.sqrt(D)
+
+    def step():
+        o, lse, p = oracle.attn_fwd(csr[1], g["etype"], q, k, v, ak, scale, precision="f32")
+        oracle.attn_bwd(csr[1], csr[0], g["etype"], q, k, v, ak, scale, o, p, d_o, precision="f32")
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    while done < steps or (time.perf_counter() - t0) < min_seconds:
+        step()
+        done += 1
+    dt = time.perf_counter() - t0
+    info = dict(cores=oracle.num_threads(), steps=done, seconds=dt, edges_per_step=E,
+                sample="1 of %d sequences (n=%d,k=%d), fp32, forward+backward, %d repetitions" %
+                       (a.seqs, a.n, a.k, done))
+    return E * done / dt, info
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(a.steps, 40))
+    value, info = cpu_reference_run(a, steps, min(a.warmup, 2))
+    line = {
+        "impl": "reference", "metric": "bpt_attention_edges_per_sec", "value": value, "unit": "edges/s",
+        "n_gpus": a.gpus, "steps": info["steps"], "warmup": min(a.warmup, 2),
+        "ms_per_step": 1e3 * info["seconds"] / info["steps"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "timed_on": "host CPU, one sequence per step"},
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": info["cores"], "kind": "port",
+                         "sample": info["sample"]},
+        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this process's GPU with nvidia-smi while the
+    timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.uuid, self.proc, self.lines = uuid, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.uuid, "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- GPU side
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from bpt_b200 import csr as csrmod, graphbuilder
+    from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
+
+    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
+    batch = csrmod.batch_graphs([g] * a.seqs)
+    plan = AttentionPlan.from_batch(batch, n_etypes=MAX_ETYPE)
+    N, E = batch.n_nodes, batch.n_edges
+    gen = torch.Generator(device="cpu").manual_seed(2 + rank)
+    host = {}
+    for name, sigma in (("q", 0.125), ("k", 0.125), ("v", 0.125), ("d_o", 1.0)):
+        host[name] = (torch.randn(N, H, D, generator=gen) * sigma).to(dtype).pin_memory()
+    ak = (torch.randn(MAX_ETYPE, D, generator=gen) * 0.125).to(dtype).to(dev)
+    q, k, v, d_o = [host[n].to(dev) for n in ("q", "k", "v", "d_o")]
+    scale = 1.0 / math.sqrt(D)
+
+    launches_fwd = 1 + (plan.counts[2] > 0)
+    launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
+
+    def step():
+        o, lse = attention_forward(plan, q, k, v, ak, scale)
+        return o, attention_backward(plan, q, k, v, ak, scale, lse, d_o)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    barrier()
+
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(a.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for i in range(a.steps):
+        ev[i][0].record()
+        o, lse = attention_forward(plan, q, k, v, ak, scale)
+        ev[i][1].record()
+        attention_backward(plan, q, k, v, ak, scale, lse, d_o)
+        ev[i][2].record()
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = start.elapsed_time(stop)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / a.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / a.steps
+    if world > 1:
+        t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, fwd_ms, bwd_ms = t.tolist()
+
+    # end to end: host buffers in, host buffers out, through the public call
+    e2e = None
+    if not a.no_e2e:
+        outs = [torch.empty((N, H, D), dtype=dtype).pin_memory() for _ in range(4)]
+        e2e_steps = max(3, min(a.steps, 10))
+
+        def e2e_step():
+            dq_, dk_, dv_, do_ = [host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "d_o")]
+            o, lse = attention_forward(plan, dq_, dk_, dv_, ak, scale)
+            grads = attention_backward(plan, dq_, dk_, dv_, ak, scale, lse, do_)
+            for dst_, src_ in zip(outs, (o, grads[0], grads[1], grads[2])):
+                dst_.copy_(src_, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        t2.record()
+        barrier()
+        e2e_ms = s2.elapsed_time(t2) / e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = t.item()
+        nbytes = N * H * D * q.element_size()
+        e2e = {"value": world * E / (e2e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": 4 * nbytes,
+               "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        fwd_bytes, bwd_bytes = algorithmic_bytes(N, E, q.element_size())
+        ms_per_step = total_ms / a.steps
+        fwd_gbs = fwd_bytes / (fwd_ms * 1e-3) / 1e9
+        bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        line = {
+            "metric": "bpt_attention_edges_per_sec", "value": world * E / (ms_per_step * 1e-3),
+            "unit": "edges/s", "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": a.dtype, "data": "synthetic",
+            "config": {"workload": workload_name(a), "nodes_per_gpu": N, "edges_per_gpu": E,
+                       "sharding": "independent graphs per rank, no data-path collective",
+                       "l2": "inputs+outputs %.0f MB per step exceed the 126 MB L2" %
+                             (8 * N * H * D * q.element_size() / 1e6)},
+            "gpu_launches": a.steps * (launches_fwd + launches_bwd),
+            "forward": {"ms": fwd_ms, "edges_per_sec": world * E / (fwd_ms * 1e-3)},
+            "backward": {"ms": bwd_ms, "edges_per_sec": world * E / (bwd_ms * 1e-3)},
+            "roofline": {"kernel": "attn_forward_kernel", "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
+                         "peak_source": peak_src, "unit": "GB/s", "frac": fwd_gbs / peak,
+                         "algorithmic_bytes": fwd_bytes, "traffic": None},
+            "roofline_backward": {"kernels": "attn_backward_{dq,dkv,dak}_kernel", "bound": "hbm",
+                                  "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
+                                  "algorithmic_bytes": bwd_bytes},
+            "clocks": clocks,
+        }
+        if e2e:
+            line["e2e"] = e2e
+        if world == 1 and not a.no_cpu_baseline:
+            value, info = cpu_reference_run(a, 1, 1, min_seconds=10.0)
+            line["cpu_baseline"] = {"value": value, "unit": "edges/s", "cores": info["cores"], "kind": "port",
+                                    "sample": info["sample"]}
+        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(traffic_path):
+            tr = json.load(open(traffic_path)).get(workload_name(a))
+            if tr:
+                line["roofline"]["traffic"] = tr
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

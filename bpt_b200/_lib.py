@@ -43,10 +43,10 @@ SIGNATURES = {
     "bpt_attn_plan_bytes": (_sz, [_i64, _i64, _int]),
     "bpt_attn_plan_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "bpt_attn_plan_build": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp, _sz, _vp, _vp]),
-    "bpt_attn_workspace_bytes": (_sz, [_i64, _vp, _int, _int, _int]),
+    "bpt_attn_workspace_bytes": (_sz, [_i64, _i64, _vp, _int, _int, _int]),
     "bpt_attn_forward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                 _int, _int, _int, _vp, _sz, _vp]),
-    "bpt_attn_backward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp,
+    "bpt_attn_backward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                  _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
 }
 

@@ -1,0 +1,145 @@
+"""Fused binary-partition graph attention: host side of bpt_attn_forward / bpt_attn_backward.
+
+`AttentionPlan` is built once per graph (per batch layout) from the COO edge list and holds
+the device blob the kernels walk.  `bpt_attention(plan, q, k, v, embed_ak, scale)` is one
+autograd function that stands for the chain of four operators in the reference's
+BPTBlock.forward (modules/attention.py:66-77, dropout off):
+
+    e     = masked_mm(..., k, q)
+    e_rel = node_mul_edge(..., q, embed_ak(etype))
+    p     = sparse_softmax(..., (e_rel + e) / sqrt(d_k))
+    a     = vec_spmm(..., p, v)
+
+Unlike the chain it never materialises the (E, d) gather of embed_ak nor any (E, h) tensor
+in the forward, and its results do not vary from run to run.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+
+class AttentionPlan:
+    """Device-resident plan of one graph for the fused kernels.
+
+    src, dst, etype: int32 CUDA tensors in edge-id order (etype may be None);
+    n_etypes: rows of the relative-position table the graph may index (every etype must be
+    smaller); defaults to max(etype) + 1.
+    """
+
+    def __init__(self, src, dst, etype, n_nodes, n_etypes=None):
+        src = src.to(torch.int32).contiguous()
+        dst = dst.to(torch.int32).contiguous()
+        _lib.require_cuda(src, dst)
+        if etype is not None:
+            etype = etype.to(torch.int32).contiguous()
+            _lib.require_cuda(etype)
+            if n_etypes is None:
+                n_etypes = int(etype.max().item()) + 1 if etype.numel() else 1
+        elif n_etypes is None:
+            n_etypes = 1
+        self.device = src.device
+        self.n_nodes, self.n_edges, self.n_etypes = int(n_nodes), int(src.numel()), int(n_etypes)
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            self.blob = _lib.workspace(L.bpt_attn_plan_bytes(self.n_nodes, self.n_edges, self.n_etypes),
+                                       self.device)
+            ws = _lib.workspace(L.bpt_attn_plan_workspace_bytes(self.n_nodes, self.n_edges, self.n_etypes),
+                                self.device)
+            self._counts = (ctypes.c_int32 * 9)()
+            _lib.check(L.bpt_attn_plan_build(_lib.ptr(src), _lib.ptr(dst), _lib.ptr(etype), self.n_edges,
+                                             self.n_nodes, self.n_etypes, self.blob.data_ptr(),
+                                             self.blob.numel(), ws.data_ptr(), ws.numel(),
+                                             ctypes.addressof(self._counts), _lib.stream()))
+        self.counts = list(self._counts)
+        self._ws = {}
+
+    @classmethod
+    def from_batch(cls, batch, n_etypes=None):
+        """From a csr.BatchedGraph."""
+        return cls(batch.src, batch.dst, batch.etype, batch.n_nodes, n_etypes)
+
+    def workspace(self, h, d, backward):
+        """Scratch for one call; cached per (h, d, direction) and reused by later calls on
+        the same stream (calls on different streams must not share a plan's scratch)."""
+        key = (h, d, bool(backward))
+        ws = self._ws.get(key)
+        if ws is None:
+            n = _lib.lib().bpt_attn_workspace_bytes(self.n_nodes, self.n_edges, ctypes.addressof(self._counts), h, d,
+                                                    int(bool(backward)))
+            ws = _lib.workspace(n, self.device)
+            self._ws[key] = ws
+        return ws
+
+    def _args(self):
+        return (self.blob.data_ptr(), ctypes.addressof(self._counts), self.n_nodes, self.n_edges, self.n_etypes)
+
+
+def attention_forward(plan, q, k, v, embed_ak, scale):
+    """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype."""
+    _lib.require_cuda(q, k, v)
+    if embed_ak is not None:
+        _lib.require_cuda(embed_ak)
+        if embed_ak.dtype != q.dtype or embed_ak.size(0) < plan.n_etypes or embed_ak.size(1) != q.size(-1):
+            raise RuntimeError("bpt_attention: embed_ak must be (>= n_etypes, d) of the dtype of q")
+    N, h, d = q.shape
+    if N != plan.n_nodes or k.shape != q.shape or v.shape != q.shape:
+        raise RuntimeError("bpt_attention: q, k, v must be (n_nodes, h, d)")
+    o = torch.empty_like(q)
+    lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        ws = plan.workspace(h, d, False)
+        _lib.check(_lib.lib().bpt_attn_forward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                               _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(),
+                                               h, d, _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(),
+                                               _lib.stream()))
+    return o, lse
+
+
+def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o):
+    """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d)."""
+    d_o = d_o.contiguous()
+    _lib.require_cuda(q, k, v, lse, d_o)
+    N, h, d = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dak = None
+    if embed_ak is not None:
+        dak = torch.zeros((embed_ak.size(0), d), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        ws = plan.workspace(h, d, True)
+        _lib.check(_lib.lib().bpt_attn_backward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                _lib.ptr(embed_ak), float(scale), lse.data_ptr(),
+                                                d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                                _lib.ptr(dak), h, d, _lib.dtype_code(q.dtype), ws.data_ptr(),
+                                                ws.numel(), _lib.stream()))
+    return dq, dk, dv, dak
+
+
+class _BPTAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, plan, q, k, v, embed_ak, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        if embed_ak is not None:
+            embed_ak = embed_ak.contiguous()
+        o, lse = attention_forward(plan, q, k, v, embed_ak, scale)
+        ctx.plan, ctx.scale = plan, scale
+        ctx.has_ak = embed_ak is not None
+        ctx.save_for_backward(q, k, v, embed_ak if ctx.has_ak else q.new_empty(0), lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, ak, lse = ctx.saved_tensors
+        ak = ak if ctx.has_ak else None
+        dq, dk, dv, dak = attention_backward(ctx.plan, q, k, v, ak, ctx.scale, lse, d_o)
+        return None, dq, dk, dv, (dak.to(ak.dtype) if dak is not None else None), None
+
+
+def bpt_attention(plan, q, k, v, embed_ak=None, scale=None):
+    """o[i,h] = sum over i's incoming edges e of softmax_e(scale * <q[i,h], k[src_e,h] +
+    embed_ak[etype_e]>) * v[src_e,h].  scale defaults to 1/sqrt(d) (modules/attention.py:73)."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.size(-1))
+    return _BPTAttention.apply(plan, q, k, v, embed_ak, scale)

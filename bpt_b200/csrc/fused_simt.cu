@@ -6,7 +6,7 @@
 // vec_spmm chain (modules/attention.py:66-77) in one pass per destination row: scores live
 // in shared memory, never in HBM; only O and the row log-sum-exp are written.
 // Backward = three segment reductions with one writer per output element:
-//   over the in-CSR   : P, dS (scratch, in-CSR order) and dQ
+//   over the in-CSR   : P, dP, delta (scratch) and dQ
 //   over the out-CSR  : dK, dV
 //   over type buckets : d embed_ak
 // Rows longer than a work item are reduced in item order by a merge kernel, so every
@@ -219,15 +219,25 @@ __global__ void attn_forward_merge_kernel(const int4 *__restrict__ split_rows, i
 }
 
 // ------------------------------------------------------------------ backward, pass over destinations
+//
+// With p_e the edge's probability and dp_e = <dO[dst], v[src_e]>, the score gradient is
+// dS_e = scale * p_e * (dp_e - delta), delta = sum_e p_e * dp_e.  delta equals <dO, O>, but O
+// is stored rounded (bf16), and on rows whose edges all share one type the gradient of
+// embed_ak is sum_e dS_e = 0 exactly only if delta is the sum over the same p_e; so delta is
+// accumulated here, in fp32, and O is not read at all.  One pass suffices because
+//   dQ = scale * (A - delta * B),  A = sum_e p_e dp_e kk_e,  B = sum_e p_e kk_e,
+// with kk_e = k[src_e] + ak[etype_e].  P and dP go to scratch in in-CSR order; the later
+// passes rebuild dS from them and delta.
 
 template <typename T, int LPH, bool kVec>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dq_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ in_src,
                         const int32_t *__restrict__ in_etype, const T *__restrict__ q,
                         const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ ak,
-                        float scale, const T *__restrict__ o, const float *__restrict__ lse,
-                        const T *__restrict__ d_o, float *__restrict__ P, float *__restrict__ dS,
-                        T *__restrict__ dq, float *__restrict__ part_dq, Geometry g) {
+                        float scale, const float *__restrict__ lse, const T *__restrict__ d_o,
+                        float *__restrict__ P, float *__restrict__ dP, float *__restrict__ delta_out,
+                        T *__restrict__ dq, float *__restrict__ part_ab, float *__restrict__ part_delta,
+                        Geometry g) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * kWarpsPerBlock + warp;
@@ -243,20 +253,15 @@ attn_backward_dq_kernel(const int4 *__restrict__ items, int n_items, const int32
     const int H = g.H, D = g.D;
     const int64_t row_off = (static_cast<int64_t>(row) * H + head) * D + d0;
 
-    float qf[16], dof[16], acc[16];
+    float qf[16], dof[16], fa[16], fb[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { qf[i] = 0.f; dof[i] = 0.f; acc[i] = 0.f; }
-    float delta = 0.f, lse2 = 0.f;
+    for (int i = 0; i < 16; ++i) { qf[i] = 0.f; dof[i] = 0.f; fa[i] = 0.f; fb[i] = 0.f; }
+    float lse2 = 0.f, delta = 0.f;
     if (active) {
-        float of[16];
         load16<T, kVec>(q + row_off, nvalid, qf);
         load16<T, kVec>(d_o + row_off, nvalid, dof);
-        load16<T, kVec>(o + row_off, nvalid, of);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) delta = fmaf(dof[i], of[i], delta);
         lse2 = lse[static_cast<int64_t>(row) * H + head] * kLog2e;
     }
-    delta = group_sum<LPH>(delta);
     const float qs = scale * kLog2e;
 #pragma unroll
     for (int i = 0; i < 16; ++i) qf[i] *= qs;
@@ -286,20 +291,56 @@ attn_backward_dq_kernel(const int4 *__restrict__ items, int n_items, const int32
         dp = group_sum<LPH>(dp);
         if (active) {
             const float p = exp2f(s - lse2);
-            const float ds = p * (dp - delta) * scale;
+            const float pdp = p * dp;
+            delta += pdp;
             if (gl == 0) {
                 P[static_cast<int64_t>(j) * H + head] = p;
-                dS[static_cast<int64_t>(j) * H + head] = ds;
+                dP[static_cast<int64_t>(j) * H + head] = dp;
             }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = fmaf(ds, kf[i], acc[i]);
+            for (int i = 0; i < 16; ++i) {
+                fa[i] = fmaf(pdp, kf[i], fa[i]);
+                fb[i] = fmaf(p, kf[i], fb[i]);
+            }
         }
     }
     if (!active) return;
-    if (slot < 0)
-        store16<T>(dq + row_off, nvalid, acc);
-    else
-        store16<float>(part_dq + (static_cast<int64_t>(slot) * H + head) * D + d0, nvalid, acc);
+    if (slot < 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) fa[i] = scale * (fa[i] - delta * fb[i]);
+        store16<T>(dq + row_off, nvalid, fa);
+        if (gl == 0) delta_out[static_cast<int64_t>(row) * H + head] = delta;
+    } else {
+        const int64_t HD = static_cast<int64_t>(H) * D;
+        float *base = part_ab + static_cast<int64_t>(slot) * 2 * HD + static_cast<int64_t>(head) * D + d0;
+        store16<float>(base, nvalid, fa);
+        store16<float>(base + HD, nvalid, fb);
+        if (gl == 0) part_delta[static_cast<int64_t>(slot) * H + head] = delta;
+    }
+}
+
+// Split rows: delta = sum of the slots' deltas, dQ = scale * (sum A - delta * sum B), slot order.
+template <typename T>
+__global__ void attn_backward_dq_merge_kernel(const int4 *__restrict__ split_rows, int n_split,
+                                              const float *__restrict__ part_ab,
+                                              const float *__restrict__ part_delta, float scale,
+                                              T *__restrict__ dq, float *__restrict__ delta_out, Geometry g) {
+    const int sr = blockIdx.x;
+    if (sr >= n_split) return;
+    const int4 rec = split_rows[sr];
+    const int row = rec.x, first = rec.y, count = rec.z;
+    const int HD = g.H * g.D;
+    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+        const int head = c / g.D;
+        float delta = 0.f, a = 0.f, b = 0.f;
+        for (int s = 0; s < count; ++s) {
+            delta += part_delta[static_cast<int64_t>(first + s) * g.H + head];
+            a += part_ab[static_cast<int64_t>(first + s) * 2 * HD + c];
+            b += part_ab[static_cast<int64_t>(first + s) * 2 * HD + HD + c];
+        }
+        dq[static_cast<int64_t>(row) * HD + c] = from_acc<T>(scale * (a - delta * b));
+        if (c % g.D == 0) delta_out[static_cast<int64_t>(row) * g.H + head] = delta;
+    }
 }
 
 // ------------------------------------------------------------------ backward, pass over sources
@@ -309,8 +350,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ out_dst,
                          const int32_t *__restrict__ out_inpos, const T *__restrict__ q,
                          const T *__restrict__ d_o, const float *__restrict__ P,
-                         const float *__restrict__ dS, T *__restrict__ dk, T *__restrict__ dv,
-                         float *__restrict__ part_dkv, Geometry g) {
+                         const float *__restrict__ dP, const float *__restrict__ delta, float scale,
+                         T *__restrict__ dk, T *__restrict__ dv, float *__restrict__ part_dkv, Geometry g) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * kWarpsPerBlock + warp;
@@ -331,7 +372,8 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
     for (int j = beg; j < end; ++j) {
         const int dst = out_dst[j];
         const int64_t pos = out_inpos[j];
-        const float ds = dS[pos * H + head], p = P[pos * H + head];
+        const float p = P[pos * H + head];
+        const float ds = scale * p * (dP[pos * H + head] - delta[static_cast<int64_t>(dst) * H + head]);
         const int64_t dst_off = (static_cast<int64_t>(dst) * H + head) * D + d0;
         float qf[16], dof[16];
         load16<T, kVec>(q + dst_off, nvalid, qf);
@@ -360,7 +402,8 @@ template <typename T, int LPH, bool kVec>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ et_dst,
                          const int32_t *__restrict__ et_inpos, const T *__restrict__ q,
-                         const float *__restrict__ dS, float *__restrict__ dak,
+                         const float *__restrict__ P, const float *__restrict__ dP,
+                         const float *__restrict__ delta, float scale, float *__restrict__ dak,
                          float *__restrict__ part_dak, Geometry g) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -381,7 +424,9 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
         if (head < H && nvalid > 0) {
             for (int j = beg; j < end; ++j) {
                 const int dst = et_dst[j];
-                const float ds = dS[static_cast<int64_t>(et_inpos[j]) * H + head];
+                const int64_t pos = et_inpos[j];
+                const float ds = scale * P[pos * H + head] *
+                                 (dP[pos * H + head] - delta[static_cast<int64_t>(dst) * H + head]);
                 float qf[16];
                 load16<T, kVec>(q + (static_cast<int64_t>(dst) * H + head) * D + d0, nvalid, qf);
 #pragma unroll
@@ -425,19 +470,17 @@ __global__ void sum_merge_kernel(const int4 *__restrict__ split_rows, int n_spli
 
 // ------------------------------------------------------------------ host side
 
-struct Scratch {
-    float *part_o, *part_ml;            // forward
-    float *P, *dS, *part_dq, *part_dkv, *part_dak;  // backward
-};
 
 size_t forward_ws_bytes(const int32_t *counts, int H, int D) {
     const size_t slots = static_cast<size_t>(counts[1]);
     return align_up(slots * H * D * 4, 256) + align_up(slots * H * 2 * 4, 256) + 512;
 }
 
-size_t backward_ws_bytes(int64_t n_edges, const int32_t *counts, int H, int D) {
+size_t backward_ws_bytes(int64_t n_nodes, int64_t n_edges, const int32_t *counts, int H, int D) {
     const size_t e = static_cast<size_t>(n_edges);
-    return 2 * align_up(e * H * 4, 256) + align_up(static_cast<size_t>(counts[1]) * H * D * 4, 256) +
+    return 2 * align_up(e * H * 4, 256) + align_up(static_cast<size_t>(n_nodes) * H * 4, 256) +
+           align_up(static_cast<size_t>(counts[1]) * 2 * H * D * 4, 256) +
+           align_up(static_cast<size_t>(counts[1]) * H * 4, 256) +
            align_up(static_cast<size_t>(counts[4]) * 2 * H * D * 4, 256) +
            align_up(static_cast<size_t>(counts[7]) * D * 4, 256) + 1024;
 }
@@ -500,41 +543,43 @@ int forward_impl(const PlanView &p, const int32_t *counts, const void *q_, const
 
 template <typename T>
 int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, const void *k_, const void *v_,
-                  const void *ak_, float scale, const void *o_, const float *lse, const void *do_,
+                  const void *ak_, float scale, const float *lse, const void *do_,
                   void *dq_, void *dk_, void *dv_, float *dak, int H, int D, void *ws_ptr, size_t ws_bytes,
                   cudaStream_t stream) {
     const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
-    const T *ak = static_cast<const T *>(ak_), *o = static_cast<const T *>(o_), *d_o = static_cast<const T *>(do_);
+    const T *ak = static_cast<const T *>(ak_), *d_o = static_cast<const T *>(do_);
     T *dq = static_cast<T *>(dq_), *dk = static_cast<T *>(dk_), *dv = static_cast<T *>(dv_);
     Workspace ws(ws_ptr, ws_bytes);
     const size_t e = static_cast<size_t>(p.n_edges);
     float *P = ws.take<float>(e * H);
-    float *dS = ws.take<float>(e * H);
-    float *part_dq = ws.take<float>(static_cast<size_t>(counts[1]) * H * D);
+    float *dP = ws.take<float>(e * H);
+    float *delta = ws.take<float>(static_cast<size_t>(p.n_nodes) * H);
+    float *part_ab = ws.take<float>(static_cast<size_t>(counts[1]) * 2 * H * D);
+    float *part_delta = ws.take<float>(static_cast<size_t>(counts[1]) * H);
     float *part_dkv = ws.take<float>(static_cast<size_t>(counts[4]) * 2 * H * D);
     float *part_dak = ws.take<float>(static_cast<size_t>(counts[7]) * D);
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward: workspace of %zu bytes is too small", ws_bytes);
     const int lph = pick_lph(D);
-    const bool vec = can_vectorise<T>(D, lph, q, k, v, ak, o, d_o) && can_vectorise<T>(D, lph, dq, dk, dv, dq, dq, dq);
+    const bool vec = can_vectorise<T>(D, lph, q, k, v, ak, d_o, d_o) && can_vectorise<T>(D, lph, dq, dk, dv, dq, dq, dq);
     const Geometry g{H, D};
     const int hpw = 32 / lph;
     const unsigned gy = (H + hpw - 1) / hpw;
     if (counts[0] > 0) {
         const dim3 grid((counts[0] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.in_work.items, counts[0], p.in_src, p.in_etype, q, k, v, ak, scale, o, lse, d_o, P, dS, dq,
-            part_dq, g)));
+            p.in_work.items, counts[0], p.in_src, p.in_etype, q, k, v, ak, scale, lse, d_o, P, dP, delta, dq,
+            part_ab, part_delta, g)));
         BPT_LAUNCH_CHECK();
         if (counts[2] > 0) {
-            sum_merge_kernel<T><<<counts[2], 256, 0, stream>>>(p.in_work.split_rows, counts[2], part_dq, H * D, 1,
-                                                              dq, dq);
+            attn_backward_dq_merge_kernel<T><<<counts[2], 256, 0, stream>>>(
+                p.in_work.split_rows, counts[2], part_ab, part_delta, scale, dq, delta, g);
             BPT_LAUNCH_CHECK();
         }
     }
     if (counts[3] > 0) {
         const dim3 grid((counts[3] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dkv_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dS, dk, dv, part_dkv, g)));
+            p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dP, delta, scale, dk, dv, part_dkv, g)));
         BPT_LAUNCH_CHECK();
         if (counts[5] > 0) {
             sum_merge_kernel<T><<<counts[5], 256, 0, stream>>>(p.out_work.split_rows, counts[5], part_dkv, H * D,
@@ -545,7 +590,7 @@ int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, cons
     if (ak != nullptr && dak != nullptr && counts[6] > 0) {
         const dim3 grid((counts[6] + kWarpsPerBlock - 1) / kWarpsPerBlock, 1);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, dS, dak, part_dak, g)));
+            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, P, dP, delta, scale, dak, part_dak, g)));
         BPT_LAUNCH_CHECK();
         if (counts[8] > 0) {
             sum_merge_kernel<float><<<counts[8], 128, 0, stream>>>(p.et_work.split_rows, counts[8], part_dak, D, 1,
@@ -571,9 +616,10 @@ int check_attn_args(const char *name, const void *plan, const int32_t *counts, i
 
 using namespace bpt;
 
-extern "C" size_t bpt_attn_workspace_bytes(int64_t n_edges, const int32_t *counts, int h, int d, int backward) {
-    if (counts == nullptr || n_edges < 0 || h < 1 || d < 1) return 0;
-    return backward ? backward_ws_bytes(n_edges, counts, h, d) : forward_ws_bytes(counts, h, d);
+extern "C" size_t bpt_attn_workspace_bytes(int64_t n_nodes, int64_t n_edges, const int32_t *counts, int h, int d,
+                                           int backward) {
+    if (counts == nullptr || n_nodes < 0 || n_edges < 0 || h < 1 || d < 1) return 0;
+    return backward ? backward_ws_bytes(n_nodes, n_edges, counts, h, d) : forward_ws_bytes(counts, h, d);
 }
 
 extern "C" int bpt_attn_forward(const void *plan, const int32_t *counts, int64_t n_nodes, int64_t n_edges,
@@ -593,17 +639,17 @@ extern "C" int bpt_attn_forward(const void *plan, const int32_t *counts, int64_t
 
 extern "C" int bpt_attn_backward(const void *plan, const int32_t *counts, int64_t n_nodes, int64_t n_edges,
                                  int n_etypes, const void *q, const void *k, const void *v, const void *ak,
-                                 double scale, const void *o, const float *lse, const void *d_o, void *dq,
+                                 double scale, const float *lse, const void *d_o, void *dq,
                                  void *dk, void *dv, float *dak, int h, int d, int dtype, void *workspace,
                                  size_t workspace_bytes, bpt_stream_t stream) {
     if (int rc = check_attn_args("attn_backward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
-    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && o && lse && d_o && dq && dk && dv), "attn_backward: null tensor");
+    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && lse && d_o && dq && dk && dv), "attn_backward: null tensor");
     BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward: ak given without dak");
     const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
     switch (dtype) {
-        case BPT_F32: return backward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
-        case BPT_BF16: return backward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
-        case BPT_F16: return backward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_F32: return backward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_BF16: return backward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_F16: return backward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
         default: return fail(BPT_ERR_UNSUPPORTED, "attn_backward: unknown dtype code %d", dtype);
     }
 }

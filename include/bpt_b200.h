@@ -194,8 +194,8 @@ int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *e
                         int32_t *counts_host, bpt_stream_t stream);
 
 /* Scratch bytes of bpt_attn_forward (backward == 0) or bpt_attn_backward (backward != 0). */
-size_t bpt_attn_workspace_bytes(int64_t n_edges, const int32_t *counts_host, int h, int d,
-                                int backward);
+size_t bpt_attn_workspace_bytes(int64_t n_nodes, int64_t n_edges, const int32_t *counts_host,
+                                int h, int d, int backward);
 
 /* q, k, v, o: (n_nodes, h, d) of `dtype` (BPT_F32, BPT_BF16 or BPT_F16; d <= 128);
  * ak: (n_etypes, d) of `dtype` or NULL for no relative-position term; lse: fp32
@@ -206,11 +206,12 @@ int bpt_attn_forward(const void *plan, const int32_t *counts_host, int64_t n_nod
                      const void *ak, double scale, void *o, float *lse, int h, int d, int dtype,
                      void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
-/* o, lse: the forward's outputs; d_o: gradient of o.  dq, dk, dv: (n_nodes, h, d) of
- * `dtype`; dak: fp32 (n_etypes, d), required when ak is given. */
+/* lse: the forward's output; d_o: gradient of o.  dq, dk, dv: (n_nodes, h, d) of `dtype`;
+ * dak: fp32 (n_etypes, d), required when ak is given.  The forward's o is not needed: the
+ * row term <dO, O> of the softmax gradient is recomputed in fp32 from the probabilities. */
 int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
                       int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
-                      const void *ak, double scale, const void *o, const float *lse,
+                      const void *ak, double scale, const float *lse,
                       const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
                       int dtype, void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 

@@ -1,0 +1,156 @@
+"""Fused attention forward/backward through the C ABI against the fp64 CPU oracle.
+
+Tolerances (max-norm relative error, ||a-b||_inf / ||b||_inf per tensor): 1e-5 for fp32
+storage, 2e-2 for bf16 storage (inputs are rounded to bf16 first, so the oracle sees the same
+numbers), as the parity bar for this path states."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import fully_connected_blocks, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 4e-3}
+
+
+def _inputs(N, H, D, T, dtype, seed, sigma=None):
+    g = torch.Generator().manual_seed(seed)
+    sigma = sigma if sigma is not None else 1.0 / np.sqrt(D)
+    mk = lambda *s: (torch.randn(*s, generator=g) * sigma).to(dtype)
+    q, k, v, ak = mk(N, H, D), mk(N, H, D), mk(N, H, D), mk(T, D)
+    d_o = torch.randn(N, H, D, generator=g).to(dtype)
+    return q, k, v, ak, d_o
+
+
+def _oracle(oracle_lib, src, dst, etype, N, q, k, v, ak, d_o, scale):
+    csr = oracle_lib.get_csrs(src, dst, N)
+    f = lambda t: None if t is None else t.float().numpy()
+    o, lse, p = oracle_lib.attn_fwd(csr[1], etype, f(q), f(k), f(v), f(ak), scale)
+    dq, dk, dv, dak = oracle_lib.attn_bwd(csr[1], csr[0], etype, f(q), f(k), f(v), f(ak), scale, o, p, f(d_o))
+    return o, lse, dq, dk, dv, dak
+
+
+def _run_gpu(src, dst, etype, N, T, q, k, v, ak, d_o, scale):
+    from bpt_b200.attention import AttentionPlan, bpt_attention, attention_forward
+    dev = "cuda"
+    plan = AttentionPlan(torch.from_numpy(src).to(dev), torch.from_numpy(dst).to(dev),
+                         None if etype is None else torch.from_numpy(etype).to(dev), N, n_etypes=T)
+    qg, kg, vg = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+    akg = None if ak is None else ak.to(dev).requires_grad_(True)
+    o = bpt_attention(plan, qg, kg, vg, akg, scale)
+    o.backward(d_o.to(dev))
+    _, lse = attention_forward(plan, qg.detach(), kg.detach(), vg.detach(), None if ak is None else akg.detach(), scale)
+    return plan, o.detach(), lse, qg.grad, kg.grad, vg.grad, None if ak is None else akg.grad
+
+
+def _compare(got, want, tol):
+    names = ("o", "lse", "dq", "dk", "dv", "dak")
+    for name, a, b in zip(names, got, want):
+        if b is None:
+            assert a is None
+            continue
+        a = a.double().cpu().numpy()
+        if name == "lse":
+            finite = np.isfinite(b)
+            assert np.array_equal(np.isfinite(a), finite)
+            assert rel_err(a[finite], b[finite]) < max(tol, 1e-5), name
+        else:
+            assert rel_err(a, b) < tol, (name, rel_err(a, b))
+
+
+GRAPHS = {
+    # three sequences incl. a non-power-of-two bidirectional one (duplicate (src,dst) pairs)
+    "bpt_batch": lambda o: o.batch_graphs([o.binary_partition(300, False, 4, 10), o.binary_partition(77, True, 2, 3),
+                                           o.binary_partition(513, False, 4, 10), o.binary_partition(1, False, 4, 10)]),
+    # config 1 of the baseline: 4 x (n=512, k=4)
+    "cfg1": lambda o: o.batch_graphs([o.binary_partition(512, False, 4, 10)] * 4),
+    # a root with 3000 incoming edges: rows split over many work items
+    "long_rows": lambda o: o.binary_partition(3000, True, 8, 6),
+}
+
+
+@pytest.mark.parametrize("graph", list(GRAPHS))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd", [(8, 64), (6, 50), (3, 32), (2, 128), (20, 16)])
+def test_fused_matches_oracle(oracle_lib, graph, dtype, hd):
+    H, D = hd
+    if graph != "bpt_batch" and hd not in ((8, 64), (6, 50)):
+        pytest.skip("shape sweep runs on one graph")
+    g = GRAPHS[graph](oracle_lib)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = _inputs(N, H, D, T, dtype, 0)
+    scale = 1.0 / np.sqrt(D)
+    want = _oracle(oracle_lib, g["src"], g["dst"], g["etype"], N, q, k, v, ak, d_o, scale)
+    got = _run_gpu(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, scale)[1:]
+    _compare(got, want, TOL[dtype])
+
+
+def test_no_relative_term_empty_rows_and_dense_blocks(oracle_lib):
+    """No embed_ak (cross-attention use, modules/attention.py:156-162), destinations without
+    incoming edges, and the fully connected blocks of graph_kernel/test.py."""
+    src, dst, N0 = fully_connected_blocks(5, 30)
+    N = N0 + 7  # seven isolated nodes at the end
+    q, k, v, _, d_o = _inputs(N, 8, 64, 1, torch.float32, 1, sigma=0.5)
+    want = _oracle(oracle_lib, src, dst, None, N, q, k, v, None, d_o, 0.125)
+    plan, *got = _run_gpu(src, dst, None, N, 1, q, k, v, None, d_o, 0.125)
+    _compare(got, want, 1e-5)
+    assert torch.all(got[0][N0:] == 0) and torch.all(torch.isinf(got[1][N0:]))
+    # dense check, as test.py:364,395,459 do
+    B, L, H, D = 5, 30, 8, 64
+    qd, kd, vd = [t[:N0].double().view(B, L, H, D).transpose(1, 2) for t in (q, k, v)]
+    dense = (torch.softmax(qd @ kd.transpose(-1, -2) * 0.125, -1) @ vd).transpose(1, 2).reshape(N0, H, D)
+    assert rel_err(got[0][:N0].double().cpu(), dense) < 1e-5
+
+
+def test_fused_equals_operator_chain(oracle_lib):
+    """The fused call and the reference-shaped chain of four operators agree."""
+    from bpt_b200 import csr as csrmod, op
+    from bpt_b200.attention import AttentionPlan, bpt_attention
+    g = GRAPHS["cfg1"](oracle_lib)
+    N, T, H, D = g["n_nodes"], int(g["etype"].max()) + 1, 8, 64
+    q, k, v, ak, d_o = [t.cuda() for t in _inputs(N, H, D, T, torch.float32, 2)]
+    src, dst, et = [torch.from_numpy(g[n]).cuda() for n in ("src", "dst", "etype")]
+    out_csr, in_csr, ROW, INDPTR_R, COL, INDPTR_C = csrmod.get_csrs(src, dst, N)
+    chain_in = [t.clone().requires_grad_(True) for t in (q, k, v, ak)]
+    qc, kc, vc, akc = chain_in
+    e = op.masked_mm(ROW, INDPTR_R, out_csr[2], out_csr[1], COL, INDPTR_C, in_csr[2], in_csr[1], kc, qc)
+    e_rel = op.node_mul_edge(COL, INDPTR_C, in_csr[2], qc, akc[et])
+    p = op.sparse_softmax(COL, INDPTR_C, in_csr[2], (e_rel + e) / np.sqrt(D))
+    a = op.vec_spmm(COL, INDPTR_C, in_csr[2], in_csr[1], ROW, INDPTR_R, out_csr[2], out_csr[1], p, vc)
+    a.backward(d_o)
+    fused_in = [t.clone().requires_grad_(True) for t in (q, k, v, ak)]
+    plan = AttentionPlan(src, dst, et, N, n_etypes=T)
+    o = bpt_attention(plan, *fused_in)
+    o.backward(d_o)
+    assert rel_err(o.detach().cpu(), a.detach().cpu()) < 1e-5
+    for f, c in zip(fused_in, chain_in):
+        assert rel_err(f.grad.cpu(), c.grad.cpu()) < 2e-5
+
+
+def test_fused_is_bitwise_reproducible(oracle_lib):
+    g = GRAPHS["long_rows"](oracle_lib)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = _inputs(N, 8, 64, T, torch.float32, 3)
+    a = _run_gpu(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)[1:]
+    b = _run_gpu(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)[1:]
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_headline_size(oracle_lib, dtype):
+    """n = 8192, k = 4, 8 heads x 64 (N = 16383, E = 745786): the size the headline metric is
+    quoted on, inputs N(0, 1/8) as the sweep configuration draws them."""
+    from bpt_b200 import graphbuilder
+    gb = graphbuilder.BinaryPartition(8192, False, 4, 10)
+    s, d, t = gb.get_edges()
+    N, T = gb.number_of_nodes, int(t.max()) + 1
+    q, k, v, ak, d_o = _inputs(N, 8, 64, T, dtype, 4, sigma=0.125)
+    want = _oracle(oracle_lib, s, d, t, N, q, k, v, ak, d_o, 0.125)
+    got = _run_gpu(s, d, t, N, T, q, k, v, ak, d_o, 0.125)[1:]
+    _compare(got, want, TOL[dtype])
+    # size-independent property: attention weights of a row sum to one, so with v = 1 the output is 1
+    ones = torch.ones_like(v)
+    o1 = _run_gpu(s, d, t, N, T, q, k, ones, ak, d_o, 0.125)[1]
+    assert rel_err(o1.float().cpu(), torch.ones(N, 8, 64)) < (1e-5 if dtype == torch.float32 else 1e-2)

@@ -48,6 +48,8 @@ SIGNATURES = {
                                 _int, _int, _int, _vp, _sz, _vp]),
     "bpt_attn_backward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                  _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+    "bpt_attn_forward_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
+                                       _int, _int, _int, _vp]),
 }
 
 _lib = None

@@ -98,6 +98,30 @@ def attention_forward(plan, q, k, v, embed_ak, scale):
     return o, lse
 
 
+def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=None):
+    """attention_forward through bpt_attn_forward_static: the library call itself allocates no
+    device memory (its scratch is an 8 MiB array built into the library).  For callers that
+    pre-allocate everything, pass `out` (like q) and `lse_out` (fp32 (N, h)) so that this
+    wrapper allocates nothing either.  Graphs whose split rows need more scratch than the
+    built-in array raise; use attention_forward for those.  Calls on one GPU share that array
+    and must not overlap in time."""
+    _lib.require_cuda(q, k, v)
+    if embed_ak is not None:
+        _lib.require_cuda(embed_ak)
+    N, h, d = q.shape
+    if N != plan.n_nodes or k.shape != q.shape or v.shape != q.shape:
+        raise RuntimeError("bpt_attention: q, k, v must be (n_nodes, h, d)")
+    o = torch.empty_like(q) if out is None else out
+    lse = torch.empty((N, h), dtype=torch.float32, device=q.device) if lse_out is None else lse_out
+    _lib.require_cuda(o, lse)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().bpt_attn_forward_static(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                      _lib.ptr(embed_ak), float(scale), o.data_ptr(),
+                                                      lse.data_ptr(), h, d, _lib.dtype_code(q.dtype),
+                                                      _lib.stream()))
+    return o, lse
+
+
 def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o):
     """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d)."""
     d_o = d_o.contiguous()

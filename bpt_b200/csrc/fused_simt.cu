@@ -11,6 +11,8 @@
 //   over type buckets : d embed_ak
 // Rows longer than a work item are reduced in item order by a merge kernel, so every
 // result is bitwise reproducible (the reference's are not: graph_kernel/atomic.cuh).
+#include <mutex>
+
 #include "plan.cuh"
 
 namespace bpt {
@@ -468,6 +470,35 @@ __global__ void sum_merge_kernel(const int4 *__restrict__ split_rows, int n_spli
     }
 }
 
+// ------------------------------------------------------------------ built-in scratch
+//
+// Scratch of bpt_attn_forward_static: lives in the library image, so each GPU that loads the
+// library holds these bytes until the process exits.  In host code `g_static_scratch` is only
+// a handle for the runtime, not a device address; the address a kernel may use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+constexpr size_t kStaticScratchBytes = BPT_ATTN_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of the built-in scratch on the current device (set-up on first use).
+int static_scratch_address(void **out) {
+    int dev = -1;
+    BPT_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(BPT_ERR_INVALID, "attn_forward_static: device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void *ptr = nullptr;
+        BPT_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (ptr == nullptr) return fail(BPT_ERR_CUDA, "attn_forward_static: no address for the built-in scratch");
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return BPT_OK;
+}
+
 // ------------------------------------------------------------------ host side
 
 
@@ -652,4 +683,24 @@ extern "C" int bpt_attn_backward(const void *plan, const int32_t *counts, int64_
         case BPT_F16: return backward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
         default: return fail(BPT_ERR_UNSUPPORTED, "attn_backward: unknown dtype code %d", dtype);
     }
+}
+
+// Same computation as bpt_attn_forward, for callers that cannot provide device scratch.
+extern "C" int bpt_attn_forward_static(const void *plan, const int32_t *counts, int64_t n_nodes,
+                                       int64_t n_edges, int n_etypes, const void *q, const void *k,
+                                       const void *v, const void *ak, double scale, void *o, float *lse,
+                                       int h, int d, int dtype, bpt_stream_t stream) {
+    if (int rc = check_attn_args("attn_forward_static", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype))
+        return rc;
+    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && o && lse), "attn_forward_static: null tensor");
+    const size_t need = forward_ws_bytes(counts, h, d);
+    if (need > kStaticScratchBytes)
+        return fail(BPT_ERR_WORKSPACE,
+                    "attn_forward_static: this graph needs %zu bytes of scratch for its split rows but the "
+                    "built-in scratch holds %zu; use bpt_attn_forward with a caller-provided workspace",
+                    need, kStaticScratchBytes);
+    void *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    return bpt_attn_forward(plan, counts, n_nodes, n_edges, n_etypes, q, k, v, ak, scale, o, lse, h, d, dtype,
+                            scratch, kStaticScratchBytes, stream);
 }

@@ -215,6 +215,30 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
                       const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
                       int dtype, void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
+/* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
+#define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* No counterpart in the reference.  bpt_attn_forward for callers that must not allocate
+ * device memory while they run: code replaying a fixed memory plan, a host thread that
+ * shares the GPU with a framework whose allocator it cannot call into, a service that
+ * pre-sizes everything at start-up.  Same arguments and results as bpt_attn_forward, minus
+ * the workspace: the scratch for rows split over several work items is a fixed
+ * BPT_ATTN_STATIC_SCRATCH_BYTES (8 MiB) array inside the library image, resident on every
+ * GPU that loads the library until the process exits.  The call allocates and frees
+ * nothing.  A graph whose split rows need more than that (about ten sequences of n = 8192,
+ * k = 4 at 8 heads x 64; one sequence of n = 65536 does not fit) is rejected with
+ * BPT_ERR_WORKSPACE and nothing is launched.
+ * The first call on each device looks up the array's device address (the device must be
+ * current, as for every call here); make that first call outside any stream capture.
+ * All calls on a device share the one array: nothing in it has to be zero beforehand
+ * (every slot that is read is written earlier in the same call), but two calls that may run
+ * at the same time on one GPU, on different streams or from different threads, overwrite
+ * each other's partial results; order them on one stream or with events. */
+int bpt_attn_forward_static(const void *plan, const int32_t *counts_host, int64_t n_nodes,
+                            int64_t n_edges, int n_etypes, const void *q, const void *k,
+                            const void *v, const void *ak, double scale, void *o, float *lse,
+                            int h, int d, int dtype, bpt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,7 @@ in the forward, and its results do not vary from run to run.
 import ctypes
 import math
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -55,6 +56,7 @@ class AttentionPlan:
                                              ctypes.addressof(self._counts), _lib.stream()))
         self.counts = list(self._counts)
         self._ws = {}
+        self.tiles = None  # TilePlan of the tensor-core forward, built on first use
 
     @classmethod
     def from_batch(cls, batch, n_etypes=None):
@@ -73,12 +75,97 @@ class AttentionPlan:
             self._ws[key] = ws
         return ws
 
+    def tile_plan(self):
+        """The tile plan of the tensor-core forward (built once, on the host, then uploaded)."""
+        if self.tiles is None:
+            self.tiles = TilePlan(self)
+        return self.tiles
+
     def _args(self):
         return (self.blob.data_ptr(), ctypes.addressof(self._counts), self.n_nodes, self.n_edges, self.n_etypes)
 
 
-def attention_forward(plan, q, k, v, embed_ak, scale):
-    """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype."""
+class TilePlan:
+    """Tiles of <= 16 destination rows x a list of source columns covering the graph, for
+    bpt_attn_forward_tc.  Planned on the host from the plan's in-CSR (integer work, once per
+    graph), kept on the device."""
+
+    def __init__(self, plan, min_density=0.25, max_cols=384, col_block=64):
+        L = _lib.lib()
+        N, E, T = plan.n_nodes, plan.n_edges, plan.n_etypes
+        indptr = np.empty(N + 1, np.int32)
+        src = np.empty(max(E, 1), np.int32)
+        etype = np.empty(max(E, 1), np.int32)
+        with torch.cuda.device(plan.device):
+            _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), N, E, T, indptr.ctypes.data, src.ctypes.data,
+                                           etype.ctypes.data, _lib.stream()))
+        handle = L.bpt_tile_plan_create(indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, N, E,
+                                        float(min_density), int(max_cols), int(col_block))
+        if not handle:
+            _lib.check(1)
+        try:
+            sizes = (ctypes.c_int64 * 8)()
+            _lib.check(L.bpt_tile_plan_sizes(handle, ctypes.addressof(sizes)))
+            (self.n_tiles, n_cols, n_et, self.n_split, self.n_slots, self.t_max, self.max_cols_pad,
+             self.n_row_tiles) = [int(x) for x in sizes]
+            tiles = np.empty(max(self.n_tiles * 40, 1), np.int32)
+            cols = np.empty(max(n_cols, 1), np.int32)
+            et = np.empty(max(n_et, 1), np.uint16)
+            split = np.empty(max(self.n_split * 4, 1), np.int32)
+            _lib.check(L.bpt_tile_plan_export(handle, tiles.ctypes.data, cols.ctypes.data, et.ctypes.data,
+                                              split.ctypes.data))
+        finally:
+            L.bpt_tile_plan_destroy(handle)
+        self.n_cells = n_et
+        self.host = dict(tiles=tiles, cols=cols, et=et, split=split)
+        dev = plan.device
+        self.tiles = torch.from_numpy(tiles).to(dev)
+        self.cols = torch.from_numpy(cols).to(dev)
+        self.et = torch.from_numpy(et.view(np.int16)).to(dev)
+        self.split = torch.from_numpy(split).to(dev)
+        self.n_etypes = T
+        self._ws = {}
+
+    def workspace(self, h, device):
+        ws = self._ws.get(h)
+        if ws is None:
+            ws = _lib.workspace(_lib.lib().bpt_attn_forward_tc_workspace_bytes(self.n_slots, h), device)
+            self._ws[h] = ws
+        return ws
+
+
+def tensor_core_eligible(q, embed_ak):
+    return q.dtype == torch.bfloat16 and q.size(-1) == 64
+
+
+def attention_forward_tc(plan, q, k, v, embed_ak, scale):
+    """Forward through bpt_attn_forward_tc (bf16, head dim 64). Returns (o, lse)."""
+    _lib.require_cuda(q, k, v)
+    if embed_ak is not None:
+        _lib.require_cuda(embed_ak)
+    tp = plan.tile_plan()
+    N, h, d = q.shape
+    if N != plan.n_nodes or k.shape != q.shape or v.shape != q.shape:
+        raise RuntimeError("bpt_attention: q, k, v must be (n_nodes, h, d)")
+    o = torch.empty_like(q)
+    lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        ws = tp.workspace(h, q.device)
+        _lib.check(_lib.lib().bpt_attn_forward_tc(
+            tp.tiles.data_ptr(), tp.n_tiles, tp.cols.data_ptr(), tp.et.data_ptr(), tp.split.data_ptr(),
+            tp.n_split, tp.n_slots, tp.max_cols_pad, tp.t_max, tp.n_etypes, q.data_ptr(), k.data_ptr(),
+            v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d,
+            _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
+    return o, lse
+
+
+def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
+    """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype.
+    bf16 with head dim 64 runs on the tensor-core kernel unless tensor_cores=False."""
+    if tensor_cores is None:
+        tensor_cores = tensor_core_eligible(q, embed_ak)
+    if tensor_cores:
+        return attention_forward_tc(plan, q, k, v, embed_ak, scale)
     _lib.require_cuda(q, k, v)
     if embed_ak is not None:
         _lib.require_cuda(embed_ak)

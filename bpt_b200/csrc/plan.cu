@@ -184,3 +184,22 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     BPT_CUDA(cudaStreamSynchronize(stream));
     return BPT_OK;
 }
+
+extern "C" int bpt_export_in_csr(const void *plan, int64_t n_nodes, int64_t n_edges, int n_etypes,
+                                 int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
+                                 bpt_stream_t stream_) {
+    BPT_CHECK_ARG(plan && in_indptr_host, "export_in_csr: null argument");
+    BPT_CHECK_ARG(n_edges == 0 || (in_src_host && in_etype_host), "export_in_csr: null argument");
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
+    cudaStream_t stream = as_stream(stream_);
+    BPT_CUDA(cudaMemcpyAsync(in_indptr_host, p.in_indptr, sizeof(int32_t) * static_cast<size_t>(n_nodes + 1),
+                             cudaMemcpyDeviceToHost, stream));
+    if (n_edges > 0) {
+        BPT_CUDA(cudaMemcpyAsync(in_src_host, p.in_src, sizeof(int32_t) * static_cast<size_t>(n_edges),
+                                 cudaMemcpyDeviceToHost, stream));
+        BPT_CUDA(cudaMemcpyAsync(in_etype_host, p.in_etype, sizeof(int32_t) * static_cast<size_t>(n_edges),
+                                 cudaMemcpyDeviceToHost, stream));
+    }
+    BPT_CUDA(cudaStreamSynchronize(stream));
+    return BPT_OK;
+}

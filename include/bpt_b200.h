@@ -215,6 +215,46 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
                       const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
                       int dtype, void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
+/* ------------------------------------------------------------------------------------
+ * Tensor-core forward (bf16, head dim 64).  Same result as bpt_attn_forward within bf16
+ * tolerance; the graph is given as a tile plan.  No counterpart in the reference beyond the
+ * operator chain named at bpt_attn_forward.
+ *
+ * The planner runs on the host (pure integer code, no GPU needed): it takes the in-CSR as
+ * host int32 arrays (in_indptr[n_nodes+1], in_src[n_edges], in_etype[n_edges] or NULL) and
+ * covers the attention matrix with tiles of <= 16 destination rows x a list of source
+ * columns.  min_density / max_cols decide when 16 consecutive rows form one tile (edges >=
+ * min_density * 16 * columns, columns <= max_cols); other rows are grouped by block of
+ * `col_block` consecutive sources.  bpt_tile_plan_sizes fills sizes[8] = {tiles, column
+ * entries, etype cells, split rows, slots, t_max, max_cols_pad, row tiles};
+ * bpt_tile_plan_export copies tiles (40 int32 each), cols (int32), et (uint16) and
+ * split_rows (4 int32 each) into host arrays of those sizes, to be uploaded as they are.
+ * bpt_export_in_csr copies the in-CSR of a bpt_attn_plan_build plan to host arrays (waits
+ * for the stream).
+ * ---------------------------------------------------------------------------------- */
+void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
+                           int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
+                           int col_block);
+int bpt_tile_plan_sizes(const void *handle, int64_t *sizes);
+int bpt_tile_plan_export(const void *handle, int32_t *tiles, int32_t *cols, uint16_t *et,
+                         int32_t *split_rows);
+void bpt_tile_plan_destroy(void *handle);
+int bpt_export_in_csr(const void *plan, int64_t n_nodes, int64_t n_edges, int n_etypes,
+                      int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
+                      bpt_stream_t stream);
+
+size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
+
+/* tiles, cols, et, split_rows: device copies of the exported plan arrays; the size
+ * arguments are the matching entries of bpt_tile_plan_sizes.  q, k, v, o: (n_nodes, h, 64)
+ * bf16, 16-byte aligned; ak: (n_etypes, 64) bf16 or NULL; lse fp32 (n_nodes, h). */
+int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const int32_t *cols, const uint16_t *et,
+                        const int32_t *split_rows, int64_t n_split, int64_t n_slots,
+                        int max_cols_pad, int t_max, int n_etypes, const void *q, const void *k,
+                        const void *v, const void *ak, double scale, void *o, float *lse, int h,
+                        int d, int dtype, void *workspace, size_t workspace_bytes,
+                        bpt_stream_t stream);
+
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

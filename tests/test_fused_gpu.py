@@ -154,3 +154,26 @@ def test_headline_size(oracle_lib, dtype):
     ones = torch.ones_like(v)
     o1 = _run_gpu(s, d, t, N, T, q, k, ones, ak, d_o, 0.125)[1]
     assert rel_err(o1.float().cpu(), torch.ones(N, 8, 64)) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_tensor_core_forward_is_used_and_matches_cuda_core_forward(oracle_lib):
+    """bf16 x head dim 64 goes through bpt_attn_forward_tc; it must agree with the CUDA-core
+    kernel on the same inputs (both see the same bf16 numbers) and be reproducible."""
+    from bpt_b200.attention import AttentionPlan, attention_forward
+    g = GRAPHS["bpt_batch"](oracle_lib)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, _ = [t.cuda() for t in _inputs(N, 8, 64, T, torch.bfloat16, 7)]
+    plan = AttentionPlan(torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda(),
+                         torch.from_numpy(g["etype"]).cuda(), N, n_etypes=T)
+    o_tc, lse_tc = attention_forward(plan, q, k, v, ak, 0.125)
+    assert plan.tiles is not None and plan.tiles.n_tiles > 0
+    o_cc, lse_cc = attention_forward(plan, q, k, v, ak, 0.125, tensor_cores=False)
+    assert rel_err(o_tc.float().cpu(), o_cc.float().cpu()) < 2e-2
+    assert rel_err(lse_tc.cpu(), lse_cc.cpu()) < 2e-3
+    o2, lse2 = attention_forward(plan, q, k, v, ak, 0.125)
+    assert torch.equal(o_tc, o2) and torch.equal(lse_tc, lse2)
+    # without the relative-position table, and with 3 heads (fewer heads than warps)
+    o_tc, lse_tc = attention_forward(plan, q[:, :3].contiguous(), k[:, :3].contiguous(), v[:, :3].contiguous(), None, 0.125)
+    o_cc, lse_cc = attention_forward(plan, q[:, :3].contiguous(), k[:, :3].contiguous(), v[:, :3].contiguous(), None,
+                                     0.125, tensor_cores=False)
+    assert rel_err(o_tc.float().cpu(), o_cc.float().cpu()) < 2e-2 and rel_err(lse_tc.cpu(), lse_cc.cpu()) < 2e-3

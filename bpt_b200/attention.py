@@ -90,7 +90,7 @@ class TilePlan:
     bpt_attn_forward_tc.  Planned on the host from the plan's in-CSR (integer work, once per
     graph), kept on the device."""
 
-    def __init__(self, plan, min_density=0.25, max_cols=384, col_block=64):
+    def __init__(self, plan, min_density=0.25, max_cols=384, col_block=64, simt_max_degree=0):
         L = _lib.lib()
         N, E, T = plan.n_nodes, plan.n_edges, plan.n_etypes
         indptr = np.empty(N + 1, np.int32)
@@ -100,29 +100,32 @@ class TilePlan:
             _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), N, E, T, indptr.ctypes.data, src.ctypes.data,
                                            etype.ctypes.data, _lib.stream()))
         handle = L.bpt_tile_plan_create(indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, N, E,
-                                        float(min_density), int(max_cols), int(col_block))
+                                        float(min_density), int(max_cols), int(col_block),
+                                        int(simt_max_degree))
         if not handle:
             _lib.check(1)
         try:
-            sizes = (ctypes.c_int64 * 8)()
+            sizes = (ctypes.c_int64 * 10)()
             _lib.check(L.bpt_tile_plan_sizes(handle, ctypes.addressof(sizes)))
             (self.n_tiles, n_cols, n_et, self.n_split, self.n_slots, self.t_max, self.max_cols_pad,
-             self.n_row_tiles) = [int(x) for x in sizes]
+             self.n_row_tiles, self.n_row_items, _) = [int(x) for x in sizes]
             tiles = np.empty(max(self.n_tiles * 40, 1), np.int32)
             cols = np.empty(max(n_cols, 1), np.int32)
             et = np.empty(max(n_et, 1), np.uint16)
             split = np.empty(max(self.n_split * 4, 1), np.int32)
+            items = np.empty(max(self.n_row_items * 4, 1), np.int32)
             _lib.check(L.bpt_tile_plan_export(handle, tiles.ctypes.data, cols.ctypes.data, et.ctypes.data,
-                                              split.ctypes.data))
+                                              split.ctypes.data, items.ctypes.data))
         finally:
             L.bpt_tile_plan_destroy(handle)
         self.n_cells = n_et
-        self.host = dict(tiles=tiles, cols=cols, et=et, split=split)
+        self.host = dict(tiles=tiles, cols=cols, et=et, split=split, items=items)
         dev = plan.device
         self.tiles = torch.from_numpy(tiles).to(dev)
         self.cols = torch.from_numpy(cols).to(dev)
         self.et = torch.from_numpy(et.view(np.int16)).to(dev)
         self.split = torch.from_numpy(split).to(dev)
+        self.items = torch.from_numpy(items).to(dev)
         self.n_etypes = T
         self._ws = {}
 
@@ -153,7 +156,8 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale):
         ws = tp.workspace(h, q.device)
         _lib.check(_lib.lib().bpt_attn_forward_tc(
             tp.tiles.data_ptr(), tp.n_tiles, tp.cols.data_ptr(), tp.et.data_ptr(), tp.split.data_ptr(),
-            tp.n_split, tp.n_slots, tp.max_cols_pad, tp.t_max, tp.n_etypes, q.data_ptr(), k.data_ptr(),
+            tp.n_split, tp.n_slots, tp.items.data_ptr(), tp.n_row_items, plan.blob.data_ptr(), plan.n_nodes,
+            plan.n_edges, tp.max_cols_pad, tp.t_max, tp.n_etypes, q.data_ptr(), k.data_ptr(),
             v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d,
             _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
     return o, lse

@@ -16,31 +16,101 @@ struct Geometry {
 // Partial results of a row that is spread over several work items or tiles: per slot and
 // head, part_ml = {m, l} (running max of the log2-domain scores, sum of 2^(s-m)) and part_o =
 // the unnormalised weighted sum of V rows.
-// Combines the partial (m, l, o) triples of a split row in slot order.
+// Combines the partial (m, l, o) triples of a split row, in slot order.  One block per row.
+// Slots are taken in batches of kMergeBatch: one thread per head turns the batch's (m, l) into
+// weights 2^(m_s - m_run) and the factor that rescales what was accumulated so far, then
+// every output column adds its batch of partial values with several loads in flight.
+constexpr int kMergeBatch = 128;
+
 template <typename T>
 __global__ void attn_forward_merge_kernel(const int4 *__restrict__ split_rows, int n_split,
                                           const float *__restrict__ part_o, const float *__restrict__ part_ml,
                                           T *__restrict__ o, float *__restrict__ lse, Geometry g) {
+    extern __shared__ float s_merge[];  // [kMergeBatch][H] m then weights | [kMergeBatch][H] l | [H] rescale | [H] 1/l
     const int sr = blockIdx.x;
     if (sr >= n_split) return;
     const int4 rec = split_rows[sr];
     const int row = rec.x, first = rec.y, count = rec.z;
-    const int HD = g.H * g.D;
-    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-        const int head = c / g.D;
-        float m = -INFINITY;
-        for (int s = 0; s < count; ++s) m = fmaxf(m, part_ml[(static_cast<int64_t>(first + s) * g.H + head) * 2]);
-        float l = 0.f, acc = 0.f;
-        for (int s = 0; s < count; ++s) {
-            const int64_t base = static_cast<int64_t>(first + s) * g.H + head;
-            const float w = exp2f(part_ml[base * 2] - m);
-            l = fmaf(part_ml[base * 2 + 1], w, l);
-            acc = fmaf(part_o[static_cast<int64_t>(first + s) * HD + c], w, acc);
+    const int H = g.H, HD = g.H * g.D;
+    float *s_w = s_merge, *s_l = s_merge + kMergeBatch * H, *s_f = s_l + kMergeBatch * H, *s_inv = s_f + H;
+    float m_run = -INFINITY, l_run = 0.f;  // meaningful in threads < H
+    // Each thread owns columns threadIdx.x, + blockDim.x, ... (at most kMaxCols of them).
+    constexpr int kMaxCols = 8;
+    float acc[kMaxCols];
+#pragma unroll
+    for (int u = 0; u < kMaxCols; ++u) acc[u] = 0.f;
+
+    for (int s0 = 0; s0 < count; s0 += kMergeBatch) {
+        const int nb = min(kMergeBatch, count - s0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nb * H; i += blockDim.x) {
+            const float2 ml = *reinterpret_cast<const float2 *>(part_ml + (static_cast<int64_t>(first + s0) * H + i) * 2);
+            s_w[i] = ml.x;
+            s_l[i] = ml.y;
         }
-        o[static_cast<int64_t>(row) * HD + c] = from_acc<T>(acc / l);
-        if (c % g.D == 0) lse[static_cast<int64_t>(row) * g.H + head] = (m + log2f(l)) * kLn2;
+        __syncthreads();
+        if (threadIdx.x < H) {
+            const int head = threadIdx.x;
+            float m = m_run;
+            for (int s = 0; s < nb; ++s) m = fmaxf(m, s_w[s * H + head]);
+            const float ms = m == -INFINITY ? 0.f : m;
+            const float f = exp2f(m_run - ms);
+            float l = l_run * f;
+            for (int s = 0; s < nb; ++s) {
+                const float w = exp2f(s_w[s * H + head] - ms);
+                l = fmaf(s_l[s * H + head], w, l);
+                s_w[s * H + head] = w;
+            }
+            s_f[head] = f;
+            m_run = m;
+            l_run = l;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < kMaxCols; ++u) {
+            const int c = threadIdx.x + u * blockDim.x;
+            if (c >= HD) break;
+            const int head = c / g.D;
+            const float *src = part_o + static_cast<int64_t>(first + s0) * HD + c;
+            float a = acc[u] * s_f[head];
+            int s = 0;
+            for (; s + 8 <= nb; s += 8) {
+                float x[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) x[v] = src[static_cast<int64_t>(s + v) * HD];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) a = fmaf(x[v], s_w[(s + v) * H + head], a);
+            }
+            for (; s < nb; ++s) a = fmaf(src[static_cast<int64_t>(s) * HD], s_w[s * H + head], a);
+            acc[u] = a;
+        }
+    }
+    if (threadIdx.x < H) {
+        s_inv[threadIdx.x] = l_run > 0.f ? 1.f / l_run : 0.f;
+        lse[static_cast<int64_t>(row) * H + threadIdx.x] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : -INFINITY;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < kMaxCols; ++u) {
+        const int c = threadIdx.x + u * blockDim.x;
+        if (c >= HD) break;
+        o[static_cast<int64_t>(row) * HD + c] = from_acc<T>(acc[u] * s_inv[c / g.D]);
     }
 }
 
+// Block size and shared memory of the merge kernel.  Needs H <= threads and H*D <= 8*threads.
+inline int merge_threads(int H, int D) {
+    int t = (H * D + 7) / 8;
+    t = t < H ? H : t;
+    t = (t + 31) / 32 * 32;
+    return t < 128 ? 128 : (t > 1024 ? 1024 : t);
+}
+inline size_t merge_smem_bytes(int H) { return (static_cast<size_t>(kMergeBatch) * H * 2 + 2 * H) * sizeof(float); }
+
+// Runs the CUDA-core forward kernel over a caller-given list of whole-row work items
+// ({row, begin, end, -1} into the in-CSR arrays); bf16 storage.  Defined in fused_simt.cu.
+int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_src, const int32_t *in_etype,
+                              const void *q, const void *k, const void *v, const void *ak, float scale,
+                              void *o, float *lse, int H, int D, cudaStream_t stream);
 
 }  // namespace bpt

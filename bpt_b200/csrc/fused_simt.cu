@@ -534,8 +534,8 @@ int forward_impl(const PlanView &p, const int32_t *counts, const void *q_, const
         p.in_work.items, n_items, p.in_src, p.in_etype, q, k, v, ak, scale, o, lse, part_o, part_ml, g)));
     BPT_LAUNCH_CHECK();
     if (n_split > 0) {
-        attn_forward_merge_kernel<T><<<n_split, 256, 0, stream>>>(p.in_work.split_rows, n_split, part_o,
-                                                                  part_ml, o, lse, g);
+        attn_forward_merge_kernel<T><<<n_split, merge_threads(H, D), merge_smem_bytes(H), stream>>>(
+            p.in_work.split_rows, n_split, part_o, part_ml, o, lse, g);
         BPT_LAUNCH_CHECK();
     }
     return BPT_OK;
@@ -601,12 +601,36 @@ int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, cons
     return BPT_OK;
 }
 
+}  // namespace
+
+int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_src, const int32_t *in_etype,
+                              const void *q_, const void *k_, const void *v_, const void *ak_, float scale,
+                              void *o_, float *lse, int H, int D, cudaStream_t stream) {
+    using T = __nv_bfloat16;
+    if (n_items == 0) return BPT_OK;
+    const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
+    const T *ak = static_cast<const T *>(ak_);
+    T *o = static_cast<T *>(o_);
+    const int lph = pick_lph(D);
+    const bool vec = can_vectorise<T>(D, lph, q, k, v, ak, o, o);
+    const Geometry g{H, D};
+    const int hpw = 32 / lph;
+    const dim3 grid((n_items + kWarpsPerBlock - 1) / kWarpsPerBlock, (H + hpw - 1) / hpw);
+    BPT_DISPATCH_LPH_VEC(lph, vec, (attn_forward_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        items, n_items, in_src, in_etype, q, k, v, ak, scale, o, lse, nullptr, nullptr, g)));
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+namespace {
+
 int check_attn_args(const char *name, const void *plan, const int32_t *counts, int64_t n_nodes,
                     int64_t n_edges, int n_etypes, int H, int D, int dtype) {
     BPT_CHECK_ARG(plan != nullptr && counts != nullptr, "%s: null plan", name);
     BPT_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && n_etypes >= 1, "%s: bad sizes", name);
     BPT_CHECK_ARG(H >= 1 && D >= 1, "%s: h and d must be positive", name);
     if (D > 128) return fail(BPT_ERR_UNSUPPORTED, "%s: head dim %d > 128 has no kernel", name, D);
+    if (H > 40) return fail(BPT_ERR_UNSUPPORTED, "%s: more than 40 heads has no kernel", name);
     if (dtype == BPT_F64) return fail(BPT_ERR_UNSUPPORTED, "%s: fp64 has no fused kernel (use the operators)", name);
     return BPT_OK;
 }

@@ -28,6 +28,7 @@ struct HostTilePlan {
     std::vector<int32_t> cols;
     std::vector<uint16_t> et;
     std::vector<int32_t> split;  // int4 records {row, first_slot, n_slots, 0}
+    std::vector<int32_t> simt;   // int4 records {row, begin, end, -1}: short rows left to the CUDA-core kernel
     int64_t n_slots = 0, t_max = 0, max_cols_pad = 0, n_cells = 0, n_row_tiles = 0;
 };
 
@@ -110,7 +111,7 @@ using namespace bpt;
 
 extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
                                       int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
-                                      int col_block) {
+                                      int col_block, int simt_max_degree) {
     if (!in_indptr || (n_edges > 0 && !in_src) || n_nodes < 0 || n_edges < 0 || max_cols < kTileChunk ||
         col_block < 1) {
         fail(BPT_ERR_INVALID, "tile_plan_create: bad arguments");
@@ -154,8 +155,18 @@ extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *i
             ++plan->n_row_tiles;
         } else {
             for (int i = 0; i < nr; ++i) {
-                if (in_indptr[rows[i] + 1] == in_indptr[rows[i]]) zero_rows.push_back(rows[i]);
-                else leftover_rows.push_back(rows[i]);
+                const int32_t deg = in_indptr[rows[i] + 1] - in_indptr[rows[i]];
+                if (deg <= simt_max_degree) {
+                    // too few edges to be worth a tile cell row: one warp walks the row instead
+                    plan->simt.push_back(rows[i]);
+                    plan->simt.push_back(in_indptr[rows[i]]);
+                    plan->simt.push_back(in_indptr[rows[i] + 1]);
+                    plan->simt.push_back(-1);
+                } else if (deg == 0) {
+                    zero_rows.push_back(rows[i]);
+                } else {
+                    leftover_rows.push_back(rows[i]);
+                }
             }
         }
     }
@@ -248,17 +259,20 @@ extern "C" int bpt_tile_plan_sizes(const void *handle, int64_t *sizes) {
     sizes[5] = p->t_max;
     sizes[6] = p->max_cols_pad;
     sizes[7] = p->n_row_tiles;
+    sizes[8] = static_cast<int64_t>(p->simt.size() / 4);
+    sizes[9] = p->n_cells;
     return BPT_OK;
 }
 
 extern "C" int bpt_tile_plan_export(const void *handle, int32_t *tiles, int32_t *cols, uint16_t *et,
-                                    int32_t *split_rows) {
+                                    int32_t *split_rows, int32_t *simt_items) {
     BPT_CHECK_ARG(handle, "tile_plan_export: null handle");
     const HostTilePlan *p = static_cast<const HostTilePlan *>(handle);
     if (tiles && !p->tiles.empty()) std::memcpy(tiles, p->tiles.data(), p->tiles.size() * sizeof(int32_t));
     if (cols && !p->cols.empty()) std::memcpy(cols, p->cols.data(), p->cols.size() * sizeof(int32_t));
     if (et && !p->et.empty()) std::memcpy(et, p->et.data(), p->et.size() * sizeof(uint16_t));
     if (split_rows && !p->split.empty()) std::memcpy(split_rows, p->split.data(), p->split.size() * sizeof(int32_t));
+    if (simt_items && !p->simt.empty()) std::memcpy(simt_items, p->simt.data(), p->simt.size() * sizeof(int32_t));
     return BPT_OK;
 }
 

@@ -225,19 +225,21 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
  * covers the attention matrix with tiles of <= 16 destination rows x a list of source
  * columns.  min_density / max_cols decide when 16 consecutive rows form one tile (edges >=
  * min_density * 16 * columns, columns <= max_cols); other rows are grouped by block of
- * `col_block` consecutive sources.  bpt_tile_plan_sizes fills sizes[8] = {tiles, column
- * entries, etype cells, split rows, slots, t_max, max_cols_pad, row tiles};
- * bpt_tile_plan_export copies tiles (40 int32 each), cols (int32), et (uint16) and
- * split_rows (4 int32 each) into host arrays of those sizes, to be uploaded as they are.
+ * `col_block` consecutive sources, except rows of at most `simt_max_degree` edges, which are
+ * listed as whole-row items {row, begin, end, -1} for the CUDA-core kernel.
+ * bpt_tile_plan_sizes fills sizes[10] = {tiles, column entries, etype cells, split rows,
+ * slots, t_max, max_cols_pad, row tiles, row items, tile cells}; bpt_tile_plan_export copies
+ * tiles (40 int32 each), cols (int32), et (uint16), split_rows and row_items (4 int32 each)
+ * into host arrays of those sizes, to be uploaded as they are.
  * bpt_export_in_csr copies the in-CSR of a bpt_attn_plan_build plan to host arrays (waits
  * for the stream).
  * ---------------------------------------------------------------------------------- */
 void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
                            int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
-                           int col_block);
+                           int col_block, int simt_max_degree);
 int bpt_tile_plan_sizes(const void *handle, int64_t *sizes);
 int bpt_tile_plan_export(const void *handle, int32_t *tiles, int32_t *cols, uint16_t *et,
-                         int32_t *split_rows);
+                         int32_t *split_rows, int32_t *row_items);
 void bpt_tile_plan_destroy(void *handle);
 int bpt_export_in_csr(const void *plan, int64_t n_nodes, int64_t n_edges, int n_etypes,
                       int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
@@ -245,11 +247,14 @@ int bpt_export_in_csr(const void *plan, int64_t n_nodes, int64_t n_edges, int n_
 
 size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
 
-/* tiles, cols, et, split_rows: device copies of the exported plan arrays; the size
+/* tiles, cols, et, split_rows, row_items: device copies of the exported arrays; attn_plan:
+ * the bpt_attn_plan_build blob of the same graph (its in-CSR is what row_items index); the size
  * arguments are the matching entries of bpt_tile_plan_sizes.  q, k, v, o: (n_nodes, h, 64)
  * bf16, 16-byte aligned; ak: (n_etypes, 64) bf16 or NULL; lse fp32 (n_nodes, h). */
 int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const int32_t *cols, const uint16_t *et,
                         const int32_t *split_rows, int64_t n_split, int64_t n_slots,
+                        const int32_t *row_items, int64_t n_row_items, const void *attn_plan,
+                        int64_t n_nodes, int64_t n_edges,
                         int max_cols_pad, int t_max, int n_etypes, const void *q, const void *k,
                         const void *v, const void *ak, double scale, void *o, float *lse, int h,
                         int d, int dtype, void *workspace, size_t workspace_bytes,

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 
-def _plan(oracle_lib, g, min_density=0.25, max_cols=384, col_block=64):
+def _plan(oracle_lib, g, min_density=0.25, max_cols=384, col_block=64, simt_max_degree=8):
     from bpt_b200 import _lib, build
     build.build()
     L = _lib.lib()
@@ -14,19 +14,21 @@ def _plan(oracle_lib, g, min_density=0.25, max_cols=384, col_block=64):
     et = g["etype"][eid]
     ip32, s32, e32 = indptr.astype(np.int32), src.astype(np.int32), et.astype(np.int32)
     h = L.bpt_tile_plan_create(ip32.ctypes.data, s32.ctypes.data, e32.ctypes.data, g["n_nodes"], len(src),
-                               min_density, max_cols, col_block)
+                               min_density, max_cols, col_block, simt_max_degree)
     assert h
-    sizes = (ctypes.c_int64 * 8)()
+    sizes = (ctypes.c_int64 * 10)()
     assert L.bpt_tile_plan_sizes(h, ctypes.addressof(sizes)) == 0
-    n_tiles, n_cols, n_et, n_split, n_slots, t_max, mcp, n_row_tiles = [int(x) for x in sizes]
+    n_tiles, n_cols, n_et, n_split, n_slots, t_max, mcp, n_row_tiles, n_items, _ = [int(x) for x in sizes]
     tiles = np.empty(n_tiles * 40, np.int32)
     cols = np.empty(max(n_cols, 1), np.int32)
     etm = np.empty(max(n_et, 1), np.uint16)
     split = np.empty(max(n_split * 4, 1), np.int32)
-    assert L.bpt_tile_plan_export(h, tiles.ctypes.data, cols.ctypes.data, etm.ctypes.data, split.ctypes.data) == 0
+    items = np.empty(max(n_items * 4, 1), np.int32)
+    assert L.bpt_tile_plan_export(h, tiles.ctypes.data, cols.ctypes.data, etm.ctypes.data, split.ctypes.data,
+                                  items.ctypes.data) == 0
     L.bpt_tile_plan_destroy(h)
     return dict(tiles=tiles.reshape(n_tiles, 40), cols=cols, et=etm, split=split[:n_split * 4].reshape(n_split, 4),
-                n_slots=n_slots, t_max=t_max, mcp=mcp, n_row_tiles=n_row_tiles, csr=(indptr, src, et))
+                items=items[:n_items * 4].reshape(n_items, 4), n_slots=n_slots, t_max=t_max, mcp=mcp, n_row_tiles=n_row_tiles, csr=(indptr, src, et))
 
 
 @pytest.mark.parametrize("spec", [[(512, False, 4, 10)], [(513, False, 4, 10), (100, True, 2, 3), (1, False, 1, 10)],
@@ -60,6 +62,11 @@ def test_tiles_cover_every_edge_once(oracle_lib, spec):
                 assert len(cs) == indptr[rows[i] + 1] - indptr[rows[i]]
             else:
                 slots.setdefault(int(rows[i]), []).append(int(slot[i]))
+    for row, beg, end, slot in p["items"]:      # short rows handed to the CUDA-core kernel, whole
+        assert slot == -1 and beg == indptr[row] and end == indptr[row + 1] and not complete[row]
+        complete[row] = True
+        rows_seen[row] += 1
+        got += [(int(row), int(src[j]), int(et[j])) for j in range(beg, end)]
     want = sorted((int(r), int(src[j]), int(et[j])) for r in range(N) for j in range(indptr[r], indptr[r + 1]))
     assert sorted(got) == want
     assert np.all(rows_seen >= 1)                       # rows without edges are covered too

@@ -40,9 +40,9 @@ SIGNATURES = {
     "bpt_vector_spmm_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
     "bpt_vector_spmm_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
                                         _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
-    "bpt_attn_plan_bytes": (_sz, [_i64, _i64, _int]),
-    "bpt_attn_plan_workspace_bytes": (_sz, [_i64, _i64, _int]),
-    "bpt_attn_plan_build": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp, _sz, _vp, _vp]),
+    "bpt_attn_plan_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "bpt_attn_plan_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "bpt_attn_plan_build": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp, _sz, _vp, _vp]),
     "bpt_attn_workspace_bytes": (_sz, [_i64, _i64, _vp, _int, _int, _int]),
     "bpt_attn_forward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                 _int, _int, _int, _vp, _sz, _vp]),
@@ -52,9 +52,9 @@ SIGNATURES = {
     "bpt_tile_plan_sizes": (_int, [_vp, _vp]),
     "bpt_tile_plan_export": (_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bpt_tile_plan_destroy": (None, [_vp]),
-    "bpt_export_in_csr": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
+    "bpt_export_in_csr": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "bpt_attn_forward_tc_workspace_bytes": (_sz, [_i64, _int]),
-    "bpt_attn_forward_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i64,
+    "bpt_attn_forward_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _vp, _i64, _i64,
                                    _int, _int, _int, _vp, _vp, _vp, _vp,
                                    _dbl, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "bpt_attn_forward_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,

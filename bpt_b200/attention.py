@@ -27,10 +27,12 @@ class AttentionPlan:
 
     src, dst, etype: int32 CUDA tensors in edge-id order (etype may be None);
     n_etypes: rows of the relative-position table the graph may index (every etype must be
-    smaller); defaults to max(etype) + 1.
+    smaller); defaults to max(etype) + 1.  n_src: number of source rows (k, v) when sources
+    and destinations are different node sets (cross-attention, a shard attending to gathered
+    K/V); defaults to n_nodes.
     """
 
-    def __init__(self, src, dst, etype, n_nodes, n_etypes=None):
+    def __init__(self, src, dst, etype, n_nodes, n_etypes=None, n_src=None):
         src = src.to(torch.int32).contiguous()
         dst = dst.to(torch.int32).contiguous()
         _lib.require_cuda(src, dst)
@@ -43,15 +45,16 @@ class AttentionPlan:
             n_etypes = 1
         self.device = src.device
         self.n_nodes, self.n_edges, self.n_etypes = int(n_nodes), int(src.numel()), int(n_etypes)
+        self.n_src = self.n_nodes if n_src is None else int(n_src)
         L = _lib.lib()
         with torch.cuda.device(self.device):
-            self.blob = _lib.workspace(L.bpt_attn_plan_bytes(self.n_nodes, self.n_edges, self.n_etypes),
+            self.blob = _lib.workspace(L.bpt_attn_plan_bytes(self.n_nodes, self.n_src, self.n_edges, self.n_etypes),
                                        self.device)
-            ws = _lib.workspace(L.bpt_attn_plan_workspace_bytes(self.n_nodes, self.n_edges, self.n_etypes),
+            ws = _lib.workspace(L.bpt_attn_plan_workspace_bytes(self.n_nodes, self.n_src, self.n_edges, self.n_etypes),
                                 self.device)
-            self._counts = (ctypes.c_int32 * 9)()
+            self._counts = (ctypes.c_int32 * 12)()
             _lib.check(L.bpt_attn_plan_build(_lib.ptr(src), _lib.ptr(dst), _lib.ptr(etype), self.n_edges,
-                                             self.n_nodes, self.n_etypes, self.blob.data_ptr(),
+                                             self.n_nodes, self.n_src, self.n_etypes, self.blob.data_ptr(),
                                              self.blob.numel(), ws.data_ptr(), ws.numel(),
                                              ctypes.addressof(self._counts), _lib.stream()))
         self.counts = list(self._counts)
@@ -97,7 +100,7 @@ class TilePlan:
         src = np.empty(max(E, 1), np.int32)
         etype = np.empty(max(E, 1), np.int32)
         with torch.cuda.device(plan.device):
-            _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), N, E, T, indptr.ctypes.data, src.ctypes.data,
+            _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), ctypes.addressof(plan._counts), N, E, T, indptr.ctypes.data, src.ctypes.data,
                                            etype.ctypes.data, _lib.stream()))
         handle = L.bpt_tile_plan_create(indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, N, E,
                                         float(min_density), int(max_cols), int(col_block),
@@ -148,15 +151,16 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale):
         _lib.require_cuda(embed_ak)
     tp = plan.tile_plan()
     N, h, d = q.shape
-    if N != plan.n_nodes or k.shape != q.shape or v.shape != q.shape:
-        raise RuntimeError("bpt_attention: q, k, v must be (n_nodes, h, d)")
+    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
+        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
         ws = tp.workspace(h, q.device)
         _lib.check(_lib.lib().bpt_attn_forward_tc(
             tp.tiles.data_ptr(), tp.n_tiles, tp.cols.data_ptr(), tp.et.data_ptr(), tp.split.data_ptr(),
-            tp.n_split, tp.n_slots, tp.items.data_ptr(), tp.n_row_items, plan.blob.data_ptr(), plan.n_nodes,
+            tp.n_split, tp.n_slots, tp.items.data_ptr(), tp.n_row_items, plan.blob.data_ptr(),
+            ctypes.addressof(plan._counts), plan.n_nodes,
             plan.n_edges, tp.max_cols_pad, tp.t_max, tp.n_etypes, q.data_ptr(), k.data_ptr(),
             v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d,
             _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
@@ -176,8 +180,8 @@ def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
         if embed_ak.dtype != q.dtype or embed_ak.size(0) < plan.n_etypes or embed_ak.size(1) != q.size(-1):
             raise RuntimeError("bpt_attention: embed_ak must be (>= n_etypes, d) of the dtype of q")
     N, h, d = q.shape
-    if N != plan.n_nodes or k.shape != q.shape or v.shape != q.shape:
-        raise RuntimeError("bpt_attention: q, k, v must be (n_nodes, h, d)")
+    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
+        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
@@ -200,8 +204,8 @@ def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=N
     if embed_ak is not None:
         _lib.require_cuda(embed_ak)
     N, h, d = q.shape
-    if N != plan.n_nodes or k.shape != q.shape or v.shape != q.shape:
-        raise RuntimeError("bpt_attention: q, k, v must be (n_nodes, h, d)")
+    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
+        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
     o = torch.empty_like(q) if out is None else out
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device) if lse_out is None else lse_out
     _lib.require_cuda(o, lse)

@@ -652,7 +652,7 @@ extern "C" int bpt_attn_forward(const void *plan, const int32_t *counts, int64_t
                                 size_t workspace_bytes, bpt_stream_t stream) {
     if (int rc = check_attn_args("attn_forward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
     BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && o && lse), "attn_forward: null tensor");
-    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts[kCountsNSrc], n_edges, n_etypes);
     switch (dtype) {
         case BPT_F32: return forward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
         case BPT_BF16: return forward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
@@ -669,7 +669,7 @@ extern "C" int bpt_attn_backward(const void *plan, const int32_t *counts, int64_
     if (int rc = check_attn_args("attn_backward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
     BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && lse && d_o && dq && dk && dv), "attn_backward: null tensor");
     BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward: ak given without dak");
-    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts[kCountsNSrc], n_edges, n_etypes);
     switch (dtype) {
         case BPT_F32: return backward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
         case BPT_BF16: return backward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));

@@ -272,7 +272,7 @@ extern "C" size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h) {
 extern "C" int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const int32_t *cols, const uint16_t *et,
                                    const int32_t *split_rows, int64_t n_split, int64_t n_slots,
                                    const int32_t *simt_items, int64_t n_simt_items, const void *attn_plan,
-                                   int64_t n_nodes, int64_t n_edges,
+                                   const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
                                    int max_cols_pad, int t_max, int n_etypes, const void *q, const void *k,
                                    const void *v, const void *ak, double scale, void *o, float *lse, int h,
                                    int d, int dtype, void *workspace, size_t workspace_bytes,
@@ -282,7 +282,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const 
         return fail(BPT_ERR_UNSUPPORTED, "attn_forward_tc: only bf16 with head dim 64 (got dtype %d, d %d)", dtype, d);
     if (n_tiles == 0 && n_simt_items == 0) return BPT_OK;
     BPT_CHECK_ARG((n_tiles == 0 || tiles) && q && k && v && o && lse, "attn_forward_tc: null argument");
-    BPT_CHECK_ARG(n_simt_items == 0 || (simt_items && attn_plan), "attn_forward_tc: null row-item list");
+    BPT_CHECK_ARG(n_simt_items == 0 || (simt_items && attn_plan && counts_host), "attn_forward_tc: null row-item list");
     BPT_CHECK_ARG(n_simt_items >= 0 && n_simt_items < (int64_t(1) << 31), "attn_forward_tc: bad row-item count");
     BPT_CHECK_ARG(max_cols_pad == 0 || (cols && et), "attn_forward_tc: null plan arrays");
     BPT_CHECK_ARG(max_cols_pad % kTileChunk == 0 && t_max % 8 == 0 && n_etypes >= 1, "attn_forward_tc: bad plan sizes");
@@ -303,7 +303,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const 
     const __nv_bfloat16 *vb = static_cast<const __nv_bfloat16 *>(v), *akb = static_cast<const __nv_bfloat16 *>(ak);
     __nv_bfloat16 *ob = static_cast<__nv_bfloat16 *>(o);
     if (n_simt_items > 0) {
-        const PlanView pv = plan_view(const_cast<void *>(attn_plan), n_nodes, n_edges, n_etypes);
+        const PlanView pv = plan_view(const_cast<void *>(attn_plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
         if (int rc = launch_forward_items_bf16(reinterpret_cast<const int4 *>(simt_items),
                                                static_cast<int>(n_simt_items), pv.in_src, pv.in_etype, q, k, v, ak,
                                                static_cast<float>(scale), o, lse, h, d, stream))

@@ -109,28 +109,29 @@ size_t work_ws_bytes(int64_t n_rows) {
 
 using namespace bpt;
 
-extern "C" size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes) {
-    if (n_nodes < 0 || n_edges < 0 || n_etypes < 1) return 0;
-    return plan_view(nullptr, n_nodes, n_edges, n_etypes).bytes;
+extern "C" size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes) {
+    if (n_nodes < 0 || n_src < 0 || n_edges < 0 || n_etypes < 1) return 0;
+    return plan_view(nullptr, n_nodes, n_src, n_edges, n_etypes).bytes;
 }
 
-extern "C" size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes) {
-    if (n_nodes < 0 || n_edges < 0 || n_etypes < 1) return 0;
-    const int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+extern "C" size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes) {
+    if (n_nodes < 0 || n_src < 0 || n_edges < 0 || n_etypes < 1) return 0;
+    int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    rows = rows > n_src ? rows : n_src;
     const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
     return 3 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 3 * work_ws_bytes(rows) + 1024;
 }
 
 extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
-                                   int64_t n_edges, int64_t n_nodes, int n_etypes, void *plan,
+                                   int64_t n_edges, int64_t n_nodes, int64_t n_src, int n_etypes, void *plan,
                                    size_t plan_bytes, void *workspace, size_t workspace_bytes,
                                    int32_t *counts_host, bpt_stream_t stream_) {
-    BPT_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && n_etypes >= 1, "attn_plan_build: bad sizes");
-    if (n_nodes >= (int64_t(1) << 31) - 1 || n_edges >= (int64_t(1) << 31) - 1)
+    BPT_CHECK_ARG(n_nodes >= 0 && n_src >= 0 && n_edges >= 0 && n_etypes >= 1, "attn_plan_build: bad sizes");
+    if (n_nodes >= (int64_t(1) << 31) - 1 || n_src >= (int64_t(1) << 31) - 1 || n_edges >= (int64_t(1) << 31) - 1)
         return fail(BPT_ERR_OVERFLOW, "attn_plan_build: nodes or edges exceed 32-bit indices");
     BPT_CHECK_ARG(plan != nullptr && counts_host != nullptr, "attn_plan_build: null output");
     BPT_CHECK_ARG(n_edges == 0 || (src && dst), "attn_plan_build: null edge arrays");
-    PlanView p = plan_view(plan, n_nodes, n_edges, n_etypes);
+    PlanView p = plan_view(plan, n_nodes, n_src, n_edges, n_etypes);
     if (plan_bytes < p.bytes) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: plan buffer too small");
     cudaStream_t stream = as_stream(stream_);
     Workspace ws(workspace, workspace_bytes);
@@ -138,7 +139,8 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     int32_t *tmp_eid = ws.take<int32_t>(e);
     int32_t *inpos_of_eid = ws.take<int32_t>(e);
     int32_t *zero_keys = ws.take<int32_t>(e);
-    const int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    rows = rows > n_src ? rows : n_src;
     const size_t csr_ws_bytes = bpt_coo_to_csr_workspace_bytes(n_edges, rows);
     char *csr_ws = ws.take<char>(csr_ws_bytes);
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: workspace too small");
@@ -153,7 +155,7 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
         BPT_LAUNCH_CHECK();
     }
     // out-CSR (rows = sources)
-    if (int rc = bpt_coo_to_csr(src, dst, n_edges, n_nodes, 4, p.out_indptr, p.out_dst, tmp_eid, csr_ws,
+    if (int rc = bpt_coo_to_csr(src, dst, n_edges, n_src, 4, p.out_indptr, p.out_dst, tmp_eid, csr_ws,
                                 csr_ws_bytes, stream_))
         return rc;
     if (n_edges > 0) {
@@ -176,21 +178,25 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     }
     // work lists
     if (int rc = build_work(p.in_indptr, n_nodes, p.in_work, ws, stream)) return rc;
-    if (int rc = build_work(p.out_indptr, n_nodes, p.out_work, ws, stream)) return rc;
+    if (int rc = build_work(p.out_indptr, n_src, p.out_work, ws, stream)) return rc;
     if (int rc = build_work(p.et_indptr, n_etypes, p.et_work, ws, stream)) return rc;
     BPT_CUDA(cudaMemcpyAsync(counts_host + 0, p.in_work.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost, stream));
     BPT_CUDA(cudaMemcpyAsync(counts_host + 3, p.out_work.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost, stream));
     BPT_CUDA(cudaMemcpyAsync(counts_host + 6, p.et_work.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost, stream));
     BPT_CUDA(cudaStreamSynchronize(stream));
+    counts_host[kCountsNSrc] = static_cast<int32_t>(n_src);
+    counts_host[10] = 0;
+    counts_host[11] = 0;
     return BPT_OK;
 }
 
-extern "C" int bpt_export_in_csr(const void *plan, int64_t n_nodes, int64_t n_edges, int n_etypes,
+extern "C" int bpt_export_in_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                                 int n_etypes,
                                  int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
                                  bpt_stream_t stream_) {
-    BPT_CHECK_ARG(plan && in_indptr_host, "export_in_csr: null argument");
+    BPT_CHECK_ARG(plan && counts_host && in_indptr_host, "export_in_csr: null argument");
     BPT_CHECK_ARG(n_edges == 0 || (in_src_host && in_etype_host), "export_in_csr: null argument");
-    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, n_edges, n_etypes);
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
     cudaStream_t stream = as_stream(stream_);
     BPT_CUDA(cudaMemcpyAsync(in_indptr_host, p.in_indptr, sizeof(int32_t) * static_cast<size_t>(n_nodes + 1),
                              cudaMemcpyDeviceToHost, stream));

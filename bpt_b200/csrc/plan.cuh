@@ -10,6 +10,11 @@ namespace bpt {
 // several items whose partial results are merged in item order.
 constexpr int kSegEdges = 128;
 
+// counts_host layout: [0..2] in-CSR items/slots/split rows, [3..5] out-CSR, [6..8] type buckets,
+// [9] number of source rows (k, v), [10..11] reserved.
+constexpr int kCountsLen = 12;
+constexpr int kCountsNSrc = 9;
+
 struct WorkList {
     int4 *items;       // {row, begin, end, slot}; slot = -1 when the item covers its whole row
     int4 *split_rows;  // {row, first_slot, n_slots, 0} for rows covered by more than one item
@@ -18,7 +23,9 @@ struct WorkList {
 };
 
 struct PlanView {
-    int64_t n_nodes, n_edges;
+    int64_t n_nodes;  // destination rows (rows of the in-CSR; q, o, lse)
+    int64_t n_src;    // source rows (rows of the out-CSR; k, v)
+    int64_t n_edges;
     int n_etypes;
     // in-CSR: rows are destinations; entries in ascending edge-id order
     int32_t *in_indptr, *in_src, *in_etype;
@@ -37,9 +44,10 @@ inline int64_t max_split_for(int64_t rows, int64_t edges) {
 }
 
 // Carves the blob. base may be null to compute only the size.
-inline PlanView plan_view(void *base, int64_t n_nodes, int64_t n_edges, int n_etypes) {
+inline PlanView plan_view(void *base, int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes) {
     PlanView p;
     p.n_nodes = n_nodes;
+    p.n_src = n_src;
     p.n_edges = n_edges;
     p.n_etypes = n_etypes;
     char *b = static_cast<char *>(base);
@@ -50,10 +58,11 @@ inline PlanView plan_view(void *base, int64_t n_nodes, int64_t n_edges, int n_et
         return ptr;
     };
     const size_t e = static_cast<size_t>(n_edges), n1 = static_cast<size_t>(n_nodes + 1);
+    const size_t s1 = static_cast<size_t>(n_src + 1);
     p.in_indptr = reinterpret_cast<int32_t *>(take(n1 * 4));
     p.in_src = reinterpret_cast<int32_t *>(take(e * 4));
     p.in_etype = reinterpret_cast<int32_t *>(take(e * 4));
-    p.out_indptr = reinterpret_cast<int32_t *>(take(n1 * 4));
+    p.out_indptr = reinterpret_cast<int32_t *>(take(s1 * 4));
     p.out_dst = reinterpret_cast<int32_t *>(take(e * 4));
     p.out_inpos = reinterpret_cast<int32_t *>(take(e * 4));
     p.et_indptr = reinterpret_cast<int32_t *>(take(static_cast<size_t>(n_etypes + 1) * 4));
@@ -69,7 +78,7 @@ inline PlanView plan_view(void *base, int64_t n_nodes, int64_t n_edges, int n_et
         return w;
     };
     p.in_work = work(n_nodes);
-    p.out_work = work(n_nodes);
+    p.out_work = work(n_src);
     p.et_work = work(n_etypes);
     p.bytes = off;
     return p;

@@ -181,15 +181,19 @@ int bpt_vector_spmm_backward(const int64_t *row, const int64_t *indptr, const in
  *
  * The graph is given as a plan: a device blob built once per graph from the COO edge list
  * (src, dst, etype: int32, edge id = position), holding the int32 in-CSR, out-CSR, per-type
- * buckets and the work lists the kernels walk.  counts_host[9] (host memory, filled by
+ * buckets and the work lists the kernels walk.  counts_host[12] (host memory, filled by
  * bpt_attn_plan_build, which waits for the stream) must be passed back to the other calls.
  * etype may be NULL (all edges type 0); every etype must be < n_etypes.
+ * Destinations and sources may be different node sets: dst ids index n_nodes rows (q, o, lse,
+ * dq), src ids index n_src rows (k, v, dk, dv).  Self-attention has n_src == n_nodes; the
+ * reference's cross-attention (BPTMemBlock, modules/attention.py:144-168) and a shard of a long
+ * sequence attending to gathered K/V have not.
  * ---------------------------------------------------------------------------------- */
 
-size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes);
-size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_edges, int n_etypes);
+size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes);
+size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes);
 int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
-                        int64_t n_edges, int64_t n_nodes, int n_etypes, void *plan,
+                        int64_t n_edges, int64_t n_nodes, int64_t n_src, int n_etypes, void *plan,
                         size_t plan_bytes, void *workspace, size_t workspace_bytes,
                         int32_t *counts_host, bpt_stream_t stream);
 
@@ -197,7 +201,7 @@ int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *e
 size_t bpt_attn_workspace_bytes(int64_t n_nodes, int64_t n_edges, const int32_t *counts_host,
                                 int h, int d, int backward);
 
-/* q, k, v, o: (n_nodes, h, d) of `dtype` (BPT_F32, BPT_BF16 or BPT_F16; d <= 128);
+/* q, o: (n_nodes, h, d), k, v: (n_src, h, d) of `dtype` (BPT_F32, BPT_BF16 or BPT_F16; d <= 128);
  * ak: (n_etypes, d) of `dtype` or NULL for no relative-position term; lse: fp32
  * (n_nodes, h), natural-log sum of exponentials of each row's scaled scores (-inf for a
  * row without incoming edges, whose o is 0). */
@@ -206,7 +210,7 @@ int bpt_attn_forward(const void *plan, const int32_t *counts_host, int64_t n_nod
                      const void *ak, double scale, void *o, float *lse, int h, int d, int dtype,
                      void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
-/* lse: the forward's output; d_o: gradient of o.  dq, dk, dv: (n_nodes, h, d) of `dtype`;
+/* lse: the forward's output; d_o: gradient of o.  dq: (n_nodes, h, d), dk, dv: (n_src, h, d);
  * dak: fp32 (n_etypes, d), required when ak is given.  The forward's o is not needed: the
  * row term <dO, O> of the softmax gradient is recomputed in fp32 from the probabilities. */
 int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
@@ -241,7 +245,8 @@ int bpt_tile_plan_sizes(const void *handle, int64_t *sizes);
 int bpt_tile_plan_export(const void *handle, int32_t *tiles, int32_t *cols, uint16_t *et,
                          int32_t *split_rows, int32_t *row_items);
 void bpt_tile_plan_destroy(void *handle);
-int bpt_export_in_csr(const void *plan, int64_t n_nodes, int64_t n_edges, int n_etypes,
+int bpt_export_in_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                      int n_etypes,
                       int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
                       bpt_stream_t stream);
 
@@ -254,7 +259,7 @@ size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
 int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const int32_t *cols, const uint16_t *et,
                         const int32_t *split_rows, int64_t n_split, int64_t n_slots,
                         const int32_t *row_items, int64_t n_row_items, const void *attn_plan,
-                        int64_t n_nodes, int64_t n_edges,
+                        const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
                         int max_cols_pad, int t_max, int n_etypes, const void *q, const void *k,
                         const void *v, const void *ak, double scale, void *o, float *lse, int h,
                         int d, int dtype, void *workspace, size_t workspace_bytes,

@@ -168,7 +168,8 @@ def attn_fwd(in_csr, etype, q, k, v, ak, scale, precision="f64", want_p=True):
 
 
 def attn_bwd(in_csr, out_csr, etype, q, k, v, ak, scale, o, p, d_o, precision="f64"):
-    """Analytic gradients of attn_fwd.  Returns (dq, dk, dv, dak or None)."""
+    """Analytic gradients of attn_fwd.  Returns (dq, dk, dv, dak or None).  k, v may have a
+    different number of rows than q (out_csr then has that many rows)."""
     dt, suf = _real(precision)
     indptr, indices, eid = [np.ascontiguousarray(a, np.int64) for a in in_csr]
     indptr_o, indices_o, eid_o = [np.ascontiguousarray(a, np.int64) for a in out_csr]
@@ -179,17 +180,18 @@ def attn_bwd(in_csr, out_csr, etype, q, k, v, ak, scale, o, p, d_o, precision="f
     o = np.ascontiguousarray(o, dt)
     p = np.ascontiguousarray(p, dt)
     N, H, D = q.shape
+    N_src = k.shape[0]
     E = len(indices)
     et = None if etype is None else np.ascontiguousarray(etype, np.int32)
     akc = None if ak is None else np.ascontiguousarray(ak, np.float32)
     T = 0 if akc is None else akc.shape[0]
     ds = np.empty((E, H), dt)
     dq = np.empty((N, H, D), dt)
-    dk = np.empty((N, H, D), dt)
-    dv = np.empty((N, H, D), dt)
+    dk = np.empty((N_src, H, D), dt)
+    dv = np.empty((N_src, H, D), dt)
     dak = None if akc is None else np.empty((T, D), dt)
     fn = getattr(lib(), "bpto_attn_bwd_" + suf)
-    fn(ctypes.c_int64(N), ctypes.c_int(H), ctypes.c_int(D), ctypes.c_int64(E), ctypes.c_int(T),
+    fn(ctypes.c_int64(N), ctypes.c_int64(N_src), ctypes.c_int(H), ctypes.c_int(D), ctypes.c_int64(E), ctypes.c_int(T),
        _p(indptr), _p(indices), _p(eid), _p(indptr_o), _p(indices_o), _p(eid_o), _p(et),
        _p(q), _p(k), _p(v), _p(akc), ctypes.c_double(scale), _p(o), _p(p), _p(d_o),
        _p(ds), _p(dq), _p(dk), _p(dv), _p(dak))

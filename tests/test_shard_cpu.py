@@ -1,0 +1,87 @@
+"""Destination-node sharding of one sequence, checked on CPU with two gloo ranks: the index
+logic of bpt_b200/shard.py (ownership, gathered-space renumbering, all-gather layout,
+reduce-scatter of the K/V gradients) with the CPU oracle doing the arithmetic each rank's GPU
+kernel would do."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, n, k, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    from bpt_b200 import shard as sh
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = oracle.binary_partition(n, False, k, 10)
+    N, H, D, T = g["n_nodes"], 2, 8, int(g["etype"].max()) + 1
+    gen = torch.Generator().manual_seed(0)
+    q, kk, v, d_o = [torch.randn(N, H, D, generator=gen) * 0.5 for _ in range(4)]
+    ak = torch.randn(T, D, generator=gen) * 0.5
+    s = sh.SequenceShard(torch.from_numpy(g["src"]), torch.from_numpy(g["dst"]), torch.from_numpy(g["etype"]),
+                         g["n_nodes_arr"], g["shift"], rank, world)
+    own = s.owned
+    k_g = sh.all_gather_rows(s, kk[own])
+    v_g = sh.all_gather_rows(s, v[own])
+    # local problem: n_owned destinations, n_gathered sources
+    src_g, dst_l, et_l = s.src_g.numpy().astype(np.int64), s.dst_l.numpy().astype(np.int64), s.etype_l.numpy()
+    in_csr = oracle.coo_to_csr(dst_l, src_g, s.n_owned)
+    out_csr = oracle.coo_to_csr(src_g, dst_l, s.n_gathered)
+    o, lse, p = oracle.attn_fwd(in_csr, et_l, q[own].numpy(), k_g.numpy(), v_g.numpy(), ak.numpy(), 0.3)
+    dq, dk_g, dv_g, dak = oracle.attn_bwd(in_csr, out_csr, et_l, q[own].numpy(), k_g.numpy(), v_g.numpy(), ak.numpy(),
+                                          0.3, o, p, d_o[own].numpy())
+    dk = sh.reduce_scatter_rows(s, torch.from_numpy(dk_g))
+    dv = sh.reduce_scatter_rows(s, torch.from_numpy(dv_g))
+    dak_t = torch.from_numpy(dak)
+    dist.all_reduce(dak_t)
+    # reference: the unsharded problem
+    csr = oracle.get_csrs(g["src"], g["dst"], N)
+    o_ref, _, p_ref = oracle.attn_fwd(csr[1], g["etype"], q.numpy(), kk.numpy(), v.numpy(), ak.numpy(), 0.3)
+    ref = oracle.attn_bwd(csr[1], csr[0], g["etype"], q.numpy(), kk.numpy(), v.numpy(), ak.numpy(), 0.3, o_ref, p_ref,
+                          d_o.numpy())
+    own_np = own.numpy()
+    errs = [np.abs(o - o_ref[own_np]).max(), np.abs(dq - ref[0][own_np]).max(), np.abs(dk.numpy() - ref[1][own_np]).max(),
+            np.abs(dv.numpy() - ref[2][own_np]).max(), np.abs(dak_t.numpy() - ref[3]).max()]
+    counts = torch.tensor([s.n_owned, int(s.eid.numel())])
+    gathered = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(gathered, counts)
+    if rank == 0:
+        out.put((float(max(errs)), [t.tolist() for t in gathered], N, g["n_edges"]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n,k", [(64, 2), (100, 4)])
+def test_two_rank_sequence_sharding_matches_unsharded(n, k):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29500 + (os.getpid() % 1000) + n
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, k, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    err, gathered, N, E = out.get(timeout=10)
+    assert err < 1e-12
+    assert sum(g[0] for g in gathered) == N      # every node has exactly one owner
+    assert sum(g[1] for g in gathered) == E      # every edge is computed by exactly one rank
+
+
+def test_ownership_partitions_every_level():
+    sys.path.insert(0, ROOT)
+    from bpt_b200 import shard as sh
+    nn, shift = [100, 50, 25, 13, 7, 4, 2, 1], [0, 100, 150, 175, 188, 195, 199, 201]
+    for world in (1, 2, 4, 8):
+        ids = torch.cat([sh.owned_nodes(nn, shift, r, world) for r in range(world)])
+        assert sorted(ids.tolist()) == list(range(202))
+        sizes = [sh.owned_nodes(nn, shift, r, world).numel() for r in range(world)]
+        assert max(sizes) - min(sizes) <= len(nn)

@@ -1,0 +1,117 @@
+"""Destination-sharded attention on the GPU: one rank's local problem (n_owned destinations,
+gathered sources) on a single device against the oracle, and the full two-rank exchange over
+NCCL when two devices are present."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_one_ranks_local_problem_matches_unsharded_oracle(oracle_lib, dtype, tol):
+    from bpt_b200 import shard as sh
+    from bpt_b200.attention import AttentionPlan, bpt_attention
+    g = oracle_lib.binary_partition(1000, False, 4, 10)
+    N, H, D, T = g["n_nodes"], 8, 64, int(g["etype"].max()) + 1
+    gen = torch.Generator().manual_seed(0)
+    q, k, v = [(torch.randn(N, H, D, generator=gen) * 0.125).to(dtype) for _ in range(3)]
+    ak = (torch.randn(T, D, generator=gen) * 0.125).to(dtype)
+    d_o = torch.randn(N, H, D, generator=gen).to(dtype)
+    csr = oracle_lib.get_csrs(g["src"], g["dst"], N)
+    f = lambda t: t.float().numpy()
+    o_ref, _, p_ref = oracle_lib.attn_fwd(csr[1], g["etype"], f(q), f(k), f(v), f(ak), 0.125)
+    ref = oracle_lib.attn_bwd(csr[1], csr[0], g["etype"], f(q), f(k), f(v), f(ak), 0.125, o_ref, p_ref, f(d_o))
+    world = 3
+    dk_sum = np.zeros((N, H, D))
+    dv_sum = np.zeros((N, H, D))
+    dak_sum = np.zeros((T, D))
+    src, dst, et = [torch.from_numpy(g[n]).cuda() for n in ("src", "dst", "etype")]
+    for rank in range(world):
+        s = sh.SequenceShard(src, dst, et, g["n_nodes_arr"], g["shift"], rank, world)
+        own = s.owned
+        # what the all-gather would deliver, built by hand: rank-major, padded
+        k_g = torch.zeros(s.n_gathered, H, D, dtype=dtype, device="cuda")
+        v_g = torch.zeros_like(k_g)
+        k_g[s.to_gathered] = k.cuda()
+        v_g[s.to_gathered] = v.cuda()
+        plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=T, n_src=s.n_gathered)
+        ql = q.cuda()[own].requires_grad_(True)
+        k_g.requires_grad_(True)
+        v_g.requires_grad_(True)
+        akl = ak.cuda().requires_grad_(True)
+        o = bpt_attention(plan, ql, k_g, v_g, akl, 0.125)
+        o.backward(d_o.cuda()[own])
+        own_np = own.cpu().numpy()
+        assert rel_err(o.detach().double().cpu(), o_ref[own_np]) < tol
+        assert rel_err(ql.grad.double().cpu(), ref[0][own_np]) < tol
+        tg = s.to_gathered.cpu().numpy()
+        dk_sum += k_g.grad.double().cpu().numpy()[tg]
+        dv_sum += v_g.grad.double().cpu().numpy()[tg]
+        dak_sum += akl.grad.double().cpu().numpy()
+    assert rel_err(dk_sum, ref[1]) < tol and rel_err(dv_sum, ref[2]) < tol and rel_err(dak_sum, ref[3]) < tol
+
+
+def _nccl_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    import torch.distributed as dist
+    from bpt_b200 import graphbuilder, shard as sh
+    from bpt_b200.attention import AttentionPlan
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    gb = graphbuilder.BinaryPartition(2048, False, 4, 10)
+    src, dst, et = gb.edges_device()
+    N, H, D, T = gb.number_of_nodes, 8, 64, 99
+    gen = torch.Generator().manual_seed(0)
+    q, k, v = [(torch.randn(N, H, D, generator=gen) * 0.125) for _ in range(3)]
+    ak = torch.randn(T, D, generator=gen) * 0.125
+    d_o = torch.randn(N, H, D, generator=gen)
+    s = sh.SequenceShard(src, dst, et, gb.n_nodes_arr, gb.shift, rank, world)
+    plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=T, n_src=s.n_gathered)
+    own = s.owned
+    ql, kl, vl = [t.cuda()[own].requires_grad_(True) for t in (q, k, v)]
+    akl = ak.cuda().requires_grad_(True)
+    o = sh.sharded_attention(s, plan, ql, kl, vl, akl, 0.125)
+    o.backward(d_o.cuda()[own])
+    dak = akl.grad.clone()
+    dist.all_reduce(dak)
+    s_np, d_np, e_np = gb.get_edges()
+    csr = oracle.get_csrs(s_np, d_np, N)
+    o_ref, _, p_ref = oracle.attn_fwd(csr[1], e_np, q.numpy(), k.numpy(), v.numpy(), ak.numpy(), 0.125)
+    ref = oracle.attn_bwd(csr[1], csr[0], e_np, q.numpy(), k.numpy(), v.numpy(), ak.numpy(), 0.125, o_ref, p_ref,
+                          d_o.numpy())
+    own_np = own.cpu().numpy()
+    rel = lambda a, b: float(np.abs(a - b).max() / np.abs(b).max())
+    errs = [rel(o.detach().double().cpu().numpy(), o_ref[own_np]), rel(ql.grad.double().cpu().numpy(), ref[0][own_np]),
+            rel(kl.grad.double().cpu().numpy(), ref[1][own_np]), rel(vl.grad.double().cpu().numpy(), ref[2][own_np]),
+            rel(dak.double().cpu().numpy(), ref[3])]
+    out.put((rank, max(errs)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_over_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    for _ in range(2):
+        rank, err = out.get(timeout=10)
+        assert err < 1e-5, (rank, err)

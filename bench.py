@@ -2,7 +2,7 @@
 """Benchmark of the fused binary-partition graph attention layer (forward + backward).
 
 One "step" is one pass of the hot path over one batch: a block-diagonal batch of `--seqs`
-independent sequences of `--n` tokens with `--k` neighbours per side per level, 8 heads x 64,
+independent sequences of `--seq-len` tokens with `--step` neighbours per side per level, 8 heads x 64,
 forward and backward.  The metric is attention edges per second (edges of the batch graph
 divided by the step time), the one BASELINE.json quotes at n = 8192, k = 4.
 
@@ -38,9 +38,12 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--seqs", type=int, default=8)
-    ap.add_argument("--n", type=int, default=8192)
-    ap.add_argument("--k", type=int, default=4)
+    ap.add_argument("--seq-len", dest="n", type=int, default=8192)
+    ap.add_argument("--step", dest="k", type=int, default=4)
     ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--mode", default="graphs", choices=["graphs", "seqshard"],
+                    help="graphs: independent sequences per rank (weak scaling); seqshard: ONE sequence of "
+                         "--seq-len tokens, destination nodes split over the ranks, K/V all-gathered (strong scaling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -172,6 +175,76 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- GPU side
+
+def run_seqshard(a):
+    """One long sequence, destination nodes sharded over the ranks (bpt_b200/shard.py).
+    Timed step = all-gather K,V -> fused forward -> fused backward -> reduce-scatter dK,dV."""
+    import torch
+    import torch.distributed as dist
+    from bpt_b200 import graphbuilder, shard as sh
+    from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
+    src, dst, et = g.edges_device()
+    s = sh.SequenceShard(src, dst, et, g.n_nodes_arr, g.shift, rank, world)
+    plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_gathered)
+    E = g.number_of_edges
+    gen = torch.Generator().manual_seed(2 + rank)
+    q, k, v, d_o = [(torch.randn(s.n_owned, H, D, generator=gen) * sg).to(dtype).to(dev)
+                    for sg in (0.125, 0.125, 0.125, 1.0)]
+    ak = (torch.randn(MAX_ETYPE, D, generator=torch.Generator().manual_seed(1)) * 0.125).to(dtype).to(dev)
+    scale = 1.0 / math.sqrt(D)
+
+    def step():
+        if world > 1:
+            k_g, v_g = sh.all_gather_rows(s, k), sh.all_gather_rows(s, v)
+        else:
+            k_g, v_g = s.pad_rows(k), s.pad_rows(v)
+        o, lse = attention_forward(plan, q, k_g, v_g, ak, scale)
+        dq, dk_g, dv_g, dak = attention_backward(plan, q, k_g, v_g, ak, scale, lse, d_o)
+        if world > 1:
+            return sh.reduce_scatter_rows(s, dk_g), sh.reduce_scatter_rows(s, dv_g)
+        return dk_g, dv_g
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(a.steps):
+        step()
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop) / a.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "bpt_attention_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
+            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": a.dtype, "data": "synthetic",
+            "config": {"workload": "bpt_attention_fwd_bwd 1x(n=%d,k=%d) destination-sharded, K/V all-gather + "
+                                   "dK/dV reduce-scatter over NCCL" % (a.n, a.k),
+                       "edges": E, "nodes": g.number_of_nodes, "owned_nodes_rank0": s.n_owned,
+                       "kv_allgather_bytes_per_rank": 2 * s.n_gathered * H * D * q.element_size()}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
 
 def run_ours(a):
     import torch
@@ -323,6 +396,8 @@ def main():
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.mode == "seqshard":
+        run_seqshard(a)
     else:
         run_ours(a)
 

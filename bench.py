@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--mode", default="graphs", choices=["graphs", "seqshard"],
                     help="graphs: independent sequences per rank (weak scaling); seqshard: ONE sequence of "
                          "--seq-len tokens, destination nodes split over the ranks, K/V all-gathered (strong scaling)")
+    ap.add_argument("--workload", default="attention", choices=["attention", "lm"],
+                    help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
+                         "forward, batch 8 x 8192 tokens per rank, tokens/s")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -246,6 +249,75 @@ def run_seqshard(a):
         dist.destroy_process_group()
 
 
+def run_lm(a):
+    """12-layer causal BPT character LM forward (d_model 512, 8 x 64, FFN 2048 GELU, vocab 256,
+    bf16 activations, fp32 softmax), batch of --seqs sequences of --seq-len tokens per rank, Zipf(1.1)
+    bytes (seed 1), weights N(0, 0.02).  tokens/s = tokens of all ranks / slowest rank's time."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from bpt_b200 import csr as csrmod, graphbuilder
+    from bpt_b200.attention import AttentionPlan
+    from bpt_b200.model import BPTLanguageModel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    g = graphbuilder.BinaryPartition(a.n, True, a.k, 10)
+    batch = csrmod.batch_graphs([g] * a.seqs)
+    plan = AttentionPlan.from_batch(batch, n_etypes=MAX_ETYPE)
+    leaf_ids = batch.leaf_ids()
+    torch.manual_seed(0)
+    model = BPTLanguageModel(256, 512, 2048, 8, 12, dropout=0.0, activation="gelu")
+    for p in model.parameters():
+        torch.nn.init.normal_(p, 0.0, 0.02)
+    model = model.to(dev).to(torch.bfloat16).eval()
+    rng = np.random.default_rng(1 + rank)
+    w = 1.0 / np.arange(1, 257) ** 1.1
+    host_tokens = torch.from_numpy(rng.choice(256, size=a.seqs * a.n, p=w / w.sum())).pin_memory()
+
+    def step():
+        tokens = host_tokens.to(dev, non_blocking=True)
+        with torch.no_grad():
+            return model(tokens, leaf_ids, plan)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(a.steps):
+        out = step()
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop) / a.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "lm_tokens_per_sec", "value": world * a.seqs * a.n / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "bpt_lm_forward 12 layers d512 8x64 ffn2048 gelu vocab256, %dx(n=%d,k=%d,causal) "
+                                   "per rank" % (a.seqs, a.n, a.k),
+                       "nodes_per_gpu": batch.n_nodes, "edges_per_gpu_per_layer": batch.n_edges,
+                       "finite": bool(torch.isfinite(out.float()).all().item())}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_ours(a):
     import torch
     import torch.distributed as dist
@@ -396,6 +468,8 @@ def main():
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "lm":
+        run_lm(a)
     elif a.mode == "seqshard":
         run_seqshard(a)
     else:

@@ -89,44 +89,48 @@ class AttentionPlan:
 
 
 class TilePlan:
-    """Tiles of <= 16 destination rows x a list of source columns covering the graph, for
+    """Groups of source columns shared by m-blocks of <= 16 destination rows, for
     bpt_attn_forward_tc.  Planned on the host from the plan's in-CSR (integer work, once per
     graph), kept on the device."""
 
-    def __init__(self, plan, min_density=0.25, max_cols=384, col_block=64, simt_max_degree=0):
+    def __init__(self, plan, min_density=0.04, max_cols=512, group_rows=128, col_block=128, simt_max_degree=0,
+                 max_mblocks=8, join_dense=False):
         L = _lib.lib()
         N, E, T = plan.n_nodes, plan.n_edges, plan.n_etypes
         indptr = np.empty(N + 1, np.int32)
         src = np.empty(max(E, 1), np.int32)
         etype = np.empty(max(E, 1), np.int32)
         with torch.cuda.device(plan.device):
-            _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), ctypes.addressof(plan._counts), N, E, T, indptr.ctypes.data, src.ctypes.data,
-                                           etype.ctypes.data, _lib.stream()))
+            _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), ctypes.addressof(plan._counts), N, E, T,
+                                           indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, _lib.stream()))
         handle = L.bpt_tile_plan_create(indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, N, E,
-                                        float(min_density), int(max_cols), int(col_block),
-                                        int(simt_max_degree))
+                                        float(min_density), int(max_cols), int(group_rows), int(col_block),
+                                        int(simt_max_degree), int(max_mblocks), int(bool(join_dense)))
         if not handle:
             _lib.check(1)
         try:
-            sizes = (ctypes.c_int64 * 10)()
+            sizes = (ctypes.c_int64 * 12)()
             _lib.check(L.bpt_tile_plan_sizes(handle, ctypes.addressof(sizes)))
-            (self.n_tiles, n_cols, n_et, self.n_split, self.n_slots, self.t_max, self.max_cols_pad,
-             self.n_row_tiles, self.n_row_items, _) = [int(x) for x in sizes]
-            tiles = np.empty(max(self.n_tiles * 40, 1), np.int32)
+            (self.n_groups, self.n_mblocks, n_cols, self.n_cells, self.n_split, self.n_slots, self.t_max,
+             self.max_cols_pad, self.max_mblocks, self.max_qr_slots, self.n_row_items,
+             self.n_dense_groups) = [int(x) for x in sizes]
+            max_et = int(etype[:E].max()) if E else 0
+            self.et_bytes = 1 if max_et < 255 else 2
+            groups = np.empty(max(self.n_groups * 8, 1), np.int32)
+            mblocks = np.empty(max(self.n_mblocks * 56, 1), np.int32)
             cols = np.empty(max(n_cols, 1), np.int32)
-            et = np.empty(max(n_et, 1), np.uint16)
+            et = np.empty(max(self.n_cells, 1), np.uint8 if self.et_bytes == 1 else np.uint16)
             split = np.empty(max(self.n_split * 4, 1), np.int32)
             items = np.empty(max(self.n_row_items * 4, 1), np.int32)
-            _lib.check(L.bpt_tile_plan_export(handle, tiles.ctypes.data, cols.ctypes.data, et.ctypes.data,
-                                              split.ctypes.data, items.ctypes.data))
+            _lib.check(L.bpt_tile_plan_export(handle, groups.ctypes.data, mblocks.ctypes.data, cols.ctypes.data,
+                                              et.ctypes.data, self.et_bytes, split.ctypes.data, items.ctypes.data))
         finally:
             L.bpt_tile_plan_destroy(handle)
-        self.n_cells = n_et
-        self.host = dict(tiles=tiles, cols=cols, et=et, split=split, items=items)
         dev = plan.device
-        self.tiles = torch.from_numpy(tiles).to(dev)
+        self.groups = torch.from_numpy(groups).to(dev)
+        self.mblocks = torch.from_numpy(mblocks).to(dev)
         self.cols = torch.from_numpy(cols).to(dev)
-        self.et = torch.from_numpy(et.view(np.int16)).to(dev)
+        self.et = torch.from_numpy(et.view(np.uint8)).to(dev)
         self.split = torch.from_numpy(split).to(dev)
         self.items = torch.from_numpy(items).to(dev)
         self.n_etypes = T
@@ -158,12 +162,12 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale):
     with torch.cuda.device(q.device):
         ws = tp.workspace(h, q.device)
         _lib.check(_lib.lib().bpt_attn_forward_tc(
-            tp.tiles.data_ptr(), tp.n_tiles, tp.cols.data_ptr(), tp.et.data_ptr(), tp.split.data_ptr(),
-            tp.n_split, tp.n_slots, tp.items.data_ptr(), tp.n_row_items, plan.blob.data_ptr(),
-            ctypes.addressof(plan._counts), plan.n_nodes,
-            plan.n_edges, tp.max_cols_pad, tp.t_max, tp.n_etypes, q.data_ptr(), k.data_ptr(),
-            v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d,
-            _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
+            tp.groups.data_ptr(), tp.n_groups, tp.mblocks.data_ptr(), tp.cols.data_ptr(), tp.et.data_ptr(),
+            tp.et_bytes, tp.split.data_ptr(), tp.n_split, tp.n_slots, tp.items.data_ptr(), tp.n_row_items,
+            plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes, plan.n_edges, tp.max_cols_pad,
+            tp.t_max, tp.max_mblocks, tp.max_qr_slots, tp.n_etypes, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d, _lib.dtype_code(q.dtype),
+            ws.data_ptr(), ws.numel(), _lib.stream()))
     return o, lse
 
 

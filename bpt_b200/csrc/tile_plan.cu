@@ -1,21 +1,25 @@
 // Host-side planner of the tensor-core attention path.
 //
-// The sparse attention matrix (rows = destinations, columns = sources) is covered by tiles of
-// at most 16 rows and an explicit list of source columns, chosen so that each tile is dense
-// enough to be computed as a masked dense block:
-//   1. every block of 16 consecutive rows whose union of sources is small and well filled
-//      becomes one tile holding all edges of its rows (binary-partition graphs: 16 consecutive
-//      leaves share ~120-150 sources at 60-70 % fill);
-//   2. the edges of all other rows are grouped by block of 64 consecutive sources; the rows
-//      touching a source block are cut into tiles of 16 (binary-partition graphs: the span
-//      nodes covering a leaf block). A row spread over several tiles gets one partial result
-//      per tile ("slot") and is combined afterwards in slot order.
+// The sparse attention matrix (rows = destinations, columns = sources) is covered by groups:
+// a group is a sorted list of source columns shared by several m-blocks of <=16 destination
+// rows each (tile_plan.cuh).  The kernel stages a group's K/V rows once per head and lets all
+// its m-blocks attend over them, so the planner's job is to put rows with overlapping sources
+// into one group:
+//   1. `group_rows` consecutive rows whose union of sources is small and reasonably filled
+//      become a dense group (binary-partition graphs: 64 consecutive leaves share ~230-260
+//      sources, against ~120-145 per 16 leaves);
+//   2. the edges of all other rows are bucketed by block of `col_block` consecutive sources and
+//      the rows of a bucket cut into m-blocks of 16.  If the dense group made of the rows with
+//      those same ids holds all of the bucket's sources as columns, the m-blocks join it and
+//      reuse its staged K/V (binary-partition graphs: the span nodes above a block of leaves
+//      attend exactly to those leaves); otherwise they form a group of their own;
+//   3. a row spread over several m-blocks gets one partial result ("slot") per m-block; slots
+//      of a row are contiguous and in m-block order, and are combined afterwards in that order.
 // Parallel edges (the reference's builder emits duplicate (src, dst) pairs for some lengths,
-// graph_builder/builder.pyx:77-85) get separate columns, so a tile cell holds at most one edge.
+// graph_builder/builder.pyx:77-85) get separate columns, so a cell holds at most one edge.
 // Pure integer host code: no CUDA calls, usable and testable without a GPU.
 #include <algorithm>
 #include <cstring>
-#include <string>
 #include <vector>
 
 #include "tile_plan.cuh"
@@ -24,12 +28,9 @@ namespace bpt {
 namespace {
 
 struct HostTilePlan {
-    std::vector<int32_t> tiles;
-    std::vector<int32_t> cols;
+    std::vector<int32_t> groups, mblocks, cols, split, simt;
     std::vector<uint16_t> et;
-    std::vector<int32_t> split;  // int4 records {row, first_slot, n_slots, 0}
-    std::vector<int32_t> simt;   // int4 records {row, begin, end, -1}: short rows left to the CUDA-core kernel
-    int64_t n_slots = 0, t_max = 0, max_cols_pad = 0, n_cells = 0, n_row_tiles = 0;
+    int64_t n_slots = 0, t_max = 0, max_cols_pad = 0, max_mblocks = 0, max_qr_slots = 0, n_dense_groups = 0;
 };
 
 struct EdgeRec {
@@ -37,21 +38,32 @@ struct EdgeRec {
     int32_t row, etype;
 };
 
-// Assigns the parallel-edge rank inside each row and returns one record per edge of `rows`.
+// An m-block before it is laid out: sorted rows and their edges (grouped by row, row order).
+struct MBlockBuild {
+    std::vector<int32_t> rows;
+    std::vector<EdgeRec> edges;
+};
+
+struct GroupBuild {
+    std::vector<int64_t> keys;  // sorted unique column keys
+    std::vector<MBlockBuild> mblocks;
+    bool dense = false;
+};
+
+// One record per edge of `rows`, with the parallel-edge rank inside each row.
 bool collect_edges(const int32_t *indptr, const int32_t *src, const int32_t *etype, const int32_t *rows,
-                   int n_rows, std::vector<EdgeRec> &out, std::vector<std::pair<int32_t, int32_t>> &tmp) {
+                   int64_t n_rows, std::vector<EdgeRec> &out, std::vector<std::pair<int32_t, int32_t>> &tmp) {
     bool ok = true;
-    for (int i = 0; i < n_rows; ++i) {
+    for (int64_t i = 0; i < n_rows; ++i) {
         const int32_t r = rows[i];
-        const int32_t b = indptr[r], e = indptr[r + 1];
         tmp.clear();
-        for (int32_t j = b; j < e; ++j) tmp.emplace_back(src[j], j);
+        for (int32_t j = indptr[r]; j < indptr[r + 1]; ++j) tmp.emplace_back(src[j], j);
         std::sort(tmp.begin(), tmp.end());
         int rank = 0;
         for (size_t p = 0; p < tmp.size(); ++p) {
             rank = (p > 0 && tmp[p].first == tmp[p - 1].first) ? rank + 1 : 0;
-            EdgeRec rec;
             if (rank > 255) ok = false;  // more than 256 parallel edges between one pair of nodes
+            EdgeRec rec;
             rec.key = (static_cast<int64_t>(tmp[p].first) << 8) | (rank & 255);
             rec.row = r;
             rec.etype = etype ? etype[tmp[p].second] : 0;
@@ -61,42 +73,75 @@ bool collect_edges(const int32_t *indptr, const int32_t *src, const int32_t *ety
     return ok;
 }
 
-// Emits one tile from edge records (all of whose rows are in `rows`).  Returns its index.
-int emit_tile(HostTilePlan &plan, const int32_t *rows, int n_rows, const EdgeRec *edges, size_t n_edges,
-              std::vector<int64_t> &keys) {
-    keys.clear();
-    for (size_t i = 0; i < n_edges; ++i) keys.push_back(edges[i].key);
-    std::sort(keys.begin(), keys.end());
-    keys.erase(std::unique(keys.begin(), keys.end()), keys.end());
-    const int ncols = static_cast<int>(keys.size());
+struct Partial {
+    int32_t row, mblock, local;
+};
+
+// Lays a group out into the plan arrays; m-blocks beyond max_mblocks spill into copies of the
+// group (same columns).  Rows whose edges are not all inside their m-block are reported as
+// partial.
+void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr, const int32_t *row_uniform_et,
+                std::vector<Partial> &partials, int max_mblocks) {
+    const int ncols = static_cast<int>(gb.keys.size());
     const int ncols_pad = (ncols + kTileChunk - 1) / kTileChunk * kTileChunk;
-    const int idx = static_cast<int>(plan.tiles.size() / kTileInts);
-    plan.tiles.resize(plan.tiles.size() + kTileInts, 0);
-    int32_t *t = &plan.tiles[static_cast<size_t>(idx) * kTileInts];
-    for (int i = 0; i < kTileRows; ++i) {
-        t[kTileRowOff + i] = i < n_rows ? rows[i] : -1;
-        t[kTileSlotOff + i] = -1;
-    }
-    t[kTileNcolsPad] = ncols_pad;
-    t[kTileColOff] = static_cast<int32_t>(plan.cols.size());
-    t[kTileEtOff] = static_cast<int32_t>(plan.et.size());
-    t[kTileNcols] = ncols;
-    for (int c = 0; c < ncols_pad; ++c)
-        plan.cols.push_back(c < ncols ? static_cast<int32_t>(keys[c] >> 8) : static_cast<int32_t>(keys[0] >> 8));
-    const size_t et_base = plan.et.size();
-    plan.et.resize(et_base + static_cast<size_t>(kTileRows) * ncols_pad, kNoEdge);
-    int max_et = -1;
-    for (size_t i = 0; i < n_edges; ++i) {
-        const int local = static_cast<int>(std::lower_bound(rows, rows + n_rows, edges[i].row) - rows);
-        const int c = static_cast<int>(std::lower_bound(keys.begin(), keys.end(), edges[i].key) - keys.begin());
-        plan.et[et_base + static_cast<size_t>(local) * ncols_pad + c] = static_cast<uint16_t>(edges[i].etype);
-        if (edges[i].etype > max_et) max_et = edges[i].etype;
-    }
-    t[kTileTq] = (max_et + 1 + 7) / 8 * 8;
-    if (t[kTileTq] > plan.t_max) plan.t_max = t[kTileTq];
+    const int n_chunks = ncols_pad / kTileChunk;
     if (ncols_pad > plan.max_cols_pad) plan.max_cols_pad = ncols_pad;
-    plan.n_cells += static_cast<int64_t>(kTileRows) * ncols_pad;
-    return idx;
+    for (size_t first = 0; first < gb.mblocks.size() || first == 0; first += max_mblocks) {
+        const size_t count = std::min<size_t>(max_mblocks, gb.mblocks.size() - first);
+        const size_t gidx = plan.groups.size();
+        plan.groups.resize(gidx + kGroupInts, 0);
+        plan.groups[gidx + kGroupColOff] = static_cast<int32_t>(plan.cols.size());
+        plan.groups[gidx + kGroupNcolsPad] = ncols_pad;
+        plan.groups[gidx + kGroupMbFirst] = static_cast<int32_t>(plan.mblocks.size() / kMbInts);
+        plan.groups[gidx + kGroupMbCount] = static_cast<int32_t>(count);
+        plan.groups[gidx + kGroupNcols] = ncols;
+        for (int c = 0; c < ncols_pad; ++c)
+            plan.cols.push_back(static_cast<int32_t>((c < ncols ? gb.keys[c] : gb.keys[0]) >> 8));
+        if (static_cast<int64_t>(count) > plan.max_mblocks) plan.max_mblocks = static_cast<int64_t>(count);
+        int n_qr = 0;
+        for (size_t b = first; b < first + count; ++b) {
+            const MBlockBuild &mb = gb.mblocks[b];
+            const int nr = static_cast<int>(mb.rows.size());
+            const int32_t midx = static_cast<int32_t>(plan.mblocks.size() / kMbInts);
+            plan.mblocks.resize(plan.mblocks.size() + kMbInts, 0);
+            int32_t *m = &plan.mblocks[static_cast<size_t>(midx) * kMbInts];
+            bool uniform = true;
+            for (int i = 0; i < kTileRows; ++i) {
+                m[kMbRowOff + i] = i < nr ? mb.rows[i] : -1;
+                m[kMbSlotOff + i] = -1;
+                m[kMbRowEtOff + i] = i < nr ? row_uniform_et[mb.rows[i]] : 0;
+                if (i < nr && row_uniform_et[mb.rows[i]] < 0) uniform = false;
+            }
+            m[kMbEtOff] = static_cast<int32_t>(plan.et.size());
+            const size_t base = plan.et.size();
+            plan.et.resize(base + static_cast<size_t>(n_chunks) * kTileRows * kTileChunk, kNoEdge);
+            uint32_t mask = 0;
+            int max_et = -1;
+            size_t p = 0;
+            for (int r = 0; r < nr; ++r) {
+                int64_t cnt = 0;
+                while (p < mb.edges.size() && mb.edges[p].row == mb.rows[r]) {
+                    const EdgeRec &e = mb.edges[p];
+                    const int c = static_cast<int>(std::lower_bound(gb.keys.begin(), gb.keys.end(), e.key) - gb.keys.begin());
+                    const int chunk = c / kTileChunk;
+                    plan.et[base + (static_cast<size_t>(chunk) * kTileRows + r) * kTileChunk + (c % kTileChunk)] =
+                        static_cast<uint16_t>(e.etype);
+                    mask |= 1u << chunk;
+                    if (e.etype > max_et) max_et = e.etype;
+                    ++cnt;
+                    ++p;
+                }
+                if (cnt != indptr[mb.rows[r] + 1] - indptr[mb.rows[r]]) partials.push_back({mb.rows[r], midx, r});
+            }
+            m[kMbChunkMask] = static_cast<int32_t>(mask);
+            m[kMbTq] = (max_et + 1 + 7) / 8 * 8;
+            m[kMbQrSlot] = uniform ? -1 : n_qr++;
+            if (!uniform && m[kMbTq] > plan.t_max) plan.t_max = m[kMbTq];
+        }
+        if (n_qr > plan.max_qr_slots) plan.max_qr_slots = n_qr;
+        if (gb.dense) ++plan.n_dense_groups;
+        if (gb.mblocks.empty()) break;
+    }
 }
 
 struct Leftover {
@@ -111,9 +156,12 @@ using namespace bpt;
 
 extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
                                       int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
-                                      int col_block, int simt_max_degree) {
+                                      int group_rows, int col_block, int simt_max_degree, int max_mblocks,
+                                      int join_dense) {
     if (!in_indptr || (n_edges > 0 && !in_src) || n_nodes < 0 || n_edges < 0 || max_cols < kTileChunk ||
-        col_block < 1) {
+        max_cols > kMaxChunks * kTileChunk || col_block < 1 || group_rows < kTileRows ||
+        group_rows % kTileRows != 0 || max_mblocks < 1 || max_mblocks > kMaxMBlocks ||
+        group_rows / kTileRows > max_mblocks) {
         fail(BPT_ERR_INVALID, "tile_plan_create: bad arguments");
         return nullptr;
     }
@@ -123,156 +171,194 @@ extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *i
                 fail(BPT_ERR_UNSUPPORTED, "tile_plan_create: edge type %d outside [0, 65535)", in_etype[j]);
                 return nullptr;
             }
+    // the single edge type of each row, or -1 if its edges differ (rows without edges: 0)
+    std::vector<int32_t> row_uniform_et(static_cast<size_t>(n_nodes), 0);
+    for (int64_t r = 0; r < n_nodes; ++r)
+        for (int32_t j = in_indptr[r]; j < in_indptr[r + 1]; ++j) {
+            const int32_t e = in_etype ? in_etype[j] : 0;
+            if (j == in_indptr[r]) row_uniform_et[r] = e;
+            else if (row_uniform_et[r] != e) row_uniform_et[r] = -1;
+        }
+
     HostTilePlan *plan = new HostTilePlan();
     std::vector<EdgeRec> edges;
     std::vector<std::pair<int32_t, int32_t>> tmp;
-    std::vector<int64_t> keys;
-    std::vector<int32_t> leftover_rows, zero_rows;
-    std::vector<int32_t> rows(kTileRows);
+    std::vector<int32_t> leftover_rows, zero_rows, rows(group_rows);
+    const int64_t n_row_groups = (n_nodes + group_rows - 1) / group_rows;
+    std::vector<GroupBuild> dense(static_cast<size_t>(n_row_groups));
+    std::vector<GroupBuild> standalone;
+    const char *too_many = "tile_plan_create: more than 256 parallel edges between two nodes";
 
-    // 1. blocks of 16 consecutive rows
-    for (int64_t r0 = 0; r0 < n_nodes; r0 += kTileRows) {
-        const int nr = static_cast<int>(std::min<int64_t>(kTileRows, n_nodes - r0));
+    // 1. dense groups of `group_rows` consecutive rows
+    for (int64_t gi = 0; gi < n_row_groups; ++gi) {
+        const int64_t r0 = gi * group_rows;
+        const int nr = static_cast<int>(std::min<int64_t>(group_rows, n_nodes - r0));
         for (int i = 0; i < nr; ++i) rows[i] = static_cast<int32_t>(r0 + i);
         const int64_t ne = in_indptr[r0 + nr] - in_indptr[r0];
-        bool as_tile = ne == 0;
-        if (!as_tile && ne <= static_cast<int64_t>(kTileRows) * max_cols) {
-            edges.clear();
+        GroupBuild &gb = dense[gi];
+        edges.clear();
+        bool accept = ne == 0;
+        if (!accept && ne <= static_cast<int64_t>(nr) * max_cols) {
             if (!collect_edges(in_indptr, in_src, in_etype, rows.data(), nr, edges, tmp)) {
-                fail(BPT_ERR_UNSUPPORTED, "tile_plan_create: more than 256 parallel edges between two nodes");
+                fail(BPT_ERR_UNSUPPORTED, "%s", too_many);
                 delete plan;
                 return nullptr;
             }
-            keys.clear();
-            for (const EdgeRec &e : edges) keys.push_back(e.key);
-            std::sort(keys.begin(), keys.end());
-            const int64_t ncols = std::unique(keys.begin(), keys.end()) - keys.begin();
-            as_tile = ncols <= max_cols && static_cast<double>(ne) >= min_density * kTileRows * ncols;
+            for (const EdgeRec &e : edges) gb.keys.push_back(e.key);
+            std::sort(gb.keys.begin(), gb.keys.end());
+            gb.keys.erase(std::unique(gb.keys.begin(), gb.keys.end()), gb.keys.end());
+            const int64_t ncols = static_cast<int64_t>(gb.keys.size());
+            accept = ncols <= max_cols && static_cast<double>(ne) >= min_density * nr * ncols;
         }
-        if (as_tile) {
-            if (ne == 0) edges.clear();
-            emit_tile(*plan, rows.data(), nr, edges.data(), edges.size(), keys);
-            ++plan->n_row_tiles;
-        } else {
+        if (!accept) {
+            gb.keys.clear();
             for (int i = 0; i < nr; ++i) {
                 const int32_t deg = in_indptr[rows[i] + 1] - in_indptr[rows[i]];
-                if (deg <= simt_max_degree) {
-                    // too few edges to be worth a tile cell row: one warp walks the row instead
-                    plan->simt.push_back(rows[i]);
-                    plan->simt.push_back(in_indptr[rows[i]]);
-                    plan->simt.push_back(in_indptr[rows[i] + 1]);
-                    plan->simt.push_back(-1);
-                } else if (deg == 0) {
-                    zero_rows.push_back(rows[i]);
-                } else {
-                    leftover_rows.push_back(rows[i]);
-                }
+                if (deg == 0) zero_rows.push_back(rows[i]);
+                else if (deg <= simt_max_degree)
+                    plan->simt.insert(plan->simt.end(), {rows[i], in_indptr[rows[i]], in_indptr[rows[i] + 1], -1});
+                else leftover_rows.push_back(rows[i]);
             }
+            continue;
+        }
+        gb.dense = true;
+        size_t p = 0;  // collect_edges walks rows in order, so edges are grouped by row
+        for (int b = 0; b < nr; b += kTileRows) {
+            MBlockBuild mb;
+            const int nb = std::min(kTileRows, nr - b);
+            mb.rows.assign(rows.begin() + b, rows.begin() + b + nb);
+            size_t q = p;
+            while (q < edges.size() && edges[q].row < rows[b] + nb) ++q;
+            mb.edges.assign(edges.begin() + p, edges.begin() + q);
+            p = q;
+            gb.mblocks.push_back(std::move(mb));
         }
     }
-    // rows without edges that were not covered above still need their zero output written
-    for (size_t i = 0; i < zero_rows.size(); i += kTileRows) {
-        const int nr = static_cast<int>(std::min<size_t>(kTileRows, zero_rows.size() - i));
-        emit_tile(*plan, &zero_rows[i], nr, nullptr, 0, keys);
-    }
 
-    // 2. remaining edges by block of `col_block` consecutive sources
-    std::vector<Leftover> left;
+    // 2. the other rows' edges, bucketed by block of `col_block` consecutive sources
     {
+        std::vector<Leftover> left;
         edges.clear();
         if (!collect_edges(in_indptr, in_src, in_etype, leftover_rows.data(),
-                           static_cast<int>(leftover_rows.size()), edges, tmp)) {
-            fail(BPT_ERR_UNSUPPORTED, "tile_plan_create: more than 256 parallel edges between two nodes");
+                           static_cast<int64_t>(leftover_rows.size()), edges, tmp)) {
+            fail(BPT_ERR_UNSUPPORTED, "%s", too_many);
             delete plan;
             return nullptr;
         }
         left.reserve(edges.size());
-        for (const EdgeRec &e : edges) {
-            Leftover l;
-            l.sblock = static_cast<int32_t>((e.key >> 8) / col_block);
-            l.row = e.row;
-            l.rec = e;
-            left.push_back(l);
-        }
+        for (const EdgeRec &e : edges) left.push_back({static_cast<int32_t>((e.key >> 8) / col_block), e.row, e});
         std::sort(left.begin(), left.end(), [](const Leftover &a, const Leftover &b) {
             if (a.sblock != b.sblock) return a.sblock < b.sblock;
             if (a.row != b.row) return a.row < b.row;
             return a.rec.key < b.rec.key;
         });
-    }
-    struct Partial { int32_t row, tile, local; };
-    std::vector<Partial> partials;
-    size_t i = 0;
-    while (i < left.size()) {
-        // one tile: up to 16 distinct rows of the same source block
-        const int32_t sb = left[i].sblock;
-        size_t j = i;
-        int nr = 0;
-        int32_t last_row = -1;
-        edges.clear();
-        while (j < left.size() && left[j].sblock == sb) {
-            if (left[j].row != last_row) {
-                if (nr == kTileRows) break;
-                rows[nr++] = left[j].row;
-                last_row = left[j].row;
+        for (size_t i = 0; i < left.size();) {
+            // all rows touching this bucket of sources: one group (their union of columns), rows cut
+            // into m-blocks of 16
+            const int32_t sb = left[i].sblock;
+            std::vector<MBlockBuild> mbs;
+            size_t j = i;
+            while (j < left.size() && left[j].sblock == sb) {
+                if (mbs.empty() || (left[j].row != mbs.back().rows.back() &&
+                                    mbs.back().rows.size() == static_cast<size_t>(kTileRows)))
+                    mbs.emplace_back();
+                MBlockBuild &mb = mbs.back();
+                if (mb.rows.empty() || left[j].row != mb.rows.back()) mb.rows.push_back(left[j].row);
+                mb.edges.push_back(left[j].rec);
+                ++j;
             }
-            edges.push_back(left[j].rec);
-            ++j;
+            // the dense group whose rows carry the ids of this bucket's sources, if it has them all as columns
+            const int64_t gi = static_cast<int64_t>(sb) * col_block / group_rows;
+            bool join = join_dense && gi < n_row_groups && dense[gi].dense && !dense[gi].keys.empty();
+            if (join)
+                for (size_t e = i; e < j && join; ++e)
+                    join = std::binary_search(dense[gi].keys.begin(), dense[gi].keys.end(), left[e].rec.key);
+            if (join) {
+                for (MBlockBuild &mb : mbs) dense[gi].mblocks.push_back(std::move(mb));
+            } else {
+                GroupBuild gb;
+                for (size_t e = i; e < j; ++e) gb.keys.push_back(left[e].rec.key);
+                std::sort(gb.keys.begin(), gb.keys.end());
+                gb.keys.erase(std::unique(gb.keys.begin(), gb.keys.end()), gb.keys.end());
+                gb.mblocks = std::move(mbs);
+                standalone.push_back(std::move(gb));
+            }
+            i = j;
         }
-        const int tile = emit_tile(*plan, rows.data(), nr, edges.data(), edges.size(), keys);
-        // a row is complete here only if this tile holds all of its edges
-        size_t p = 0;
-        for (int r = 0; r < nr; ++r) {
-            int64_t cnt = 0;
-            while (p < edges.size() && edges[p].row == rows[r]) { ++cnt; ++p; }
-            if (cnt != in_indptr[rows[r] + 1] - in_indptr[rows[r]]) partials.push_back({rows[r], tile, r});
-        }
-        i = j;
     }
-    // 3. slots, contiguous per row, in tile order
+    // rows without edges that no dense group covers still need their zero output written
+    for (size_t i = 0; i < zero_rows.size(); i += kTileRows) {
+        GroupBuild gb;
+        MBlockBuild mb;
+        mb.rows.assign(zero_rows.begin() + i, zero_rows.begin() + std::min(zero_rows.size(), i + kTileRows));
+        gb.mblocks.push_back(std::move(mb));
+        standalone.push_back(std::move(gb));
+    }
+
+    std::vector<Partial> partials;
+    for (const GroupBuild &gb : dense)
+        if (gb.dense) emit_group(*plan, gb, in_indptr, row_uniform_et.data(), partials, max_mblocks);
+    for (const GroupBuild &gb : standalone) emit_group(*plan, gb, in_indptr, row_uniform_et.data(), partials, max_mblocks);
+
+    // 3. slots, contiguous per row, in m-block order
     std::stable_sort(partials.begin(), partials.end(), [](const Partial &a, const Partial &b) { return a.row < b.row; });
     for (size_t p = 0; p < partials.size();) {
         size_t q = p;
         while (q < partials.size() && partials[q].row == partials[p].row) {
-            plan->tiles[static_cast<size_t>(partials[q].tile) * kTileInts + kTileSlotOff + partials[q].local] =
+            plan->mblocks[static_cast<size_t>(partials[q].mblock) * kMbInts + kMbSlotOff + partials[q].local] =
                 static_cast<int32_t>(q);
             ++q;
         }
-        plan->split.push_back(partials[p].row);
-        plan->split.push_back(static_cast<int32_t>(p));
-        plan->split.push_back(static_cast<int32_t>(q - p));
-        plan->split.push_back(0);
+        plan->split.insert(plan->split.end(), {partials[p].row, static_cast<int32_t>(p), static_cast<int32_t>(q - p), 0});
         p = q;
     }
     plan->n_slots = static_cast<int64_t>(partials.size());
     return plan;
 }
 
+// sizes[12] = {groups, m-blocks, column entries, etype cells, split rows, slots, t_max,
+//              max_cols_pad, max m-blocks per group, max QR slots per group, row items, dense groups}
 extern "C" int bpt_tile_plan_sizes(const void *handle, int64_t *sizes) {
     BPT_CHECK_ARG(handle && sizes, "tile_plan_sizes: null argument");
     const HostTilePlan *p = static_cast<const HostTilePlan *>(handle);
-    sizes[0] = static_cast<int64_t>(p->tiles.size() / kTileInts);
-    sizes[1] = static_cast<int64_t>(p->cols.size());
-    sizes[2] = static_cast<int64_t>(p->et.size());
-    sizes[3] = static_cast<int64_t>(p->split.size() / 4);
-    sizes[4] = p->n_slots;
-    sizes[5] = p->t_max;
-    sizes[6] = p->max_cols_pad;
-    sizes[7] = p->n_row_tiles;
-    sizes[8] = static_cast<int64_t>(p->simt.size() / 4);
-    sizes[9] = p->n_cells;
+    sizes[0] = static_cast<int64_t>(p->groups.size() / kGroupInts);
+    sizes[1] = static_cast<int64_t>(p->mblocks.size() / kMbInts);
+    sizes[2] = static_cast<int64_t>(p->cols.size());
+    sizes[3] = static_cast<int64_t>(p->et.size());
+    sizes[4] = static_cast<int64_t>(p->split.size() / 4);
+    sizes[5] = p->n_slots;
+    sizes[6] = p->t_max;
+    sizes[7] = p->max_cols_pad;
+    sizes[8] = p->max_mblocks;
+    sizes[9] = p->max_qr_slots;
+    sizes[10] = static_cast<int64_t>(p->simt.size() / 4);
+    sizes[11] = p->n_dense_groups;
     return BPT_OK;
 }
 
-extern "C" int bpt_tile_plan_export(const void *handle, int32_t *tiles, int32_t *cols, uint16_t *et,
-                                    int32_t *split_rows, int32_t *simt_items) {
+// et_bytes = 1 stores edge types as uint8 (0xFF = no edge; needs every type < 255), 2 as uint16.
+extern "C" int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols, void *et,
+                                    int et_bytes, int32_t *split_rows, int32_t *row_items) {
     BPT_CHECK_ARG(handle, "tile_plan_export: null handle");
+    BPT_CHECK_ARG(et_bytes == 1 || et_bytes == 2, "tile_plan_export: et_bytes must be 1 or 2");
     const HostTilePlan *p = static_cast<const HostTilePlan *>(handle);
-    if (tiles && !p->tiles.empty()) std::memcpy(tiles, p->tiles.data(), p->tiles.size() * sizeof(int32_t));
+    if (groups && !p->groups.empty()) std::memcpy(groups, p->groups.data(), p->groups.size() * sizeof(int32_t));
+    if (mblocks && !p->mblocks.empty()) std::memcpy(mblocks, p->mblocks.data(), p->mblocks.size() * sizeof(int32_t));
     if (cols && !p->cols.empty()) std::memcpy(cols, p->cols.data(), p->cols.size() * sizeof(int32_t));
-    if (et && !p->et.empty()) std::memcpy(et, p->et.data(), p->et.size() * sizeof(uint16_t));
+    if (et && !p->et.empty()) {
+        if (et_bytes == 2) {
+            std::memcpy(et, p->et.data(), p->et.size() * sizeof(uint16_t));
+        } else {
+            uint8_t *out = static_cast<uint8_t *>(et);
+            for (size_t i = 0; i < p->et.size(); ++i) {
+                if (p->et[i] != kNoEdge && p->et[i] >= kNoEdge8)
+                    return fail(BPT_ERR_UNSUPPORTED, "tile_plan_export: edge type %d does not fit 8 bits", p->et[i]);
+                out[i] = p->et[i] == kNoEdge ? kNoEdge8 : static_cast<uint8_t>(p->et[i]);
+            }
+        }
+    }
     if (split_rows && !p->split.empty()) std::memcpy(split_rows, p->split.data(), p->split.size() * sizeof(int32_t));
-    if (simt_items && !p->simt.empty()) std::memcpy(simt_items, p->simt.data(), p->simt.size() * sizeof(int32_t));
+    if (row_items && !p->simt.empty()) std::memcpy(row_items, p->simt.data(), p->simt.size() * sizeof(int32_t));
     return BPT_OK;
 }
 

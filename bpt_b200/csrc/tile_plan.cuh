@@ -1,20 +1,40 @@
 // Record layout of the tensor-core path's tile plan, shared by the host planner and the kernel.
+//
+// A *group* is a sorted list of source columns (padded to a multiple of 64) plus up to
+// kMaxMBlocks *m-blocks*; an m-block is <=16 destination rows with a dense matrix of edge
+// types over the group's columns (kNoEdge = no edge in that cell).  One thread block stages
+// the group's K/V rows once per head and every m-block (one warp each) attends over them.
 #pragma once
 
 #include "common.cuh"
 
 namespace bpt {
 
-constexpr int kTileRows = 16;    // destination rows per tile (one mma M block)
-constexpr int kTileChunk = 64;   // source columns processed per inner step; column counts are padded to it
-constexpr int kTileInts = 40;    // int32 words per tile record
-constexpr int kTileRowOff = 0;   // [0,16): destination row ids, -1 = unused
-constexpr int kTileSlotOff = 16; // [16,32): partial-result slot per row, -1 = the tile holds the whole row
-constexpr int kTileNcolsPad = 32;
-constexpr int kTileColOff = 33;  // offset of the tile's column list in `cols`
-constexpr int kTileEtOff = 34;   // offset of the tile's [16][ncols_pad] edge-type matrix in `et`
-constexpr int kTileTq = 35;      // edge types [0, tq) occur in the tile (multiple of 8)
-constexpr int kTileNcols = 36;   // columns before padding
+constexpr int kTileRows = 16;     // destination rows per m-block (one mma M block)
+constexpr int kTileChunk = 64;    // source columns per pipeline step; column counts are padded to it
+constexpr int kMaxMBlocks = 8;    // m-blocks (warps) per group at most
+constexpr int kMaxChunks = 32;    // chunk activity is a 32-bit mask
+
+// group record: kGroupInts int32 words
+constexpr int kGroupInts = 8;
+constexpr int kGroupColOff = 0;    // offset of the column list in `cols`
+constexpr int kGroupNcolsPad = 1;  // padded column count (multiple of kTileChunk, may be 0)
+constexpr int kGroupMbFirst = 2;   // first m-block record
+constexpr int kGroupMbCount = 3;
+constexpr int kGroupNcols = 4;     // columns before padding
+
+// m-block record: kMbInts int32 words
+constexpr int kMbInts = 56;
+constexpr int kMbRowOff = 0;       // [0,16): destination row ids, -1 = unused
+constexpr int kMbSlotOff = 16;     // [16,32): partial-result slot per row, -1 = this m-block holds the whole row
+constexpr int kMbRowEtOff = 32;    // [32,48): the row's single edge type when kMbQrSlot < 0
+constexpr int kMbEtOff = 48;       // offset (in cells) of the [chunks][16][64] edge-type matrix in `et`
+constexpr int kMbChunkMask = 49;   // bit c set = some row has an edge in column chunk c
+constexpr int kMbTq = 50;          // edge types [0, tq) occur (multiple of 8)
+constexpr int kMbQrSlot = 51;      // >= 0: needs the per-row relative-position table, in this shared-memory
+                                   // slot; -1: every row's edges share one type, so the term is a per-row
+                                   // constant that cancels in the softmax and only shifts lse
 constexpr uint16_t kNoEdge = 0xFFFF;
+constexpr uint8_t kNoEdge8 = 0xFF;
 
 }  // namespace bpt

@@ -224,46 +224,54 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
  * tolerance; the graph is given as a tile plan.  No counterpart in the reference beyond the
  * operator chain named at bpt_attn_forward.
  *
- * The planner runs on the host (pure integer code, no GPU needed): it takes the in-CSR as
+ * The planner runs on the host (pure integer code, no GPU needed).  It takes the in-CSR as
  * host int32 arrays (in_indptr[n_nodes+1], in_src[n_edges], in_etype[n_edges] or NULL) and
- * covers the attention matrix with tiles of <= 16 destination rows x a list of source
- * columns.  min_density / max_cols decide when 16 consecutive rows form one tile (edges >=
- * min_density * 16 * columns, columns <= max_cols); other rows are grouped by block of
- * `col_block` consecutive sources, except rows of at most `simt_max_degree` edges, which are
- * listed as whole-row items {row, begin, end, -1} for the CUDA-core kernel.
- * bpt_tile_plan_sizes fills sizes[10] = {tiles, column entries, etype cells, split rows,
- * slots, t_max, max_cols_pad, row tiles, row items, tile cells}; bpt_tile_plan_export copies
- * tiles (40 int32 each), cols (int32), et (uint16), split_rows and row_items (4 int32 each)
- * into host arrays of those sizes, to be uploaded as they are.
- * bpt_export_in_csr copies the in-CSR of a bpt_attn_plan_build plan to host arrays (waits
- * for the stream).
+ * covers the attention matrix with groups: a sorted list of source columns shared by up to
+ * 8 m-blocks of <= 16 destination rows, each m-block holding a dense matrix of edge types
+ * over those columns.  `group_rows` consecutive rows form a dense group when their union of
+ * sources has at most `max_cols` columns and edges >= min_density * rows * columns; other
+ * rows are bucketed by block of `col_block` consecutive sources: the rows of a bucket form a
+ * group of their own or, with join_dense != 0, join the dense group that already stages
+ * those sources; a group holds at most `max_mblocks` (<= 8) m-blocks, more spill into a
+ * copy of the group; rows of at most
+ * `simt_max_degree` edges outside dense groups are listed as whole-row items
+ * {row, begin, end, -1} for the CUDA-core kernel instead.
+ * bpt_tile_plan_sizes fills sizes[12] = {groups, m-blocks, column entries, etype cells, split
+ * rows, slots, t_max, max_cols_pad, max m-blocks per group, max QR slots per group, row
+ * items, dense groups}.  bpt_tile_plan_export copies groups (8 int32 each), mblocks (56 int32
+ * each), cols (int32), et (uint8 if et_bytes == 1, which needs every type < 255, else
+ * uint16), split_rows and row_items (4 int32 each) into host arrays of those sizes, to be
+ * uploaded as they are.  bpt_export_in_csr copies the in-CSR of a bpt_attn_plan_build plan
+ * to host arrays (waits for the stream).
  * ---------------------------------------------------------------------------------- */
 void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
                            int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
-                           int col_block, int simt_max_degree);
+                           int group_rows, int col_block, int simt_max_degree, int max_mblocks,
+                           int join_dense);
 int bpt_tile_plan_sizes(const void *handle, int64_t *sizes);
-int bpt_tile_plan_export(const void *handle, int32_t *tiles, int32_t *cols, uint16_t *et,
-                         int32_t *split_rows, int32_t *row_items);
+int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols, void *et,
+                         int et_bytes, int32_t *split_rows, int32_t *row_items);
 void bpt_tile_plan_destroy(void *handle);
 int bpt_export_in_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
-                      int n_etypes,
-                      int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
+                      int n_etypes, int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
                       bpt_stream_t stream);
 
 size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
 
-/* tiles, cols, et, split_rows, row_items: device copies of the exported arrays; attn_plan:
- * the bpt_attn_plan_build blob of the same graph (its in-CSR is what row_items index); the size
- * arguments are the matching entries of bpt_tile_plan_sizes.  q, k, v, o: (n_nodes, h, 64)
- * bf16, 16-byte aligned; ak: (n_etypes, 64) bf16 or NULL; lse fp32 (n_nodes, h). */
-int bpt_attn_forward_tc(const int32_t *tiles, int64_t n_tiles, const int32_t *cols, const uint16_t *et,
-                        const int32_t *split_rows, int64_t n_split, int64_t n_slots,
-                        const int32_t *row_items, int64_t n_row_items, const void *attn_plan,
-                        const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
-                        int max_cols_pad, int t_max, int n_etypes, const void *q, const void *k,
-                        const void *v, const void *ak, double scale, void *o, float *lse, int h,
-                        int d, int dtype, void *workspace, size_t workspace_bytes,
-                        bpt_stream_t stream);
+/* groups, mblocks, cols, et, split_rows, row_items: device copies of the exported arrays;
+ * attn_plan / counts_host: the bpt_attn_plan_build plan of the same graph (its in-CSR is what
+ * row_items index; may be NULL when there are no row items); the size arguments are the
+ * matching entries of bpt_tile_plan_sizes.  q, o: (n_nodes, h, 64), k, v: (n_src, h, 64) bf16,
+ * 16-byte aligned; ak: (n_etypes, 64) bf16 or NULL; lse fp32 (n_nodes, h). */
+int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, const int32_t *mblocks,
+                        const int32_t *cols, const void *et, int et_bytes, const int32_t *split_rows,
+                        int64_t n_split, int64_t n_slots, const int32_t *row_items,
+                        int64_t n_row_items, const void *attn_plan, const int32_t *counts_host,
+                        int64_t n_nodes, int64_t n_edges, int max_cols_pad, int t_max,
+                        int max_mblocks, int max_qr_slots, int n_etypes, const void *q,
+                        const void *k, const void *v, const void *ak, double scale, void *o,
+                        float *lse, int h, int d, int dtype, void *workspace,
+                        size_t workspace_bytes, bpt_stream_t stream);
 
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)

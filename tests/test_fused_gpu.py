@@ -166,7 +166,7 @@ def test_tensor_core_forward_is_used_and_matches_cuda_core_forward(oracle_lib):
     plan = AttentionPlan(torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda(),
                          torch.from_numpy(g["etype"]).cuda(), N, n_etypes=T)
     o_tc, lse_tc = attention_forward(plan, q, k, v, ak, 0.125)
-    assert plan.tiles is not None and plan.tiles.n_tiles > 0
+    assert plan.tiles is not None and plan.tiles.n_groups > 0
     o_cc, lse_cc = attention_forward(plan, q, k, v, ak, 0.125, tensor_cores=False)
     assert rel_err(o_tc.float().cpu(), o_cc.float().cpu()) < 2e-2
     assert rel_err(lse_tc.cpu(), lse_cc.cpu()) < 2e-3

@@ -1,12 +1,14 @@
-"""The host-side tile planner of the tensor-core path: every edge lands in exactly one tile
-cell, rows marked complete really are, and split rows' slots are contiguous. Runs without a GPU."""
+"""The host-side tile planner of the tensor-core path: every edge lands in exactly one cell of
+one m-block, rows marked complete really are, split rows' slots are contiguous, and span rows
+of binary-partition graphs join the leaf group that stages their sources. Runs without a GPU."""
 import ctypes
 
 import numpy as np
 import pytest
 
 
-def _plan(oracle_lib, g, min_density=0.25, max_cols=384, col_block=64, simt_max_degree=8):
+def _plan(oracle_lib, g, min_density=0.05, max_cols=384, group_rows=64, col_block=64, simt_max_degree=0, et_bytes=2,
+          max_mblocks=8, join_dense=1):
     from bpt_b200 import _lib, build
     build.build()
     L = _lib.lib()
@@ -14,54 +16,87 @@ def _plan(oracle_lib, g, min_density=0.25, max_cols=384, col_block=64, simt_max_
     et = g["etype"][eid]
     ip32, s32, e32 = indptr.astype(np.int32), src.astype(np.int32), et.astype(np.int32)
     h = L.bpt_tile_plan_create(ip32.ctypes.data, s32.ctypes.data, e32.ctypes.data, g["n_nodes"], len(src),
-                               min_density, max_cols, col_block, simt_max_degree)
+                               min_density, max_cols, group_rows, col_block, simt_max_degree, max_mblocks,
+                               join_dense)
     assert h
-    sizes = (ctypes.c_int64 * 10)()
+    sizes = (ctypes.c_int64 * 12)()
     assert L.bpt_tile_plan_sizes(h, ctypes.addressof(sizes)) == 0
-    n_tiles, n_cols, n_et, n_split, n_slots, t_max, mcp, n_row_tiles, n_items, _ = [int(x) for x in sizes]
-    tiles = np.empty(n_tiles * 40, np.int32)
+    (n_groups, n_mb, n_cols, n_cells, n_split, n_slots, t_max, mcp, max_mb, max_qr, n_items, n_dense) = \
+        [int(x) for x in sizes]
+    groups = np.empty(max(n_groups * 8, 1), np.int32)
+    mblocks = np.empty(max(n_mb * 56, 1), np.int32)
     cols = np.empty(max(n_cols, 1), np.int32)
-    etm = np.empty(max(n_et, 1), np.uint16)
+    etm = np.empty(max(n_cells, 1), np.uint8 if et_bytes == 1 else np.uint16)
     split = np.empty(max(n_split * 4, 1), np.int32)
     items = np.empty(max(n_items * 4, 1), np.int32)
-    assert L.bpt_tile_plan_export(h, tiles.ctypes.data, cols.ctypes.data, etm.ctypes.data, split.ctypes.data,
-                                  items.ctypes.data) == 0
+    assert L.bpt_tile_plan_export(h, groups.ctypes.data, mblocks.ctypes.data, cols.ctypes.data, etm.ctypes.data,
+                                  et_bytes, split.ctypes.data, items.ctypes.data) == 0
     L.bpt_tile_plan_destroy(h)
-    return dict(tiles=tiles.reshape(n_tiles, 40), cols=cols, et=etm, split=split[:n_split * 4].reshape(n_split, 4),
-                items=items[:n_items * 4].reshape(n_items, 4), n_slots=n_slots, t_max=t_max, mcp=mcp, n_row_tiles=n_row_tiles, csr=(indptr, src, et))
+    return dict(groups=groups[:n_groups * 8].reshape(n_groups, 8), mblocks=mblocks[:n_mb * 56].reshape(n_mb, 56),
+                cols=cols, et=etm, split=split[:n_split * 4].reshape(n_split, 4),
+                items=items[:n_items * 4].reshape(n_items, 4), n_slots=n_slots, t_max=t_max, mcp=mcp,
+                max_mb=max_mb, max_qr=max_qr, n_dense=n_dense, csr=(indptr, src, et))
 
 
-@pytest.mark.parametrize("spec", [[(512, False, 4, 10)], [(513, False, 4, 10), (100, True, 2, 3), (1, False, 1, 10)],
-                                  [(3000, True, 8, 6)], [(37, False, 1, 0)]])
-def test_tiles_cover_every_edge_once(oracle_lib, spec):
+@pytest.mark.parametrize("spec,kw", [
+    ([(512, False, 4, 10)], {}),
+    ([(513, False, 4, 10), (100, True, 2, 3), (1, False, 1, 10)], {}),
+    ([(3000, True, 8, 6)], {"et_bytes": 1}),
+    ([(37, False, 1, 0)], {"simt_max_degree": 4}),
+    ([(700, False, 4, 10)], {"group_rows": 32, "col_block": 32}),
+    ([(2000, False, 4, 10)], {"group_rows": 128, "col_block": 128, "max_mblocks": 8, "join_dense": 0, "max_cols": 512}),
+])
+def test_plan_covers_every_edge_once(oracle_lib, spec, kw):
     g = oracle_lib.batch_graphs([oracle_lib.binary_partition(*s) for s in spec])
-    p = _plan(oracle_lib, g)
+    p = _plan(oracle_lib, g, **kw)
+    none = 0xFF if kw.get("et_bytes") == 1 else 0xFFFF
     indptr, src, et = p["csr"]
     N = g["n_nodes"]
-    got = []          # (row, src, etype) per cell
+    got = []
     rows_seen = np.zeros(N, np.int64)
     complete = np.zeros(N, bool)
     slots = {}
-    for t in p["tiles"]:
-        rows, slot, ncp, coff, eoff, tq, ncols = t[0:16], t[16:32], t[32], t[33], t[34], t[35], t[36]
-        assert ncp % 64 == 0 and ncols <= ncp <= p["mcp"] and tq % 8 == 0 and tq <= p["t_max"]
+    uniform = np.array([len(set(et[indptr[r]:indptr[r + 1]])) <= 1 for r in range(N)])
+    mb_seen = 0
+    for grp in p["groups"]:
+        coff, ncp, mb_first, mb_count, ncols = grp[:5]
+        assert ncp % 64 == 0 and ncols <= ncp <= p["mcp"] and 1 <= mb_count <= min(kw.get("max_mblocks", 8), p["max_mb"])
+        assert mb_first == mb_seen          # m-blocks of a group are contiguous, groups in order
+        mb_seen += mb_count
         cols = p["cols"][coff:coff + ncp]
-        m = p["et"][eoff:eoff + 16 * ncp].reshape(16, ncp)
-        assert np.all(m[:, ncols:] == 0xFFFF)
-        for i in range(16):
-            if rows[i] < 0:
-                assert np.all(m[i] == 0xFFFF)
-                continue
-            rows_seen[rows[i]] += 1
-            cs = np.nonzero(m[i] != 0xFFFF)[0]
-            assert np.all(m[i][cs] < max(tq, 1))
-            got += [(int(rows[i]), int(cols[c]), int(m[i][c])) for c in cs]
-            if slot[i] < 0:
-                assert not complete[rows[i]]
-                complete[rows[i]] = True
-                assert len(cs) == indptr[rows[i] + 1] - indptr[rows[i]]
+        assert np.all(np.diff(cols[:ncols]) >= 0)
+        n_qr = 0
+        for m in p["mblocks"][mb_first:mb_first + mb_count]:
+            rows, slot, row_et, eoff, mask, tq, qr = m[0:16], m[16:32], m[32:48], m[48], m[49], m[50], m[51]
+            cells = p["et"][eoff:eoff + 16 * ncp].reshape(ncp // 64, 16, 64)
+            valid = rows[rows >= 0]
+            assert np.all(np.diff(valid) > 0)
+            if qr >= 0:
+                assert qr == n_qr and tq <= p["t_max"] and not all(uniform[valid])
+                n_qr += 1
             else:
-                slots.setdefault(int(rows[i]), []).append(int(slot[i]))
+                assert all(uniform[valid])
+            for ch in range(ncp // 64):
+                assert bool((int(mask) >> ch) & 1) == bool(np.any(cells[ch] != none))
+            for i in range(16):
+                row_cells = cells[:, i, :].reshape(-1)
+                if rows[i] < 0:
+                    assert np.all(row_cells == none)
+                    continue
+                rows_seen[rows[i]] += 1
+                cs = np.nonzero(row_cells != none)[0]
+                assert np.all(cs < ncols)
+                got += [(int(rows[i]), int(cols[c]), int(row_cells[c])) for c in cs]
+                if qr < 0 and len(cs):
+                    assert np.all(row_cells[cs] == row_et[i])
+                if slot[i] < 0:
+                    assert not complete[rows[i]]
+                    complete[rows[i]] = True
+                    assert len(cs) == indptr[rows[i] + 1] - indptr[rows[i]]
+                else:
+                    slots.setdefault(int(rows[i]), []).append(int(slot[i]))
+        assert n_qr <= p["max_qr"]
+    assert mb_seen == len(p["mblocks"])
     for row, beg, end, slot in p["items"]:      # short rows handed to the CUDA-core kernel, whole
         assert slot == -1 and beg == indptr[row] and end == indptr[row + 1] and not complete[row]
         complete[row] = True
@@ -72,17 +107,25 @@ def test_tiles_cover_every_edge_once(oracle_lib, spec):
     assert np.all(rows_seen >= 1)                       # rows without edges are covered too
     assert not any(complete[r] for r in slots)          # a row is either complete or split
     assert np.all(complete | np.isin(np.arange(N), list(slots)))
-    all_slots = sorted(s for v in slots.values() for s in v)
-    assert all_slots == list(range(p["n_slots"]))
+    assert sorted(s for v in slots.values() for s in v) == list(range(p["n_slots"]))
     assert len(p["split"]) == len(slots)
     for row, first, count, _ in p["split"]:
-        assert sorted(slots[int(row)]) == list(range(first, first + count))
+        assert slots[int(row)] == list(range(first, first + count))   # in m-block order
 
 
-def test_leaf_blocks_become_row_tiles(oracle_lib):
+def test_leaf_blocks_become_dense_groups(oracle_lib):
+    """Production parameters on the headline graph: 128 consecutive leaves share one group of 8
+    m-blocks; span rows are grouped by the 128 leaves they cover; only leaf m-blocks need the
+    relative-position table (span rows have a single edge type each)."""
     g = oracle_lib.binary_partition(8192, False, 4, 10)
-    p = _plan(oracle_lib, g)
-    assert p["n_row_tiles"] >= 512           # the 512 blocks of 16 leaves
-    leaf_tiles = [t for t in p["tiles"] if 0 <= t[0] < 8192 and t[15] < 8192 and t[15] >= 0]
-    ncols = np.array([t[36] for t in leaf_tiles[:512]])
-    assert ncols.max() <= 192 and 100 < ncols.mean() < 140
+    p = _plan(oracle_lib, g, min_density=0.04, max_cols=512, group_rows=128, col_block=128, max_mblocks=8, join_dense=0)
+    assert p["n_dense"] == 64
+    leaf_groups = p["groups"][:64]
+    assert np.all(leaf_groups[:, 3] == 8)
+    assert 330 < leaf_groups[:, 4].mean() < 420 and leaf_groups[:, 1].max() <= 512
+    assert p["max_qr"] == 8 and p["max_mb"] == 8
+    span_groups = p["groups"][64:]
+    assert np.all(span_groups[:, 4] <= 128)
+    qr = p["mblocks"][:, 51]
+    first_span_mb = span_groups[0][2]
+    assert np.all(qr[first_span_mb:] == -1)

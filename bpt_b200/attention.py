@@ -93,8 +93,8 @@ class TilePlan:
     bpt_attn_forward_tc.  Planned on the host from the plan's in-CSR (integer work, once per
     graph), kept on the device."""
 
-    def __init__(self, plan, min_density=0.04, max_cols=512, group_rows=128, col_block=128, simt_max_degree=0,
-                 max_mblocks=8, join_dense=False):
+    def __init__(self, plan, min_density=0.25, max_cols=384, group_rows=16, col_block=64, simt_max_degree=0,
+                 max_mblocks=1, join_dense=False):
         L = _lib.lib()
         N, E, T = plan.n_nodes, plan.n_edges, plan.n_etypes
         indptr = np.empty(N + 1, np.int32)

@@ -164,6 +164,7 @@ attn_forward_kernel(const int4 *__restrict__ items, int n_items, const int32_t *
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
     if (active) {
+        #pragma unroll 4
         for (int j = 0; j < n; ++j) {
             const int src = in_src[beg + j];
             const float p = sc[j * HPW + hl];
@@ -340,6 +341,7 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
     float dkf[16], dvf[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) { dkf[i] = 0.f; dvf[i] = 0.f; }
+    #pragma unroll 4
     for (int j = beg; j < end; ++j) {
         const int dst = out_dst[j];
         const int64_t pos = out_inpos[j];
@@ -393,6 +395,7 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
     for (int h0 = 0; h0 < H; h0 += HPW) {
         const int head = h0 + hl;
         if (head < H && nvalid > 0) {
+            #pragma unroll 4
             for (int j = beg; j < end; ++j) {
                 const int dst = et_dst[j];
                 const int64_t pos = et_inpos[j];

@@ -24,6 +24,10 @@ SIGNATURES = {
     "bpt_bp_count_workspace_bytes": (_sz, [_i64]),
     "bpt_bp_count": (_int, [_i64, _int, _int, _int, _vp, _vp, _sz, _vp, _vp]),
     "bpt_bp_fill": (_int, [_i64, _int, _int, _int, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "bpt_fc_count": (_int, [_i64, _int, _i64, _vp, _vp, _sz, _vp, _vp]),
+    "bpt_fc_fill": (_int, [_i64, _int, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "bpt_oas_count": (_int, [_i64, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),
+    "bpt_oas_fill": (_int, [_i64, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "bpt_coo_to_csr_workspace_bytes": (_sz, [_i64, _i64]),
     "bpt_coo_to_csr": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
     "bpt_partition_csr_workspace_bytes": (_sz, [_i64]),

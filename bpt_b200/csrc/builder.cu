@@ -238,6 +238,101 @@ __global__ void chunk_fill_kernel(const int64_t *__restrict__ indptr, int64_t n_
     indptr_out[c] = indptr[lo] + (c - chunk_offsets[lo]) * chunk;
 }
 
+// ------------------------------------------------------------------ baseline graphs
+// FullyConnected (graph_builder/builder.pyx:228-274) and OpenAISparse (:154-196): token nodes
+// [0, length) plus one root node `length`.  Each leaf's edge run has a closed-form length and
+// every edge a closed-form position inside the run, so one block fills one leaf's run.
+
+// builder.pyx:243-265: self edge, then for j = 1 .. min(length, window+1)-1: left (i >= j, type
+// 2j-1), right (!triu and i+j < length, type 2j); then the edge to the root.
+__device__ __host__ inline int64_t fc_leaf_count(int64_t i, int64_t length, int64_t jmax, bool triu) {
+    const int64_t left = i < jmax ? i : jmax;
+    const int64_t right = triu ? 0 : ((length - 1 - i) < jmax ? (length - 1 - i) : jmax);
+    return 2 + left + right;
+}
+
+__global__ void fc_count_kernel(int64_t length, int64_t jmax, bool triu, int64_t *__restrict__ counts) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i > length) return;
+    counts[i] = i < length ? fc_leaf_count(i, length, jmax, triu) : 0;
+}
+
+template <typename I>
+__global__ void fc_fill_kernel(int64_t length, int64_t jmax, bool triu, const int64_t *__restrict__ leaf_offsets,
+                               int64_t v_shift, I *__restrict__ src, I *__restrict__ dst, I *__restrict__ etype) {
+    const int64_t i = blockIdx.x;
+    const int64_t base = leaf_offsets[i];
+    const int64_t right_max = length - 1 - i;
+    auto put = [&](int64_t e, int64_t s, int64_t d, int64_t t) {
+        if (src) src[e] = static_cast<I>(s + v_shift);
+        if (dst) dst[e] = static_cast<I>(d + v_shift);
+        if (etype) etype[e] = static_cast<I>(t);
+    };
+    if (threadIdx.x == 0) {
+        put(base, i, i, 0);
+        put(base + fc_leaf_count(i, length, jmax, triu) - 1, i, length, 0);
+    }
+    for (int64_t j = 1 + threadIdx.x; j <= jmax; j += blockDim.x) {
+        // edges emitted by iterations j' < j: one left each while j' <= i, one right each while j' <= right_max
+        int64_t e = base + 1 + ((j - 1) < i ? (j - 1) : i);
+        if (!triu) e += (j - 1) < right_max ? (j - 1) : right_max;
+        if (i >= j) { put(e, i - j, i, 2 * j - 1); ++e; }
+        if (!triu && j <= right_max) put(e, i + j, i, 2 * j);
+    }
+}
+
+// builder.pyx:171-194: sources of leaf i: its stride block up to itself, then the last c
+// positions of every earlier block boundary j*stride (skipped when c > j*stride: the unsigned
+// start of the reference's range wraps and the range is empty), then the edge to the root.
+__device__ __host__ inline int64_t oas_first_j(int64_t stride, int64_t c) {
+    const int64_t j = (c + stride - 1) / stride;
+    return j < 1 ? 1 : j;
+}
+__device__ __host__ inline int64_t oas_leaf_count(int64_t i, int64_t stride, int64_t c) {
+    const int64_t nb = i / stride, j0 = oas_first_j(stride, c);
+    return (i - nb * stride + 1) + (nb >= j0 ? (nb - j0 + 1) * c : 0) + 1;
+}
+
+__global__ void oas_count_kernel(int64_t length, int64_t stride, int64_t c, int64_t *__restrict__ counts) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i > length) return;
+    counts[i] = i < length ? oas_leaf_count(i, stride, c) : 0;
+}
+
+template <typename I>
+__global__ void oas_fill_kernel(int64_t length, int64_t stride, int64_t c, const int64_t *__restrict__ leaf_offsets,
+                                int64_t v_shift, I *__restrict__ src, I *__restrict__ dst, I *__restrict__ etype) {
+    const int64_t i = blockIdx.x;
+    const int64_t base = leaf_offsets[i];
+    const int64_t nb = i / stride, j0 = oas_first_j(stride, c);
+    const int64_t inside = i - nb * stride + 1;
+    const int64_t total = oas_leaf_count(i, stride, c);
+    for (int64_t e = threadIdx.x; e < total; e += blockDim.x) {
+        int64_t s, d = i;
+        if (e < inside) {
+            s = nb * stride + e;
+        } else if (e < total - 1) {
+            const int64_t r = e - inside;
+            const int64_t j = j0 + r / c;
+            s = stride * j - c + r % c;
+        } else {
+            s = i;
+            d = length;
+        }
+        if (src) src[base + e] = static_cast<I>(s + v_shift);
+        if (dst) dst[base + e] = static_cast<I>(d + v_shift);
+        if (etype) etype[base + e] = 0;
+    }
+}
+
+// pos of the baseline graphs: leaves i, root `root_pos` (builder.pyx:173,196 / :245,267).
+template <typename I>
+__global__ void baseline_pos_kernel(int64_t length, int64_t root_pos, I *__restrict__ pos) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i > length) return;
+    pos[i] = static_cast<I>(i < length ? i : root_pos);
+}
+
 }  // namespace
 }  // namespace bpt
 
@@ -394,6 +489,102 @@ extern "C" int bpt_partition_csr_fill(const int64_t *indptr, int64_t n_rows, int
     const unsigned blocks = static_cast<unsigned>((n_chunks + 1 + 255) / 256);
     chunk_fill_kernel<<<blocks, 256, 0, as_stream(stream_)>>>(indptr, n_rows, chunk_size, chunk_offsets,
                                                              row, indptr_out);
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+// ---- baseline graphs -------------------------------------------------------------------
+
+namespace {
+// Exclusive scan of the per-leaf counts (carved first from `ws` by the caller) into leaf_offsets.
+int baseline_scan(int64_t length, const int64_t *counts, int64_t *leaf_offsets, Workspace &ws,
+                  int64_t *n_edges_host, cudaStream_t stream) {
+    size_t temp_bytes = scan_temp_bytes(length + 1);
+    char *temp = ws.take<char>(temp_bytes > 0 ? temp_bytes : 1);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "baseline graph: workspace of %zu bytes is too small", ws.size);
+    BPT_CUDA(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, counts, leaf_offsets, length + 1, stream));
+    if (n_edges_host) {
+        BPT_CUDA(cudaMemcpyAsync(n_edges_host, leaf_offsets + length, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+        BPT_CUDA(cudaStreamSynchronize(stream));
+    }
+    return BPT_OK;
+}
+}  // namespace
+
+extern "C" int bpt_fc_count(int64_t length, int triu, int64_t window, int64_t *leaf_offsets, void *workspace,
+                            size_t workspace_bytes, int64_t *n_edges_host, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(length >= 1 && length <= (int64_t(1) << 30) && window >= 0, "fc_count: bad length or window");
+    BPT_CHECK_ARG(leaf_offsets != nullptr, "fc_count: leaf_offsets is null");
+    cudaStream_t stream = as_stream(stream_);
+    Workspace ws(workspace, workspace_bytes);
+    int64_t *counts = ws.take<int64_t>(static_cast<size_t>(length + 1));
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "fc_count: workspace of %zu bytes is too small", workspace_bytes);
+    const int64_t jmax = (length < window + 1 ? length : window + 1) - 1;  // builder.pyx:251
+    fc_count_kernel<<<static_cast<unsigned>((length + 1 + 255) / 256), 256, 0, stream>>>(length, jmax, triu != 0, counts);
+    BPT_LAUNCH_CHECK();
+    return baseline_scan(length, counts, leaf_offsets, ws, n_edges_host, stream);
+}
+
+extern "C" int bpt_fc_fill(int64_t length, int triu, int64_t window, const int64_t *leaf_offsets, int64_t v_shift,
+                           int index_bytes, void *src, void *dst, void *etype, void *pos, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(length >= 1 && length <= (int64_t(1) << 30) && window >= 0, "fc_fill: bad length or window");
+    BPT_CHECK_ARG(index_bytes == 4 || index_bytes == 8, "fc_fill: index_bytes must be 4 or 8");
+    BPT_CHECK_ARG(leaf_offsets != nullptr, "fc_fill: leaf_offsets is null");
+    if (index_bytes == 4) BPT_CHECK_ARG(length + 1 + v_shift < (int64_t(1) << 31), "fc_fill: node ids exceed int32");
+    cudaStream_t stream = as_stream(stream_);
+    const int64_t jmax = (length < window + 1 ? length : window + 1) - 1;
+    const unsigned pb = static_cast<unsigned>((length + 1 + 255) / 256);
+    if (index_bytes == 4) {
+        if (src || dst || etype)
+            fc_fill_kernel<int32_t><<<static_cast<unsigned>(length), 128, 0, stream>>>(
+                length, jmax, triu != 0, leaf_offsets, v_shift, static_cast<int32_t *>(src),
+                static_cast<int32_t *>(dst), static_cast<int32_t *>(etype));
+        if (pos) baseline_pos_kernel<int32_t><<<pb, 256, 0, stream>>>(length, length, static_cast<int32_t *>(pos));
+    } else {
+        if (src || dst || etype)
+            fc_fill_kernel<int64_t><<<static_cast<unsigned>(length), 128, 0, stream>>>(
+                length, jmax, triu != 0, leaf_offsets, v_shift, static_cast<int64_t *>(src),
+                static_cast<int64_t *>(dst), static_cast<int64_t *>(etype));
+        if (pos) baseline_pos_kernel<int64_t><<<pb, 256, 0, stream>>>(length, length, static_cast<int64_t *>(pos));
+    }
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+extern "C" int bpt_oas_count(int64_t length, int64_t stride, int64_t c, int64_t *leaf_offsets, void *workspace,
+                             size_t workspace_bytes, int64_t *n_edges_host, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(length >= 1 && length <= (int64_t(1) << 30) && stride >= 1 && c >= 0, "oas_count: bad arguments");
+    BPT_CHECK_ARG(leaf_offsets != nullptr, "oas_count: leaf_offsets is null");
+    cudaStream_t stream = as_stream(stream_);
+    Workspace ws(workspace, workspace_bytes);
+    int64_t *counts = ws.take<int64_t>(static_cast<size_t>(length + 1));
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "oas_count: workspace of %zu bytes is too small", workspace_bytes);
+    oas_count_kernel<<<static_cast<unsigned>((length + 1 + 255) / 256), 256, 0, stream>>>(length, stride, c, counts);
+    BPT_LAUNCH_CHECK();
+    return baseline_scan(length, counts, leaf_offsets, ws, n_edges_host, stream);
+}
+
+extern "C" int bpt_oas_fill(int64_t length, int64_t stride, int64_t c, const int64_t *leaf_offsets, int64_t v_shift,
+                            int index_bytes, void *src, void *dst, void *etype, void *pos, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(length >= 1 && length <= (int64_t(1) << 30) && stride >= 1 && c >= 0, "oas_fill: bad arguments");
+    BPT_CHECK_ARG(index_bytes == 4 || index_bytes == 8, "oas_fill: index_bytes must be 4 or 8");
+    BPT_CHECK_ARG(leaf_offsets != nullptr, "oas_fill: leaf_offsets is null");
+    if (index_bytes == 4) BPT_CHECK_ARG(length + 1 + v_shift < (int64_t(1) << 31), "oas_fill: node ids exceed int32");
+    cudaStream_t stream = as_stream(stream_);
+    const unsigned pb = static_cast<unsigned>((length + 1 + 255) / 256);
+    if (index_bytes == 4) {
+        if (src || dst || etype)
+            oas_fill_kernel<int32_t><<<static_cast<unsigned>(length), 128, 0, stream>>>(
+                length, stride, c, leaf_offsets, v_shift, static_cast<int32_t *>(src), static_cast<int32_t *>(dst),
+                static_cast<int32_t *>(etype));
+        if (pos) baseline_pos_kernel<int32_t><<<pb, 256, 0, stream>>>(length, length - 1, static_cast<int32_t *>(pos));
+    } else {
+        if (src || dst || etype)
+            oas_fill_kernel<int64_t><<<static_cast<unsigned>(length), 128, 0, stream>>>(
+                length, stride, c, leaf_offsets, v_shift, static_cast<int64_t *>(src), static_cast<int64_t *>(dst),
+                static_cast<int64_t *>(etype));
+        if (pos) baseline_pos_kernel<int64_t><<<pb, 256, 0, stream>>>(length, length - 1, static_cast<int64_t *>(pos));
+    }
     BPT_LAUNCH_CHECK();
     return BPT_OK;
 }

@@ -1,8 +1,9 @@
 """GPU counterpart of the reference's `graphbuilder` module (graph_builder/builder.pyx).
 
-Same names, arguments and return types as the reference for the binary-partition path:
-`BinaryPartition(length, triu=False, step=1, clip_dist=10)` with its properties and
-accessors (builder.pyx:29-152) and `partition_csr(indptr, chunk_size=32)` (:305-321).
+Same names, arguments and return types as the reference: `BinaryPartition(length,
+triu=False, step=1, clip_dist=10)` with its properties and accessors (builder.pyx:29-152),
+the baseline graphs `FullyConnected` (:228-303) and `OpenAISparse` (:154-225), and
+`partition_csr(indptr, chunk_size=32)` (:305-321).
 The graph is built on the current CUDA device by the kernels behind bpt_bp_count /
 bpt_bp_fill and is bit-identical to the reference's.  The numpy-returning accessors copy to
 the host as the reference's callers expect; the `*_device` accessors hand out the device
@@ -133,6 +134,101 @@ class BinaryPartition:
         the block-diagonal placement of graph/lm.py:76-91."""
         fill_edges(self.length, self.triu, self.step, self.clip_dist, self._offsets, v_shift,
                    src, dst, etype, pos)
+
+
+class _BaselineGraph:
+    """Shared part of the two baseline graphs: `length` tokens plus one root node."""
+
+    def _build(self, count, fill):
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            self._offsets = torch.empty(self.length + 1, dtype=torch.int64, device=self.device)
+            ws = _lib.workspace(L.bpt_bp_count_workspace_bytes(self.length), self.device)
+            n_edges = ctypes.c_int64(0)
+            _lib.check(count(self._offsets.data_ptr(), ws.data_ptr(), ws.numel(), ctypes.addressof(n_edges),
+                             _lib.stream()))
+            self.n_edges = int(n_edges.value)
+            self._src, self._dst, self._etype = [torch.empty(self.n_edges, dtype=torch.int32, device=self.device)
+                                                 for _ in range(3)]
+            self._pos = torch.empty(self.n_nodes, dtype=torch.int32, device=self.device)
+            self._fill = fill
+            self.fill_into(0, self._src, self._dst, self._etype, self._pos)
+
+    def fill_into(self, v_shift, src, dst, etype, pos):
+        some = next(t for t in (src, dst, etype, pos) if t is not None)
+        with torch.cuda.device(some.device):
+            _lib.check(self._fill(self._offsets.data_ptr(), int(v_shift), some.element_size(), _lib.ptr(src),
+                                  _lib.ptr(dst), _lib.ptr(etype), _lib.ptr(pos), _lib.stream()))
+
+    @property
+    def number_of_nodes(self):
+        return self.n_nodes
+
+    @property
+    def number_of_edges(self):
+        return self.n_edges
+
+    @property
+    def is_triu(self):
+        return self.triu
+
+    def get_pos(self):
+        return self._pos.cpu().numpy().astype(np.int64)
+
+    def get_edges(self, v_shift=0):
+        return (self._src.cpu().numpy().astype(np.int64) + v_shift,
+                self._dst.cpu().numpy().astype(np.int64) + v_shift,
+                self._etype.cpu().numpy().astype(np.int64))
+
+    def root_id(self, v_shift=0):
+        return v_shift + self.n_nodes - 1
+
+    def leaf_ids(self, v_shift=0, start=0):
+        return np.arange(v_shift + start, v_shift + self.length)
+
+    def internal_ids(self, v_shift=0):
+        return np.arange(v_shift + self.length, v_shift + self.n_nodes)
+
+    def edges_device(self):
+        return self._src, self._dst, self._etype
+
+    def pos_device(self):
+        return self._pos
+
+
+class FullyConnected(_BaselineGraph):
+    """builder.pyx:228-303: dense (or windowed) attention graph with a root node."""
+
+    def __init__(self, length, triu=False, window=8192, device=None):
+        self.length, self.triu, self.window = int(length), bool(triu), int(window)
+        if self.length < 1:
+            raise ValueError("FullyConnected: length must be >= 1")
+        self.n_nodes = self.length + 1
+        self.device = _device(device)
+        L = _lib.lib()
+        self._build(lambda *a: L.bpt_fc_count(self.length, int(self.triu), self.window, *a),
+                    lambda *a: L.bpt_fc_fill(self.length, int(self.triu), self.window, *a))
+
+    def __reduce__(self):
+        return FullyConnected, (self.length, self.triu, self.window)
+
+
+class OpenAISparse(_BaselineGraph):
+    """builder.pyx:154-225: strided causal graph of the Sparse Transformer baseline."""
+
+    def __init__(self, length, stride, c, triu=True, device=None):
+        assert triu, "bidirectional model is not supported"  # builder.pyx:165
+        self.length, self.stride, self.c, self.triu = int(length), int(stride), int(c), True
+        if self.length < 1 or self.stride < 1:
+            raise ValueError("OpenAISparse: length and stride must be >= 1")
+        self.n_nodes = self.length + 1
+        self.device = _device(device)
+        L = _lib.lib()
+        self._build(lambda *a: L.bpt_oas_count(self.length, self.stride, self.c, *a),
+                    lambda *a: L.bpt_oas_fill(self.length, self.stride, self.c, *a))
+
+    def __reduce__(self):
+        return OpenAISparse, (self.length, self.stride, self.c, self.triu)
 
 
 def partition_csr(indptr, chunk_size=32):

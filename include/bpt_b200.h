@@ -68,6 +68,23 @@ int bpt_bp_fill(int64_t length, int triu, int step, int clip_dist,
                 const int64_t *leaf_offsets, int64_t v_shift, int index_bytes,
                 void *src, void *dst, void *etype, void *pos, bpt_stream_t stream);
 
+/* Baseline graphs of the reference's dense / strided configurations: `length` token nodes plus
+ * one root node (id `length`) that every token feeds.  Same two-step protocol and outputs as
+ * bpt_bp_count / bpt_bp_fill (workspace size: bpt_bp_count_workspace_bytes(length)).
+ * bpt_fc_*: FullyConnected(length, triu, window), graph_builder/builder.pyx:228-274 (every
+ * token attends to the tokens within `window` positions, left only when triu; edge type
+ * 2j-1 / 2j for distance j to the left / right).
+ * bpt_oas_*: OpenAISparse(length, stride, c), builder.pyx:154-196 (causal: a token attends to
+ * its stride block up to itself and to the last c tokens before every earlier block boundary). */
+int bpt_fc_count(int64_t length, int triu, int64_t window, int64_t *leaf_offsets, void *workspace,
+                 size_t workspace_bytes, int64_t *n_edges_host, bpt_stream_t stream);
+int bpt_fc_fill(int64_t length, int triu, int64_t window, const int64_t *leaf_offsets, int64_t v_shift,
+                int index_bytes, void *src, void *dst, void *etype, void *pos, bpt_stream_t stream);
+int bpt_oas_count(int64_t length, int64_t stride, int64_t c, int64_t *leaf_offsets, void *workspace,
+                  size_t workspace_bytes, int64_t *n_edges_host, bpt_stream_t stream);
+int bpt_oas_fill(int64_t length, int64_t stride, int64_t c, const int64_t *leaf_offsets, int64_t v_shift,
+                 int index_bytes, void *src, void *dst, void *etype, void *pos, bpt_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * CSR extraction.  Replaces get_csrs(), graph/base.py:71-86 (two COO->CSR conversions and
  * two partition_csr calls).  Entries of a row are in ascending edge-id order.

@@ -122,6 +122,61 @@ int64_t bpto_build(int64_t length, int triu, int step, int clip_dist,
     return e;
 }
 
+/* ------------------------------------------------------------------ baseline graphs */
+
+/* FullyConnected.build_graph, graph_builder/builder.pyx:243-267.  Returns the edge count;
+ * with src == NULL only counts.  pos (length+1 entries) may be NULL. */
+int64_t bpto_fully_connected(int64_t length, int triu, int64_t window,
+                             uint32_t *src, uint32_t *dst, uint32_t *etype, uint32_t *pos) {
+    int64_t e = 0;
+    const int64_t jend = length < window + 1 ? length : window + 1;
+    for (int64_t i = 0; i < length; ++i) {
+        if (pos) pos[i] = (uint32_t)i;
+        if (src) { src[e] = (uint32_t)i; dst[e] = (uint32_t)i; etype[e] = 0; }
+        e++;
+        for (int64_t j = 1; j < jend; ++j) {
+            if (i >= j) {
+                if (src) { src[e] = (uint32_t)(i - j); dst[e] = (uint32_t)i; etype[e] = (uint32_t)(2 * j - 1); }
+                e++;
+            }
+            if (!triu && i + j < length) {
+                if (src) { src[e] = (uint32_t)(i + j); dst[e] = (uint32_t)i; etype[e] = (uint32_t)(2 * j); }
+                e++;
+            }
+        }
+        if (src) { src[e] = (uint32_t)i; dst[e] = (uint32_t)length; etype[e] = 0; }
+        e++;
+    }
+    if (pos) pos[length] = (uint32_t)length;
+    return e;
+}
+
+/* OpenAISparse.build_graph, graph_builder/builder.pyx:171-196.  The reference's loop bounds are
+ * unsigned: when c exceeds stride*j the start of range(stride*j - c, stride*j) wraps around and
+ * the range is empty. */
+int64_t bpto_openai_sparse(int64_t length, int64_t stride, int64_t c,
+                           uint32_t *src, uint32_t *dst, uint32_t *etype, uint32_t *pos) {
+    int64_t e = 0;
+    for (int64_t i = 0; i < length; ++i) {
+        if (pos) pos[i] = (uint32_t)i;
+        for (int64_t j = (i / stride) * stride; j < i + 1; ++j) {
+            if (src) { src[e] = (uint32_t)j; dst[e] = (uint32_t)i; etype[e] = 0; }
+            e++;
+        }
+        for (int64_t j = 1; j < i / stride + 1; ++j) {
+            if (stride * j < c) continue;
+            for (int64_t k = stride * j - c; k < stride * j; ++k) {
+                if (src) { src[e] = (uint32_t)k; dst[e] = (uint32_t)i; etype[e] = 0; }
+                e++;
+            }
+        }
+        if (src) { src[e] = (uint32_t)i; dst[e] = (uint32_t)length; etype[e] = 0; }
+        e++;
+    }
+    if (pos) pos[length] = (uint32_t)(length - 1);
+    return e;
+}
+
 /* ------------------------------------------------------------------ CSR helpers */
 
 /* builder.pyx:305-321.  With row == NULL only counts. Returns the number of chunks. */

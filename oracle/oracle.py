@@ -39,6 +39,8 @@ def lib():
         L.bpto_levels.restype = ctypes.c_int
         L.bpto_build.restype = ctypes.c_int64
         L.bpto_partition_csr.restype = ctypes.c_int64
+        L.bpto_fully_connected.restype = ctypes.c_int64
+        L.bpto_openai_sparse.restype = ctypes.c_int64
         L.bpto_num_threads.restype = ctypes.c_int
         _lib = L
     return _lib
@@ -87,6 +89,25 @@ def binary_partition(length, triu=False, step=1, clip_dist=10):
     return dict(src=src.astype(np.int64), dst=dst.astype(np.int64), etype=et.astype(np.int64),
                 pos=pos.astype(np.int64), n_nodes=tot, n_levels=len(nn), n_nodes_arr=nn,
                 shift=sh, n_edges=int(e))
+
+
+def _baseline(fn, length, *args):
+    e = fn(ctypes.c_int64(length), *args, None, None, None, None)
+    src, dst, et = [np.empty(e, np.uint32) for _ in range(3)]
+    pos = np.empty(length + 1, np.uint32)
+    fn(ctypes.c_int64(length), *args, _p(src), _p(dst), _p(et), _p(pos))
+    return dict(src=src.astype(np.int64), dst=dst.astype(np.int64), etype=et.astype(np.int64),
+                pos=pos.astype(np.int64), n_nodes=length + 1, n_edges=int(e))
+
+
+def fully_connected(length, triu=False, window=8192):
+    """FullyConnected(length, triu, window) of graph_builder/builder.pyx:228-274."""
+    return _baseline(lib().bpto_fully_connected, length, ctypes.c_int(bool(triu)), ctypes.c_int64(window))
+
+
+def openai_sparse(length, stride, c):
+    """OpenAISparse(length, stride, c, triu=True) of graph_builder/builder.pyx:154-196."""
+    return _baseline(lib().bpto_openai_sparse, length, ctypes.c_int64(stride), ctypes.c_int64(c))
 
 
 def partition_csr(indptr, chunk_size=32):

@@ -58,6 +58,18 @@ def main():
         if n <= 9 and step <= 2 and clip == 10:
             rec["arrays"] = dict(src=s.tolist(), dst=d.tolist(), etype=t.tolist(), pos=p.tolist())
         out["cases"].append(rec)
+    out["baselines"] = []
+    for (n, triu, window) in [(1, False, 8192), (2, True, 1), (7, False, 3), (30, False, 8192), (30, True, 8192),
+                              (100, False, 8), (100, True, 0), (513, False, 64), (2000, True, 128)]:
+        g = ref.FullyConnected(n, triu, window)
+        s, d, t = g.get_edges()
+        out["baselines"].append(dict(kind="fc", length=n, triu=triu, window=window, n_edges=int(g.number_of_edges),
+                                     sha256=digest(np.concatenate([s, d, t, g.get_pos()]))))
+    for (n, stride, c) in [(1, 4, 2), (9, 4, 2), (64, 8, 3), (100, 16, 16), (100, 4, 6), (1000, 32, 8), (4096, 128, 32)]:
+        g = ref.OpenAISparse(n, stride, c)
+        s, d, t = g.get_edges()
+        out["baselines"].append(dict(kind="oas", length=n, stride=stride, c=c, n_edges=int(g.number_of_edges),
+                                     sha256=digest(np.concatenate([s, d, t, g.get_pos()]))))
     rng = np.random.default_rng(7)
     for n_rows, hi, chunk in ((1, 5, 32), (17, 100, 32), (64, 40, 4), (200, 300, 32), (50, 3, 1)):
         deg = rng.integers(0, hi, n_rows)

@@ -112,3 +112,53 @@ def test_large_graph_digest(golden):
     assert g.number_of_edges == rec["n_edges"] == 13239926
     s, d, t = g.get_edges()
     assert digest(s, d, t, g.get_pos()) == rec["sha256"]
+
+
+def test_baseline_graphs_match_golden_and_oracle(golden, oracle_lib):
+    """FullyConnected / OpenAISparse on the GPU: golden digests of the reference's builder, then
+    seeded parameter sweeps against the oracle, with v_shift and pickling."""
+    gb = _gb()
+    for r in golden["baselines"]:
+        g = gb.FullyConnected(r["length"], r["triu"], r["window"]) if r["kind"] == "fc" else \
+            gb.OpenAISparse(r["length"], r["stride"], r["c"])
+        s, d, t = g.get_edges()
+        assert g.number_of_edges == r["n_edges"] and g.number_of_nodes == r["length"] + 1, r
+        assert digest(s, d, t, g.get_pos()) == r["sha256"], r
+    rng = np.random.default_rng(9)
+    for _ in range(40):
+        n, w, triu = int(rng.integers(1, 400)), int(rng.integers(0, 500)), bool(rng.integers(0, 2))
+        g, o = gb.FullyConnected(n, triu, w), oracle_lib.fully_connected(n, triu, w)
+        s, d, t = g.get_edges(5)
+        assert np.array_equal(s, o["src"] + 5) and np.array_equal(d, o["dst"] + 5) and np.array_equal(t, o["etype"])
+        assert np.array_equal(g.get_pos(), o["pos"]) and g.root_id(5) == n + 5
+        n, stride, c = int(rng.integers(1, 600)), int(rng.integers(1, 40)), int(rng.integers(0, 50))
+        g, o = gb.OpenAISparse(n, stride, c), oracle_lib.openai_sparse(n, stride, c)
+        s, d, t = g.get_edges()
+        assert np.array_equal(s, o["src"]) and np.array_equal(d, o["dst"]) and np.array_equal(t, o["etype"])
+        assert np.array_equal(g.get_pos(), o["pos"]) and g.is_triu
+    g2 = pickle.loads(pickle.dumps(gb.OpenAISparse(50, 8, 3)))
+    assert g2.number_of_edges == oracle_lib.openai_sparse(50, 8, 3)["n_edges"]
+    with pytest.raises(AssertionError):
+        gb.OpenAISparse(10, 4, 2, triu=False)
+
+
+def test_fused_attention_on_baseline_graph(oracle_lib):
+    """The dense baseline graph through the fused path (fp32 CUDA cores, bf16 tensor cores)."""
+    import torch
+    from bpt_b200.attention import AttentionPlan, attention_forward
+    gb = _gb()
+    g = gb.FullyConnected(150, True, 64)
+    s, d, t = g.get_edges()
+    N, T = g.number_of_nodes, int(t.max()) + 1
+    csr = oracle_lib.get_csrs(s, d, N)
+    gen = torch.Generator().manual_seed(0)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        q, k, v = [(torch.randn(N, 8, 64, generator=gen) * 0.125).to(dtype) for _ in range(3)]
+        ak = (torch.randn(T, 64, generator=gen) * 0.125).to(dtype)
+        want, _, _ = oracle_lib.attn_fwd(csr[1], t, q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                                         ak.float().numpy(), 0.125)
+        src, dst, et = g.edges_device()
+        plan = AttentionPlan(src, dst, et, N, n_etypes=T)
+        o, _ = attention_forward(plan, q.cuda(), k.cuda(), v.cuda(), ak.cuda(), 0.125)
+        err = np.abs(o.double().cpu().numpy() - want).max() / np.abs(want).max()
+        assert err < tol, (dtype, err)

@@ -69,3 +69,13 @@ def test_csr_order_and_chunks(oracle_lib):
             assert np.array_equal(indices[indptr[r]:indptr[r + 1]], other[seg])
     assert np.all(np.diff(INDPTR_C) <= 32) and np.all(np.diff(INDPTR_C) > 0)
     assert np.all(np.diff(COL) >= 0)
+
+
+def test_oracle_baseline_graphs_match_golden(oracle_lib, golden):
+    """FullyConnected / OpenAISparse (graph_builder/builder.pyx:154-303) against digests made
+    from the compiled reference."""
+    for r in golden["baselines"]:
+        g = oracle_lib.fully_connected(r["length"], r["triu"], r["window"]) if r["kind"] == "fc" else \
+            oracle_lib.openai_sparse(r["length"], r["stride"], r["c"])
+        assert g["n_edges"] == r["n_edges"], r
+        assert digest(g["src"], g["dst"], g["etype"], g["pos"]) == r["sha256"], r

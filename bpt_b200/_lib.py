@@ -52,15 +52,20 @@ SIGNATURES = {
                                 _int, _int, _int, _vp, _sz, _vp]),
     "bpt_attn_backward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                  _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
-    "bpt_tile_plan_create": (_vp, [_vp, _vp, _vp, _i64, _i64, _dbl, _int, _int, _int, _int, _int, _int]),
+    "bpt_tile_plan_create": (_vp, [_vp, _vp, _vp, _vp, _i64, _i64, _dbl, _int, _int, _int, _int, _int, _int]),
     "bpt_tile_plan_sizes": (_int, [_vp, _vp]),
-    "bpt_tile_plan_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
+    "bpt_tile_plan_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "bpt_tile_plan_destroy": (None, [_vp]),
     "bpt_export_in_csr": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
+    "bpt_export_out_csr": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "bpt_attn_forward_tc_workspace_bytes": (_sz, [_i64, _int]),
     "bpt_attn_forward_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp, _vp,
                                    _i64, _i64, _int, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _dbl, _vp,
                                    _vp, _int, _int, _int, _vp, _sz, _vp]),
+    "bpt_attn_backward_scratch": (_int, [_vp, _sz, _i64, _i64, _int, _vp, _vp, _vp]),
+    "bpt_attn_backward_dkv_tc_workspace_bytes": (_sz, [_i64, _int]),
+    "bpt_attn_backward_dkv_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp,
+                                        _dbl, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "bpt_attn_forward_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                        _int, _int, _int, _vp]),
 }

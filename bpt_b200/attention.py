@@ -59,7 +59,8 @@ class AttentionPlan:
                                              ctypes.addressof(self._counts), _lib.stream()))
         self.counts = list(self._counts)
         self._ws = {}
-        self.tiles = None  # TilePlan of the tensor-core forward, built on first use
+        self.tiles = None    # TilePlan of the tensor-core forward, built on first use
+        self.tiles_t = None  # transposed TilePlan of the tensor-core dK/dV kernel
 
     @classmethod
     def from_batch(cls, batch, n_etypes=None):
@@ -84,26 +85,37 @@ class AttentionPlan:
             self.tiles = TilePlan(self)
         return self.tiles
 
+    def tile_plan_t(self):
+        """The transposed tile plan (rows = sources) of the tensor-core dK/dV kernel."""
+        if self.tiles_t is None:
+            self.tiles_t = TilePlan(self, transposed=True, min_density=0.15, simt_max_degree=0)
+        return self.tiles_t
+
     def _args(self):
         return (self.blob.data_ptr(), ctypes.addressof(self._counts), self.n_nodes, self.n_edges, self.n_etypes)
 
 
 class TilePlan:
-    """Groups of source columns shared by m-blocks of <= 16 destination rows, for
-    bpt_attn_forward_tc.  Planned on the host from the plan's in-CSR (integer work, once per
-    graph), kept on the device."""
+    """Groups of columns shared by m-blocks of <= 16 rows, for the tensor-core kernels.
+    Planned on the host from a CSR of the plan (integer work, once per graph), kept on the
+    device.  transposed=False: rows are destinations, columns sources, cells carry edge types
+    (bpt_attn_forward_tc).  transposed=True: rows are sources, columns destinations, cells
+    carry the edge's position in the in-CSR (bpt_attn_backward_dkv_tc)."""
 
-    def __init__(self, plan, min_density=0.25, max_cols=384, group_rows=16, col_block=64, simt_max_degree=0,
-                 max_mblocks=1, join_dense=False):
+    def __init__(self, plan, transposed=False, min_density=0.25, max_cols=384, group_rows=16, col_block=64,
+                 simt_max_degree=0, max_mblocks=1, join_dense=False):
         L = _lib.lib()
-        N, E, T = plan.n_nodes, plan.n_edges, plan.n_etypes
-        indptr = np.empty(N + 1, np.int32)
-        src = np.empty(max(E, 1), np.int32)
-        etype = np.empty(max(E, 1), np.int32)
+        E, T = plan.n_edges, plan.n_etypes
+        n_rows = plan.n_src if transposed else plan.n_nodes
+        indptr = np.empty(n_rows + 1, np.int32)
+        other = np.empty(max(E, 1), np.int32)
+        extra = np.empty(max(E, 1), np.int32)
+        export = L.bpt_export_out_csr if transposed else L.bpt_export_in_csr
         with torch.cuda.device(plan.device):
-            _lib.check(L.bpt_export_in_csr(plan.blob.data_ptr(), ctypes.addressof(plan._counts), N, E, T,
-                                           indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, _lib.stream()))
-        handle = L.bpt_tile_plan_create(indptr.ctypes.data, src.ctypes.data, etype.ctypes.data, N, E,
+            _lib.check(export(plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes, E, T,
+                              indptr.ctypes.data, other.ctypes.data, extra.ctypes.data, _lib.stream()))
+        etype_ptr, payload_ptr = (None, extra.ctypes.data) if transposed else (extra.ctypes.data, None)
+        handle = L.bpt_tile_plan_create(indptr.ctypes.data, other.ctypes.data, etype_ptr, payload_ptr, n_rows, E,
                                         float(min_density), int(max_cols), int(group_rows), int(col_block),
                                         int(simt_max_degree), int(max_mblocks), int(bool(join_dense)))
         if not handle:
@@ -114,32 +126,40 @@ class TilePlan:
             (self.n_groups, self.n_mblocks, n_cols, self.n_cells, self.n_split, self.n_slots, self.t_max,
              self.max_cols_pad, self.max_mblocks, self.max_qr_slots, self.n_row_items,
              self.n_dense_groups) = [int(x) for x in sizes]
-            max_et = int(etype[:E].max()) if E else 0
+            max_et = 0 if transposed or not E else int(extra[:E].max())
             self.et_bytes = 1 if max_et < 255 else 2
             groups = np.empty(max(self.n_groups * 8, 1), np.int32)
             mblocks = np.empty(max(self.n_mblocks * 56, 1), np.int32)
             cols = np.empty(max(n_cols, 1), np.int32)
             et = np.empty(max(self.n_cells, 1), np.uint8 if self.et_bytes == 1 else np.uint16)
+            cellpos = np.empty(max(self.n_cells, 1), np.int32) if transposed else None
             split = np.empty(max(self.n_split * 4, 1), np.int32)
             items = np.empty(max(self.n_row_items * 4, 1), np.int32)
             _lib.check(L.bpt_tile_plan_export(handle, groups.ctypes.data, mblocks.ctypes.data, cols.ctypes.data,
-                                              et.ctypes.data, self.et_bytes, split.ctypes.data, items.ctypes.data))
+                                              et.ctypes.data, self.et_bytes,
+                                              cellpos.ctypes.data if transposed else None, split.ctypes.data,
+                                              items.ctypes.data))
         finally:
             L.bpt_tile_plan_destroy(handle)
         dev = plan.device
         self.groups = torch.from_numpy(groups).to(dev)
         self.mblocks = torch.from_numpy(mblocks).to(dev)
         self.cols = torch.from_numpy(cols).to(dev)
-        self.et = torch.from_numpy(et.view(np.uint8)).to(dev)
+        self.et = None if transposed else torch.from_numpy(et.view(np.uint8)).to(dev)
+        self.cellpos = torch.from_numpy(cellpos).to(dev) if transposed else None
         self.split = torch.from_numpy(split).to(dev)
         self.items = torch.from_numpy(items).to(dev)
         self.n_etypes = T
+        self.transposed = transposed
         self._ws = {}
 
     def workspace(self, h, device):
         ws = self._ws.get(h)
         if ws is None:
-            ws = _lib.workspace(_lib.lib().bpt_attn_forward_tc_workspace_bytes(self.n_slots, h), device)
+            L = _lib.lib()
+            n = L.bpt_attn_backward_dkv_tc_workspace_bytes(self.n_slots, h) if self.transposed else \
+                L.bpt_attn_forward_tc_workspace_bytes(self.n_slots, h)
+            ws = _lib.workspace(n, device)
             self._ws[h] = ws
         return ws
 
@@ -221,22 +241,38 @@ def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=N
     return o, lse
 
 
-def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o):
-    """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d)."""
+def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, tensor_cores=None):
+    """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d).
+    bf16 with head dim 64 computes dK/dV on the tensor-core kernel unless tensor_cores=False."""
     d_o = d_o.contiguous()
     _lib.require_cuda(q, k, v, lse, d_o)
     N, h, d = q.shape
+    if tensor_cores is None:
+        tensor_cores = tensor_core_eligible(q, embed_ak)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dak = None
     if embed_ak is not None:
         dak = torch.zeros((embed_ak.size(0), d), dtype=torch.float32, device=q.device)
+    L = _lib.lib()
     with torch.cuda.device(q.device):
         ws = plan.workspace(h, d, True)
-        _lib.check(_lib.lib().bpt_attn_backward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                                _lib.ptr(embed_ak), float(scale), lse.data_ptr(),
-                                                d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                                _lib.ptr(dak), h, d, _lib.dtype_code(q.dtype), ws.data_ptr(),
-                                                ws.numel(), _lib.stream()))
+        _lib.check(L.bpt_attn_backward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                       _lib.ptr(embed_ak), float(scale), lse.data_ptr(), d_o.data_ptr(),
+                                       dq.data_ptr(), None if tensor_cores else dk.data_ptr(),
+                                       None if tensor_cores else dv.data_ptr(), _lib.ptr(dak), h, d,
+                                       _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
+        if tensor_cores:
+            tp = plan.tile_plan_t()
+            P, dP, delta = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+            _lib.check(L.bpt_attn_backward_scratch(ws.data_ptr(), ws.numel(), plan.n_nodes, plan.n_edges, h,
+                                                   ctypes.addressof(P), ctypes.addressof(dP),
+                                                   ctypes.addressof(delta)))
+            ws2 = tp.workspace(h, q.device)
+            _lib.check(L.bpt_attn_backward_dkv_tc(
+                tp.groups.data_ptr(), tp.n_groups, tp.mblocks.data_ptr(), tp.cols.data_ptr(), tp.cellpos.data_ptr(),
+                tp.split.data_ptr(), tp.n_split, tp.n_slots, tp.max_cols_pad, P, dP, delta, q.data_ptr(),
+                d_o.data_ptr(), float(scale), dk.data_ptr(), dv.data_ptr(), h, d, _lib.dtype_code(q.dtype),
+                ws2.data_ptr(), ws2.numel(), _lib.stream()))
     return dq, dk, dv, dak
 
 

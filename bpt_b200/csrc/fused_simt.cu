@@ -579,7 +579,7 @@ int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, cons
             BPT_LAUNCH_CHECK();
         }
     }
-    if (counts[3] > 0) {
+    if (counts[3] > 0 && dk != nullptr && dv != nullptr) {
         const dim3 grid((counts[3] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dkv_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
             p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dP, delta, scale, dk, dv, part_dkv, g)));
@@ -670,7 +670,8 @@ extern "C" int bpt_attn_backward(const void *plan, const int32_t *counts, int64_
                                  void *dk, void *dv, float *dak, int h, int d, int dtype, void *workspace,
                                  size_t workspace_bytes, bpt_stream_t stream) {
     if (int rc = check_attn_args("attn_backward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
-    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && lse && d_o && dq && dk && dv), "attn_backward: null tensor");
+    BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && lse && d_o && dq), "attn_backward: null tensor");
+    BPT_CHECK_ARG((dk == nullptr) == (dv == nullptr), "attn_backward: dk and dv must both be given or both be NULL");
     BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward: ak given without dak");
     const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts[kCountsNSrc], n_edges, n_etypes);
     switch (dtype) {
@@ -699,4 +700,18 @@ extern "C" int bpt_attn_forward_static(const void *plan, const int32_t *counts, 
     if (int rc = static_scratch_address(&scratch)) return rc;
     return bpt_attn_forward(plan, counts, n_nodes, n_edges, n_etypes, q, k, v, ak, scale, o, lse, h, d, dtype,
                             scratch, kStaticScratchBytes, stream);
+}
+
+// Where bpt_attn_backward leaves P, dP (fp32 (n_edges, h), in-CSR order) and delta (fp32
+// (n_nodes, h)) inside its workspace, for the tensor-core dK/dV kernel that runs after it.
+extern "C" int bpt_attn_backward_scratch(void *workspace, size_t workspace_bytes, int64_t n_nodes, int64_t n_edges,
+                                         int h, float **P, float **dP, float **delta) {
+    BPT_CHECK_ARG(workspace && P && dP && delta && n_nodes >= 0 && n_edges >= 0 && h >= 1,
+                  "attn_backward_scratch: bad argument");
+    Workspace ws(workspace, workspace_bytes);
+    *P = ws.take<float>(static_cast<size_t>(n_edges) * h);
+    *dP = ws.take<float>(static_cast<size_t>(n_edges) * h);
+    *delta = ws.take<float>(static_cast<size_t>(n_nodes) * h);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_scratch: workspace too small");
+    return BPT_OK;
 }

@@ -209,3 +209,22 @@ extern "C" int bpt_export_in_csr(const void *plan, const int32_t *counts_host, i
     BPT_CUDA(cudaStreamSynchronize(stream));
     return BPT_OK;
 }
+
+extern "C" int bpt_export_out_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                                  int n_etypes, int32_t *out_indptr_host, int32_t *out_dst_host,
+                                  int32_t *out_inpos_host, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(plan && counts_host && out_indptr_host, "export_out_csr: null argument");
+    BPT_CHECK_ARG(n_edges == 0 || (out_dst_host && out_inpos_host), "export_out_csr: null argument");
+    const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
+    cudaStream_t stream = as_stream(stream_);
+    BPT_CUDA(cudaMemcpyAsync(out_indptr_host, p.out_indptr, sizeof(int32_t) * static_cast<size_t>(p.n_src + 1),
+                             cudaMemcpyDeviceToHost, stream));
+    if (n_edges > 0) {
+        BPT_CUDA(cudaMemcpyAsync(out_dst_host, p.out_dst, sizeof(int32_t) * static_cast<size_t>(n_edges),
+                                 cudaMemcpyDeviceToHost, stream));
+        BPT_CUDA(cudaMemcpyAsync(out_inpos_host, p.out_inpos, sizeof(int32_t) * static_cast<size_t>(n_edges),
+                                 cudaMemcpyDeviceToHost, stream));
+    }
+    BPT_CUDA(cudaStreamSynchronize(stream));
+    return BPT_OK;
+}

@@ -30,12 +30,13 @@ namespace {
 struct HostTilePlan {
     std::vector<int32_t> groups, mblocks, cols, split, simt;
     std::vector<uint16_t> et;
+    std::vector<int32_t> cellpos;  // per cell, parallel to et: the edge's payload (CSR position), -1 = no edge
     int64_t n_slots = 0, t_max = 0, max_cols_pad = 0, max_mblocks = 0, max_qr_slots = 0, n_dense_groups = 0;
 };
 
 struct EdgeRec {
     int64_t key;  // (src << 8) | rank among parallel edges of the same (row, src)
-    int32_t row, etype;
+    int32_t row, etype, pos;
 };
 
 // An m-block before it is laid out: sorted rows and their edges (grouped by row, row order).
@@ -51,8 +52,9 @@ struct GroupBuild {
 };
 
 // One record per edge of `rows`, with the parallel-edge rank inside each row.
-bool collect_edges(const int32_t *indptr, const int32_t *src, const int32_t *etype, const int32_t *rows,
-                   int64_t n_rows, std::vector<EdgeRec> &out, std::vector<std::pair<int32_t, int32_t>> &tmp) {
+bool collect_edges(const int32_t *indptr, const int32_t *src, const int32_t *etype, const int32_t *payload,
+                   const int32_t *rows, int64_t n_rows, std::vector<EdgeRec> &out,
+                   std::vector<std::pair<int32_t, int32_t>> &tmp) {
     bool ok = true;
     for (int64_t i = 0; i < n_rows; ++i) {
         const int32_t r = rows[i];
@@ -67,6 +69,7 @@ bool collect_edges(const int32_t *indptr, const int32_t *src, const int32_t *ety
             rec.key = (static_cast<int64_t>(tmp[p].first) << 8) | (rank & 255);
             rec.row = r;
             rec.etype = etype ? etype[tmp[p].second] : 0;
+            rec.pos = payload ? payload[tmp[p].second] : tmp[p].second;
             out.push_back(rec);
         }
     }
@@ -115,6 +118,7 @@ void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr,
             m[kMbEtOff] = static_cast<int32_t>(plan.et.size());
             const size_t base = plan.et.size();
             plan.et.resize(base + static_cast<size_t>(n_chunks) * kTileRows * kTileChunk, kNoEdge);
+            plan.cellpos.resize(plan.et.size(), -1);
             uint32_t mask = 0;
             int max_et = -1;
             size_t p = 0;
@@ -124,8 +128,9 @@ void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr,
                     const EdgeRec &e = mb.edges[p];
                     const int c = static_cast<int>(std::lower_bound(gb.keys.begin(), gb.keys.end(), e.key) - gb.keys.begin());
                     const int chunk = c / kTileChunk;
-                    plan.et[base + (static_cast<size_t>(chunk) * kTileRows + r) * kTileChunk + (c % kTileChunk)] =
-                        static_cast<uint16_t>(e.etype);
+                    const size_t cell = base + (static_cast<size_t>(chunk) * kTileRows + r) * kTileChunk + (c % kTileChunk);
+                    plan.et[cell] = static_cast<uint16_t>(e.etype);
+                    plan.cellpos[cell] = e.pos;
                     mask |= 1u << chunk;
                     if (e.etype > max_et) max_et = e.etype;
                     ++cnt;
@@ -155,7 +160,7 @@ struct Leftover {
 using namespace bpt;
 
 extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
-                                      int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
+                                      const int32_t *in_payload, int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
                                       int group_rows, int col_block, int simt_max_degree, int max_mblocks,
                                       int join_dense) {
     if (!in_indptr || (n_edges > 0 && !in_src) || n_nodes < 0 || n_edges < 0 || max_cols < kTileChunk ||
@@ -199,7 +204,7 @@ extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *i
         edges.clear();
         bool accept = ne == 0;
         if (!accept && ne <= static_cast<int64_t>(nr) * max_cols) {
-            if (!collect_edges(in_indptr, in_src, in_etype, rows.data(), nr, edges, tmp)) {
+            if (!collect_edges(in_indptr, in_src, in_etype, in_payload, rows.data(), nr, edges, tmp)) {
                 fail(BPT_ERR_UNSUPPORTED, "%s", too_many);
                 delete plan;
                 return nullptr;
@@ -239,7 +244,7 @@ extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *i
     {
         std::vector<Leftover> left;
         edges.clear();
-        if (!collect_edges(in_indptr, in_src, in_etype, leftover_rows.data(),
+        if (!collect_edges(in_indptr, in_src, in_etype, in_payload, leftover_rows.data(),
                            static_cast<int64_t>(leftover_rows.size()), edges, tmp)) {
             fail(BPT_ERR_UNSUPPORTED, "%s", too_many);
             delete plan;
@@ -338,7 +343,7 @@ extern "C" int bpt_tile_plan_sizes(const void *handle, int64_t *sizes) {
 
 // et_bytes = 1 stores edge types as uint8 (0xFF = no edge; needs every type < 255), 2 as uint16.
 extern "C" int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols, void *et,
-                                    int et_bytes, int32_t *split_rows, int32_t *row_items) {
+                                    int et_bytes, int32_t *cell_pos, int32_t *split_rows, int32_t *row_items) {
     BPT_CHECK_ARG(handle, "tile_plan_export: null handle");
     BPT_CHECK_ARG(et_bytes == 1 || et_bytes == 2, "tile_plan_export: et_bytes must be 1 or 2");
     const HostTilePlan *p = static_cast<const HostTilePlan *>(handle);
@@ -357,6 +362,7 @@ extern "C" int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t
             }
         }
     }
+    if (cell_pos && !p->cellpos.empty()) std::memcpy(cell_pos, p->cellpos.data(), p->cellpos.size() * sizeof(int32_t));
     if (split_rows && !p->split.empty()) std::memcpy(split_rows, p->split.data(), p->split.size() * sizeof(int32_t));
     if (row_items && !p->simt.empty()) std::memcpy(row_items, p->simt.data(), p->simt.size() * sizeof(int32_t));
     return BPT_OK;

@@ -227,7 +227,8 @@ int bpt_attn_forward(const void *plan, const int32_t *counts_host, int64_t n_nod
                      const void *ak, double scale, void *o, float *lse, int h, int d, int dtype,
                      void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
-/* lse: the forward's output; d_o: gradient of o.  dq: (n_nodes, h, d), dk, dv: (n_src, h, d);
+/* lse: the forward's output; d_o: gradient of o.  dq: (n_nodes, h, d), dk, dv: (n_src, h, d),
+ * or both NULL to skip them (bpt_attn_backward_dkv_tc then computes them from the scratch);
  * dak: fp32 (n_etypes, d), required when ak is given.  The forward's o is not needed: the
  * row term <dO, O> of the softmax gradient is recomputed in fp32 from the probabilities. */
 int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
@@ -258,20 +259,29 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
  * items, dense groups}.  bpt_tile_plan_export copies groups (8 int32 each), mblocks (56 int32
  * each), cols (int32), et (uint8 if et_bytes == 1, which needs every type < 255, else
  * uint16), split_rows and row_items (4 int32 each) into host arrays of those sizes, to be
- * uploaded as they are.  bpt_export_in_csr copies the in-CSR of a bpt_attn_plan_build plan
- * to host arrays (waits for the stream).
+ * uploaded as they are; cell_pos (int32 per etype cell, may be NULL) is the cell's edge
+ * payload: in_payload[j] of CSR entry j, or j itself when in_payload is NULL, -1 without an
+ * edge.  The same planner serves the transposed problem (rows = sources): feed it the
+ * out-CSR with in_payload = each entry's position in the in-CSR.
+ * bpt_export_in_csr / bpt_export_out_csr copy the in-CSR (indptr, src, etype) / out-CSR (indptr
+ * over n_src rows, dst, position in the in-CSR) of a bpt_attn_plan_build plan to host arrays
+ * (they wait for the stream).
  * ---------------------------------------------------------------------------------- */
 void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
-                           int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
+                           const int32_t *in_payload, int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,
                            int group_rows, int col_block, int simt_max_degree, int max_mblocks,
                            int join_dense);
 int bpt_tile_plan_sizes(const void *handle, int64_t *sizes);
 int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols, void *et,
-                         int et_bytes, int32_t *split_rows, int32_t *row_items);
+                         int et_bytes, int32_t *cell_pos, int32_t *split_rows, int32_t *row_items);
 void bpt_tile_plan_destroy(void *handle);
 int bpt_export_in_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
                       int n_etypes, int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
                       bpt_stream_t stream);
+
+int bpt_export_out_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                       int n_etypes, int32_t *out_indptr_host, int32_t *out_dst_host,
+                       int32_t *out_inpos_host, bpt_stream_t stream);
 
 size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
 
@@ -289,6 +299,25 @@ int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, const int32_t *
                         const void *k, const void *v, const void *ak, double scale, void *o,
                         float *lse, int h, int d, int dtype, void *workspace,
                         size_t workspace_bytes, bpt_stream_t stream);
+
+/* Tensor-core dK / dV (bf16, head dim 64) from what bpt_attn_backward left in its workspace.
+ * Call bpt_attn_backward with dk = dv = NULL first, fetch the scratch pointers with
+ * bpt_attn_backward_scratch (same workspace, n_nodes, n_edges, h), then this.  The plan is a
+ * tile plan of the TRANSPOSED problem: bpt_tile_plan_create fed with the out-CSR
+ * (bpt_export_out_csr: indptr over n_src rows, dst as columns, in_etype = NULL, in_payload =
+ * positions in the in-CSR), exported with cell_pos.  q, d_o: (n_nodes, h, 64); dk, dv:
+ * (n_src, h, 64); all bf16, 16-byte aligned.  Rows keep one writer and a fixed summation
+ * order: bitwise reproducible.  No counterpart in the reference beyond the gradients of
+ * maskedmm_csr / vector_spmm (graph_kernel/graphop_kernel.cu:100-112, :151-163). */
+int bpt_attn_backward_scratch(void *workspace, size_t workspace_bytes, int64_t n_nodes, int64_t n_edges,
+                              int h, float **P, float **dP, float **delta);
+size_t bpt_attn_backward_dkv_tc_workspace_bytes(int64_t n_slots, int h);
+int bpt_attn_backward_dkv_tc(const int32_t *groups, int64_t n_groups, const int32_t *mblocks,
+                             const int32_t *cols, const int32_t *cell_pos, const int32_t *split_rows,
+                             int64_t n_split, int64_t n_slots, int max_cols_pad, const float *P,
+                             const float *dP, const float *delta, const void *q, const void *d_o,
+                             double scale, void *dk, void *dv, int h, int d, int dtype,
+                             void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)

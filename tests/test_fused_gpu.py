@@ -177,3 +177,23 @@ def test_tensor_core_forward_is_used_and_matches_cuda_core_forward(oracle_lib):
     o_cc, lse_cc = attention_forward(plan, q[:, :3].contiguous(), k[:, :3].contiguous(), v[:, :3].contiguous(), None,
                                      0.125, tensor_cores=False)
     assert rel_err(o_tc.float().cpu(), o_cc.float().cpu()) < 2e-2 and rel_err(lse_tc.cpu(), lse_cc.cpu()) < 2e-3
+
+
+def test_tensor_core_dkv_matches_cuda_core_backward(oracle_lib):
+    """dK/dV from the tensor-core kernel on the transposed tile plan against the CUDA-core
+    segment reduction (same bf16 inputs), with different source and destination sets too."""
+    from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
+    g = GRAPHS["bpt_batch"](oracle_lib)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = [t.cuda() for t in _inputs(N, 8, 64, T, torch.bfloat16, 11)]
+    plan = AttentionPlan(torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda(),
+                         torch.from_numpy(g["etype"]).cuda(), N, n_etypes=T)
+    o, lse = attention_forward(plan, q, k, v, ak, 0.125)
+    a = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o)
+    b = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o, tensor_cores=False)
+    assert plan.tiles_t is not None and plan.tiles_t.n_groups > 0
+    for x, y in zip(a, b):
+        assert rel_err(x.float().cpu(), y.float().cpu()) < 1e-2
+    a2 = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o)
+    for x, y in zip(a, a2):
+        assert torch.equal(x, y)

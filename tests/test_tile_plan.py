@@ -15,7 +15,7 @@ def _plan(oracle_lib, g, min_density=0.05, max_cols=384, group_rows=64, col_bloc
     indptr, src, eid = oracle_lib.coo_to_csr(g["dst"], g["src"], g["n_nodes"])
     et = g["etype"][eid]
     ip32, s32, e32 = indptr.astype(np.int32), src.astype(np.int32), et.astype(np.int32)
-    h = L.bpt_tile_plan_create(ip32.ctypes.data, s32.ctypes.data, e32.ctypes.data, g["n_nodes"], len(src),
+    h = L.bpt_tile_plan_create(ip32.ctypes.data, s32.ctypes.data, e32.ctypes.data, None, g["n_nodes"], len(src),
                                min_density, max_cols, group_rows, col_block, simt_max_degree, max_mblocks,
                                join_dense)
     assert h
@@ -27,13 +27,14 @@ def _plan(oracle_lib, g, min_density=0.05, max_cols=384, group_rows=64, col_bloc
     mblocks = np.empty(max(n_mb * 56, 1), np.int32)
     cols = np.empty(max(n_cols, 1), np.int32)
     etm = np.empty(max(n_cells, 1), np.uint8 if et_bytes == 1 else np.uint16)
+    cellpos = np.empty(max(n_cells, 1), np.int32)
     split = np.empty(max(n_split * 4, 1), np.int32)
     items = np.empty(max(n_items * 4, 1), np.int32)
     assert L.bpt_tile_plan_export(h, groups.ctypes.data, mblocks.ctypes.data, cols.ctypes.data, etm.ctypes.data,
-                                  et_bytes, split.ctypes.data, items.ctypes.data) == 0
+                                  et_bytes, cellpos.ctypes.data, split.ctypes.data, items.ctypes.data) == 0
     L.bpt_tile_plan_destroy(h)
     return dict(groups=groups[:n_groups * 8].reshape(n_groups, 8), mblocks=mblocks[:n_mb * 56].reshape(n_mb, 56),
-                cols=cols, et=etm, split=split[:n_split * 4].reshape(n_split, 4),
+                cols=cols, et=etm, cellpos=cellpos, split=split[:n_split * 4].reshape(n_split, 4),
                 items=items[:n_items * 4].reshape(n_items, 4), n_slots=n_slots, t_max=t_max, mcp=mcp,
                 max_mb=max_mb, max_qr=max_qr, n_dense=n_dense, csr=(indptr, src, et))
 
@@ -69,6 +70,8 @@ def test_plan_covers_every_edge_once(oracle_lib, spec, kw):
         for m in p["mblocks"][mb_first:mb_first + mb_count]:
             rows, slot, row_et, eoff, mask, tq, qr = m[0:16], m[16:32], m[32:48], m[48], m[49], m[50], m[51]
             cells = p["et"][eoff:eoff + 16 * ncp].reshape(ncp // 64, 16, 64)
+            cpos = p["cellpos"][eoff:eoff + 16 * ncp].reshape(ncp // 64, 16, 64)
+            assert np.array_equal(cpos >= 0, cells != none)
             valid = rows[rows >= 0]
             assert np.all(np.diff(valid) > 0)
             if qr >= 0:
@@ -87,6 +90,9 @@ def test_plan_covers_every_edge_once(oracle_lib, spec, kw):
                 cs = np.nonzero(row_cells != none)[0]
                 assert np.all(cs < ncols)
                 got += [(int(rows[i]), int(cols[c]), int(row_cells[c])) for c in cs]
+                row_pos = cpos[:, i, :].reshape(-1)[cs]
+                assert np.all((row_pos >= indptr[rows[i]]) & (row_pos < indptr[rows[i] + 1]))
+                assert np.array_equal(src[row_pos], cols[cs]) and np.array_equal(et[row_pos], row_cells[cs])
                 if qr < 0 and len(cs):
                     assert np.all(row_cells[cs] == row_et[i])
                 if slot[i] < 0:

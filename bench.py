@@ -212,7 +212,7 @@ def run_seqshard(a):
         else:
             k_g, v_g = s.pad_rows(k), s.pad_rows(v)
         o, lse = attention_forward(plan, q, k_g, v_g, ak, scale)
-        dq, dk_g, dv_g, dak = attention_backward(plan, q, k_g, v_g, ak, scale, lse, d_o)
+        dq, dk_g, dv_g, dak = attention_backward(plan, q, k_g, v_g, ak, scale, lse, d_o, o=o)
         if world > 1:
             return sh.reduce_scatter_rows(s, dk_g), sh.reduce_scatter_rows(s, dv_g)
         return dk_g, dv_g
@@ -359,7 +359,7 @@ def run_ours(a):
 
     def step():
         o, lse = attention_forward(plan, q, k, v, ak, scale)
-        return o, attention_backward(plan, q, k, v, ak, scale, lse, d_o)
+        return o, attention_backward(plan, q, k, v, ak, scale, lse, d_o, o=o)
 
     def barrier():
         if world > 1:
@@ -381,7 +381,7 @@ def run_ours(a):
         ev[i][0].record()
         o, lse = attention_forward(plan, q, k, v, ak, scale)
         ev[i][1].record()
-        attention_backward(plan, q, k, v, ak, scale, lse, d_o)
+        attention_backward(plan, q, k, v, ak, scale, lse, d_o, o=o)
         ev[i][2].record()
     stop.record()
     barrier()
@@ -424,7 +424,7 @@ def run_ours(a):
                 s_main.wait_event(ev_out[b])         # the previous results of this set have left the device
                 q_, k_, v_, do_ = dev_in[b]
                 o, lse = attention_forward(plan, q_, k_, v_, ak, scale)
-                grads = attention_backward(plan, q_, k_, v_, ak, scale, lse, do_)
+                grads = attention_backward(plan, q_, k_, v_, ak, scale, lse, do_, o=o)
                 results[b] = (o, grads[0], grads[1], grads[2])
                 ev_done[b].record(s_main)
                 with torch.cuda.stream(s_out):

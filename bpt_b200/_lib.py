@@ -66,9 +66,21 @@ SIGNATURES = {
     "bpt_attn_backward_dkv_tc_workspace_bytes": (_sz, [_i64, _int]),
     "bpt_attn_backward_dkv_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp,
                                         _dbl, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+    "bpt_attn_backward_tc_workspace_bytes": (_sz, [_vp, _vp, _vp, _i64, _i64, _int]),
+    "bpt_attn_backward_tc": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp,
+                                    _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "bpt_attn_forward_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                        _int, _int, _int, _vp]),
 }
+
+class TilePlanStruct(ctypes.Structure):
+    """bpt_tile_plan_t of include/bpt_b200.h."""
+    _fields_ = [("groups", _vp), ("mblocks", _vp), ("cols", _vp), ("et", _vp), ("cell_pos", _vp),
+                ("split_rows", _vp), ("row_items", _vp),
+                ("n_groups", _i64), ("n_split", _i64), ("n_slots", _i64), ("n_row_items", _i64),
+                ("et_bytes", ctypes.c_int32), ("max_cols_pad", ctypes.c_int32), ("t_max", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
 
 _lib = None
 

@@ -132,12 +132,12 @@ class TilePlan:
             mblocks = np.empty(max(self.n_mblocks * 56, 1), np.int32)
             cols = np.empty(max(n_cols, 1), np.int32)
             et = np.empty(max(self.n_cells, 1), np.uint8 if self.et_bytes == 1 else np.uint16)
-            cellpos = np.empty(max(self.n_cells, 1), np.int32) if transposed else None
+            cellpos = np.empty(max(self.n_cells, 1), np.int32)
             split = np.empty(max(self.n_split * 4, 1), np.int32)
             items = np.empty(max(self.n_row_items * 4, 1), np.int32)
             _lib.check(L.bpt_tile_plan_export(handle, groups.ctypes.data, mblocks.ctypes.data, cols.ctypes.data,
                                               et.ctypes.data, self.et_bytes,
-                                              cellpos.ctypes.data if transposed else None, split.ctypes.data,
+                                              cellpos.ctypes.data, split.ctypes.data,
                                               items.ctypes.data))
         finally:
             L.bpt_tile_plan_destroy(handle)
@@ -146,12 +146,23 @@ class TilePlan:
         self.mblocks = torch.from_numpy(mblocks).to(dev)
         self.cols = torch.from_numpy(cols).to(dev)
         self.et = None if transposed else torch.from_numpy(et.view(np.uint8)).to(dev)
-        self.cellpos = torch.from_numpy(cellpos).to(dev) if transposed else None
+        self.cellpos = torch.from_numpy(cellpos).to(dev)
         self.split = torch.from_numpy(split).to(dev)
         self.items = torch.from_numpy(items).to(dev)
         self.n_etypes = T
         self.transposed = transposed
         self._ws = {}
+
+    def struct(self):
+        """The bpt_tile_plan_t view of the device arrays."""
+        s = _lib.TilePlanStruct()
+        s.groups, s.mblocks, s.cols = self.groups.data_ptr(), self.mblocks.data_ptr(), self.cols.data_ptr()
+        s.et = None if self.et is None else self.et.data_ptr()
+        s.cell_pos = self.cellpos.data_ptr()
+        s.split_rows, s.row_items = self.split.data_ptr(), self.items.data_ptr()
+        s.n_groups, s.n_split, s.n_slots, s.n_row_items = self.n_groups, self.n_split, self.n_slots, self.n_row_items
+        s.et_bytes, s.max_cols_pad, s.t_max = self.et_bytes, self.max_cols_pad, self.t_max
+        return s
 
     def workspace(self, h, device):
         ws = self._ws.get(h)
@@ -241,38 +252,43 @@ def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=N
     return o, lse
 
 
-def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, tensor_cores=None):
+def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_cores=None):
     """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d).
-    bf16 with head dim 64 computes dK/dV on the tensor-core kernel unless tensor_cores=False."""
+    bf16 with head dim 64 runs on the tensor-core kernels when the forward's output `o` is given
+    (they take delta = <dO, O> from it) unless tensor_cores=False."""
     d_o = d_o.contiguous()
     _lib.require_cuda(q, k, v, lse, d_o)
     N, h, d = q.shape
     if tensor_cores is None:
-        tensor_cores = tensor_core_eligible(q, embed_ak)
+        tensor_cores = o is not None and tensor_core_eligible(q, embed_ak)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dak = None
     if embed_ak is not None:
         dak = torch.zeros((embed_ak.size(0), d), dtype=torch.float32, device=q.device)
     L = _lib.lib()
     with torch.cuda.device(q.device):
-        ws = plan.workspace(h, d, True)
-        _lib.check(L.bpt_attn_backward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                       _lib.ptr(embed_ak), float(scale), lse.data_ptr(), d_o.data_ptr(),
-                                       dq.data_ptr(), None if tensor_cores else dk.data_ptr(),
-                                       None if tensor_cores else dv.data_ptr(), _lib.ptr(dak), h, d,
-                                       _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
         if tensor_cores:
-            tp = plan.tile_plan_t()
-            P, dP, delta = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
-            _lib.check(L.bpt_attn_backward_scratch(ws.data_ptr(), ws.numel(), plan.n_nodes, plan.n_edges, h,
-                                                   ctypes.addressof(P), ctypes.addressof(dP),
-                                                   ctypes.addressof(delta)))
-            ws2 = tp.workspace(h, q.device)
-            _lib.check(L.bpt_attn_backward_dkv_tc(
-                tp.groups.data_ptr(), tp.n_groups, tp.mblocks.data_ptr(), tp.cols.data_ptr(), tp.cellpos.data_ptr(),
-                tp.split.data_ptr(), tp.n_split, tp.n_slots, tp.max_cols_pad, P, dP, delta, q.data_ptr(),
-                d_o.data_ptr(), float(scale), dk.data_ptr(), dv.data_ptr(), h, d, _lib.dtype_code(q.dtype),
-                ws2.data_ptr(), ws2.numel(), _lib.stream()))
+            if o is None:
+                raise RuntimeError("bpt_attention: the tensor-core backward needs the forward's output o")
+            _lib.require_cuda(o)
+            dst_tiles, src_tiles = plan.tile_plan().struct(), plan.tile_plan_t().struct()
+            ws = plan._ws.get(("tc_bwd", h))
+            if ws is None:
+                ws = _lib.workspace(L.bpt_attn_backward_tc_workspace_bytes(
+                    ctypes.addressof(dst_tiles), ctypes.addressof(src_tiles), ctypes.addressof(plan._counts),
+                    plan.n_nodes, plan.n_edges, h), q.device)
+                plan._ws[("tc_bwd", h)] = ws
+            _lib.check(L.bpt_attn_backward_tc(
+                ctypes.addressof(dst_tiles), ctypes.addressof(src_tiles), *plan._args(), q.data_ptr(), k.data_ptr(),
+                v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), d_o.data_ptr(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(dak), h, d, _lib.dtype_code(q.dtype),
+                ws.data_ptr(), ws.numel(), _lib.stream()))
+        else:
+            ws = plan.workspace(h, d, True)
+            _lib.check(L.bpt_attn_backward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                           _lib.ptr(embed_ak), float(scale), lse.data_ptr(), d_o.data_ptr(),
+                                           dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(dak), h, d,
+                                           _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
     return dq, dk, dv, dak
 
 
@@ -285,14 +301,14 @@ class _BPTAttention(torch.autograd.Function):
         o, lse = attention_forward(plan, q, k, v, embed_ak, scale)
         ctx.plan, ctx.scale = plan, scale
         ctx.has_ak = embed_ak is not None
-        ctx.save_for_backward(q, k, v, embed_ak if ctx.has_ak else q.new_empty(0), lse)
+        ctx.save_for_backward(q, k, v, embed_ak if ctx.has_ak else q.new_empty(0), lse, o)
         return o
 
     @staticmethod
     def backward(ctx, d_o):
-        q, k, v, ak, lse = ctx.saved_tensors
+        q, k, v, ak, lse, o = ctx.saved_tensors
         ak = ak if ctx.has_ak else None
-        dq, dk, dv, dak = attention_backward(ctx.plan, q, k, v, ak, ctx.scale, lse, d_o)
+        dq, dk, dv, dak = attention_backward(ctx.plan, q, k, v, ak, ctx.scale, lse, d_o, o=o)
         return None, dq, dk, dv, (dak.to(ak.dtype) if dak is not None else None), None
 
 

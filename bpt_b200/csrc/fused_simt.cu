@@ -421,6 +421,48 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
     }
 }
 
+// dQ += scale * sum_e p_e (dp_e - delta) * ak[etype_e]: the relative-position part of dQ, for the
+// tensor-core backward, whose destination-side kernel only does the K part.  One warp per
+// destination row (whole row, fixed edge order); rows whose edges share one type are skipped:
+// their sum of dS is zero.
+template <typename T, int LPH, bool kVec>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
+                           const int32_t *__restrict__ row_uniform, int n_rows, const T *__restrict__ ak,
+                           const float *__restrict__ P, const float *__restrict__ dP,
+                           const float *__restrict__ delta, float scale, T *__restrict__ dq, Geometry g) {
+    constexpr int HPW = 32 / LPH;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarpsPerBlock + warp;
+    if (row >= n_rows || row_uniform[row]) return;
+    const int hl = lane / LPH, gl = lane % LPH;
+    const int head = blockIdx.y * HPW + hl;
+    const int d0 = gl * 16;
+    int nvalid = g.D - d0;
+    nvalid = nvalid > 16 ? 16 : nvalid;
+    if (!(head < g.H && nvalid > 0)) return;
+    const int H = g.H, D = g.D;
+    const float dl = delta[static_cast<int64_t>(row) * H + head];
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    const int beg = in_indptr[row], end = in_indptr[row + 1];
+#pragma unroll 4
+    for (int j = beg; j < end; ++j) {
+        const float ds = scale * P[static_cast<int64_t>(j) * H + head] * (dP[static_cast<int64_t>(j) * H + head] - dl);
+        float af[16];
+        load16<T, kVec>(ak + static_cast<int64_t>(in_etype[j]) * D + d0, nvalid, af);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = fmaf(ds, af[i], acc[i]);
+    }
+    T *out = dq + (static_cast<int64_t>(row) * H + head) * D + d0;
+    float cur[16];
+    load16<T, kVec>(out, nvalid, cur);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] += cur[i];
+    store16<T>(out, nvalid, acc);
+}
+
 // out[row, c] = sum over the row's slots, in slot order, of part[slot * stride + c], for
 // `n_out` output arrays laid side by side in a slot (dK|dV share a slot).
 template <typename T>
@@ -622,6 +664,39 @@ int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_
     BPT_DISPATCH_LPH_VEC(lph, vec, (attn_forward_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
         items, n_items, in_src, in_etype, q, k, v, ak, scale, o, lse, nullptr, nullptr, g)));
     BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+// The pieces of the CUDA-core backward that the tensor-core backward keeps (bf16): the
+// relative-position part of dQ and the gradient of the type table, both from P, dP, delta.
+int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, const void *q_, const void *ak_,
+                                  const float *P, const float *dP, const float *delta, float scale, void *dq_,
+                                  float *dak, float *part_dak, int H, int D, cudaStream_t stream) {
+    using T = __nv_bfloat16;
+    const T *q = static_cast<const T *>(q_), *ak = static_cast<const T *>(ak_);
+    T *dq = static_cast<T *>(dq_);
+    if (ak == nullptr) return BPT_OK;
+    const int lph = pick_lph(D);
+    const bool vec = can_vectorise<T>(D, lph, q, ak, dq, dq, dq, dq);
+    const Geometry g{H, D};
+    const int hpw = 32 / lph;
+    if (p.n_nodes > 0) {
+        const dim3 grid(static_cast<unsigned>((p.n_nodes + kWarpsPerBlock - 1) / kWarpsPerBlock), (H + hpw - 1) / hpw);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_ak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.in_indptr, p.in_etype, p.row_uniform, static_cast<int>(p.n_nodes), ak, P, dP, delta, scale, dq, g)));
+        BPT_LAUNCH_CHECK();
+    }
+    if (dak != nullptr && counts[6] > 0) {
+        const dim3 grid((counts[6] + kWarpsPerBlock - 1) / kWarpsPerBlock, 1);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, P, dP, delta, scale, dak, part_dak, g)));
+        BPT_LAUNCH_CHECK();
+        if (counts[8] > 0) {
+            sum_merge_kernel<float><<<counts[8], 128, 0, stream>>>(p.et_work.split_rows, counts[8], part_dak, D, 1,
+                                                                  dak, dak);
+            BPT_LAUNCH_CHECK();
+        }
+    }
     return BPT_OK;
 }
 

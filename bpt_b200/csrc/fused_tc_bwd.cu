@@ -1,5 +1,8 @@
-// dK and dV of the fused attention backward on tensor cores (bf16, head dim 64).
+// Fused attention backward on tensor cores (bf16, head dim 64): the destination-side kernel
+// (P, dP, delta, K part of dQ) on the forward's tile plan and the source-side kernel (dK, dV) on
+// the transposed tile plan.
 //
+// ---- dK and dV ----
 // Works on the transposed tile plan: an m-block is <=16 SOURCE rows, its columns are the
 // destinations that attend to them, and every cell knows its edge's position in the in-CSR.
 // The destination-side pass (bpt_attn_backward) has already left P, dP = <dO[dst], v[src]> and
@@ -11,6 +14,7 @@
 // one m-block is written once; rows spread over several m-blocks write fp32 partials that are
 // summed in slot order.  No atomics: results are bitwise reproducible.
 #include "fused_common.cuh"
+#include "plan.cuh"
 #include "tile_plan.cuh"
 
 namespace bpt {
@@ -184,14 +188,314 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
     }
 }
 
+// ---- destination side ----
+// One block per m-block of the forward's tile plan, one warp per head.  With lse from the forward
+// and delta = <dO, O> per row, every cell's gradient is local:
+//     p = exp2(s - lse),  dp = <dO[row], v[col]>,  dS = scale * p * (dp - delta).
+// Per 64 columns the warp stages their K rows once in swizzled shared memory (cp.async); per 32
+// columns it computes dP = dO V^T (V rows gathered straight into B fragments, head dimension
+// permuted like dO's), S = Q K^T (ldmatrix B fragments), looks the relative-position term and
+// the edge mask up in the same fp16 table as the forward, scatters p and dp to the per-edge
+// scratch (in-CSR order, for the source-side kernel and the gradient of the type table) and
+// accumulates dQ += dS K (ldmatrix.trans B fragments).  The relative-position part of dQ is
+// added afterwards by a CUDA-core kernel.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+
+// Standard mma A-fragment words of one 64-element row for lane column t: w[2s] = elements
+// (16s + 2t, +1), w[2s+1] = (16s + 8 + 2t, +1).  Also the B-fragment words of a row used as a column.
+__device__ __forceinline__ void load_a_row(const __nv_bfloat16 *__restrict__ row, int t, uint32_t (&w)[8]) {
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(row);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        w[2 * s] = __ldg(p + 8 * s + t);
+        w[2 * s + 1] = __ldg(p + 8 * s + 4 + t);
+    }
+}
+// Permuted share of a row for products whose two operands are both read this way: the 16-byte
+// pieces at elements [8t, 8t+8) and [32+8t, 32+8t+8).
+__device__ __forceinline__ void load_row_frag(const __nv_bfloat16 *__restrict__ row, int t, uint32_t (&w)[8]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(row + 8 * t));
+    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(row + 32 + 8 * t));
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+
+template <typename ET> struct EtTraits;
+template <> struct EtTraits<uint8_t> { static constexpr uint32_t kNone = kNoEdge8; };
+template <> struct EtTraits<uint16_t> { static constexpr uint32_t kNone = kNoEdge; };
+
+constexpr int kIdxPad = 8;
+constexpr int kKStageBytes = kTileChunk * kRowBytes;  // 8 KB: K rows of 64 columns
+
+struct DqParams {
+    const int32_t *groups, *mblocks, *cols, *cellpos;
+    const void *et;
+    const __nv_bfloat16 *q, *k, *v, *ak, *o, *d_o;
+    const float *lse;
+    float *P, *dP, *delta, *part_dq;
+    __nv_bfloat16 *dq;
+    int n_etypes, H, max_cols_pad, t_max;
+    float scale;
+};
+
+template <typename ET, bool kHasBias>
+__global__ void __launch_bounds__(kWarps * 32, 2)
+attn_backward_dq_tile_kernel(const DqParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    // layout: K stages (one per warp, 8 KB) | column ids | table indices of the m-block | tables (fp16, per warp)
+    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKStageBytes);
+    uint16_t *s_idx = reinterpret_cast<uint16_t *>(s_cols + p.max_cols_pad);
+    const int idx_stride = p.max_cols_pad + kIdxPad;
+    __half *s_tab_all = reinterpret_cast<__half *>(s_idx + kTileRows * idx_stride);
+    const int tab_stride = p.t_max + 8;
+
+    const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
+    const int ncols_pad = grp[kGroupNcolsPad];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int H = p.H;
+    const uint32_t s_k = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kKStageBytes));
+    __half *s_tab = s_tab_all + static_cast<int64_t>(warp) * kTileRows * tab_stride;
+    const float sl2 = p.scale * kLog2e;
+    const ET *et_base = static_cast<const ET *>(p.et);
+    {
+        const int32_t *gc = p.cols + grp[kGroupColOff];
+        for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
+    }
+    for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
+        const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
+        const bool use_qr = kHasBias && mb[kMbQrSlot] >= 0;
+        const int tq = use_qr ? mb[kMbTq] : 0;
+        const uint32_t none_idx = use_qr ? tq : 1;
+        const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
+        const int32_t *cell_pos = p.cellpos + mb[kMbEtOff];
+        __syncthreads();
+        {
+            constexpr int kCellsPerPiece = 16 / static_cast<int>(sizeof(ET));
+            const uint4 *ge = reinterpret_cast<const uint4 *>(et_base + mb[kMbEtOff]);
+            const int pieces = kTileRows * ncols_pad / kCellsPerPiece;
+            for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+                const int cell = i * kCellsPerPiece;
+                const int chunk = cell / (kTileRows * kTileChunk), rem = cell % (kTileRows * kTileChunk);
+                const int r = rem / kTileChunk, c = rem % kTileChunk;
+                const uint4 raw = __ldg(ge + i);
+                const ET *e = reinterpret_cast<const ET *>(&raw);
+                uint16_t *dst = s_idx + r * idx_stride + chunk * kTileChunk + c;
+#pragma unroll
+                for (int u = 0; u < kCellsPerPiece; ++u)
+                    dst[u] = static_cast<uint16_t>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
+            }
+        }
+        __syncthreads();
+
+        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
+        for (int h = warp; h < H; h += kWarps) {
+            const int64_t off_lo = (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim;
+            const int64_t off_hi = (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim;
+            uint32_t q_lo[8], q_hi[8], do_lo[8], do_hi[8];
+            load_a_row(p.q + off_lo, t, q_lo);
+            load_a_row(p.q + off_hi, t, q_hi);
+            load_row_frag(p.d_o + off_lo, t, do_lo);
+            load_row_frag(p.d_o + off_hi, t, do_hi);
+            // delta = <dO, O> of the two rows
+            float delta_lo, delta_hi;
+            {
+                uint32_t o_lo[8], o_hi[8];
+                load_row_frag(p.o + off_lo, t, o_lo);
+                load_row_frag(p.o + off_hi, t, o_hi);
+                float a = 0.f, b = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&do_lo[i]));
+                    const float2 y0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&o_lo[i]));
+                    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&do_hi[i]));
+                    const float2 y1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&o_hi[i]));
+                    a = fmaf(x0.x, y0.x, fmaf(x0.y, y0.y, a));
+                    b = fmaf(x1.x, y1.x, fmaf(x1.y, y1.y, b));
+                }
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                b += __shfl_xor_sync(0xffffffffu, b, 1);
+                b += __shfl_xor_sync(0xffffffffu, b, 2);
+                delta_lo = a;
+                delta_hi = b;
+            }
+            float lse2_lo = row_lo < 0 ? 0.f : p.lse[static_cast<int64_t>(row_lo) * H + h];
+            float lse2_hi = row_hi < 0 ? 0.f : p.lse[static_cast<int64_t>(row_hi) * H + h];
+            lse2_lo = lse2_lo == -INFINITY ? 0.f : lse2_lo * kLog2e;
+            lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
+            if (use_qr) {
+                for (int nt = 0; nt < tq; nt += 8) {
+                    int type = nt + g;
+                    type = type < p.n_etypes ? type : p.n_etypes - 1;
+                    uint32_t b[8];
+                    load_a_row(p.ak + static_cast<int64_t>(type) * kHeadDim, t, b);
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int s = 0; s < 4; ++s)
+                        mma_bf16(c, q_lo[2 * s], q_hi[2 * s], q_lo[2 * s + 1], q_hi[2 * s + 1], b[2 * s], b[2 * s + 1]);
+                    *reinterpret_cast<__half2 *>(s_tab + g * tab_stride + nt + 2 * t) = __floats2half2_rn(c[0] * sl2, c[1] * sl2);
+                    *reinterpret_cast<__half2 *>(s_tab + (g + 8) * tab_stride + nt + 2 * t) = __floats2half2_rn(c[2] * sl2, c[3] * sl2);
+                }
+                if (t == 0) {
+                    s_tab[g * tab_stride + tq] = __float2half_rn(-INFINITY);
+                    s_tab[(g + 8) * tab_stride + tq] = __float2half_rn(-INFINITY);
+                }
+            } else {
+                if (t == 0) {
+                    *reinterpret_cast<__half2 *>(s_tab + g * tab_stride) = __floats2half2_rn(0.f, -INFINITY);
+                    *reinterpret_cast<__half2 *>(s_tab + (g + 8) * tab_stride) = __floats2half2_rn(0.f, -INFINITY);
+                }
+                if (kHasBias) {
+                    // single-type rows: the forward folded scale * <q, ak[type]> into lse; take it out again
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        int type = mb[kMbRowEtOff + g + 8 * half];
+                        type = type < 0 ? 0 : (type < p.n_etypes ? type : p.n_etypes - 1);
+                        uint32_t a[8];
+                        load_a_row(p.ak + static_cast<int64_t>(type) * kHeadDim, t, a);
+                        float sum = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(half ? &q_hi[i] : &q_lo[i]));
+                            const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&a[i]));
+                            sum = fmaf(x.x, y.x, fmaf(x.y, y.y, sum));
+                        }
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                        (half ? lse2_hi : lse2_lo) -= sum * sl2;
+                    }
+                }
+            }
+            __syncwarp();
+
+            float acc[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { acc[i][0] = 0.f; acc[i][1] = 0.f; acc[i][2] = 0.f; acc[i][3] = 0.f; }
+
+            for (int c0 = 0; c0 < ncols_pad; c0 += kTileChunk) {
+                if (!((chunk_mask >> (c0 / kTileChunk)) & 1u)) continue;
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                    const int id = i * 32 + lane;
+                    const int r = id >> 3, piece = id & 7;
+                    cp_async16(s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4),
+                               p.k + (static_cast<int64_t>(s_cols[c0 + r]) * H + h) * kHeadDim + piece * 8);
+                }
+                cp_async_commit();
+                const int32_t *chunk_pos = cell_pos + static_cast<int64_t>(c0 / kTileChunk) * kTileRows * kTileChunk;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int cb = c0 + half * kHalf;
+                    // dP = dO V^T for 4 column groups of 8 (V rows straight from global memory)
+                    float dp[4][4];
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        uint32_t b[8];
+                        load_row_frag(p.v + (static_cast<int64_t>(s_cols[cb + nt * 8 + g]) * H + h) * kHeadDim, t, b);
+                        dp[nt][0] = 0.f; dp[nt][1] = 0.f; dp[nt][2] = 0.f; dp[nt][3] = 0.f;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+                            mma_bf16(dp[nt], do_lo[2 * ks], do_hi[2 * ks], do_lo[2 * ks + 1], do_hi[2 * ks + 1], b[2 * ks],
+                                     b[2 * ks + 1]);
+                    }
+                    if (half == 0) {
+                        cp_async_wait_all();
+                        __syncwarp();
+                    }
+                    // S = Q K^T from the staged K rows
+                    float s[4][4];
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        s[nt][0] = 0.f; s[nt][1] = 0.f; s[nt][2] = 0.f; s[nt][3] = 0.f;
+                        const int r = half * kHalf + nt * 8 + (lane & 7);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            uint32_t b[4];
+                            const int piece = 4 * j + (lane >> 3);
+                            ldmatrix_x4(b, s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4));
+                            mma_bf16(s[nt], q_lo[4 * j], q_hi[4 * j], q_lo[4 * j + 1], q_hi[4 * j + 1], b[0], b[1]);
+                            mma_bf16(s[nt], q_lo[4 * j + 2], q_hi[4 * j + 2], q_lo[4 * j + 3], q_hi[4 * j + 3], b[2], b[3]);
+                        }
+                    }
+                    // probabilities, per-edge scratch, dS (kept in s)
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        const int c = cb + nt * 8 + 2 * t;
+                        const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c);
+                        const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c);
+                        const int2 pos_lo = __ldg(reinterpret_cast<const int2 *>(chunk_pos + g * kTileChunk + (c - c0)));
+                        const int2 pos_hi = __ldg(reinterpret_cast<const int2 *>(chunk_pos + (g + 8) * kTileChunk + (c - c0)));
+                        const float tab[4] = {__half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]),
+                                              __half2float(s_tab[g * tab_stride + (i_lo >> 16)]),
+                                              __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]),
+                                              __half2float(s_tab[(g + 8) * tab_stride + (i_hi >> 16)])};
+                        const int pos[4] = {pos_lo.x, pos_lo.y, pos_hi.x, pos_hi.y};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
+                            if (pos[i] >= 0) {
+                                p.P[static_cast<int64_t>(pos[i]) * H + h] = pr;
+                                p.dP[static_cast<int64_t>(pos[i]) * H + h] = dp[nt][i];
+                            }
+                            s[nt][i] = p.scale * pr * (dp[nt][i] - (i < 2 ? delta_lo : delta_hi));
+                        }
+                    }
+                    // dQ += dS K
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks) {
+                        const uint32_t a0 = pack_bf16(s[2 * ks][0], s[2 * ks][1]), a1 = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+                        const uint32_t a2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+                        const uint32_t a3 = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+                        const int r = half * kHalf + ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+                        for (int dn = 0; dn < 8; dn += 2) {
+                            const int piece = dn + (lane >> 4);
+                            uint32_t b[4];
+                            ldmatrix_x4_trans(b, s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4));
+                            mma_bf16(acc[dn], a0, a1, a2, a3, b[0], b[1]);
+                            mma_bf16(acc[dn + 1], a0, a1, a2, a3, b[2], b[3]);
+                        }
+                    }
+                }
+                __syncwarp();  // the K stage is rewritten by the next step
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = half ? row_hi : row_lo;
+                if (row < 0) continue;
+                const int slot = mb[kMbSlotOff + g + 8 * half];
+                if (t == 0) p.delta[static_cast<int64_t>(row) * H + h] = half ? delta_hi : delta_lo;
+                if (slot < 0) {
+                    __nv_bfloat16 *dst = p.dq + (static_cast<int64_t>(row) * H + h) * kHeadDim + 2 * t;
+#pragma unroll
+                    for (int dn = 0; dn < 8; ++dn)
+                        *reinterpret_cast<uint32_t *>(dst + dn * 8) = pack_bf16(acc[dn][2 * half], acc[dn][2 * half + 1]);
+                } else {
+                    float *dst = p.part_dq + (static_cast<int64_t>(slot) * H + h) * kHeadDim + 2 * t;
+#pragma unroll
+                    for (int dn = 0; dn < 8; ++dn)
+                        *reinterpret_cast<float2 *>(dst + dn * 8) = make_float2(acc[dn][2 * half], acc[dn][2 * half + 1]);
+                }
+            }
+            __syncwarp();  // the table is rewritten for the next head
+        }
+    }
+}
+
 // out0[row] | out1[row] = sum over the row's slots, in slot order, of the slot's two halves.
+// (out1 == nullptr: a slot holds one array of `width` values.)
 __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_split, const float *__restrict__ part,
                                      int width, __nv_bfloat16 *__restrict__ out0, __nv_bfloat16 *__restrict__ out1) {
     const int sr = blockIdx.x;
     if (sr >= n_split) return;
     const int4 rec = split_rows[sr];
     const int row = rec.x, first = rec.y, count = rec.z;
-    const int stride = 2 * width;
+    const int stride = out1 ? 2 * width : width;
     for (int c = threadIdx.x; c < stride; c += blockDim.x) {
         const float *src = part + static_cast<int64_t>(first) * stride + c;
         float acc = 0.f;
@@ -219,45 +523,161 @@ extern "C" size_t bpt_attn_backward_dkv_tc_workspace_bytes(int64_t n_slots, int 
     return align_up(static_cast<size_t>(n_slots) * 2 * h * kHeadDim * 4, 256) + 256;
 }
 
+namespace {
+
+int check_tile_plan(const char *name, const bpt_tile_plan_t *tp, bool need_et, bool need_pos) {
+    BPT_CHECK_ARG(tp != nullptr, "%s: null tile plan", name);
+    BPT_CHECK_ARG(tp->n_groups >= 0 && tp->n_split >= 0 && tp->n_slots >= 0 && tp->n_groups < (int64_t(1) << 31),
+                  "%s: bad tile plan sizes", name);
+    BPT_CHECK_ARG(tp->n_groups == 0 || (tp->groups && tp->mblocks), "%s: null tile plan arrays", name);
+    BPT_CHECK_ARG(tp->max_cols_pad % kTileChunk == 0 && tp->max_cols_pad <= kMaxChunks * kTileChunk && tp->t_max % 8 == 0,
+                  "%s: bad tile plan sizes", name);
+    BPT_CHECK_ARG(tp->max_cols_pad == 0 || tp->cols, "%s: null tile plan arrays", name);
+    if (need_et) BPT_CHECK_ARG(tp->max_cols_pad == 0 || (tp->et && (tp->et_bytes == 1 || tp->et_bytes == 2)), "%s: tile plan without edge types", name);
+    if (need_pos) BPT_CHECK_ARG(tp->max_cols_pad == 0 || tp->cell_pos, "%s: tile plan without cell positions", name);
+    BPT_CHECK_ARG(tp->n_split == 0 || tp->split_rows, "%s: null split rows", name);
+    return BPT_OK;
+}
+
+int run_dkv(const bpt_tile_plan_t *tp, const float *P, const float *dP, const float *delta, const void *q,
+            const void *d_o, float scale, void *dk, void *dv, int h, float *part, cudaStream_t stream) {
+    if (tp->n_groups == 0) return BPT_OK;
+    DkvParams p;
+    p.groups = tp->groups; p.mblocks = tp->mblocks; p.cols = tp->cols; p.cellpos = tp->cell_pos;
+    p.P = P; p.dP = dP; p.delta = delta;
+    p.q = static_cast<const __nv_bfloat16 *>(q); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
+    p.dk = static_cast<__nv_bfloat16 *>(dk); p.dv = static_cast<__nv_bfloat16 *>(dv);
+    p.part = part; p.H = h; p.max_cols_pad = tp->max_cols_pad; p.scale = scale;
+    const size_t smem = static_cast<size_t>(kWarps) * 2 * kStageBytes + static_cast<size_t>(tp->max_cols_pad) * 4 +
+                        static_cast<size_t>(kTileRows) * (tp->max_cols_pad + kPosPad) * 4;
+    if (smem > 227 * 1024)
+        return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: transposed tile plan needs %zu bytes of shared memory", smem);
+    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dkv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+    attn_backward_dkv_tile_kernel<<<static_cast<unsigned>(tp->n_groups), kWarps * 32, smem, stream>>>(p);
+    BPT_LAUNCH_CHECK();
+    if (tp->n_split > 0) {
+        dkv_sum_merge_kernel<<<static_cast<unsigned>(tp->n_split), 256, 0, stream>>>(
+            reinterpret_cast<const int4 *>(tp->split_rows), static_cast<int>(tp->n_split), part, h * kHeadDim, p.dk, p.dv);
+        BPT_LAUNCH_CHECK();
+    }
+    return BPT_OK;
+}
+
+template <typename ET, bool kHasBias>
+int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
+    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dq_tile_kernel<ET, kHasBias>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attn_backward_dq_tile_kernel<ET, kHasBias><<<static_cast<unsigned>(n_groups), kWarps * 32, smem, stream>>>(p);
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+}  // namespace
+
 extern "C" int bpt_attn_backward_dkv_tc(const int32_t *groups, int64_t n_groups, const int32_t *mblocks,
                                         const int32_t *cols, const int32_t *cell_pos, const int32_t *split_rows,
                                         int64_t n_split, int64_t n_slots, int max_cols_pad, const float *P,
                                         const float *dP, const float *delta, const void *q, const void *d_o,
                                         double scale, void *dk, void *dv, int h, int d, int dtype,
                                         void *workspace, size_t workspace_bytes, bpt_stream_t stream_) {
-    BPT_CHECK_ARG(n_groups >= 0 && n_split >= 0 && n_slots >= 0 && h >= 1, "attn_backward_dkv_tc: bad sizes");
     if (d != kHeadDim || dtype != BPT_BF16)
         return fail(BPT_ERR_UNSUPPORTED, "attn_backward_dkv_tc: only bf16 with head dim 64 (got dtype %d, d %d)", dtype, d);
+    bpt_tile_plan_t tp = {};
+    tp.groups = groups; tp.mblocks = mblocks; tp.cols = cols; tp.cell_pos = cell_pos; tp.split_rows = split_rows;
+    tp.n_groups = n_groups; tp.n_split = n_split; tp.n_slots = n_slots; tp.max_cols_pad = max_cols_pad;
+    if (int rc = check_tile_plan("attn_backward_dkv_tc", &tp, false, true)) return rc;
     if (n_groups == 0) return BPT_OK;
-    BPT_CHECK_ARG(groups && mblocks && P && dP && delta && q && d_o && dk && dv, "attn_backward_dkv_tc: null argument");
-    BPT_CHECK_ARG(max_cols_pad == 0 || (cols && cell_pos), "attn_backward_dkv_tc: null plan arrays");
-    BPT_CHECK_ARG(max_cols_pad % kTileChunk == 0 && max_cols_pad <= kMaxChunks * kTileChunk,
-                  "attn_backward_dkv_tc: bad plan sizes");
-    BPT_CHECK_ARG(n_groups < (int64_t(1) << 31), "attn_backward_dkv_tc: too many groups");
+    BPT_CHECK_ARG(h >= 1 && P && dP && delta && q && d_o && dk && dv, "attn_backward_dkv_tc: null argument");
     BPT_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(d_o) | reinterpret_cast<uintptr_t>(dk) |
                     reinterpret_cast<uintptr_t>(dv)) & 15) == 0, "attn_backward_dkv_tc: tensors must be 16-byte aligned");
-    cudaStream_t stream = as_stream(stream_);
     Workspace ws(workspace, workspace_bytes);
     float *part = ws.take<float>(static_cast<size_t>(n_slots) * 2 * h * kHeadDim);
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_dkv_tc: workspace of %zu bytes is too small", workspace_bytes);
-    DkvParams p;
-    p.groups = groups; p.mblocks = mblocks; p.cols = cols; p.cellpos = cell_pos;
-    p.P = P; p.dP = dP; p.delta = delta;
-    p.q = static_cast<const __nv_bfloat16 *>(q); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
-    p.dk = static_cast<__nv_bfloat16 *>(dk); p.dv = static_cast<__nv_bfloat16 *>(dv);
-    p.part = part; p.H = h; p.max_cols_pad = max_cols_pad; p.scale = static_cast<float>(scale);
-    const size_t smem = static_cast<size_t>(kWarps) * 2 * kStageBytes + static_cast<size_t>(max_cols_pad) * 4 +
-                        static_cast<size_t>(kTileRows) * (max_cols_pad + kPosPad) * 4;
-    if (smem > 227 * 1024)
-        return fail(BPT_ERR_UNSUPPORTED, "attn_backward_dkv_tc: tile plan needs %zu bytes of shared memory", smem);
-    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dkv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(smem)));
-    attn_backward_dkv_tile_kernel<<<static_cast<unsigned>(n_groups), kWarps * 32, smem, stream>>>(p);
-    BPT_LAUNCH_CHECK();
-    if (n_split > 0) {
-        dkv_sum_merge_kernel<<<static_cast<unsigned>(n_split), 256, 0, stream>>>(
-            reinterpret_cast<const int4 *>(split_rows), static_cast<int>(n_split), part, h * kHeadDim, p.dk, p.dv);
-        BPT_LAUNCH_CHECK();
+    return run_dkv(&tp, P, dP, delta, q, d_o, static_cast<float>(scale), dk, dv, h, part, as_stream(stream_));
+}
+
+extern "C" size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
+                                                       const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                                                       int h) {
+    if (!dst_tiles || !src_tiles || !counts_host || n_nodes < 0 || n_edges < 0 || h < 1) return 0;
+    const size_t e = static_cast<size_t>(n_edges);
+    return 2 * align_up(e * h * 4, 256) + align_up(static_cast<size_t>(n_nodes) * h * 4, 256) +
+           align_up(static_cast<size_t>(dst_tiles->n_slots) * h * kHeadDim * 4, 256) +
+           align_up(static_cast<size_t>(src_tiles->n_slots) * 2 * h * kHeadDim * 4, 256) +
+           align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) + 2048;
+}
+
+extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
+                                    const void *attn_plan, const int32_t *counts_host, int64_t n_nodes,
+                                    int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
+                                    const void *ak, double scale, const void *o, const float *lse, const void *d_o,
+                                    void *dq, void *dk, void *dv, float *dak, int h, int d, int dtype,
+                                    void *workspace, size_t workspace_bytes, bpt_stream_t stream_) {
+    if (d != kHeadDim || dtype != BPT_BF16)
+        return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: only bf16 with head dim 64 (got dtype %d, d %d)", dtype, d);
+    if (int rc = check_tile_plan("attn_backward_tc", dst_tiles, true, true)) return rc;
+    if (int rc = check_tile_plan("attn_backward_tc", src_tiles, false, true)) return rc;
+    BPT_CHECK_ARG(attn_plan && counts_host && n_nodes >= 0 && n_edges >= 0 && n_etypes >= 1 && h >= 1,
+                  "attn_backward_tc: bad plan arguments");
+    BPT_CHECK_ARG(dst_tiles->n_row_items == 0, "attn_backward_tc: the tile plan must not hold CUDA-core row items");
+    if (n_nodes == 0) return BPT_OK;
+    BPT_CHECK_ARG(q && k && v && o && lse && d_o && dq && dk && dv, "attn_backward_tc: null tensor");
+    BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward_tc: ak given without dak");
+    BPT_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                    reinterpret_cast<uintptr_t>(ak) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o) |
+                    reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15) == 0,
+                  "attn_backward_tc: tensors must be 16-byte aligned");
+    cudaStream_t stream = as_stream(stream_);
+    const PlanView pv = plan_view(const_cast<void *>(attn_plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
+    Workspace ws(workspace, workspace_bytes);
+    const size_t e = static_cast<size_t>(n_edges);
+    float *P = ws.take<float>(e * h);
+    float *dP = ws.take<float>(e * h);
+    float *delta = ws.take<float>(static_cast<size_t>(n_nodes) * h);
+    float *part_dq = ws.take<float>(static_cast<size_t>(dst_tiles->n_slots) * h * kHeadDim);
+    float *part_dkv = ws.take<float>(static_cast<size_t>(src_tiles->n_slots) * 2 * h * kHeadDim);
+    float *part_dak = ws.take<float>(static_cast<size_t>(counts_host[7]) * kHeadDim);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_tc: workspace of %zu bytes is too small", workspace_bytes);
+    const float sc = static_cast<float>(scale);
+
+    // 1. destination side: P, dP, delta, K part of dQ
+    if (dst_tiles->n_groups > 0) {
+        const bool bias = ak != nullptr;
+        DqParams p;
+        p.groups = dst_tiles->groups; p.mblocks = dst_tiles->mblocks; p.cols = dst_tiles->cols;
+        p.cellpos = dst_tiles->cell_pos; p.et = dst_tiles->et;
+        p.q = static_cast<const __nv_bfloat16 *>(q); p.k = static_cast<const __nv_bfloat16 *>(k);
+        p.v = static_cast<const __nv_bfloat16 *>(v); p.ak = static_cast<const __nv_bfloat16 *>(ak);
+        p.o = static_cast<const __nv_bfloat16 *>(o); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
+        p.lse = lse; p.P = P; p.dP = dP; p.delta = delta; p.part_dq = part_dq;
+        p.dq = static_cast<__nv_bfloat16 *>(dq);
+        p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = dst_tiles->max_cols_pad;
+        p.t_max = bias ? dst_tiles->t_max : 0;
+        p.scale = sc;
+        const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes + static_cast<size_t>(p.max_cols_pad) * 4 +
+                            static_cast<size_t>(kTileRows) * (p.max_cols_pad + kIdxPad) * 2 +
+                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2;
+        if (smem > 227 * 1024)
+            return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: tile plan needs %zu bytes of shared memory", smem);
+        int rc;
+        if (dst_tiles->et_bytes == 1)
+            rc = bias ? launch_dq_kernel<uint8_t, true>(p, dst_tiles->n_groups, smem, stream)
+                      : launch_dq_kernel<uint8_t, false>(p, dst_tiles->n_groups, smem, stream);
+        else
+            rc = bias ? launch_dq_kernel<uint16_t, true>(p, dst_tiles->n_groups, smem, stream)
+                      : launch_dq_kernel<uint16_t, false>(p, dst_tiles->n_groups, smem, stream);
+        if (rc) return rc;
+        if (dst_tiles->n_split > 0) {
+            dkv_sum_merge_kernel<<<static_cast<unsigned>(dst_tiles->n_split), 256, 0, stream>>>(
+                reinterpret_cast<const int4 *>(dst_tiles->split_rows), static_cast<int>(dst_tiles->n_split), part_dq,
+                h * kHeadDim, static_cast<__nv_bfloat16 *>(dq), nullptr);
+            BPT_LAUNCH_CHECK();
+        }
     }
-    return BPT_OK;
+    // 2. relative-position part of dQ and the gradient of the type table (CUDA cores)
+    if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, P, dP, delta, sc, dq, dak, part_dak, h, d, stream))
+        return rc;
+    // 3. source side: dK, dV
+    return run_dkv(src_tiles, P, dP, delta, q, d_o, sc, dk, dv, h, part_dkv, stream);
 }

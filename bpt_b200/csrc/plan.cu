@@ -26,9 +26,25 @@ __global__ void gather_kernel(const int32_t *__restrict__ idx, const int32_t *__
     if (p < n) out[p] = table[idx[p]];
 }
 
-__global__ void zero_keys_kernel(int64_t n, int32_t *__restrict__ out) {
-    const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    if (p < n) out[p] = 0;
+// row_uniform[r] = 1 when the row's incoming edges all have one type (or it has none).
+__global__ void row_uniform_kernel(const int32_t *__restrict__ indptr, const int32_t *__restrict__ in_etype,
+                                   int64_t n_rows, int32_t *__restrict__ row_uniform) {
+    const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (r >= n_rows) return;
+    const int beg = indptr[r], end = indptr[r + 1];
+    int uniform = 1;
+    for (int j = beg + 1; j < end; ++j)
+        if (in_etype[j] != in_etype[beg]) { uniform = 0; break; }
+    row_uniform[r] = uniform;
+}
+
+// Bucket key of every edge (edge-id order): its type, or n_etypes when its destination row is uniform.
+__global__ void bucket_keys_kernel(const int32_t *__restrict__ etype, const int32_t *__restrict__ dst,
+                                   const int32_t *__restrict__ row_uniform, int64_t n_edges, int n_etypes,
+                                   int32_t *__restrict__ keys) {
+    const int64_t e = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (e >= n_edges) return;
+    keys[e] = row_uniform[dst[e]] ? n_etypes : (etype ? etype[e] : 0);
 }
 
 // Per row: how many items, slots and split-row records it contributes.
@@ -116,7 +132,7 @@ extern "C" size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_src, int64_t n_
 
 extern "C" size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes) {
     if (n_nodes < 0 || n_src < 0 || n_edges < 0 || n_etypes < 1) return 0;
-    int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    int64_t rows = n_nodes > n_etypes + 1 ? n_nodes : n_etypes + 1;
     rows = rows > n_src ? rows : n_src;
     const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
     return 3 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 3 * work_ws_bytes(rows) + 1024;
@@ -138,8 +154,8 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
     int32_t *tmp_eid = ws.take<int32_t>(e);
     int32_t *inpos_of_eid = ws.take<int32_t>(e);
-    int32_t *zero_keys = ws.take<int32_t>(e);
-    int64_t rows = n_nodes > n_etypes ? n_nodes : n_etypes;
+    int32_t *bucket_keys = ws.take<int32_t>(e);
+    int64_t rows = n_nodes > n_etypes + 1 ? n_nodes : n_etypes + 1;
     rows = rows > n_src ? rows : n_src;
     const size_t csr_ws_bytes = bpt_coo_to_csr_workspace_bytes(n_edges, rows);
     char *csr_ws = ws.take<char>(csr_ws_bytes);
@@ -162,14 +178,17 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
         gather_kernel<<<eb, 256, 0, stream>>>(tmp_eid, inpos_of_eid, n_edges, p.out_inpos);
         BPT_LAUNCH_CHECK();
     }
-    // buckets by edge type
-    const int32_t *keys = etype;
-    if (etype == nullptr && n_edges > 0) {
-        zero_keys_kernel<<<eb, 256, 0, stream>>>(n_edges, zero_keys);
+    // buckets by edge type; edges into uniform rows (zero gradient of the type table) go last
+    if (n_nodes > 0) {
+        row_uniform_kernel<<<static_cast<unsigned>((n_nodes + 255) / 256), 256, 0, stream>>>(
+            p.in_indptr, p.in_etype, n_nodes, p.row_uniform);
         BPT_LAUNCH_CHECK();
-        keys = zero_keys;
     }
-    if (int rc = bpt_coo_to_csr(keys, dst, n_edges, n_etypes, 4, p.et_indptr, p.et_dst, tmp_eid, csr_ws,
+    if (n_edges > 0) {
+        bucket_keys_kernel<<<eb, 256, 0, stream>>>(etype, dst, p.row_uniform, n_edges, n_etypes, bucket_keys);
+        BPT_LAUNCH_CHECK();
+    }
+    if (int rc = bpt_coo_to_csr(bucket_keys, dst, n_edges, n_etypes + 1, 4, p.et_indptr, p.et_dst, tmp_eid, csr_ws,
                                 csr_ws_bytes, stream_))
         return rc;
     if (n_edges > 0) {

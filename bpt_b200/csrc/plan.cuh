@@ -29,9 +29,13 @@ struct PlanView {
     int n_etypes;
     // in-CSR: rows are destinations; entries in ascending edge-id order
     int32_t *in_indptr, *in_src, *in_etype;
+    // 1 where all incoming edges of the row have one type (or there are none): the relative-position
+    // term is then a per-row constant, cancels in the softmax and has zero gradient
+    int32_t *row_uniform;
     // out-CSR: rows are sources; out_inpos = position of the same edge in the in-CSR
     int32_t *out_indptr, *out_dst, *out_inpos;
-    // edges bucketed by type: et_dst = destination, et_inpos = position in the in-CSR
+    // edges bucketed by type: et_dst = destination, et_inpos = position in the in-CSR; edges into
+    // uniform rows sit in an extra last bucket (n_etypes) that nothing reads
     int32_t *et_indptr, *et_dst, *et_inpos;
     WorkList in_work, out_work, et_work;
     size_t bytes;
@@ -62,10 +66,11 @@ inline PlanView plan_view(void *base, int64_t n_nodes, int64_t n_src, int64_t n_
     p.in_indptr = reinterpret_cast<int32_t *>(take(n1 * 4));
     p.in_src = reinterpret_cast<int32_t *>(take(e * 4));
     p.in_etype = reinterpret_cast<int32_t *>(take(e * 4));
+    p.row_uniform = reinterpret_cast<int32_t *>(take(n1 * 4));
     p.out_indptr = reinterpret_cast<int32_t *>(take(s1 * 4));
     p.out_dst = reinterpret_cast<int32_t *>(take(e * 4));
     p.out_inpos = reinterpret_cast<int32_t *>(take(e * 4));
-    p.et_indptr = reinterpret_cast<int32_t *>(take(static_cast<size_t>(n_etypes + 1) * 4));
+    p.et_indptr = reinterpret_cast<int32_t *>(take(static_cast<size_t>(n_etypes + 2) * 4));
     p.et_dst = reinterpret_cast<int32_t *>(take(e * 4));
     p.et_inpos = reinterpret_cast<int32_t *>(take(e * 4));
     auto work = [&](int64_t rows) {

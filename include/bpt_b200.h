@@ -283,6 +283,16 @@ int bpt_export_out_csr(const void *plan, const int32_t *counts_host, int64_t n_n
                        int n_etypes, int32_t *out_indptr_host, int32_t *out_dst_host,
                        int32_t *out_inpos_host, bpt_stream_t stream);
 
+/* Device copies of an exported tile plan and the matching bpt_tile_plan_sizes entries. */
+typedef struct {
+    const int32_t *groups, *mblocks, *cols;
+    const void *et;          /* edge types per cell, uint8 or uint16 (et_bytes); may be NULL for transposed plans */
+    const int32_t *cell_pos; /* edge payload per cell; may be NULL for the forward */
+    const int32_t *split_rows, *row_items;
+    int64_t n_groups, n_split, n_slots, n_row_items;
+    int32_t et_bytes, max_cols_pad, t_max, reserved;
+} bpt_tile_plan_t;
+
 size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
 
 /* groups, mblocks, cols, et, split_rows, row_items: device copies of the exported arrays;
@@ -318,6 +328,23 @@ int bpt_attn_backward_dkv_tc(const int32_t *groups, int64_t n_groups, const int3
                              const float *dP, const float *delta, const void *q, const void *d_o,
                              double scale, void *dk, void *dv, int h, int d, int dtype,
                              void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+
+/* The whole backward on the tensor-core path (bf16, head dim 64): dst_tiles = the forward's tile
+ * plan exported WITH cell_pos and without row items, src_tiles = the transposed tile plan
+ * (see bpt_attn_backward_dkv_tc), attn_plan / counts_host = the bpt_attn_plan_build plan of the
+ * same graph.  o and lse are the forward's outputs (delta = <dO, O> per row here).  Runs the
+ * destination-side tile kernel (per-edge P and dP into the workspace, K part of dQ), the
+ * CUDA-core kernels for the relative-position part of dQ and for d embed_ak, then the
+ * source-side tile kernel (dK, dV).  Single writer per output element, fixed summation orders. */
+size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
+                                            const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                                            int h);
+int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
+                         const void *attn_plan, const int32_t *counts_host, int64_t n_nodes,
+                         int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
+                         const void *ak, double scale, const void *o, const float *lse, const void *d_o,
+                         void *dq, void *dk, void *dv, float *dak, int h, int d, int dtype,
+                         void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)

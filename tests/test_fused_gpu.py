@@ -179,9 +179,9 @@ def test_tensor_core_forward_is_used_and_matches_cuda_core_forward(oracle_lib):
     assert rel_err(o_tc.float().cpu(), o_cc.float().cpu()) < 2e-2 and rel_err(lse_tc.cpu(), lse_cc.cpu()) < 2e-3
 
 
-def test_tensor_core_dkv_matches_cuda_core_backward(oracle_lib):
-    """dK/dV from the tensor-core kernel on the transposed tile plan against the CUDA-core
-    segment reduction (same bf16 inputs), with different source and destination sets too."""
+def test_tensor_core_backward_matches_cuda_core_backward(oracle_lib):
+    """The tensor-core backward (destination-side tiles, source-side transposed tiles) against
+    the CUDA-core segment reductions on the same bf16 inputs, and run to run."""
     from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
     g = GRAPHS["bpt_batch"](oracle_lib)
     N, T = g["n_nodes"], int(g["etype"].max()) + 1
@@ -189,11 +189,18 @@ def test_tensor_core_dkv_matches_cuda_core_backward(oracle_lib):
     plan = AttentionPlan(torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda(),
                          torch.from_numpy(g["etype"]).cuda(), N, n_etypes=T)
     o, lse = attention_forward(plan, q, k, v, ak, 0.125)
-    a = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o)
+    a = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o, o=o)
     b = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o, tensor_cores=False)
     assert plan.tiles_t is not None and plan.tiles_t.n_groups > 0
-    for x, y in zip(a, b):
-        assert rel_err(x.float().cpu(), y.float().cpu()) < 1e-2
-    a2 = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o)
+    for name, x, y in zip(("dq", "dk", "dv", "dak"), a, b):
+        assert rel_err(x.float().cpu(), y.float().cpu()) < 1e-2, name
+    a2 = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o, o=o)
     for x, y in zip(a, a2):
         assert torch.equal(x, y)
+    # no relative-position table, three heads
+    q3, k3, v3, d3 = [x[:, :3].contiguous() for x in (q, k, v, d_o)]
+    o3, lse3 = attention_forward(plan, q3, k3, v3, None, 0.125)
+    a = attention_backward(plan, q3, k3, v3, None, 0.125, lse3, d3, o=o3)
+    b = attention_backward(plan, q3, k3, v3, None, 0.125, lse3, d3, tensor_cores=False)
+    for x, y in zip(a[:3], b[:3]):
+        assert rel_err(x.float().cpu(), y.float().cpu()) < 1e-2

@@ -62,10 +62,6 @@ SIGNATURES = {
     "bpt_attn_forward_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp, _vp,
                                    _i64, _i64, _int, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _dbl, _vp,
                                    _vp, _int, _int, _int, _vp, _sz, _vp]),
-    "bpt_attn_backward_scratch": (_int, [_vp, _sz, _i64, _i64, _int, _vp, _vp, _vp]),
-    "bpt_attn_backward_dkv_tc_workspace_bytes": (_sz, [_i64, _int]),
-    "bpt_attn_backward_dkv_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp,
-                                        _dbl, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "bpt_attn_backward_tc_workspace_bytes": (_sz, [_vp, _vp, _vp, _i64, _i64, _int]),
     "bpt_attn_backward_tc": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp,
                                     _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),

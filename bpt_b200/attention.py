@@ -100,7 +100,7 @@ class TilePlan:
     Planned on the host from a CSR of the plan (integer work, once per graph), kept on the
     device.  transposed=False: rows are destinations, columns sources, cells carry edge types
     (bpt_attn_forward_tc).  transposed=True: rows are sources, columns destinations, cells
-    carry the edge's position in the in-CSR (bpt_attn_backward_dkv_tc)."""
+    carry the edge's position in the in-CSR (source side of bpt_attn_backward_tc)."""
 
     def __init__(self, plan, transposed=False, min_density=0.25, max_cols=384, group_rows=16, col_block=64,
                  simt_max_degree=0, max_mblocks=1, join_dense=False):
@@ -168,8 +168,7 @@ class TilePlan:
         ws = self._ws.get(h)
         if ws is None:
             L = _lib.lib()
-            n = L.bpt_attn_backward_dkv_tc_workspace_bytes(self.n_slots, h) if self.transposed else \
-                L.bpt_attn_forward_tc_workspace_bytes(self.n_slots, h)
+            n = L.bpt_attn_forward_tc_workspace_bytes(self.n_slots, h)
             ws = _lib.workspace(n, device)
             self._ws[h] = ws
         return ws

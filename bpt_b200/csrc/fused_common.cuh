@@ -116,9 +116,10 @@ int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_
 
 struct PlanView;
 // Defined in fused_simt.cu: dQ += relative-position part, and d embed_ak (with its split-row merge),
-// from per-edge P, dP (in-CSR order) and per-row delta; bf16 storage.  part_dak: counts[7] * D floats.
+// from the per-edge scratch PS (in-CSR order, one word {bf16 p, bf16 dS} per (edge, head)); bf16
+// storage.  part_dak: counts[7] * D floats.
 int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, const void *q, const void *ak,
-                                  const float *P, const float *dP, const float *delta, float scale, void *dq,
-                                  float *dak, float *part_dak, int H, int D, cudaStream_t stream);
+                                  const uint32_t *PS, void *dq, float *dak, float *part_dak, int H, int D,
+                                  cudaStream_t stream);
 
 }  // namespace bpt

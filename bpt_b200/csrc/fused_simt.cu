@@ -371,7 +371,8 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
 
 // ------------------------------------------------------------------ backward, pass over type buckets
 
-template <typename T, int LPH, bool kVec>
+// kPacked: the per-edge scratch is one 32-bit word {bf16 p, bf16 dS} per (edge, head), passed as P.
+template <typename T, int LPH, bool kVec, bool kPacked = false>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ et_dst,
                          const int32_t *__restrict__ et_inpos, const T *__restrict__ q,
@@ -399,8 +400,11 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
             for (int j = beg; j < end; ++j) {
                 const int dst = et_dst[j];
                 const int64_t pos = et_inpos[j];
-                const float ds = scale * P[pos * H + head] *
-                                 (dP[pos * H + head] - delta[static_cast<int64_t>(dst) * H + head]);
+                float ds;
+                if (kPacked)
+                    ds = __uint_as_float(reinterpret_cast<const uint32_t *>(P)[pos * H + head] & 0xffff0000u);
+                else
+                    ds = scale * P[pos * H + head] * (dP[pos * H + head] - delta[static_cast<int64_t>(dst) * H + head]);
                 float qf[16];
                 load16<T, kVec>(q + (static_cast<int64_t>(dst) * H + head) * D + d0, nvalid, qf);
 #pragma unroll
@@ -421,16 +425,15 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
     }
 }
 
-// dQ += scale * sum_e p_e (dp_e - delta) * ak[etype_e]: the relative-position part of dQ, for the
-// tensor-core backward, whose destination-side kernel only does the K part.  One warp per
+// dQ += sum_e dS_e * ak[etype_e]: the relative-position part of dQ, for the tensor-core backward,
+// whose destination-side kernel only does the K part and leaves {bf16 p, bf16 dS} per (edge, head).  One warp per
 // destination row (whole row, fixed edge order); rows whose edges share one type are skipped:
 // their sum of dS is zero.
 template <typename T, int LPH, bool kVec>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
                            const int32_t *__restrict__ row_uniform, int n_rows, const T *__restrict__ ak,
-                           const float *__restrict__ P, const float *__restrict__ dP,
-                           const float *__restrict__ delta, float scale, T *__restrict__ dq, Geometry g) {
+                           const uint32_t *__restrict__ PS, T *__restrict__ dq, Geometry g) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerBlock + warp;
@@ -442,14 +445,13 @@ attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t 
     nvalid = nvalid > 16 ? 16 : nvalid;
     if (!(head < g.H && nvalid > 0)) return;
     const int H = g.H, D = g.D;
-    const float dl = delta[static_cast<int64_t>(row) * H + head];
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
     const int beg = in_indptr[row], end = in_indptr[row + 1];
 #pragma unroll 4
     for (int j = beg; j < end; ++j) {
-        const float ds = scale * P[static_cast<int64_t>(j) * H + head] * (dP[static_cast<int64_t>(j) * H + head] - dl);
+        const float ds = __uint_as_float(PS[static_cast<int64_t>(j) * H + head] & 0xffff0000u);
         float af[16];
         load16<T, kVec>(ak + static_cast<int64_t>(in_etype[j]) * D + d0, nvalid, af);
 #pragma unroll
@@ -670,8 +672,8 @@ int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_
 // The pieces of the CUDA-core backward that the tensor-core backward keeps (bf16): the
 // relative-position part of dQ and the gradient of the type table, both from P, dP, delta.
 int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, const void *q_, const void *ak_,
-                                  const float *P, const float *dP, const float *delta, float scale, void *dq_,
-                                  float *dak, float *part_dak, int H, int D, cudaStream_t stream) {
+                                  const uint32_t *PS, void *dq_, float *dak, float *part_dak, int H, int D,
+                                  cudaStream_t stream) {
     using T = __nv_bfloat16;
     const T *q = static_cast<const T *>(q_), *ak = static_cast<const T *>(ak_);
     T *dq = static_cast<T *>(dq_);
@@ -683,13 +685,14 @@ int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, cons
     if (p.n_nodes > 0) {
         const dim3 grid(static_cast<unsigned>((p.n_nodes + kWarpsPerBlock - 1) / kWarpsPerBlock), (H + hpw - 1) / hpw);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_ak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.in_indptr, p.in_etype, p.row_uniform, static_cast<int>(p.n_nodes), ak, P, dP, delta, scale, dq, g)));
+            p.in_indptr, p.in_etype, p.row_uniform, static_cast<int>(p.n_nodes), ak, PS, dq, g)));
         BPT_LAUNCH_CHECK();
     }
     if (dak != nullptr && counts[6] > 0) {
         const dim3 grid((counts[6] + kWarpsPerBlock - 1) / kWarpsPerBlock, 1);
-        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, P, dP, delta, scale, dak, part_dak, g)));
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC, true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, reinterpret_cast<const float *>(PS), nullptr,
+            nullptr, 1.f, dak, part_dak, g)));
         BPT_LAUNCH_CHECK();
         if (counts[8] > 0) {
             sum_merge_kernel<float><<<counts[8], 128, 0, stream>>>(p.et_work.split_rows, counts[8], part_dak, D, 1,
@@ -775,18 +778,4 @@ extern "C" int bpt_attn_forward_static(const void *plan, const int32_t *counts, 
     if (int rc = static_scratch_address(&scratch)) return rc;
     return bpt_attn_forward(plan, counts, n_nodes, n_edges, n_etypes, q, k, v, ak, scale, o, lse, h, d, dtype,
                             scratch, kStaticScratchBytes, stream);
-}
-
-// Where bpt_attn_backward leaves P, dP (fp32 (n_edges, h), in-CSR order) and delta (fp32
-// (n_nodes, h)) inside its workspace, for the tensor-core dK/dV kernel that runs after it.
-extern "C" int bpt_attn_backward_scratch(void *workspace, size_t workspace_bytes, int64_t n_nodes, int64_t n_edges,
-                                         int h, float **P, float **dP, float **delta) {
-    BPT_CHECK_ARG(workspace && P && dP && delta && n_nodes >= 0 && n_edges >= 0 && h >= 1,
-                  "attn_backward_scratch: bad argument");
-    Workspace ws(workspace, workspace_bytes);
-    *P = ws.take<float>(static_cast<size_t>(n_edges) * h);
-    *dP = ws.take<float>(static_cast<size_t>(n_edges) * h);
-    *delta = ws.take<float>(static_cast<size_t>(n_nodes) * h);
-    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_scratch: workspace too small");
-    return BPT_OK;
 }

@@ -5,9 +5,9 @@
 // ---- dK and dV ----
 // Works on the transposed tile plan: an m-block is <=16 SOURCE rows, its columns are the
 // destinations that attend to them, and every cell knows its edge's position in the in-CSR.
-// The destination-side pass (bpt_attn_backward) has already left P, dP = <dO[dst], v[src]> and
-// delta per edge / destination in scratch, so a cell's weights are two gathers away:
-//     dV[src] = sum_dst P * dO[dst],   dK[src] = sum_dst scale * P * (dP - delta[dst]) * q[dst].
+// The destination-side kernel has already left one word {bf16 p, bf16 dS} per (edge, head) in
+// scratch, so a cell's two weights are one gather away:
+//     dV[src] = sum_dst p * dO[dst],   dK[src] = sum_dst dS * q[dst].
 // One block per m-block, one warp per head; per 32 destinations the warp stages their dO and Q
 // rows in swizzled shared memory (cp.async), packs the gathered weights into mma A fragments
 // and accumulates both products with ldmatrix.trans B fragments.  A source row wholly inside
@@ -51,12 +51,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct DkvParams {
     const int32_t *groups, *mblocks, *cols, *cellpos;
-    const float *P, *dP, *delta;
+    const uint32_t *PS;  // per (edge, head): {bf16 p (low half), bf16 dS (high half)}, in-CSR order
     const __nv_bfloat16 *q, *d_o;
     __nv_bfloat16 *dk, *dv;
     float *part;
     int H, max_cols_pad;
-    float scale;
 };
 
 __global__ void __launch_bounds__(kWarps * 32, 2)
@@ -114,37 +113,29 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
                     cp_async16(s_q + dst, p.q + off);
                 }
                 cp_async_commit();
-                // weights of this lane's 16 cells: rows g / g+8, destinations c0 + 8nt + 2t, +1
-                float wp[4][4], ws[4][4];
+                // weights of this lane's 16 cells: rows g / g+8, destinations c0 + 8nt + 2t, +1; each
+                // is one packed word {p, dS}; A fragments are pairs of low halves / high halves
+                uint32_t wp[4][2], ws[4][2];
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const int c = c0 + nt * 8 + 2 * t;
                     const int2 pos_lo = *reinterpret_cast<const int2 *>(s_pos + g * pos_stride + c);
                     const int2 pos_hi = *reinterpret_cast<const int2 *>(s_pos + (g + 8) * pos_stride + c);
-                    const int pos[4] = {pos_lo.x, pos_lo.y, pos_hi.x, pos_hi.y};
-                    const float d0 = p.delta[static_cast<int64_t>(s_cols[c]) * H + h];
-                    const float d1 = p.delta[static_cast<int64_t>(s_cols[c + 1]) * H + h];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float pr = 0.f, ds = 0.f;
-                        if (pos[i] >= 0) {
-                            pr = p.P[static_cast<int64_t>(pos[i]) * H + h];
-                            ds = p.scale * pr * (p.dP[static_cast<int64_t>(pos[i]) * H + h] - ((i & 1) ? d1 : d0));
-                        }
-                        wp[nt][i] = pr;
-                        ws[nt][i] = ds;
-                    }
+                    const uint32_t w0 = pos_lo.x >= 0 ? p.PS[static_cast<int64_t>(pos_lo.x) * H + h] : 0u;
+                    const uint32_t w1 = pos_lo.y >= 0 ? p.PS[static_cast<int64_t>(pos_lo.y) * H + h] : 0u;
+                    const uint32_t w2 = pos_hi.x >= 0 ? p.PS[static_cast<int64_t>(pos_hi.x) * H + h] : 0u;
+                    const uint32_t w3 = pos_hi.y >= 0 ? p.PS[static_cast<int64_t>(pos_hi.y) * H + h] : 0u;
+                    wp[nt][0] = __byte_perm(w0, w1, 0x5410);
+                    wp[nt][1] = __byte_perm(w2, w3, 0x5410);
+                    ws[nt][0] = __byte_perm(w0, w1, 0x7632);
+                    ws[nt][1] = __byte_perm(w2, w3, 0x7632);
                 }
                 cp_async_wait_all();
                 __syncwarp();
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks) {
-                    const uint32_t p0 = pack_bf16(wp[2 * ks][0], wp[2 * ks][1]), p1 = pack_bf16(wp[2 * ks][2], wp[2 * ks][3]);
-                    const uint32_t p2 = pack_bf16(wp[2 * ks + 1][0], wp[2 * ks + 1][1]);
-                    const uint32_t p3 = pack_bf16(wp[2 * ks + 1][2], wp[2 * ks + 1][3]);
-                    const uint32_t s0 = pack_bf16(ws[2 * ks][0], ws[2 * ks][1]), s1 = pack_bf16(ws[2 * ks][2], ws[2 * ks][3]);
-                    const uint32_t s2 = pack_bf16(ws[2 * ks + 1][0], ws[2 * ks + 1][1]);
-                    const uint32_t s3 = pack_bf16(ws[2 * ks + 1][2], ws[2 * ks + 1][3]);
+                    const uint32_t p0 = wp[2 * ks][0], p1 = wp[2 * ks][1], p2 = wp[2 * ks + 1][0], p3 = wp[2 * ks + 1][1];
+                    const uint32_t s0 = ws[2 * ks][0], s1 = ws[2 * ks][1], s2 = ws[2 * ks + 1][0], s3 = ws[2 * ks + 1][1];
                     const int r = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
                     for (int dn = 0; dn < 8; dn += 2) {
@@ -195,8 +186,8 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
 // Per 64 columns the warp stages their K rows once in swizzled shared memory (cp.async); per 32
 // columns it computes dP = dO V^T (V rows gathered straight into B fragments, head dimension
 // permuted like dO's), S = Q K^T (ldmatrix B fragments), looks the relative-position term and
-// the edge mask up in the same fp16 table as the forward, scatters p and dp to the per-edge
-// scratch (in-CSR order, for the source-side kernel and the gradient of the type table) and
+// the edge mask up in the same fp16 table as the forward, scatters {p, dS} as two bf16 to the
+// per-edge scratch (in-CSR order, for the source-side kernel and the gradient of the type table) and
 // accumulates dQ += dS K (ldmatrix.trans B fragments).  The relative-position part of dQ is
 // added afterwards by a CUDA-core kernel.
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
@@ -236,7 +227,8 @@ struct DqParams {
     const void *et;
     const __nv_bfloat16 *q, *k, *v, *ak, *o, *d_o;
     const float *lse;
-    float *P, *dP, *delta, *part_dq;
+    uint32_t *PS;
+    float *part_dq;
     __nv_bfloat16 *dq;
     int n_etypes, H, max_cols_pad, t_max;
     float scale;
@@ -438,11 +430,8 @@ attn_backward_dq_tile_kernel(const DqParams p) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
-                            if (pos[i] >= 0) {
-                                p.P[static_cast<int64_t>(pos[i]) * H + h] = pr;
-                                p.dP[static_cast<int64_t>(pos[i]) * H + h] = dp[nt][i];
-                            }
                             s[nt][i] = p.scale * pr * (dp[nt][i] - (i < 2 ? delta_lo : delta_hi));
+                            if (pos[i] >= 0) p.PS[static_cast<int64_t>(pos[i]) * H + h] = pack_bf16(pr, s[nt][i]);
                         }
                     }
                     // dQ += dS K
@@ -469,7 +458,6 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                 const int row = half ? row_hi : row_lo;
                 if (row < 0) continue;
                 const int slot = mb[kMbSlotOff + g + 8 * half];
-                if (t == 0) p.delta[static_cast<int64_t>(row) * H + h] = half ? delta_hi : delta_lo;
                 if (slot < 0) {
                     __nv_bfloat16 *dst = p.dq + (static_cast<int64_t>(row) * H + h) * kHeadDim + 2 * t;
 #pragma unroll
@@ -518,11 +506,6 @@ __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_
 
 using namespace bpt;
 
-extern "C" size_t bpt_attn_backward_dkv_tc_workspace_bytes(int64_t n_slots, int h) {
-    if (n_slots < 0 || h < 1) return 0;
-    return align_up(static_cast<size_t>(n_slots) * 2 * h * kHeadDim * 4, 256) + 256;
-}
-
 namespace {
 
 int check_tile_plan(const char *name, const bpt_tile_plan_t *tp, bool need_et, bool need_pos) {
@@ -539,15 +522,15 @@ int check_tile_plan(const char *name, const bpt_tile_plan_t *tp, bool need_et, b
     return BPT_OK;
 }
 
-int run_dkv(const bpt_tile_plan_t *tp, const float *P, const float *dP, const float *delta, const void *q,
-            const void *d_o, float scale, void *dk, void *dv, int h, float *part, cudaStream_t stream) {
+int run_dkv(const bpt_tile_plan_t *tp, const uint32_t *PS, const void *q, const void *d_o, void *dk, void *dv, int h,
+            float *part, cudaStream_t stream) {
     if (tp->n_groups == 0) return BPT_OK;
     DkvParams p;
     p.groups = tp->groups; p.mblocks = tp->mblocks; p.cols = tp->cols; p.cellpos = tp->cell_pos;
-    p.P = P; p.dP = dP; p.delta = delta;
+    p.PS = PS;
     p.q = static_cast<const __nv_bfloat16 *>(q); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
     p.dk = static_cast<__nv_bfloat16 *>(dk); p.dv = static_cast<__nv_bfloat16 *>(dv);
-    p.part = part; p.H = h; p.max_cols_pad = tp->max_cols_pad; p.scale = scale;
+    p.part = part; p.H = h; p.max_cols_pad = tp->max_cols_pad;
     const size_t smem = static_cast<size_t>(kWarps) * 2 * kStageBytes + static_cast<size_t>(tp->max_cols_pad) * 4 +
                         static_cast<size_t>(kTileRows) * (tp->max_cols_pad + kPosPad) * 4;
     if (smem > 227 * 1024)
@@ -575,34 +558,12 @@ int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStrea
 
 }  // namespace
 
-extern "C" int bpt_attn_backward_dkv_tc(const int32_t *groups, int64_t n_groups, const int32_t *mblocks,
-                                        const int32_t *cols, const int32_t *cell_pos, const int32_t *split_rows,
-                                        int64_t n_split, int64_t n_slots, int max_cols_pad, const float *P,
-                                        const float *dP, const float *delta, const void *q, const void *d_o,
-                                        double scale, void *dk, void *dv, int h, int d, int dtype,
-                                        void *workspace, size_t workspace_bytes, bpt_stream_t stream_) {
-    if (d != kHeadDim || dtype != BPT_BF16)
-        return fail(BPT_ERR_UNSUPPORTED, "attn_backward_dkv_tc: only bf16 with head dim 64 (got dtype %d, d %d)", dtype, d);
-    bpt_tile_plan_t tp = {};
-    tp.groups = groups; tp.mblocks = mblocks; tp.cols = cols; tp.cell_pos = cell_pos; tp.split_rows = split_rows;
-    tp.n_groups = n_groups; tp.n_split = n_split; tp.n_slots = n_slots; tp.max_cols_pad = max_cols_pad;
-    if (int rc = check_tile_plan("attn_backward_dkv_tc", &tp, false, true)) return rc;
-    if (n_groups == 0) return BPT_OK;
-    BPT_CHECK_ARG(h >= 1 && P && dP && delta && q && d_o && dk && dv, "attn_backward_dkv_tc: null argument");
-    BPT_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(d_o) | reinterpret_cast<uintptr_t>(dk) |
-                    reinterpret_cast<uintptr_t>(dv)) & 15) == 0, "attn_backward_dkv_tc: tensors must be 16-byte aligned");
-    Workspace ws(workspace, workspace_bytes);
-    float *part = ws.take<float>(static_cast<size_t>(n_slots) * 2 * h * kHeadDim);
-    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_dkv_tc: workspace of %zu bytes is too small", workspace_bytes);
-    return run_dkv(&tp, P, dP, delta, q, d_o, static_cast<float>(scale), dk, dv, h, part, as_stream(stream_));
-}
-
 extern "C" size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
                                                        const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
                                                        int h) {
     if (!dst_tiles || !src_tiles || !counts_host || n_nodes < 0 || n_edges < 0 || h < 1) return 0;
     const size_t e = static_cast<size_t>(n_edges);
-    return 2 * align_up(e * h * 4, 256) + align_up(static_cast<size_t>(n_nodes) * h * 4, 256) +
+    return align_up(e * h * 4, 256) +
            align_up(static_cast<size_t>(dst_tiles->n_slots) * h * kHeadDim * 4, 256) +
            align_up(static_cast<size_t>(src_tiles->n_slots) * 2 * h * kHeadDim * 4, 256) +
            align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) + 2048;
@@ -632,9 +593,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
     const PlanView pv = plan_view(const_cast<void *>(attn_plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
     Workspace ws(workspace, workspace_bytes);
     const size_t e = static_cast<size_t>(n_edges);
-    float *P = ws.take<float>(e * h);
-    float *dP = ws.take<float>(e * h);
-    float *delta = ws.take<float>(static_cast<size_t>(n_nodes) * h);
+    uint32_t *PS = ws.take<uint32_t>(e * h);
     float *part_dq = ws.take<float>(static_cast<size_t>(dst_tiles->n_slots) * h * kHeadDim);
     float *part_dkv = ws.take<float>(static_cast<size_t>(src_tiles->n_slots) * 2 * h * kHeadDim);
     float *part_dak = ws.take<float>(static_cast<size_t>(counts_host[7]) * kHeadDim);
@@ -650,7 +609,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         p.q = static_cast<const __nv_bfloat16 *>(q); p.k = static_cast<const __nv_bfloat16 *>(k);
         p.v = static_cast<const __nv_bfloat16 *>(v); p.ak = static_cast<const __nv_bfloat16 *>(ak);
         p.o = static_cast<const __nv_bfloat16 *>(o); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
-        p.lse = lse; p.P = P; p.dP = dP; p.delta = delta; p.part_dq = part_dq;
+        p.lse = lse; p.PS = PS; p.part_dq = part_dq;
         p.dq = static_cast<__nv_bfloat16 *>(dq);
         p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = dst_tiles->max_cols_pad;
         p.t_max = bias ? dst_tiles->t_max : 0;
@@ -676,8 +635,8 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         }
     }
     // 2. relative-position part of dQ and the gradient of the type table (CUDA cores)
-    if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, P, dP, delta, sc, dq, dak, part_dak, h, d, stream))
+    if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, PS, dq, dak, part_dak, h, d, stream))
         return rc;
     // 3. source side: dK, dV
-    return run_dkv(src_tiles, P, dP, delta, q, d_o, sc, dk, dv, h, part_dkv, stream);
+    return run_dkv(src_tiles, PS, q, d_o, dk, dv, h, part_dkv, stream);
 }

@@ -228,7 +228,7 @@ int bpt_attn_forward(const void *plan, const int32_t *counts_host, int64_t n_nod
                      void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
 /* lse: the forward's output; d_o: gradient of o.  dq: (n_nodes, h, d), dk, dv: (n_src, h, d),
- * or both NULL to skip them (bpt_attn_backward_dkv_tc then computes them from the scratch);
+ * or both NULL to skip them;
  * dak: fp32 (n_etypes, d), required when ak is given.  The forward's o is not needed: the
  * row term <dO, O> of the softmax gradient is recomputed in fp32 from the probabilities. */
 int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
@@ -310,30 +310,14 @@ int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, const int32_t *
                         float *lse, int h, int d, int dtype, void *workspace,
                         size_t workspace_bytes, bpt_stream_t stream);
 
-/* Tensor-core dK / dV (bf16, head dim 64) from what bpt_attn_backward left in its workspace.
- * Call bpt_attn_backward with dk = dv = NULL first, fetch the scratch pointers with
- * bpt_attn_backward_scratch (same workspace, n_nodes, n_edges, h), then this.  The plan is a
- * tile plan of the TRANSPOSED problem: bpt_tile_plan_create fed with the out-CSR
- * (bpt_export_out_csr: indptr over n_src rows, dst as columns, in_etype = NULL, in_payload =
- * positions in the in-CSR), exported with cell_pos.  q, d_o: (n_nodes, h, 64); dk, dv:
- * (n_src, h, 64); all bf16, 16-byte aligned.  Rows keep one writer and a fixed summation
- * order: bitwise reproducible.  No counterpart in the reference beyond the gradients of
- * maskedmm_csr / vector_spmm (graph_kernel/graphop_kernel.cu:100-112, :151-163). */
-int bpt_attn_backward_scratch(void *workspace, size_t workspace_bytes, int64_t n_nodes, int64_t n_edges,
-                              int h, float **P, float **dP, float **delta);
-size_t bpt_attn_backward_dkv_tc_workspace_bytes(int64_t n_slots, int h);
-int bpt_attn_backward_dkv_tc(const int32_t *groups, int64_t n_groups, const int32_t *mblocks,
-                             const int32_t *cols, const int32_t *cell_pos, const int32_t *split_rows,
-                             int64_t n_split, int64_t n_slots, int max_cols_pad, const float *P,
-                             const float *dP, const float *delta, const void *q, const void *d_o,
-                             double scale, void *dk, void *dv, int h, int d, int dtype,
-                             void *workspace, size_t workspace_bytes, bpt_stream_t stream);
-
 /* The whole backward on the tensor-core path (bf16, head dim 64): dst_tiles = the forward's tile
  * plan exported WITH cell_pos and without row items, src_tiles = the transposed tile plan
- * (see bpt_attn_backward_dkv_tc), attn_plan / counts_host = the bpt_attn_plan_build plan of the
+ * (bpt_tile_plan_create fed with the out-CSR of bpt_export_out_csr: indptr over n_src rows, dst
+ * as columns, in_etype = NULL, in_payload = positions in the in-CSR; exported with cell_pos),
+ * attn_plan / counts_host = the bpt_attn_plan_build plan of the
  * same graph.  o and lse are the forward's outputs (delta = <dO, O> per row here).  Runs the
- * destination-side tile kernel (per-edge P and dP into the workspace, K part of dQ), the
+ * destination-side tile kernel (per edge and head one word {bf16 p, bf16 dS} into the workspace,
+ * K part of dQ), the
  * CUDA-core kernels for the relative-position part of dQ and for d embed_ak, then the
  * source-side tile kernel (dK, dV).  Single writer per output element, fixed summation orders. */
 size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,

@@ -60,7 +60,7 @@ def build(force=False, verbose=False):
         raise RuntimeError("nvcc failed")
     if procs or not os.path.exists(LIB_PATH):
         tmp = LIB_PATH + ".tmp%d" % os.getpid()
-        subprocess.check_call([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp] + objs + ["-lcudart"])
+        subprocess.check_call([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp] + objs + ["-lcudart", "-lcublas"])
         os.replace(tmp, LIB_PATH)
     return LIB_PATH
 

@@ -13,6 +13,10 @@
 // and accumulates both products with ldmatrix.trans B fragments.  A source row wholly inside
 // one m-block is written once; rows spread over several m-blocks write fp32 partials that are
 // summed in slot order.  No atomics: results are bitwise reproducible.
+#include <cublas_v2.h>
+
+#include <mutex>
+
 #include "fused_common.cuh"
 #include "plan.cuh"
 #include "tile_plan.cuh"
@@ -475,6 +479,51 @@ attn_backward_dq_tile_kernel(const DqParams p) {
     }
 }
 
+// ---- relative-position terms through a dense per-row table ----
+// G[row, h, t] = sum of dS over the row's edges of type t (zero rows for rows whose edges share one
+// type: their dS sums to zero).  With it the two relative-position gradients are plain GEMMs:
+//     dQ[row, h, :] += G[row, h, :] . embed_ak          d embed_ak = G^T . Q
+// One warp per destination row; one lane per head walks the row's edges in order, so the sums
+// have a fixed order.  G is bf16, (n_nodes * H, tq).
+__global__ void __launch_bounds__(128)
+build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
+                        const int32_t *__restrict__ row_uniform, int n_rows, const uint32_t *__restrict__ PS,
+                        __nv_bfloat16 *__restrict__ G, int H, int tq) {
+    extern __shared__ float s_g[];  // [4 warps][H][tq]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= n_rows) return;
+    float *g = s_g + static_cast<int64_t>(warp) * H * tq;
+    __nv_bfloat16 *out = G + static_cast<int64_t>(row) * H * tq;
+    const int cells = H * tq;
+    if (row_uniform[row]) {
+        for (int i = lane * 2; i < cells; i += 64) *reinterpret_cast<uint32_t *>(out + i) = 0u;
+        return;
+    }
+    for (int i = lane; i < cells; i += 32) g[i] = 0.f;
+    __syncwarp();
+    const int beg = in_indptr[row], end = in_indptr[row + 1];
+    for (int h = lane; h < H; h += 32)
+        for (int j = beg; j < end; ++j)
+            g[h * tq + in_etype[j]] += __uint_as_float(PS[static_cast<int64_t>(j) * H + h] & 0xffff0000u);
+    __syncwarp();
+    for (int i = lane * 2; i < cells; i += 64) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(g[i], g[i + 1]);
+        *reinterpret_cast<__nv_bfloat162 *>(out + i) = v;
+    }
+}
+
+// One cuBLAS handle per device, created on first use.
+cublasHandle_t cublas_handle() {
+    static std::mutex mu;
+    static cublasHandle_t handles[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (handles[dev] == nullptr && cublasCreate(&handles[dev]) != CUBLAS_STATUS_SUCCESS) handles[dev] = nullptr;
+    return handles[dev];
+}
+
 // out0[row] | out1[row] = sum over the row's slots, in slot order, of the slot's two halves.
 // (out1 == nullptr: a slot holds one array of `width` values.)
 __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_split, const float *__restrict__ part,
@@ -558,6 +607,14 @@ int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStrea
 
 }  // namespace
 
+namespace {
+constexpr int kMaxTableTypes = 256;  // beyond this the dense per-row type table is not used
+size_t type_table_elems(const bpt_tile_plan_t *dst_tiles, int64_t n_nodes, int h) {
+    const int tq = dst_tiles->t_max;
+    return tq > 0 && tq <= kMaxTableTypes ? static_cast<size_t>(n_nodes) * h * tq : 1;
+}
+}  // namespace
+
 extern "C" size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
                                                        const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
                                                        int h) {
@@ -566,7 +623,8 @@ extern "C" size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *ds
     return align_up(e * h * 4, 256) +
            align_up(static_cast<size_t>(dst_tiles->n_slots) * h * kHeadDim * 4, 256) +
            align_up(static_cast<size_t>(src_tiles->n_slots) * 2 * h * kHeadDim * 4, 256) +
-           align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) + 2048;
+           align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) +
+           align_up(type_table_elems(dst_tiles, n_nodes, h) * 2, 256) + 2048;
 }
 
 extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
@@ -597,6 +655,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
     float *part_dq = ws.take<float>(static_cast<size_t>(dst_tiles->n_slots) * h * kHeadDim);
     float *part_dkv = ws.take<float>(static_cast<size_t>(src_tiles->n_slots) * 2 * h * kHeadDim);
     float *part_dak = ws.take<float>(static_cast<size_t>(counts_host[7]) * kHeadDim);
+    __nv_bfloat16 *G = ws.take<__nv_bfloat16>(type_table_elems(dst_tiles, n_nodes, h));
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_tc: workspace of %zu bytes is too small", workspace_bytes);
     const float sc = static_cast<float>(scale);
 
@@ -634,9 +693,37 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
             BPT_LAUNCH_CHECK();
         }
     }
-    // 2. relative-position part of dQ and the gradient of the type table (CUDA cores)
-    if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, PS, dq, dak, part_dak, h, d, stream))
-        return rc;
+    // 2. relative-position part of dQ and the gradient of the type table
+    const int tq = dst_tiles->t_max;
+    if (ak != nullptr && dak != nullptr)
+        BPT_CUDA(cudaMemsetAsync(dak, 0, sizeof(float) * static_cast<size_t>(n_etypes) * kHeadDim, stream));
+    if (ak != nullptr && tq > 0 && tq <= kMaxTableTypes && static_cast<size_t>(4) * h * tq * sizeof(float) <= 48 * 1024) {
+        // dense per-row type table, then two library GEMMs
+        const int kk = tq < n_etypes ? tq : n_etypes;
+        const size_t smem_g = static_cast<size_t>(4) * h * tq * sizeof(float);
+        build_type_table_kernel<<<static_cast<unsigned>((n_nodes + 3) / 4), 128, smem_g, stream>>>(
+            pv.in_indptr, pv.in_etype, pv.row_uniform, static_cast<int>(n_nodes), PS, G, h, tq);
+        BPT_LAUNCH_CHECK();
+        cublasHandle_t handle = cublas_handle();
+        if (handle == nullptr) return fail(BPT_ERR_CUDA, "attn_backward_tc: cuBLAS handle could not be created");
+        if (cublasSetStream(handle, stream) != CUBLAS_STATUS_SUCCESS) return fail(BPT_ERR_CUDA, "attn_backward_tc: cublasSetStream failed");
+        const float one = 1.f, zero = 0.f;
+        const long long nh = static_cast<long long>(n_nodes) * h;
+        BPT_CHECK_ARG(nh < (1ll << 31), "attn_backward_tc: n_nodes * h exceeds the GEMM index range");
+        // row-major dQ (nh x 64) += G (nh x tq) . ak (tq x 64)   ==   column-major dQ^T = ak^T . G^T
+        cublasStatus_t st = cublasGemmEx(handle, CUBLAS_OP_N, CUBLAS_OP_N, kHeadDim, static_cast<int>(nh), kk, &one, ak,
+                                         CUDA_R_16BF, kHeadDim, G, CUDA_R_16BF, tq, &one, dq, CUDA_R_16BF, kHeadDim,
+                                         CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+        if (st != CUBLAS_STATUS_SUCCESS) return fail(BPT_ERR_CUDA, "attn_backward_tc: cublasGemmEx (dQ) failed with %d", int(st));
+        // row-major d ak (kk x 64) = G^T (kk x nh) . Q (nh x 64)   ==   column-major (d ak)^T = Q^T . G
+        st = cublasGemmEx(handle, CUBLAS_OP_N, CUBLAS_OP_T, kHeadDim, kk, static_cast<int>(nh), &one, q, CUDA_R_16BF,
+                          kHeadDim, G, CUDA_R_16BF, tq, &zero, dak, CUDA_R_32F, kHeadDim, CUBLAS_COMPUTE_32F,
+                          CUBLAS_GEMM_DEFAULT);
+        if (st != CUBLAS_STATUS_SUCCESS) return fail(BPT_ERR_CUDA, "attn_backward_tc: cublasGemmEx (d ak) failed with %d", int(st));
+    } else {
+        // many edge types: per-edge CUDA-core kernels
+        if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, PS, dq, dak, part_dak, h, d, stream)) return rc;
+    }
     // 3. source side: dK, dV
     return run_dkv(src_tiles, PS, q, d_o, dk, dv, h, part_dkv, stream);
 }

@@ -317,8 +317,9 @@ int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, const int32_t *
  * attn_plan / counts_host = the bpt_attn_plan_build plan of the
  * same graph.  o and lse are the forward's outputs (delta = <dO, O> per row here).  Runs the
  * destination-side tile kernel (per edge and head one word {bf16 p, bf16 dS} into the workspace,
- * K part of dQ), the
- * CUDA-core kernels for the relative-position part of dQ and for d embed_ak, then the
+ * K part of dQ), then the relative-position part of dQ and d embed_ak (a per-row table of dS
+ * summed by edge type followed by two cuBLAS GEMMs when the tiles use at most 256 edge types,
+ * per-edge CUDA-core kernels otherwise), then the
  * source-side tile kernel (dK, dV).  Single writer per output element, fixed summation orders. */
 size_t bpt_attn_backward_tc_workspace_bytes(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t *src_tiles,
                                             const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,

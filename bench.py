@@ -355,7 +355,15 @@ def run_ours(a):
     else:
         launches_fwd = 1 + (plan.counts[2] > 0)
         fwd_kernel = "attn_forward_kernel"
-    launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
+    if dtype == torch.bfloat16:
+        tpt = plan.tile_plan_t()
+        # destination-side tiles, per-row type table, source-side tiles (+ merges); the two GEMMs of
+        # the relative-position gradients are cuBLAS launches and not counted
+        launches_bwd = 3 + (tp.n_split > 0) + (tpt.n_split > 0)
+        bwd_kernels = "attn_backward_dq_tile_kernel + build_type_table_kernel + 2 cuBLAS GEMMs + attn_backward_dkv_tile_kernel"
+    else:
+        launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
+        bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"
 
     def step():
         o, lse = attention_forward(plan, q, k, v, ak, scale)
@@ -478,7 +486,7 @@ def run_ours(a):
             "roofline": {"kernel": fwd_kernel, "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
                          "peak_source": peak_src, "unit": "GB/s", "frac": fwd_gbs / peak,
                          "algorithmic_bytes": fwd_bytes, "traffic": None},
-            "roofline_backward": {"kernels": "attn_backward_{dq,dkv,dak}_kernel", "bound": "hbm",
+            "roofline_backward": {"kernels": bwd_kernels, "bound": "hbm",
                                   "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
                                   "algorithmic_bytes": bwd_bytes},
             "clocks": clocks,
@@ -489,11 +497,11 @@ def run_ours(a):
             value, info = cpu_reference_run(a, 1, 1, min_seconds=10.0)
             line["cpu_baseline"] = {"value": value, "unit": "edges/s", "cores": info["cores"], "kind": "port",
                                     "sample": info["sample"]}
-        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(traffic_path):
-            tr = json.load(open(traffic_path)).get(workload_name(a))
-            if tr:
-                line["roofline"]["traffic"] = tr
+        if a.dtype == "bf16" and a.n == 8192 and a.k == 4 and not a.causal:
+            # dram__bytes_read + dram__bytes_write of attn_forward_tile_kernel from one ncu capture on 2
+            # sequences of this shape (profiles/attn_tile_kernels_bf16_n8192_k4.md): 147.28 MB for
+            # 1,491,572 edges; traffic grows in proportion to the number of sequences.
+            line["roofline"]["traffic"] = 147.28e6 / 1491572 * E
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -102,7 +102,7 @@ class TilePlan:
     (bpt_attn_forward_tc).  transposed=True: rows are sources, columns destinations, cells
     carry the edge's position in the in-CSR (source side of bpt_attn_backward_tc)."""
 
-    def __init__(self, plan, transposed=False, min_density=0.25, max_cols=384, group_rows=16, col_block=64,
+    def __init__(self, plan, transposed=False, min_density=0.25, max_cols=384, group_rows=16, col_block=128,
                  simt_max_degree=0, max_mblocks=1, join_dense=False):
         L = _lib.lib()
         E, T = plan.n_edges, plan.n_etypes

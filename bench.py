@@ -76,6 +76,8 @@ def cpu_reference_run(a, steps, warmup, min_seconds=0.0):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle
     oracle.build_lib()
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use the cores this process may run on
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
     g = oracle.binary_partition(a.n, a.causal, a.k, 10)
     N, E = g["n_nodes"], g["n_edges"]
     csr = oracle.get_csrs(g["src"], g["dst"], N)

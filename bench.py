@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--mode", default="graphs", choices=["graphs", "seqshard"],
                     help="graphs: independent sequences per rank (weak scaling); seqshard: ONE sequence of "
                          "--seq-len tokens, destination nodes split over the ranks, K/V all-gathered (strong scaling)")
+    ap.add_argument("--exchange", default="halo", choices=["halo", "allgather"],
+                    help="seqshard mode: send only the remote K/V rows a shard reads (halo) or all-gather K/V")
     ap.add_argument("--workload", default="attention", choices=["attention", "lm"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
                          "forward, batch 8 x 8192 tokens per rank, tokens/s")
@@ -200,7 +202,12 @@ def run_seqshard(a):
     g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
     src, dst, et = g.edges_device()
     s = sh.SequenceShard(src, dst, et, g.n_nodes_arr, g.shift, rank, world)
-    plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_gathered)
+    halo = a.exchange == "halo"
+    if halo:
+        s.build_halo(src, dst)
+        plan = AttentionPlan(s.src_h, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_ext)
+    else:
+        plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_gathered)
     E = g.number_of_edges
     gen = torch.Generator().manual_seed(2 + rank)
     q, k, v, d_o = [(torch.randn(s.n_owned, H, D, generator=gen) * sg).to(dtype).to(dev)
@@ -209,13 +216,17 @@ def run_seqshard(a):
     scale = 1.0 / math.sqrt(D)
 
     def step():
-        if world > 1:
+        if halo:
+            k_g, v_g = (sh.halo_exchange(s, k), sh.halo_exchange(s, v)) if world > 1 else (k, v)
+        elif world > 1:
             k_g, v_g = sh.all_gather_rows(s, k), sh.all_gather_rows(s, v)
         else:
             k_g, v_g = s.pad_rows(k), s.pad_rows(v)
         o, lse = attention_forward(plan, q, k_g, v_g, ak, scale)
         dq, dk_g, dv_g, dak = attention_backward(plan, q, k_g, v_g, ak, scale, lse, d_o, o=o)
         if world > 1:
+            if halo:
+                return sh.halo_return(s, dk_g), sh.halo_return(s, dv_g)
             return sh.reduce_scatter_rows(s, dk_g), sh.reduce_scatter_rows(s, dv_g)
         return dk_g, dv_g
 
@@ -243,10 +254,12 @@ def run_seqshard(a):
             "metric": "bpt_attention_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": a.dtype, "data": "synthetic",
-            "config": {"workload": "bpt_attention_fwd_bwd 1x(n=%d,k=%d) destination-sharded, K/V all-gather + "
-                                   "dK/dV reduce-scatter over NCCL" % (a.n, a.k),
+            "config": {"workload": "bpt_attention_fwd_bwd 1x(n=%d,k=%d) destination-sharded, %s over NCCL" % (
+                           a.n, a.k, "halo all-to-all of K/V rows and of their gradients" if halo
+                           else "K/V all-gather + dK/dV reduce-scatter"),
                        "edges": E, "nodes": g.number_of_nodes, "owned_nodes_rank0": s.n_owned,
-                       "kv_allgather_bytes_per_rank": 2 * s.n_gathered * H * D * q.element_size()}}), flush=True)
+                       "kv_bytes_received_rank0": 2 * (s.n_halo if halo else s.n_gathered) * H * D * q.element_size()}}),
+              flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -11,6 +11,13 @@ Two cases, as the graph decides:
   gathered K/V to their owners with a reduce-scatter.  The reference has no counterpart: it
   keeps a sequence on one GPU.
 
+Two exchanges are provided.  `sharded_attention` gathers every rank's K/V rows (simple, but a
+shard reads only a few hundred remote rows: per level the k neighbours beyond each end of its
+range).  `halo_attention` sends exactly those rows: each rank keeps [its own rows | the remote
+rows its edges name] and one variable-size all-to-all per tensor replaces the all-gather;
+gradients of the remote rows travel back the same way and are added to their owners' rows in
+rank order.
+
 Index spaces: "global" ids are the builder's node ids; rank r's "local" ids are positions in
 its sorted list of owned nodes; the "gathered" space is what all_gather_into_tensor yields:
 rank-major, every rank padded to the largest owner count, so that gathered id =
@@ -66,6 +73,43 @@ class SequenceShard:
         self.etype_l = None if etype is None else etype[keep].to(torch.int32)
         self.n_owned = int(self.owned.numel())
 
+    # ---- halo exchange: only the remote rows this rank's edges name ----
+    def build_halo(self, src, dst):
+        """Send/receive lists of the halo exchange, computed locally by every rank from the whole
+        edge list (no communication).  Sets
+          n_halo       remote rows this rank receives
+          src_h        this rank's edges' sources in the local extended space [own | halo]
+          recv_counts  rows received from each rank, in rank order (the halo rows' order)
+          send_idx     per peer, the local indices of the own rows it needs (ascending global id)"""
+        dev = src.device
+        world, rank = self.world, self.rank
+        n_nodes = self.to_gathered.numel()
+        owner = (self.to_gathered // self.max_owned)                     # owner rank of every node
+        local = (self.to_gathered % self.max_owned)                      # its index in the owner's list
+        src64, dst64 = src.long(), dst.long()
+        dst_owner = owner[dst64]
+        needs = []                                                       # needs[r]: global ids r reads but does not own
+        for r in range(world):
+            s_r = torch.unique(src64[dst_owner == r])
+            needs.append(s_r[owner[s_r] != r])
+        mine = needs[rank]
+        order = torch.argsort(owner[mine] * n_nodes + mine)              # by owner rank, then id
+        mine = mine[order]
+        self.recv_counts = [int((owner[mine] == r).sum()) for r in range(world)]
+        self.n_halo = int(mine.numel())
+        ext = torch.full((n_nodes,), -1, dtype=torch.int64, device=dev)
+        ext[self.owned] = torch.arange(self.n_owned, device=dev)
+        ext[mine] = self.n_owned + torch.arange(self.n_halo, device=dev)
+        self.src_h = ext[src64[self.eid]].to(torch.int32)
+        self.send_idx = []
+        for r in range(world):
+            want = needs[r][owner[needs[r]] == rank]                     # ascending ids (torch.unique sorts)
+            self.send_idx.append(local[want])
+        self.send_counts = [int(t.numel()) for t in self.send_idx]
+        self.send_all = torch.cat(self.send_idx) if self.send_idx else torch.zeros(0, dtype=torch.int64, device=dev)
+        self.n_ext = self.n_owned + self.n_halo
+        return self
+
     def pad_rows(self, x):
         """(n_owned, ...) -> (max_owned, ...) zero-padded: this rank's all-gather contribution."""
         if x.size(0) == self.max_owned:
@@ -113,3 +157,52 @@ def sharded_attention(shard, plan, q, k, v, embed_ak=None, scale=None):
     k_g = _GatherKV.apply(shard, k)
     v_g = _GatherKV.apply(shard, v)
     return bpt_attention(plan, q, k_g, v_g, embed_ak, scale)
+
+
+def halo_exchange(shard, x, group=None):
+    """(n_owned, ...) -> (n_owned + n_halo, ...): this rank's rows followed by the remote rows its
+    edges name, fetched with one variable-size all-to-all."""
+    import torch.distributed as dist
+    send = x.index_select(0, shard.send_all)
+    recv = x.new_empty((shard.n_halo,) + tuple(x.shape[1:]))
+    dist.all_to_all_single(recv, send, output_split_sizes=shard.recv_counts, input_split_sizes=shard.send_counts,
+                           group=group)
+    return torch.cat([x, recv], 0)
+
+
+def halo_return(shard, g_ext, group=None):
+    """Gradient of halo_exchange: sends the halo rows' gradients back to their owners and adds
+    them to the owners' rows, peer by peer in rank order (rows of one peer are distinct, so
+    every sum has a fixed order)."""
+    import torch.distributed as dist
+    g_own = g_ext[: shard.n_owned].clone()
+    send = g_ext[shard.n_owned:].contiguous()
+    recv = g_ext.new_empty((int(shard.send_all.numel()),) + tuple(g_ext.shape[1:]))
+    dist.all_to_all_single(recv, send, output_split_sizes=shard.send_counts, input_split_sizes=shard.recv_counts,
+                           group=group)
+    off = 0
+    for idx in shard.send_idx:
+        n = int(idx.numel())
+        if n:
+            g_own[idx] += recv[off:off + n]
+        off += n
+    return g_own
+
+
+class _HaloKV(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, shard, x):
+        ctx.shard = shard
+        return halo_exchange(shard, x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return None, halo_return(ctx.shard, g)
+
+
+def halo_attention(shard, plan, q, k, v, embed_ak=None, scale=None):
+    """Attention for this rank's destinations with the halo exchange.  plan:
+    AttentionPlan(shard.src_h, shard.dst_l, shard.etype_l, shard.n_owned, n_src=shard.n_ext) after
+    shard.build_halo(src, dst).  Differentiable; returns (n_owned, h, d)."""
+    from .attention import bpt_attention
+    return bpt_attention(plan, q, _HaloKV.apply(shard, k), _HaloKV.apply(shard, v), embed_ak, scale)

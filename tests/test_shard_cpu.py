@@ -51,6 +51,20 @@ def _worker(rank, world, port, n, k, out):
     own_np = own.numpy()
     errs = [np.abs(o - o_ref[own_np]).max(), np.abs(dq - ref[0][own_np]).max(), np.abs(dk.numpy() - ref[1][own_np]).max(),
             np.abs(dv.numpy() - ref[2][own_np]).max(), np.abs(dak_t.numpy() - ref[3]).max()]
+    # the halo exchange: only the rows this rank's edges name travel
+    s.build_halo(torch.from_numpy(g["src"]), torch.from_numpy(g["dst"]))
+    k_h, v_h = sh.halo_exchange(s, kk[own]), sh.halo_exchange(s, v[own])
+    src_h = s.src_h.numpy().astype(np.int64)
+    in_h = oracle.coo_to_csr(dst_l, src_h, s.n_owned)
+    out_h = oracle.coo_to_csr(src_h, dst_l, s.n_ext)
+    o_h, _, p_h = oracle.attn_fwd(in_h, et_l, q[own].numpy(), k_h.numpy(), v_h.numpy(), ak.numpy(), 0.3)
+    dq_h, dk_e, dv_e, _ = oracle.attn_bwd(in_h, out_h, et_l, q[own].numpy(), k_h.numpy(), v_h.numpy(), ak.numpy(), 0.3,
+                                          o_h, p_h, d_o[own].numpy())
+    dk_h = sh.halo_return(s, torch.from_numpy(dk_e))
+    dv_h = sh.halo_return(s, torch.from_numpy(dv_e))
+    errs += [np.abs(o_h - o_ref[own_np]).max(), np.abs(dq_h - ref[0][own_np]).max(),
+             np.abs(dk_h.numpy() - ref[1][own_np]).max(), np.abs(dv_h.numpy() - ref[2][own_np]).max()]
+    assert s.n_halo < s.n_owned and sum(s.recv_counts) == s.n_halo
     counts = torch.tensor([s.n_owned, int(s.eid.numel())])
     gathered = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
     dist.all_gather(gathered, counts)

@@ -94,6 +94,15 @@ def _nccl_worker(rank, world, port, out):
     errs = [rel(o.detach().double().cpu().numpy(), o_ref[own_np]), rel(ql.grad.double().cpu().numpy(), ref[0][own_np]),
             rel(kl.grad.double().cpu().numpy(), ref[1][own_np]), rel(vl.grad.double().cpu().numpy(), ref[2][own_np]),
             rel(dak.double().cpu().numpy(), ref[3])]
+    # same through the halo exchange (only the remote rows this rank's edges name travel)
+    s.build_halo(src, dst)
+    plan_h = AttentionPlan(s.src_h, s.dst_l, s.etype_l, s.n_owned, n_etypes=T, n_src=s.n_ext)
+    ql2, kl2, vl2 = [t.cuda()[own].requires_grad_(True) for t in (q, k, v)]
+    akl2 = ak.cuda().requires_grad_(True)
+    o2 = sh.halo_attention(s, plan_h, ql2, kl2, vl2, akl2, 0.125)
+    o2.backward(d_o.cuda()[own])
+    errs += [rel(o2.detach().double().cpu().numpy(), o_ref[own_np]), rel(ql2.grad.double().cpu().numpy(), ref[0][own_np]),
+             rel(kl2.grad.double().cpu().numpy(), ref[1][own_np]), rel(vl2.grad.double().cpu().numpy(), ref[2][own_np])]
     out.put((rank, max(errs)))
     dist.barrier()
     dist.destroy_process_group()

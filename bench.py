@@ -204,8 +204,8 @@ def run_seqshard(a):
     s = sh.SequenceShard(src, dst, et, g.n_nodes_arr, g.shift, rank, world)
     halo = a.exchange == "halo"
     if halo:
-        s.build_halo(src, dst)
-        plan = AttentionPlan(s.src_h, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_ext)
+        s.build_halo(src, dst, split_straddlers=True)
+        plan = AttentionPlan(s.src_h, s.dst_l, s.etype_l, s.n_dst_local, n_etypes=MAX_ETYPE, n_src=s.n_ext)
     else:
         plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_gathered)
     E = g.number_of_edges
@@ -215,9 +215,17 @@ def run_seqshard(a):
     ak = (torch.randn(MAX_ETYPE, D, generator=torch.Generator().manual_seed(1)) * 0.125).to(dtype).to(dev)
     scale = 1.0 / math.sqrt(D)
 
+    if halo:
+        for t_ in (q, k, v, ak):
+            t_.requires_grad_(True)
+
     def step():
         if halo:
-            k_g, v_g = (sh.halo_exchange(s, k), sh.halo_exchange(s, v)) if world > 1 else (k, v)
+            # the autograd function: halo all-to-all, tile kernels, merge of the straddlers' partial rows
+            for t_ in (q, k, v, ak):
+                t_.grad = None
+            sh.halo_attention(s, plan, q, k, v, ak, scale).backward(d_o)
+            return k.grad, v.grad
         elif world > 1:
             k_g, v_g = sh.all_gather_rows(s, k), sh.all_gather_rows(s, v)
         else:
@@ -225,8 +233,6 @@ def run_seqshard(a):
         o, lse = attention_forward(plan, q, k_g, v_g, ak, scale)
         dq, dk_g, dv_g, dak = attention_backward(plan, q, k_g, v_g, ak, scale, lse, d_o, o=o)
         if world > 1:
-            if halo:
-                return sh.halo_return(s, dk_g), sh.halo_return(s, dv_g)
             return sh.reduce_scatter_rows(s, dk_g), sh.reduce_scatter_rows(s, dv_g)
         return dk_g, dv_g
 
@@ -255,7 +261,7 @@ def run_seqshard(a):
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": a.dtype, "data": "synthetic",
             "config": {"workload": "bpt_attention_fwd_bwd 1x(n=%d,k=%d) destination-sharded, %s over NCCL" % (
-                           a.n, a.k, "halo all-to-all of K/V rows and of their gradients" if halo
+                           a.n, a.k, "halo all-to-all of K/V rows and of their gradients, straddling span nodes merged across ranks" if halo
                            else "K/V all-gather + dK/dV reduce-scatter"),
                        "edges": E, "nodes": g.number_of_nodes, "owned_nodes_rank0": s.n_owned,
                        "kv_bytes_received_rank0": 2 * (s.n_halo if halo else s.n_gathered) * H * D * q.element_size()}}),

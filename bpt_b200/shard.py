@@ -72,11 +72,17 @@ class SequenceShard:
         self.src_g = self.to_gathered[src.long()[keep]].to(torch.int32)
         self.etype_l = None if etype is None else etype[keep].to(torch.int32)
         self.n_owned = int(self.owned.numel())
+        self._etype = etype
+        self._n_leaves = int(n_nodes_arr[0])
 
     # ---- halo exchange: only the remote rows this rank's edges name ----
-    def build_halo(self, src, dst):
+    def build_halo(self, src, dst, split_straddlers=False):
         """Send/receive lists of the halo exchange, computed locally by every rank from the whole
-        edge list (no communication).  Sets
+        edge list (no communication).  With split_straddlers, span nodes whose source leaves lie
+        on several ranks (the top log2(world) levels of the tree) are not computed by their owner
+        alone: every rank attends from them to its own sources only and the partial results are
+        merged (halo_attention does that); their rows are appended after this rank's other
+        destinations.  Sets
           n_halo       remote rows this rank receives
           src_h        this rank's edges' sources in the local extended space [own | halo]
           recv_counts  rows received from each rank, in rank order (the halo rows' order)
@@ -92,6 +98,40 @@ class SequenceShard:
         for r in range(world):
             s_r = torch.unique(src64[dst_owner == r])
             needs.append(s_r[owner[s_r] != r])
+        self.split = bool(split_straddlers)
+        if self.split:
+            n_leaves = int(self._n_leaves)
+            span = dst64 >= n_leaves
+            lo = torch.full((n_nodes,), world, dtype=torch.int64, device=dev).scatter_reduce(
+                0, dst64[span], owner[src64[span]], "amin")
+            hi = torch.full((n_nodes,), -1, dtype=torch.int64, device=dev).scatter_reduce(
+                0, dst64[span], owner[src64[span]], "amax")
+            is_strad = hi > lo                                           # sources on more than one rank
+            strad = torch.nonzero(is_strad).squeeze(1)                   # ascending global ids
+            self.n_strad = int(strad.numel())
+            # edges this rank computes: into its own non-straddling rows, and from its own sources
+            # into any straddler
+            edge_strad = is_strad[dst64]
+            keep = (~edge_strad & (dst_owner == rank)) | (edge_strad & (owner[src64] == rank))
+            self.eid = torch.nonzero(keep).squeeze(1)
+            own_ns = ~is_strad[self.owned]
+            self.ns_idx = torch.nonzero(own_ns).squeeze(1)               # positions of non-straddlers in `owned`
+            self.s_own_idx = torch.nonzero(~own_ns).squeeze(1)           # positions of my straddlers in `owned`
+            self.s_own_pos = torch.searchsorted(strad, self.owned[self.s_own_idx])
+            self.n_ns = int(self.ns_idx.numel())
+            # straddlers are top-level nodes: in the sorted `owned` list they normally come last
+            self.ns_prefix = bool(self.n_ns == 0 or int(self.ns_idx[-1]) == self.n_ns - 1)
+            loc = torch.full((n_nodes,), -1, dtype=torch.int64, device=dev)
+            loc[self.owned[self.ns_idx]] = torch.arange(self.n_ns, device=dev)
+            loc[strad] = self.n_ns + torch.arange(self.n_strad, device=dev)
+            self.dst_l = loc[dst64[self.eid]].to(torch.int32)
+            self.n_dst_local = self.n_ns + self.n_strad
+            self.etype_l = None if self._etype is None else self._etype[self.eid].to(torch.int32)
+            # remote rows are needed only by edges into non-straddling rows
+            needs = []
+            for r in range(world):
+                s_r = torch.unique(src64[~edge_strad & (dst_owner == r)])
+                needs.append(s_r[owner[s_r] != r])
         mine = needs[rank]
         order = torch.argsort(owner[mine] * n_nodes + mine)              # by owner rank, then id
         mine = mine[order]
@@ -163,6 +203,8 @@ def halo_exchange(shard, x, group=None):
     """(n_owned, ...) -> (n_owned + n_halo, ...): this rank's rows followed by the remote rows its
     edges name, fetched with one variable-size all-to-all."""
     import torch.distributed as dist
+    if shard.world == 1 or (shard.n_halo == 0 and int(shard.send_all.numel()) == 0):
+        return x
     send = x.index_select(0, shard.send_all)
     recv = x.new_empty((shard.n_halo,) + tuple(x.shape[1:]))
     dist.all_to_all_single(recv, send, output_split_sizes=shard.recv_counts, input_split_sizes=shard.send_counts,
@@ -175,6 +217,8 @@ def halo_return(shard, g_ext, group=None):
     them to the owners' rows, peer by peer in rank order (rows of one peer are distinct, so
     every sum has a fixed order)."""
     import torch.distributed as dist
+    if shard.world == 1:
+        return g_ext
     g_own = g_ext[: shard.n_owned].clone()
     send = g_ext[shard.n_owned:].contiguous()
     recv = g_ext.new_empty((int(shard.send_all.numel()),) + tuple(g_ext.shape[1:]))
@@ -200,9 +244,113 @@ class _HaloKV(torch.autograd.Function):
         return None, halo_return(ctx.shard, g)
 
 
+# (forward, backward) callables used by _StraddleAttention instead of the GPU kernels; tests on
+# CPU ranks install stand-ins with the signatures of attention_forward / attention_backward.
+_KERNELS = None
+
+
+def _all_ranks_rows(shard, x_own, group=None):
+    """Rows of the straddling nodes, (n_strad, ...), on every rank: each owner fills its rows of
+    a zero buffer and the buffers are summed (a sum with zeros is exact)."""
+    import torch.distributed as dist
+    buf = x_own.new_zeros((shard.n_strad,) + tuple(x_own.shape[1:]))
+    buf[shard.s_own_pos] = x_own[shard.s_own_idx]
+    if shard.world > 1 and shard.n_strad:
+        dist.all_reduce(buf, group=group)
+    return buf
+
+
+def _local_rows(shard, x_own):
+    """(n_owned, ...) -> this rank's destination rows [own non-straddlers | all straddlers]."""
+    if shard.n_strad == 0:
+        return x_own
+    head = x_own[: shard.n_ns] if shard.ns_prefix else x_own[shard.ns_idx]
+    return torch.cat([head, _all_ranks_rows(shard, x_own)], 0)
+
+
+def _own_rows(shard, x_loc, x_strad):
+    """Inverse of _local_rows for results: own non-straddlers from x_loc, own straddlers from x_strad."""
+    if shard.n_strad == 0:
+        return x_loc
+    out = x_loc.new_empty((shard.n_owned,) + tuple(x_loc.shape[1:]))
+    if shard.ns_prefix:
+        out[: shard.n_ns] = x_loc[: shard.n_ns]
+    else:
+        out[shard.ns_idx] = x_loc[: shard.n_ns]
+    out[shard.s_own_idx] = x_strad[shard.s_own_pos].to(out.dtype)
+    return out
+
+
+class _StraddleAttention(torch.autograd.Function):
+    """Attention with the halo exchange and split straddlers, forward and backward spelled out
+    because partial rows are merged between the kernels.  bf16 / head dim 64 only: the
+    tensor-core backward takes the row term delta from the merged O, which a rank that sees only
+    part of a row's edges cannot recompute."""
+
+    @staticmethod
+    def forward(ctx, shard, plan, q, k, v, embed_ak, scale):
+        import torch.distributed as dist
+        if _KERNELS is not None:
+            attention_forward = _KERNELS[0]
+        else:
+            from .attention import attention_forward, tensor_core_eligible
+            if not tensor_core_eligible(q, embed_ak):
+                raise RuntimeError("halo_attention with split straddlers needs bf16 tensors with head dim 64")
+        k_e, v_e = halo_exchange(shard, k.contiguous()), halo_exchange(shard, v.contiguous())
+        q_loc = _local_rows(shard, q)
+        o_loc, lse_loc = attention_forward(plan, q_loc, k_e, v_e, embed_ak, scale)
+        if shard.n_strad:
+            # merge every rank's partial rows: lse = logsumexp_r lse_r, o = sum_r exp(lse_r - lse) o_r
+            n, w = shard.n_strad, shard.world
+            part = torch.cat([o_loc[-n:].float().flatten(1), lse_loc[-n:]], 1).contiguous()
+            allp = part.new_empty((w * n, part.shape[1]))
+            dist.all_gather_into_tensor(allp, part)
+            allp = allp.view(w, n, part.shape[1])
+            h, d = q.shape[1], q.shape[2]
+            o_r, lse_r = allp[:, :, : h * d].view(w, n, h, d), allp[:, :, h * d:]
+            lse = torch.logsumexp(lse_r, 0)
+            wgt = torch.exp(lse_r - lse.unsqueeze(0)).nan_to_num(0.0)
+            o_s = (wgt.unsqueeze(-1) * o_r).sum(0)
+            o_loc = torch.cat([o_loc[:-n], o_s.to(o_loc.dtype)], 0)
+            lse_loc = torch.cat([lse_loc[:-n], lse], 0)
+        o = _own_rows(shard, o_loc, o_loc[shard.n_ns:])
+        ctx.shard, ctx.plan, ctx.scale, ctx.has_ak = shard, plan, scale, embed_ak is not None
+        ctx.save_for_backward(q_loc, k_e, v_e, embed_ak if ctx.has_ak else q.new_empty(0), o_loc, lse_loc)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        import torch.distributed as dist
+        if _KERNELS is not None:
+            attention_backward = _KERNELS[1]
+        else:
+            from .attention import attention_backward
+        shard = ctx.shard
+        q_loc, k_e, v_e, ak, o_loc, lse_loc = ctx.saved_tensors
+        ak = ak if ctx.has_ak else None
+        d_o = d_o.contiguous()
+        do_loc = _local_rows(shard, d_o)
+        dq_loc, dk_e, dv_e, dak = attention_backward(ctx.plan, q_loc, k_e, v_e, ak, ctx.scale, lse_loc, do_loc,
+                                                     o=o_loc)
+        dq_s = dq_loc[shard.n_ns:].float()
+        if shard.n_strad and shard.world > 1:
+            dist.all_reduce(dq_s)                       # every rank's share of the straddlers' dQ
+        dq = _own_rows(shard, dq_loc, dq_s)
+        dk, dv = halo_return(shard, dk_e), halo_return(shard, dv_e)
+        return None, None, dq, dk, dv, (dak.to(ak.dtype) if dak is not None else None), None
+
+
 def halo_attention(shard, plan, q, k, v, embed_ak=None, scale=None):
-    """Attention for this rank's destinations with the halo exchange.  plan:
-    AttentionPlan(shard.src_h, shard.dst_l, shard.etype_l, shard.n_owned, n_src=shard.n_ext) after
-    shard.build_halo(src, dst).  Differentiable; returns (n_owned, h, d)."""
+    """Attention for this rank's destinations with the halo exchange.  After
+    shard.build_halo(src, dst[, split_straddlers=True]) the plan is
+    AttentionPlan(shard.src_h, shard.dst_l, shard.etype_l, n_dst, n_src=shard.n_ext) with n_dst =
+    shard.n_dst_local when straddlers are split, else shard.n_owned.  q, k, v: (n_owned, h, d) of
+    the nodes this rank owns.  Differentiable; returns (n_owned, h, d).  The gradient of embed_ak
+    is this rank's share (sum it over ranks like any data-parallel parameter gradient)."""
+    import math
     from .attention import bpt_attention
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.size(-1))
+    if getattr(shard, "split", False):
+        return _StraddleAttention.apply(shard, plan, q, k, v, embed_ak, scale)
     return bpt_attention(plan, q, _HaloKV.apply(shard, k), _HaloKV.apply(shard, v), embed_ak, scale)

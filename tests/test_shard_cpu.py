@@ -99,3 +99,83 @@ def test_ownership_partitions_every_level():
         assert sorted(ids.tolist()) == list(range(202))
         sizes = [sh.owned_nodes(nn, shift, r, world).numel() for r in range(world)]
         assert max(sizes) - min(sizes) <= len(nn)
+
+
+def _straddle_worker(rank, world, port, n, k, out):
+    """halo_attention with split straddlers on CPU ranks: the real autograd function (index
+    logic, partial merges, collectives) with the oracle standing in for the two GPU kernels."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import types
+    import oracle
+    from bpt_b200 import shard as sh
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = oracle.binary_partition(n, False, k, 10)
+    N, H, D, T = g["n_nodes"], 2, 8, int(g["etype"].max()) + 1
+    gen = torch.Generator().manual_seed(0)
+    q, kk, v, d_o = [torch.randn(N, H, D, generator=gen) * 0.5 for _ in range(4)]
+    ak = torch.randn(T, D, generator=gen) * 0.5
+    src, dst, et = [torch.from_numpy(g[x]) for x in ("src", "dst", "etype")]
+    s = sh.SequenceShard(src, dst, et, g["n_nodes_arr"], g["shift"], rank, world)
+    s.build_halo(src, dst, split_straddlers=True)
+    src_h, dst_l, et_l = s.src_h.numpy().astype(np.int64), s.dst_l.numpy().astype(np.int64), s.etype_l.numpy()
+    plan = types.SimpleNamespace(in_csr=oracle.coo_to_csr(dst_l, src_h, s.n_dst_local),
+                                 out_csr=oracle.coo_to_csr(src_h, dst_l, s.n_ext), etype=et_l)
+
+    def fwd(plan, q_, k_, v_, ak_, scale):
+        o, lse, _ = oracle.attn_fwd(plan.in_csr, plan.etype, q_.numpy(), k_.numpy(), v_.numpy(), ak_.numpy(), scale)
+        return torch.from_numpy(o).float(), torch.from_numpy(lse).float()
+
+    def bwd(plan, q_, k_, v_, ak_, scale, lse, d_o_, o=None):
+        _, lse_loc, p = oracle.attn_fwd(plan.in_csr, plan.etype, q_.numpy(), k_.numpy(), v_.numpy(), ak_.numpy(), scale)
+        # probabilities against the merged (global) lse of each destination row
+        shift = np.exp(np.nan_to_num(lse_loc - lse.double().numpy(), neginf=0.0))
+        row_of = np.repeat(np.arange(len(plan.in_csr[0]) - 1), np.diff(plan.in_csr[0]))
+        p_glob = np.empty_like(p)
+        p_glob[plan.in_csr[2]] = p[plan.in_csr[2]] * shift[row_of]
+        r = oracle.attn_bwd(plan.in_csr, plan.out_csr, plan.etype, q_.numpy(), k_.numpy(), v_.numpy(), ak_.numpy(),
+                            scale, o.double().numpy(), p_glob, d_o_.numpy())
+        return tuple(torch.from_numpy(x).float() for x in r)
+
+    sh._KERNELS = (fwd, bwd)
+    own = s.owned
+    ql, kl, vl = [x[own].clone().requires_grad_(True) for x in (q, kk, v)]
+    akl = ak.clone().requires_grad_(True)
+    o = sh.halo_attention(s, plan, ql, kl, vl, akl, 0.3)
+    o.backward(d_o[own])
+    dak = akl.grad.clone()
+    dist.all_reduce(dak)
+    csr = oracle.get_csrs(g["src"], g["dst"], N)
+    o_ref, _, p_ref = oracle.attn_fwd(csr[1], g["etype"], q.numpy(), kk.numpy(), v.numpy(), ak.numpy(), 0.3)
+    ref = oracle.attn_bwd(csr[1], csr[0], g["etype"], q.numpy(), kk.numpy(), v.numpy(), ak.numpy(), 0.3, o_ref, p_ref,
+                          d_o.numpy())
+    own_np = own.numpy()
+    errs = [np.abs(o.detach().numpy() - o_ref[own_np]).max(), np.abs(ql.grad.numpy() - ref[0][own_np]).max(),
+            np.abs(kl.grad.numpy() - ref[1][own_np]).max(), np.abs(vl.grad.numpy() - ref[2][own_np]).max(),
+            np.abs(dak.numpy() - ref[3]).max()]
+    info = torch.tensor([s.n_strad, s.n_halo, int(s.eid.numel())])
+    gathered = [torch.zeros(3, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(gathered, info)
+    if rank == 0:
+        out.put((float(max(errs)), [t.tolist() for t in gathered], g["n_edges"]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n,k", [(2, 128, 2), (4, 256, 4)])
+def test_split_straddlers_match_unsharded(world, n, k):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29300 + (os.getpid() % 500) + world
+    procs = [ctx.Process(target=_straddle_worker, args=(r, world, port, n, k, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+        assert p.exitcode == 0
+    err, gathered, E = out.get(timeout=10)
+    assert err < 2e-5                                    # the stand-in kernels return fp32
+    assert all(g[0] == world - 1 for g in gathered)      # world-1 span nodes straddle the ranks' leaf ranges
+    assert sum(g[2] for g in gathered) == E              # every edge is computed by exactly one rank
+    assert max(g[1] for g in gathered) < 2 * n // world  # the halo stays below a shard's own node count

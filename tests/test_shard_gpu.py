@@ -67,7 +67,9 @@ def _nccl_worker(rank, world, port, out):
     from bpt_b200.attention import AttentionPlan
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     gb = graphbuilder.BinaryPartition(2048, False, 4, 10)
     src, dst, et = gb.edges_device()
     N, H, D, T = gb.number_of_nodes, 8, 64, 99
@@ -103,7 +105,24 @@ def _nccl_worker(rank, world, port, out):
     o2.backward(d_o.cuda()[own])
     errs += [rel(o2.detach().double().cpu().numpy(), o_ref[own_np]), rel(ql2.grad.double().cpu().numpy(), ref[0][own_np]),
              rel(kl2.grad.double().cpu().numpy(), ref[1][own_np]), rel(vl2.grad.double().cpu().numpy(), ref[2][own_np])]
-    out.put((rank, max(errs)))
+    # bf16, straddling span nodes split over the ranks and merged (tensor-core kernels)
+    s.build_halo(src, dst, split_straddlers=True)
+    plan_s = AttentionPlan(s.src_h, s.dst_l, s.etype_l, s.n_dst_local, n_etypes=T, n_src=s.n_ext)
+    bf = torch.bfloat16
+    qb, kb, vb, akb, dob = [t.to(bf) for t in (q, k, v, ak, d_o)]
+    ql3, kl3, vl3 = [t.cuda()[own].requires_grad_(True) for t in (qb, kb, vb)]
+    akl3 = akb.cuda().requires_grad_(True)
+    o3 = sh.halo_attention(s, plan_s, ql3, kl3, vl3, akl3, 0.125)
+    o3.backward(dob.cuda()[own])
+    dak3 = akl3.grad.float().clone()
+    dist.all_reduce(dak3)
+    f = lambda t: t.float().numpy()
+    o_rb, _, p_rb = oracle.attn_fwd(csr[1], e_np, f(qb), f(kb), f(vb), f(akb), 0.125)
+    refb = oracle.attn_bwd(csr[1], csr[0], e_np, f(qb), f(kb), f(vb), f(akb), 0.125, o_rb, p_rb, f(dob))
+    errs_bf16 = [rel(o3.detach().double().cpu().numpy(), o_rb[own_np]), rel(ql3.grad.double().cpu().numpy(), refb[0][own_np]),
+                 rel(kl3.grad.double().cpu().numpy(), refb[1][own_np]), rel(vl3.grad.double().cpu().numpy(), refb[2][own_np]),
+                 rel(dak3.double().cpu().numpy(), refb[3])]
+    out.put((rank, max(errs), max(errs_bf16), s.n_strad, s.n_halo))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -119,8 +138,10 @@ def test_two_ranks_over_nccl():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=300)
+        p.join(timeout=200)
         assert p.exitcode == 0
     for _ in range(2):
-        rank, err = out.get(timeout=10)
+        rank, err, err_bf16, n_strad, n_halo = out.get(timeout=10)
         assert err < 1e-5, (rank, err)
+        assert err_bf16 < 2e-2, (rank, err_bf16)
+        assert n_strad == 1 and n_halo < 200, (n_strad, n_halo)

@@ -203,7 +203,7 @@ def halo_exchange(shard, x, group=None):
     """(n_owned, ...) -> (n_owned + n_halo, ...): this rank's rows followed by the remote rows its
     edges name, fetched with one variable-size all-to-all."""
     import torch.distributed as dist
-    if shard.world == 1 or (shard.n_halo == 0 and int(shard.send_all.numel()) == 0):
+    if shard.world == 1:
         return x
     send = x.index_select(0, shard.send_all)
     recv = x.new_empty((shard.n_halo,) + tuple(x.shape[1:]))

@@ -26,7 +26,9 @@ namespace {
 
 constexpr int kHeadDim = 64;
 constexpr int kRowBytes = kHeadDim * 2;                  // one head row of K or V: 128 B = 8 pieces of 16 B
-constexpr int kKvStageBytes = kTileChunk * kRowBytes;    // 8 KB per matrix per stage
+constexpr int kStep = 32;                                // source columns per pipeline step
+constexpr int kStepBytes = kStep * kRowBytes;            // 4 KB: one step's K (or V) rows of one head
+constexpr int kKvStageBytes = 2 * kStepBytes;            // per warp: one K buffer and one V buffer
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -37,6 +39,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(smem_addr));
 }
@@ -52,14 +59,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-// A lane's share of one 64-element head row for the QK^T-type products: the two 16-byte pieces
-// at elements [8t, 8t+8) and [32+8t, 32+8t+8), t = lane % 4.  Words w[2s], w[2s+1] feed k-step s;
-// Q, K and embed_ak rows are all read this way, so the products pair the same elements.
+// A lane's share of one 64-element head row in mma operand order: for k-step s the element pairs
+// at 16s + 2t and 16s + 8 + 2t (t = lane % 4) in w[2s], w[2s+1].  Q rows (A operand, rows g and
+// g+8) and embed_ak rows (B operand, column g) are read this way; K comes through ldmatrix, which
+// hands out the same pairs.
 __device__ __forceinline__ void load_row_frag(const __nv_bfloat16 *__restrict__ row, int t, uint32_t (&w)[8]) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(row + 8 * t));
-    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(row + 32 + 8 * t));
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    const uint32_t *r32 = reinterpret_cast<const uint32_t *>(row);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        w[2 * s] = __ldg(r32 + 8 * s + t);
+        w[2 * s + 1] = __ldg(r32 + 8 * s + 4 + t);
+    }
 }
 
 template <typename ET> struct EtTraits;
@@ -83,19 +93,25 @@ template <typename ET, bool kHasBias>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 attn_forward_tile_kernel(const TcParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: V stages (one per warp, 8 KB) | column ids | table indices of the m-block | tables (fp16, one per warp)
+    // layout: K and V buffers (one pair per warp, 8 KB) | column ids | table indices of the m-block |
+    // tables (fp16, one per warp) | embed_ak rows
     int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKvStageBytes);
     uint16_t *s_idx = reinterpret_cast<uint16_t *>(s_cols + p.max_cols_pad);
     const int idx_stride = p.max_cols_pad + kEtPad;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx + kTileRows * idx_stride);
     const int tab_stride = p.t_max + 8;  // t_max types + the -inf entry, padded; >= 8
+    // embed_ak rows [0, t_max), staged once per block (16-byte aligned: every region before it is)
+    const uint32_t s_ak_addr = static_cast<uint32_t>(
+        __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
 
     const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
     const int ncols_pad = grp[kGroupNcolsPad];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int H = p.H;
-    const uint32_t s_v_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kKvStageBytes));
+    const uint32_t s_k_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kKvStageBytes));
+    const uint32_t s_v_addr = s_k_addr + kStepBytes;
+    const int n_steps = ncols_pad / kStep;
     __half *s_tab = s_tab_all + static_cast<int64_t>(warp) * kTileRows * tab_stride;
     const float sl2 = p.scale * kLog2e;
     const ET *et_base = static_cast<const ET *>(p.et);
@@ -104,6 +120,26 @@ attn_forward_tile_kernel(const TcParams p) {
         const int32_t *gc = p.cols + grp[kGroupColOff];
         for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
     }
+    if (kHasBias) {
+        for (int i = threadIdx.x; i < p.t_max * 8; i += blockDim.x) {
+            const int r = i >> 3, piece = i & 7;
+            const int type = r < p.n_etypes ? r : p.n_etypes - 1;
+            cp_async16(s_ak_addr + r * kRowBytes + ((piece ^ (r & 7)) << 4),
+                       p.ak + static_cast<int64_t>(type) * kHeadDim + piece * 8);
+        }
+    }
+    cp_async_commit();
+
+    // 32 rows of K or V of head h for step j -> the warp's buffer (16-byte pieces, piece index XOR (row & 7))
+    auto issue_rows = [&](uint32_t dst, const __nv_bfloat16 *__restrict__ base, int h, int j) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int id = i * 32 + lane;
+            const int r = id >> 3, piece = id & 7;
+            cp_async16(dst + r * kRowBytes + ((piece ^ (r & 7)) << 4),
+                       base + (static_cast<int64_t>(s_cols[j * kStep + r]) * H + h) * kHeadDim + piece * 8);
+        }
+    };
 
     for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
         const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
@@ -111,7 +147,27 @@ attn_forward_tile_kernel(const TcParams p) {
         const int tq = use_qr ? mb[kMbTq] : 0;            // table entry tq (or 1) is the -inf entry
         const uint32_t none_idx = use_qr ? tq : 1;
         const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
+        // first step after j whose 64-column chunk has an edge in this m-block; n_steps if none
+        auto next_step = [&](int j) {
+            ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 1)) & 1u)) ++j;
+            return j;
+        };
         __syncthreads();  // previous m-block's indices are no longer read; s_cols is visible
+        // The warp's first K and V rows start travelling now; the cells, Q and the table follow
+        // while they are in flight.
+        int primed_step = -1;
+        if (warp < H) primed_step = next_step(-1);
+        if (primed_step >= 0 && primed_step < n_steps) issue_rows(s_k_addr, p.k, warp, primed_step);
+        cp_async_commit();
+        if (primed_step >= 0 && primed_step < n_steps) issue_rows(s_v_addr, p.v, warp, primed_step);
+        cp_async_commit();
+        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
+        uint32_t q_lo[8], q_hi[8];
+        if (warp < H) {
+            load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + warp) * kHeadDim, t, q_lo);
+            load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + warp) * kHeadDim, t, q_hi);
+        }
         {
             // stage the m-block's cells as table indices: edge type, or the -inf entry; 16 bytes of
             // cells per thread and step (the matrix is [chunk][16][64], so a piece stays in one row)
@@ -130,25 +186,27 @@ attn_forward_tile_kernel(const TcParams p) {
                     dst[u] = static_cast<uint16_t>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
             }
         }
+        cp_async_wait<2>();  // embed_ak rows have landed (the two newest groups are the first K and V)
         __syncthreads();
 
-        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
         for (int h = warp; h < H; h += kWarps) {
-            uint32_t q_lo[8], q_hi[8];
-            load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim, t, q_lo);
-            load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim, t, q_hi);
+            if (h != warp) {
+                load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim, t, q_lo);
+                load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim, t, q_hi);
+            }
             float bias_lo = 0.f, bias_hi = 0.f;  // per-row constant of m-blocks without a table (log2 domain)
             if (use_qr) {
                 // table[row][type] = scale * log2(e) * <q[row], ak[type]> for the types of this m-block
                 for (int nt = 0; nt < tq; nt += 8) {
-                    int type = nt + g;
-                    type = type < p.n_etypes ? type : p.n_etypes - 1;
-                    uint32_t b[8];
-                    load_row_frag(p.ak + static_cast<int64_t>(type) * kHeadDim, t, b);
+                    const int r = nt + (lane & 7), pc = lane >> 3;
+                    uint32_t b0[4], b1[4];
+                    ldmatrix_x4(b0, s_ak_addr + r * kRowBytes + ((pc ^ (r & 7)) << 4));
+                    ldmatrix_x4(b1, s_ak_addr + r * kRowBytes + (((pc + 4) ^ (r & 7)) << 4));
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int s = 0; s < 4; ++s)
-                        mma_bf16(c, q_lo[2 * s], q_hi[2 * s], q_lo[2 * s + 1], q_hi[2 * s + 1], b[2 * s], b[2 * s + 1]);
+                    mma_bf16(c, q_lo[0], q_hi[0], q_lo[1], q_hi[1], b0[0], b0[1]);
+                    mma_bf16(c, q_lo[2], q_hi[2], q_lo[3], q_hi[3], b0[2], b0[3]);
+                    mma_bf16(c, q_lo[4], q_hi[4], q_lo[5], q_hi[5], b1[0], b1[1]);
+                    mma_bf16(c, q_lo[6], q_hi[6], q_lo[7], q_hi[7], b1[2], b1[3]);
                     *reinterpret_cast<__half2 *>(s_tab + g * tab_stride + nt + 2 * t) =
                         __floats2half2_rn(c[0] * sl2, c[1] * sl2);
                     *reinterpret_cast<__half2 *>(s_tab + (g + 8) * tab_stride + nt + 2 * t) =
@@ -192,33 +250,44 @@ attn_forward_tile_kernel(const TcParams p) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) { acc[i][0] = 0.f; acc[i][1] = 0.f; acc[i][2] = 0.f; acc[i][3] = 0.f; }
 
-            for (int c0 = 0; c0 < ncols_pad; c0 += kTileChunk) {
-                if (!((chunk_mask >> (c0 / kTileChunk)) & 1u)) continue;
-                // V rows of this step -> shared memory, 16-byte pieces, piece index XOR (row & 7)
-#pragma unroll 4
-                for (int i = 0; i < 16; ++i) {
-                    const int id = i * 32 + lane;
-                    const int r = id >> 3, piece = id & 7;
-                    cp_async16(s_v_addr + r * kRowBytes + ((piece ^ (r & 7)) << 4),
-                               p.v + (static_cast<int64_t>(s_cols[c0 + r]) * H + h) * kHeadDim + piece * 8);
-                }
+            // Software pipeline over the active 32-column steps: K and V each have one buffer; K of
+            // the next step is fetched while this step's softmax and PV run, V of the next step while
+            // the next step's QK^T runs.  Every iteration commits two cp.async groups (possibly empty),
+            // so "all but the newest group" is always the data the next phase needs.
+            int j = primed_step;
+            if (j < 0) {
+                j = next_step(-1);
+                if (j < n_steps) issue_rows(s_k_addr, p.k, h, j);
                 cp_async_commit();
-                // S = Q K^T for 8 column groups of 8
-                float s[8][4];
+                if (j < n_steps) issue_rows(s_v_addr, p.v, h, j);
+                cp_async_commit();
+            }
+            primed_step = -1;
+            while (j < n_steps) {
+                const int nj = next_step(j);
+                const int c0 = j * kStep;
+                cp_async_wait<1>();  // K of this step has landed
+                __syncwarp();
+                float s[4][4];
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
-                    uint32_t b[8];
-                    load_row_frag(p.k + (static_cast<int64_t>(s_cols[c0 + nt * 8 + g]) * H + h) * kHeadDim, t, b);
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int r = nt * 8 + (lane & 7), pc = lane >> 3;
+                    uint32_t b0[4], b1[4];
+                    ldmatrix_x4(b0, s_k_addr + r * kRowBytes + ((pc ^ (r & 7)) << 4));
+                    ldmatrix_x4(b1, s_k_addr + r * kRowBytes + (((pc + 4) ^ (r & 7)) << 4));
                     s[nt][0] = 0.f; s[nt][1] = 0.f; s[nt][2] = 0.f; s[nt][3] = 0.f;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        mma_bf16(s[nt], q_lo[2 * ks], q_hi[2 * ks], q_lo[2 * ks + 1], q_hi[2 * ks + 1], b[2 * ks],
-                                 b[2 * ks + 1]);
+                    mma_bf16(s[nt], q_lo[0], q_hi[0], q_lo[1], q_hi[1], b0[0], b0[1]);
+                    mma_bf16(s[nt], q_lo[2], q_hi[2], q_lo[3], q_hi[3], b0[2], b0[3]);
+                    mma_bf16(s[nt], q_lo[4], q_hi[4], q_lo[5], q_hi[5], b1[0], b1[1]);
+                    mma_bf16(s[nt], q_lo[6], q_hi[6], q_lo[7], q_hi[7], b1[2], b1[3]);
                 }
+                __syncwarp();  // every lane has read K: its buffer may be refilled
+                if (nj < n_steps) issue_rows(s_k_addr, p.k, h, nj);
+                cp_async_commit();
                 // scale, relative-position term and mask: one table entry per cell
                 float cmax_lo = -INFINITY, cmax_hi = -INFINITY;
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
+                for (int nt = 0; nt < 4; ++nt) {
                     const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c0 + nt * 8 + 2 * t);
                     const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c0 + nt * 8 + 2 * t);
                     s[nt][0] = fmaf(s[nt][0], sl2, __half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]));
@@ -247,7 +316,7 @@ attn_forward_tile_kernel(const TcParams p) {
                     m_hi = mn_hi;
                 }
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
+                for (int nt = 0; nt < 4; ++nt) {
                     s[nt][0] = exp2f(s[nt][0] - ms_lo);
                     s[nt][1] = exp2f(s[nt][1] - ms_lo);
                     s[nt][2] = exp2f(s[nt][2] - ms_hi);
@@ -256,10 +325,10 @@ attn_forward_tile_kernel(const TcParams p) {
                     l_hi += s[nt][2] + s[nt][3];
                 }
                 // O += P V
-                cp_async_wait<0>();
+                cp_async_wait<1>();  // V of this step has landed (the newest group is the next K)
                 __syncwarp();
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
+                for (int ks = 0; ks < 2; ++ks) {
                     const uint32_t a0 = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
                     const uint32_t a1 = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
                     const uint32_t a2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
@@ -274,8 +343,12 @@ attn_forward_tile_kernel(const TcParams p) {
                         mma_bf16(acc[dn + 1], a0, a1, a2, a3, b[2], b[3]);
                     }
                 }
-                __syncwarp();  // the stage is rewritten by the next step
+                __syncwarp();  // every lane has read V: its buffer may be refilled
+                if (nj < n_steps) issue_rows(s_v_addr, p.v, h, nj);
+                cp_async_commit();
+                j = nj;
             }
+            cp_async_wait<0>();
 
             // row sums live per lane: finish them across the quad
             l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -316,7 +389,7 @@ attn_forward_tile_kernel(const TcParams p) {
 size_t tc_smem_bytes(int max_cols_pad, int t_max) {
     return static_cast<size_t>(kWarps) * kKvStageBytes + static_cast<size_t>(max_cols_pad) * 4 +
            static_cast<size_t>(kTileRows) * (max_cols_pad + kEtPad) * 2 +
-           static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2;
+           static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2 + static_cast<size_t>(t_max) * kRowBytes;
 }
 
 template <typename ET, bool kHasBias>

@@ -371,14 +371,15 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
 
 // ------------------------------------------------------------------ backward, pass over type buckets
 
-// kPacked: the per-edge scratch is one 32-bit word {bf16 p, bf16 dS} per (edge, head), passed as P.
+// kPacked: the per-edge scratch is one 32-bit word {bf16 p, bf16 dS}, laid out [head][in-CSR position]
+// with `ps_edges` positions per head, passed as P.
 template <typename T, int LPH, bool kVec, bool kPacked = false>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int32_t *__restrict__ et_dst,
                          const int32_t *__restrict__ et_inpos, const T *__restrict__ q,
                          const float *__restrict__ P, const float *__restrict__ dP,
                          const float *__restrict__ delta, float scale, float *__restrict__ dak,
-                         float *__restrict__ part_dak, Geometry g) {
+                         float *__restrict__ part_dak, Geometry g, int64_t ps_edges = 0) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * kWarpsPerBlock + warp;
@@ -402,7 +403,7 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
                 const int64_t pos = et_inpos[j];
                 float ds;
                 if (kPacked)
-                    ds = __uint_as_float(reinterpret_cast<const uint32_t *>(P)[pos * H + head] & 0xffff0000u);
+                    ds = __uint_as_float(reinterpret_cast<const uint32_t *>(P)[head * ps_edges + pos] & 0xffff0000u);
                 else
                     ds = scale * P[pos * H + head] * (dP[pos * H + head] - delta[static_cast<int64_t>(dst) * H + head]);
                 float qf[16];
@@ -433,7 +434,7 @@ template <typename T, int LPH, bool kVec>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
                            const int32_t *__restrict__ row_uniform, int n_rows, const T *__restrict__ ak,
-                           const uint32_t *__restrict__ PS, T *__restrict__ dq, Geometry g) {
+                           const uint32_t *__restrict__ PS, int64_t ps_edges, T *__restrict__ dq, Geometry g) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerBlock + warp;
@@ -451,7 +452,7 @@ attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t 
     const int beg = in_indptr[row], end = in_indptr[row + 1];
 #pragma unroll 4
     for (int j = beg; j < end; ++j) {
-        const float ds = __uint_as_float(PS[static_cast<int64_t>(j) * H + head] & 0xffff0000u);
+        const float ds = __uint_as_float(PS[head * ps_edges + j] & 0xffff0000u);
         float af[16];
         load16<T, kVec>(ak + static_cast<int64_t>(in_etype[j]) * D + d0, nvalid, af);
 #pragma unroll
@@ -685,14 +686,14 @@ int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, cons
     if (p.n_nodes > 0) {
         const dim3 grid(static_cast<unsigned>((p.n_nodes + kWarpsPerBlock - 1) / kWarpsPerBlock), (H + hpw - 1) / hpw);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_ak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.in_indptr, p.in_etype, p.row_uniform, static_cast<int>(p.n_nodes), ak, PS, dq, g)));
+            p.in_indptr, p.in_etype, p.row_uniform, static_cast<int>(p.n_nodes), ak, PS, p.n_edges, dq, g)));
         BPT_LAUNCH_CHECK();
     }
     if (dak != nullptr && counts[6] > 0) {
         const dim3 grid((counts[6] + kWarpsPerBlock - 1) / kWarpsPerBlock, 1);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC, true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
             p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, reinterpret_cast<const float *>(PS), nullptr,
-            nullptr, 1.f, dak, part_dak, g)));
+            nullptr, 1.f, dak, part_dak, g, p.n_edges)));
         BPT_LAUNCH_CHECK();
         if (counts[8] > 0) {
             sum_merge_kernel<float><<<counts[8], 128, 0, stream>>>(p.et_work.split_rows, counts[8], part_dak, D, 1,

@@ -8,9 +8,10 @@
 // The destination-side kernel has already left one word {bf16 p, bf16 dS} per (edge, head) in
 // scratch, so a cell's two weights are one gather away:
 //     dV[src] = sum_dst p * dO[dst],   dK[src] = sum_dst dS * q[dst].
-// One block per m-block, one warp per head; per 32 destinations the warp stages their dO and Q
-// rows in swizzled shared memory (cp.async), packs the gathered weights into mma A fragments
-// and accumulates both products with ldmatrix.trans B fragments.  A source row wholly inside
+// One block per m-block, one warp per head; per 16 destinations the warp stages their dO and Q
+// rows in swizzled shared memory (cp.async, two buffers so that the next step's rows and
+// weights travel while this step's products run), packs the gathered weights into mma A
+// fragments and accumulates both products with ldmatrix.trans B fragments.  A source row wholly inside
 // one m-block is written once; rows spread over several m-blocks write fp32 partials that are
 // summed in slot order.  No atomics: results are bitwise reproducible.
 #include <cublas_v2.h>
@@ -30,6 +31,8 @@ constexpr int kHalf = 32;                               // destinations staged p
 constexpr int kRowBytes = kHeadDim * 2;
 constexpr int kStageBytes = kHalf * kRowBytes;          // 4 KB per matrix
 constexpr int kPosPad = 4;                              // int32 padding per staged position row
+constexpr int kDkvStep = 16;                            // destinations per pipeline step of the dK/dV kernel
+constexpr int kDkvBufBytes = 2 * kDkvStep * kRowBytes;  // one buffer: dO rows then Q rows of a step (4 KB)
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -48,6 +51,7 @@ __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *gptr)
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
@@ -55,7 +59,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct DkvParams {
     const int32_t *groups, *mblocks, *cols, *cellpos;
-    const uint32_t *PS;  // per (edge, head): {bf16 p (low half), bf16 dS (high half)}, in-CSR order
+    const uint32_t *PS;  // [head][in-CSR position]: {bf16 p (low half), bf16 dS (high half)}
+    int64_t n_edges;
     const __nv_bfloat16 *q, *d_o;
     __nv_bfloat16 *dk, *dv;
     float *part;
@@ -76,15 +81,54 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
     const int g = lane >> 2, t = lane & 3;
     const int H = p.H;
     const uint32_t s_do = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * 2 * kStageBytes));
-    const uint32_t s_q = s_do + kStageBytes;
     {
         const int32_t *gc = p.cols + grp[kGroupColOff];
         for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
     }
+    const int n_steps = ncols_pad / kDkvStep;
+    // dO and Q rows of head h for the 16 destinations of step j -> buffer b of the warp
+    auto issue_rows = [&](int h, int j, int b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int id = i * 32 + lane;
+            const int r = id >> 3, piece = id & 7;
+            const int64_t off = (static_cast<int64_t>(s_cols[j * kDkvStep + r]) * H + h) * kHeadDim + piece * 8;
+            const uint32_t dst = b * kDkvBufBytes + r * kRowBytes + ((piece ^ (r & 7)) << 4);
+            cp_async16(s_do + dst, p.d_o + off);
+            cp_async16(s_do + kDkvBufBytes / 2 + dst, p.q + off);
+        }
+    };
     for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
         const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
         const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
+        // first step after j whose 64-column chunk has a cell in this m-block; n_steps if none
+        auto next_step = [&](int j) {
+            ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 2)) & 1u)) ++j;
+            return j;
+        };
+        // packed {p, dS} words of this lane's 8 cells of step j: rows g / g+8, destinations 8nt + 2t, +1
+        auto gather_weights = [&](int h, int j, uint32_t (&w)[8]) {
+            const uint32_t *__restrict__ ps_h = p.PS + static_cast<int64_t>(h) * p.n_edges;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int c = j * kDkvStep + nt * 8 + 2 * t;
+                const int2 pos_lo = *reinterpret_cast<const int2 *>(s_pos + g * pos_stride + c);
+                const int2 pos_hi = *reinterpret_cast<const int2 *>(s_pos + (g + 8) * pos_stride + c);
+                w[4 * nt + 0] = pos_lo.x >= 0 ? __ldg(ps_h + pos_lo.x) : 0u;
+                w[4 * nt + 1] = pos_lo.y >= 0 ? __ldg(ps_h + pos_lo.y) : 0u;
+                w[4 * nt + 2] = pos_hi.x >= 0 ? __ldg(ps_h + pos_hi.x) : 0u;
+                w[4 * nt + 3] = pos_hi.y >= 0 ? __ldg(ps_h + pos_hi.y) : 0u;
+            }
+        };
         __syncthreads();
+        // the first head's first rows start travelling before the cells are staged
+        int primed_step = -1;
+        if (warp < H) {
+            primed_step = next_step(-1);
+            if (primed_step < n_steps) issue_rows(warp, primed_step, 0);
+        }
+        cp_async_commit();
         {
             // the cell matrix is [chunk][16][64]; 4 positions (16 bytes) per thread and step
             const int4 *gp = reinterpret_cast<const int4 *>(p.cellpos + mb[kMbEtOff]);
@@ -104,58 +148,55 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
             for (int i = 0; i < 8; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { dk[i][j] = 0.f; dv[i][j] = 0.f; }
-            for (int c0 = 0; c0 < ncols_pad; c0 += kHalf) {
-                if (!((chunk_mask >> (c0 / kTileChunk)) & 1u)) continue;
-                // dO and Q rows of these 32 destinations -> shared memory
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int id = i * 32 + lane;
-                    const int r = id >> 3, piece = id & 7;
-                    const int64_t off = (static_cast<int64_t>(s_cols[c0 + r]) * H + h) * kHeadDim + piece * 8;
-                    const uint32_t dst = r * kRowBytes + ((piece ^ (r & 7)) << 4);
-                    cp_async16(s_do + dst, p.d_o + off);
-                    cp_async16(s_q + dst, p.q + off);
+            // Two buffers: while the products of one step run, the next step's rows (cp.async) and
+            // weights (registers) are in flight.  One cp.async group per iteration, possibly empty.
+            int j = primed_step;
+            if (j < 0) {
+                j = next_step(-1);
+                if (j < n_steps) issue_rows(h, j, 0);
+                cp_async_commit();
+            }
+            primed_step = -1;
+            uint32_t w[8];
+            if (j < n_steps) gather_weights(h, j, w);
+            int buf = 0;
+            while (j < n_steps) {
+                const int nj = next_step(j);
+                uint32_t wn[8];
+                if (nj < n_steps) {
+                    issue_rows(h, nj, buf ^ 1);
+                    gather_weights(h, nj, wn);
                 }
                 cp_async_commit();
-                // weights of this lane's 16 cells: rows g / g+8, destinations c0 + 8nt + 2t, +1; each
-                // is one packed word {p, dS}; A fragments are pairs of low halves / high halves
-                uint32_t wp[4][2], ws[4][2];
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    const int c = c0 + nt * 8 + 2 * t;
-                    const int2 pos_lo = *reinterpret_cast<const int2 *>(s_pos + g * pos_stride + c);
-                    const int2 pos_hi = *reinterpret_cast<const int2 *>(s_pos + (g + 8) * pos_stride + c);
-                    const uint32_t w0 = pos_lo.x >= 0 ? p.PS[static_cast<int64_t>(pos_lo.x) * H + h] : 0u;
-                    const uint32_t w1 = pos_lo.y >= 0 ? p.PS[static_cast<int64_t>(pos_lo.y) * H + h] : 0u;
-                    const uint32_t w2 = pos_hi.x >= 0 ? p.PS[static_cast<int64_t>(pos_hi.x) * H + h] : 0u;
-                    const uint32_t w3 = pos_hi.y >= 0 ? p.PS[static_cast<int64_t>(pos_hi.y) * H + h] : 0u;
-                    wp[nt][0] = __byte_perm(w0, w1, 0x5410);
-                    wp[nt][1] = __byte_perm(w2, w3, 0x5410);
-                    ws[nt][0] = __byte_perm(w0, w1, 0x7632);
-                    ws[nt][1] = __byte_perm(w2, w3, 0x7632);
-                }
-                cp_async_wait_all();
+                cp_async_wait_one();  // this step's rows have landed; the newest group is the next step's
                 __syncwarp();
-#pragma unroll
-                for (int ks = 0; ks < 2; ++ks) {
-                    const uint32_t p0 = wp[2 * ks][0], p1 = wp[2 * ks][1], p2 = wp[2 * ks + 1][0], p3 = wp[2 * ks + 1][1];
-                    const uint32_t s0 = ws[2 * ks][0], s1 = ws[2 * ks][1], s2 = ws[2 * ks + 1][0], s3 = ws[2 * ks + 1][1];
-                    const int r = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                {
+                    // A fragments: pairs of low halves (p) / high halves (dS) of the packed words
+                    const uint32_t p0 = __byte_perm(w[0], w[1], 0x5410), p1 = __byte_perm(w[2], w[3], 0x5410);
+                    const uint32_t p2 = __byte_perm(w[4], w[5], 0x5410), p3 = __byte_perm(w[6], w[7], 0x5410);
+                    const uint32_t s0 = __byte_perm(w[0], w[1], 0x7632), s1 = __byte_perm(w[2], w[3], 0x7632);
+                    const uint32_t s2 = __byte_perm(w[4], w[5], 0x7632), s3 = __byte_perm(w[6], w[7], 0x7632);
+                    const int r = ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
                     for (int dn = 0; dn < 8; dn += 2) {
                         const int piece = dn + (lane >> 4);
-                        const uint32_t off = r * kRowBytes + ((piece ^ (r & 7)) << 4);
+                        const uint32_t off = buf * kDkvBufBytes + r * kRowBytes + ((piece ^ (r & 7)) << 4);
                         uint32_t b[4];
                         ldmatrix_x4_trans(b, s_do + off);
                         mma_bf16(dv[dn], p0, p1, p2, p3, b[0], b[1]);
                         mma_bf16(dv[dn + 1], p0, p1, p2, p3, b[2], b[3]);
-                        ldmatrix_x4_trans(b, s_q + off);
+                        ldmatrix_x4_trans(b, s_do + kDkvBufBytes / 2 + off);
                         mma_bf16(dk[dn], s0, s1, s2, s3, b[0], b[1]);
                         mma_bf16(dk[dn + 1], s0, s1, s2, s3, b[2], b[3]);
                     }
                 }
-                __syncwarp();  // the stages are rewritten by the next step
+                __syncwarp();  // this buffer is refilled by the step after next
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[i] = wn[i];
+                j = nj;
+                buf ^= 1;
             }
+            cp_async_wait_all();
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = half ? row_hi : row_lo;
@@ -231,7 +272,8 @@ struct DqParams {
     const void *et;
     const __nv_bfloat16 *q, *k, *v, *ak, *o, *d_o;
     const float *lse;
-    uint32_t *PS;
+    uint32_t *PS;  // [head][in-CSR position]
+    int64_t n_edges;
     float *part_dq;
     __nv_bfloat16 *dq;
     int n_etypes, H, max_cols_pad, t_max;
@@ -242,12 +284,15 @@ template <typename ET, bool kHasBias>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 attn_backward_dq_tile_kernel(const DqParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: K stages (one per warp, 8 KB) | column ids | table indices of the m-block | tables (fp16, per warp)
+    // layout: K stages (one per warp, 8 KB) | column ids | table indices of the m-block | tables (fp16, per warp) |
+    // embed_ak rows [0, t_max)
     int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKStageBytes);
     uint16_t *s_idx = reinterpret_cast<uint16_t *>(s_cols + p.max_cols_pad);
     const int idx_stride = p.max_cols_pad + kIdxPad;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx + kTileRows * idx_stride);
     const int tab_stride = p.t_max + 8;
+    const uint32_t s_ak = static_cast<uint32_t>(
+        __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
 
     const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
     const int ncols_pad = grp[kGroupNcolsPad];
@@ -262,6 +307,24 @@ attn_backward_dq_tile_kernel(const DqParams p) {
         const int32_t *gc = p.cols + grp[kGroupColOff];
         for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
     }
+    if (kHasBias) {
+        for (int i = threadIdx.x; i < p.t_max * 8; i += blockDim.x) {
+            const int r = i >> 3, piece = i & 7;
+            const int type = r < p.n_etypes ? r : p.n_etypes - 1;
+            cp_async16(s_ak + r * kRowBytes + ((piece ^ (r & 7)) << 4), p.ak + static_cast<int64_t>(type) * kHeadDim + piece * 8);
+        }
+    }
+    cp_async_commit();
+    // K rows of head h for the 64 columns from c0 -> the warp's stage
+    auto issue_k = [&](int h, int c0) {
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+            const int id = i * 32 + lane;
+            const int r = id >> 3, piece = id & 7;
+            cp_async16(s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4),
+                       p.k + (static_cast<int64_t>(s_cols[c0 + r]) * H + h) * kHeadDim + piece * 8);
+        }
+    };
     for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
         const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
         const bool use_qr = kHasBias && mb[kMbQrSlot] >= 0;
@@ -269,7 +332,50 @@ attn_backward_dq_tile_kernel(const DqParams p) {
         const uint32_t none_idx = use_qr ? tq : 1;
         const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
         const int32_t *cell_pos = p.cellpos + mb[kMbEtOff];
+        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
+        uint32_t q_lo[8], q_hi[8], do_lo[8], do_hi[8];
+        float delta_lo = 0.f, delta_hi = 0.f, lse2_lo = 0.f, lse2_hi = 0.f;
+        // a head's rows of Q and dO, delta = <dO, O> and lse (log2 domain) of the two rows of this lane
+        auto load_head = [&](int h) {
+            const int64_t off_lo = (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim;
+            const int64_t off_hi = (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim;
+            load_a_row(p.q + off_lo, t, q_lo);
+            load_a_row(p.q + off_hi, t, q_hi);
+            load_row_frag(p.d_o + off_lo, t, do_lo);
+            load_row_frag(p.d_o + off_hi, t, do_hi);
+            uint32_t o_lo[8], o_hi[8];
+            load_row_frag(p.o + off_lo, t, o_lo);
+            load_row_frag(p.o + off_hi, t, o_hi);
+            lse2_lo = row_lo < 0 ? 0.f : p.lse[static_cast<int64_t>(row_lo) * H + h];
+            lse2_hi = row_hi < 0 ? 0.f : p.lse[static_cast<int64_t>(row_hi) * H + h];
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&do_lo[i]));
+                const float2 y0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&o_lo[i]));
+                const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&do_hi[i]));
+                const float2 y1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&o_hi[i]));
+                a = fmaf(x0.x, y0.x, fmaf(x0.y, y0.y, a));
+                b = fmaf(x1.x, y1.x, fmaf(x1.y, y1.y, b));
+            }
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 2);
+            delta_lo = a;
+            delta_hi = b;
+            lse2_lo = lse2_lo == -INFINITY ? 0.f : lse2_lo * kLog2e;
+            lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
+        };
         __syncthreads();
+        // The first head's K rows and operand rows start travelling before the cells are staged.
+        int primed_c0 = -1;
+        if (warp < H && chunk_mask != 0u) {
+            primed_c0 = (__ffs(chunk_mask) - 1) * kTileChunk;
+            if (primed_c0 < ncols_pad) issue_k(warp, primed_c0); else primed_c0 = -1;
+        }
+        cp_async_commit();
+        if (warp < H) load_head(warp);
         {
             constexpr int kCellsPerPiece = 16 / static_cast<int>(sizeof(ET));
             const uint4 *ge = reinterpret_cast<const uint4 *>(et_base + mb[kMbEtOff]);
@@ -286,54 +392,22 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                     dst[u] = static_cast<uint16_t>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
             }
         }
+        cp_async_wait_one();  // embed_ak rows have landed; the newest group is the first K
         __syncthreads();
 
-        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
         for (int h = warp; h < H; h += kWarps) {
-            const int64_t off_lo = (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim;
-            const int64_t off_hi = (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim;
-            uint32_t q_lo[8], q_hi[8], do_lo[8], do_hi[8];
-            load_a_row(p.q + off_lo, t, q_lo);
-            load_a_row(p.q + off_hi, t, q_hi);
-            load_row_frag(p.d_o + off_lo, t, do_lo);
-            load_row_frag(p.d_o + off_hi, t, do_hi);
-            // delta = <dO, O> of the two rows
-            float delta_lo, delta_hi;
-            {
-                uint32_t o_lo[8], o_hi[8];
-                load_row_frag(p.o + off_lo, t, o_lo);
-                load_row_frag(p.o + off_hi, t, o_hi);
-                float a = 0.f, b = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&do_lo[i]));
-                    const float2 y0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&o_lo[i]));
-                    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&do_hi[i]));
-                    const float2 y1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&o_hi[i]));
-                    a = fmaf(x0.x, y0.x, fmaf(x0.y, y0.y, a));
-                    b = fmaf(x1.x, y1.x, fmaf(x1.y, y1.y, b));
-                }
-                a += __shfl_xor_sync(0xffffffffu, a, 1);
-                a += __shfl_xor_sync(0xffffffffu, a, 2);
-                b += __shfl_xor_sync(0xffffffffu, b, 1);
-                b += __shfl_xor_sync(0xffffffffu, b, 2);
-                delta_lo = a;
-                delta_hi = b;
-            }
-            float lse2_lo = row_lo < 0 ? 0.f : p.lse[static_cast<int64_t>(row_lo) * H + h];
-            float lse2_hi = row_hi < 0 ? 0.f : p.lse[static_cast<int64_t>(row_hi) * H + h];
-            lse2_lo = lse2_lo == -INFINITY ? 0.f : lse2_lo * kLog2e;
-            lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
+            if (h != warp) load_head(h);
             if (use_qr) {
                 for (int nt = 0; nt < tq; nt += 8) {
-                    int type = nt + g;
-                    type = type < p.n_etypes ? type : p.n_etypes - 1;
-                    uint32_t b[8];
-                    load_a_row(p.ak + static_cast<int64_t>(type) * kHeadDim, t, b);
+                    const int r = nt + (lane & 7), pc = lane >> 3;
+                    uint32_t b0[4], b1[4];
+                    ldmatrix_x4(b0, s_ak + r * kRowBytes + ((pc ^ (r & 7)) << 4));
+                    ldmatrix_x4(b1, s_ak + r * kRowBytes + (((pc + 4) ^ (r & 7)) << 4));
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int s = 0; s < 4; ++s)
-                        mma_bf16(c, q_lo[2 * s], q_hi[2 * s], q_lo[2 * s + 1], q_hi[2 * s + 1], b[2 * s], b[2 * s + 1]);
+                    mma_bf16(c, q_lo[0], q_hi[0], q_lo[1], q_hi[1], b0[0], b0[1]);
+                    mma_bf16(c, q_lo[2], q_hi[2], q_lo[3], q_hi[3], b0[2], b0[3]);
+                    mma_bf16(c, q_lo[4], q_hi[4], q_lo[5], q_hi[5], b1[0], b1[1]);
+                    mma_bf16(c, q_lo[6], q_hi[6], q_lo[7], q_hi[7], b1[2], b1[3]);
                     *reinterpret_cast<__half2 *>(s_tab + g * tab_stride + nt + 2 * t) = __floats2half2_rn(c[0] * sl2, c[1] * sl2);
                     *reinterpret_cast<__half2 *>(s_tab + (g + 8) * tab_stride + nt + 2 * t) = __floats2half2_rn(c[2] * sl2, c[3] * sl2);
                 }
@@ -372,16 +446,11 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             float acc[8][4];
 #pragma unroll
             for (int i = 0; i < 8; ++i) { acc[i][0] = 0.f; acc[i][1] = 0.f; acc[i][2] = 0.f; acc[i][3] = 0.f; }
+            uint32_t *__restrict__ ps_h = p.PS + static_cast<int64_t>(h) * p.n_edges;
 
             for (int c0 = 0; c0 < ncols_pad; c0 += kTileChunk) {
                 if (!((chunk_mask >> (c0 / kTileChunk)) & 1u)) continue;
-#pragma unroll 4
-                for (int i = 0; i < 16; ++i) {
-                    const int id = i * 32 + lane;
-                    const int r = id >> 3, piece = id & 7;
-                    cp_async16(s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4),
-                               p.k + (static_cast<int64_t>(s_cols[c0 + r]) * H + h) * kHeadDim + piece * 8);
-                }
+                if (!(h == warp && c0 == primed_c0)) issue_k(h, c0);
                 cp_async_commit();
                 const int32_t *chunk_pos = cell_pos + static_cast<int64_t>(c0 / kTileChunk) * kTileRows * kTileChunk;
 #pragma unroll
@@ -435,7 +504,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                         for (int i = 0; i < 4; ++i) {
                             const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
                             s[nt][i] = p.scale * pr * (dp[nt][i] - (i < 2 ? delta_lo : delta_hi));
-                            if (pos[i] >= 0) p.PS[static_cast<int64_t>(pos[i]) * H + h] = pack_bf16(pr, s[nt][i]);
+                            if (pos[i] >= 0) ps_h[pos[i]] = pack_bf16(pr, s[nt][i]);
                         }
                     }
                     // dQ += dS K
@@ -483,12 +552,15 @@ attn_backward_dq_tile_kernel(const DqParams p) {
 // G[row, h, t] = sum of dS over the row's edges of type t (zero rows for rows whose edges share one
 // type: their dS sums to zero).  With it the two relative-position gradients are plain GEMMs:
 //     dQ[row, h, :] += G[row, h, :] . embed_ak          d embed_ak = G^T . Q
-// One warp per destination row; one lane per head walks the row's edges in order, so the sums
-// have a fixed order.  G is bf16, (n_nodes * H, tq).
+// One warp per destination row, 32 edges at a time (one per lane, coalesced per head).  When the
+// 32 types differ (the usual case: a leaf's edges all differ in level or offset) the lanes add
+// into their own bins at once; otherwise they add one after the other in lane order.  Either
+// way every bin sees its edges in CSR order, so the sums have a fixed order.
+// G is bf16, (n_nodes * H, tq); PS is [head][in-CSR position].
 __global__ void __launch_bounds__(128)
 build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
                         const int32_t *__restrict__ row_uniform, int n_rows, const uint32_t *__restrict__ PS,
-                        __nv_bfloat16 *__restrict__ G, int H, int tq) {
+                        int64_t n_edges, __nv_bfloat16 *__restrict__ G, int H, int tq) {
     extern __shared__ float s_g[];  // [4 warps][H][tq]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;
@@ -503,10 +575,24 @@ build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__
     for (int i = lane; i < cells; i += 32) g[i] = 0.f;
     __syncwarp();
     const int beg = in_indptr[row], end = in_indptr[row + 1];
-    for (int h = lane; h < H; h += 32)
-        for (int j = beg; j < end; ++j)
-            g[h * tq + in_etype[j]] += __uint_as_float(PS[static_cast<int64_t>(j) * H + h] & 0xffff0000u);
-    __syncwarp();
+    for (int j0 = beg; j0 < end; j0 += 32) {
+        const int j = j0 + lane;
+        const bool valid = j < end;
+        const int type = valid ? in_etype[j] : -1 - lane;  // idle lanes get distinct keys
+        const bool distinct = __all_sync(0xffffffffu, __match_any_sync(0xffffffffu, type) == (1u << lane));
+        for (int h = 0; h < H; ++h) {
+            const float ds = valid ? __uint_as_float(PS[static_cast<int64_t>(h) * n_edges + j] & 0xffff0000u) : 0.f;
+            if (distinct) {
+                if (valid) g[h * tq + type] += ds;
+            } else {
+                for (int i = 0; i < 32; ++i) {
+                    if (lane == i && valid) g[h * tq + type] += ds;
+                    __syncwarp();
+                }
+            }
+        }
+        __syncwarp();
+    }
     for (int i = lane * 2; i < cells; i += 64) {
         __nv_bfloat162 v = __floats2bfloat162_rn(g[i], g[i + 1]);
         *reinterpret_cast<__nv_bfloat162 *>(out + i) = v;
@@ -571,12 +657,12 @@ int check_tile_plan(const char *name, const bpt_tile_plan_t *tp, bool need_et, b
     return BPT_OK;
 }
 
-int run_dkv(const bpt_tile_plan_t *tp, const uint32_t *PS, const void *q, const void *d_o, void *dk, void *dv, int h,
+int run_dkv(const bpt_tile_plan_t *tp, const uint32_t *PS, int64_t n_edges, const void *q, const void *d_o, void *dk, void *dv, int h,
             float *part, cudaStream_t stream) {
     if (tp->n_groups == 0) return BPT_OK;
     DkvParams p;
     p.groups = tp->groups; p.mblocks = tp->mblocks; p.cols = tp->cols; p.cellpos = tp->cell_pos;
-    p.PS = PS;
+    p.PS = PS; p.n_edges = n_edges;
     p.q = static_cast<const __nv_bfloat16 *>(q); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
     p.dk = static_cast<__nv_bfloat16 *>(dk); p.dv = static_cast<__nv_bfloat16 *>(dv);
     p.part = part; p.H = h; p.max_cols_pad = tp->max_cols_pad;
@@ -668,14 +754,15 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         p.q = static_cast<const __nv_bfloat16 *>(q); p.k = static_cast<const __nv_bfloat16 *>(k);
         p.v = static_cast<const __nv_bfloat16 *>(v); p.ak = static_cast<const __nv_bfloat16 *>(ak);
         p.o = static_cast<const __nv_bfloat16 *>(o); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
-        p.lse = lse; p.PS = PS; p.part_dq = part_dq;
+        p.lse = lse; p.PS = PS; p.n_edges = n_edges; p.part_dq = part_dq;
         p.dq = static_cast<__nv_bfloat16 *>(dq);
         p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = dst_tiles->max_cols_pad;
         p.t_max = bias ? dst_tiles->t_max : 0;
         p.scale = sc;
         const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes + static_cast<size_t>(p.max_cols_pad) * 4 +
                             static_cast<size_t>(kTileRows) * (p.max_cols_pad + kIdxPad) * 2 +
-                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2;
+                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2 +
+                            static_cast<size_t>(p.t_max) * kRowBytes;
         if (smem > 227 * 1024)
             return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: tile plan needs %zu bytes of shared memory", smem);
         int rc;
@@ -702,7 +789,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         const int kk = tq < n_etypes ? tq : n_etypes;
         const size_t smem_g = static_cast<size_t>(4) * h * tq * sizeof(float);
         build_type_table_kernel<<<static_cast<unsigned>((n_nodes + 3) / 4), 128, smem_g, stream>>>(
-            pv.in_indptr, pv.in_etype, pv.row_uniform, static_cast<int>(n_nodes), PS, G, h, tq);
+            pv.in_indptr, pv.in_etype, pv.row_uniform, static_cast<int>(n_nodes), PS, n_edges, G, h, tq);
         BPT_LAUNCH_CHECK();
         cublasHandle_t handle = cublas_handle();
         if (handle == nullptr) return fail(BPT_ERR_CUDA, "attn_backward_tc: cuBLAS handle could not be created");
@@ -725,5 +812,5 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, PS, dq, dak, part_dak, h, d, stream)) return rc;
     }
     // 3. source side: dK, dV
-    return run_dkv(src_tiles, PS, q, d_o, dk, dv, h, part_dkv, stream);
+    return run_dkv(src_tiles, PS, n_edges, q, d_o, dk, dv, h, part_dkv, stream);
 }

@@ -10,12 +10,14 @@
 namespace bpt {
 namespace {
 
-__global__ void permute_in_kernel(const int32_t *__restrict__ in_eid, const int32_t *__restrict__ etype,
-                                  int64_t n_edges, int32_t *__restrict__ in_etype,
-                                  int32_t *__restrict__ inpos_of_eid) {
+// in_rank[p] = rank in the by-source order of the edge at in-CSR position p; eid_by_src maps that
+// rank to the edge id.
+__global__ void permute_in_kernel(const int32_t *__restrict__ in_rank, const int32_t *__restrict__ eid_by_src,
+                                  const int32_t *__restrict__ etype, int64_t n_edges,
+                                  int32_t *__restrict__ in_etype, int32_t *__restrict__ inpos_of_eid) {
     const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (p >= n_edges) return;
-    const int32_t e = in_eid[p];
+    const int32_t e = eid_by_src[in_rank[p]];
     in_etype[p] = etype ? etype[e] : 0;
     inpos_of_eid[e] = static_cast<int32_t>(p);
 }
@@ -135,7 +137,7 @@ extern "C" size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_src, 
     int64_t rows = n_nodes > n_etypes + 1 ? n_nodes : n_etypes + 1;
     rows = rows > n_src ? rows : n_src;
     const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
-    return 3 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 3 * work_ws_bytes(rows) + 1024;
+    return 5 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 3 * work_ws_bytes(rows) + 1024;
 }
 
 extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
@@ -155,6 +157,8 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     int32_t *tmp_eid = ws.take<int32_t>(e);
     int32_t *inpos_of_eid = ws.take<int32_t>(e);
     int32_t *bucket_keys = ws.take<int32_t>(e);
+    int32_t *eid_by_src = ws.take<int32_t>(e);
+    int32_t *src_by_src = ws.take<int32_t>(e);
     int64_t rows = n_nodes > n_etypes + 1 ? n_nodes : n_etypes + 1;
     rows = rows > n_src ? rows : n_src;
     const size_t csr_ws_bytes = bpt_coo_to_csr_workspace_bytes(n_edges, rows);
@@ -162,20 +166,24 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: workspace too small");
     const unsigned eb = static_cast<unsigned>((n_edges + 255) / 256);
 
-    // in-CSR (rows = destinations)
-    if (int rc = bpt_coo_to_csr(dst, src, n_edges, n_nodes, 4, p.in_indptr, p.in_src, tmp_eid, csr_ws,
+    // out-CSR (rows = sources, edge-id order inside a row)
+    if (int rc = bpt_coo_to_csr(src, dst, n_edges, n_src, 4, p.out_indptr, p.out_dst, eid_by_src, csr_ws,
                                 csr_ws_bytes, stream_))
         return rc;
+    // in-CSR (rows = destinations), a row's edges ordered by source and then by edge id: the stable
+    // sort by destination of the by-source order.  Neighbouring cells of a row of the tile plans
+    // (whose columns are sorted sources) are then neighbours in every per-edge array.
     if (n_edges > 0) {
-        permute_in_kernel<<<eb, 256, 0, stream>>>(tmp_eid, etype, n_edges, p.in_etype, inpos_of_eid);
+        gather_kernel<<<eb, 256, 0, stream>>>(eid_by_src, src, n_edges, src_by_src);
         BPT_LAUNCH_CHECK();
     }
-    // out-CSR (rows = sources)
-    if (int rc = bpt_coo_to_csr(src, dst, n_edges, n_src, 4, p.out_indptr, p.out_dst, tmp_eid, csr_ws,
+    if (int rc = bpt_coo_to_csr(p.out_dst, src_by_src, n_edges, n_nodes, 4, p.in_indptr, p.in_src, tmp_eid, csr_ws,
                                 csr_ws_bytes, stream_))
         return rc;
     if (n_edges > 0) {
-        gather_kernel<<<eb, 256, 0, stream>>>(tmp_eid, inpos_of_eid, n_edges, p.out_inpos);
+        permute_in_kernel<<<eb, 256, 0, stream>>>(tmp_eid, eid_by_src, etype, n_edges, p.in_etype, inpos_of_eid);
+        BPT_LAUNCH_CHECK();
+        gather_kernel<<<eb, 256, 0, stream>>>(eid_by_src, inpos_of_eid, n_edges, p.out_inpos);
         BPT_LAUNCH_CHECK();
     }
     // buckets by edge type; edges into uniform rows (zero gradient of the type table) go last

@@ -27,7 +27,7 @@ struct PlanView {
     int64_t n_src;    // source rows (rows of the out-CSR; k, v)
     int64_t n_edges;
     int n_etypes;
-    // in-CSR: rows are destinations; entries in ascending edge-id order
+    // in-CSR: rows are destinations; a row's entries are ordered by source, then by edge id
     int32_t *in_indptr, *in_src, *in_etype;
     // 1 where all incoming edges of the row have one type (or there are none): the relative-position
     // term is then a per-row constant, cancels in the softmax and has zero gradient

@@ -263,9 +263,10 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
  * payload: in_payload[j] of CSR entry j, or j itself when in_payload is NULL, -1 without an
  * edge.  The same planner serves the transposed problem (rows = sources): feed it the
  * out-CSR with in_payload = each entry's position in the in-CSR.
- * bpt_export_in_csr / bpt_export_out_csr copy the in-CSR (indptr, src, etype) / out-CSR (indptr
- * over n_src rows, dst, position in the in-CSR) of a bpt_attn_plan_build plan to host arrays
- * (they wait for the stream).
+ * bpt_export_in_csr / bpt_export_out_csr copy the in-CSR (indptr, src, etype; a row's entries
+ * ordered by source, then by edge id) / out-CSR (indptr over n_src rows, dst, position in the
+ * in-CSR; a row's entries in edge-id order) of a bpt_attn_plan_build plan to host arrays (they
+ * wait for the stream).
  * ---------------------------------------------------------------------------------- */
 void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *in_src, const int32_t *in_etype,
                            const int32_t *in_payload, int64_t n_nodes, int64_t n_edges, double min_density, int max_cols,

@@ -520,9 +520,9 @@ def run_ours(a):
                                     "sample": info["sample"]}
         if a.dtype == "bf16" and a.n == 8192 and a.k == 4 and not a.causal:
             # dram__bytes_read + dram__bytes_write of attn_forward_tile_kernel from one ncu capture on 2
-            # sequences of this shape (profiles/attn_tile_kernels_bf16_n8192_k4.md): 147.28 MB for
+            # sequences of this shape (profiles/attn_tile_kernels_bf16_n8192_k4.md): 151.35 MB for
             # 1,491,572 edges; traffic grows in proportion to the number of sequences.
-            line["roofline"]["traffic"] = 147.28e6 / 1491572 * E
+            line["roofline"]["traffic"] = 151.35e6 / 1491572 * E
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

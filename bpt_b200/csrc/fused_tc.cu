@@ -1,19 +1,21 @@
 // Fused graph attention forward on tensor cores (bf16 storage, fp32 accumulation, head dim 64).
 //
-// One thread block per group of the tile plan (tile_plan.cuh), one warp per head.  For each
-// m-block of the group (<=16 destination rows x the group's column list) and each 64-column
-// step a warp
-//   1. gathers the K rows of the step's columns straight into mma B fragments (each lane
-//      loads two 16-byte pieces of a row; the head dimension is permuted identically for Q, K
-//      and embed_ak, which a dot product does not notice),
-//   2. S = Q K^T on tensor cores; the relative-position term and the edge mask come from one
-//      table lookup per cell: table[row][etype] = scale * <q[row], embed_ak[etype]> (computed on
-//      tensor cores once per m-block and head, parked in shared memory as fp16 in the log2
-//      domain) with an extra entry of -inf that cells without an edge point to.  M-blocks whose
-//      rows each have a single edge type use a two-entry table {0, -inf}: the term is then a
-//      per-row constant that cancels in the softmax and is added to lse at the end,
+// One thread block per group of the tile plan (tile_plan.cuh), one warp per head.  The block
+// stages the group's column ids, the m-block's cells (as table indices) and the embed_ak rows it
+// can meet once; the warp's first K and V rows are already travelling while that happens.  For
+// each m-block of the group (<=16 destination rows x the group's column list) and each active
+// 32-column step a warp
+//   1. takes the step's K rows from its K buffer (cp.async, swizzled; ldmatrix B fragments),
+//   2. S = Q K^T on tensor cores, then refills the K buffer with the next step's rows; the
+//      relative-position term and the edge mask come from one table lookup per cell:
+//      table[row][etype] = scale * <q[row], embed_ak[etype]> (computed on tensor cores once per
+//      m-block and head, parked in shared memory as fp16 in the log2 domain) with an extra entry
+//      of -inf that cells without an edge point to.  M-blocks whose rows each have a single edge
+//      type use a two-entry table {0, -inf}: the term is then a per-row constant that cancels in
+//      the softmax and is added to lse at the end,
 //   3. online softmax in registers, P packed to bf16 A fragments in place,
-//   4. O += P V with V staged through swizzled shared memory (cp.async + ldmatrix.trans).
+//   4. O += P V from its V buffer (ldmatrix.trans), then refills the V buffer.
+// So K of step j+1 travels during softmax and PV of step j, V of step j+1 during QK^T of j+1.
 // Scores never leave the SM.  Rows wholly inside one m-block are written as final O / lse; rows
 // spread over several m-blocks write (m, l, O) partials that a merge kernel combines in slot
 // order, so results are bitwise reproducible.

@@ -73,7 +73,6 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
     // layout: per warp {dO stage, Q stage} (8 KB) | destination ids | edge positions of the m-block
     int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * 2 * kStageBytes);
     int32_t *s_pos = s_cols + p.max_cols_pad;
-    const int pos_stride = p.max_cols_pad + kPosPad;
 
     const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
     const int ncols_pad = grp[kGroupNcolsPad];
@@ -112,13 +111,12 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
             const uint32_t *__restrict__ ps_h = p.PS + static_cast<int64_t>(h) * p.n_edges;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                const int c = j * kDkvStep + nt * 8 + 2 * t;
-                const int2 pos_lo = *reinterpret_cast<const int2 *>(s_pos + g * pos_stride + c);
-                const int2 pos_hi = *reinterpret_cast<const int2 *>(s_pos + (g + 8) * pos_stride + c);
-                w[4 * nt + 0] = pos_lo.x >= 0 ? __ldg(ps_h + pos_lo.x) : 0u;
-                w[4 * nt + 1] = pos_lo.y >= 0 ? __ldg(ps_h + pos_lo.y) : 0u;
-                w[4 * nt + 2] = pos_hi.x >= 0 ? __ldg(ps_h + pos_hi.x) : 0u;
-                w[4 * nt + 3] = pos_hi.y >= 0 ? __ldg(ps_h + pos_hi.y) : 0u;
+                // step j covers column groups 2j and 2j+1 (8 columns each; four groups per 32 columns)
+                const int4 pos = reinterpret_cast<const int4 *>(s_pos)[(j * 2 + nt) * 32 + lane];
+                w[4 * nt + 0] = pos.x >= 0 ? __ldg(ps_h + pos.x) : 0u;
+                w[4 * nt + 1] = pos.y >= 0 ? __ldg(ps_h + pos.y) : 0u;
+                w[4 * nt + 2] = pos.z >= 0 ? __ldg(ps_h + pos.z) : 0u;
+                w[4 * nt + 3] = pos.w >= 0 ? __ldg(ps_h + pos.w) : 0u;
             }
         };
         __syncthreads();
@@ -130,15 +128,10 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
         }
         cp_async_commit();
         {
-            // the cell matrix is [chunk][16][64]; 4 positions (16 bytes) per thread and step
+            // the cells' positions come in fragment order (cell_pos_index) and are staged as they are
             const int4 *gp = reinterpret_cast<const int4 *>(p.cellpos + mb[kMbEtOff]);
             const int pieces = kTileRows * ncols_pad / 4;
-            for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
-                const int cell = i * 4;
-                const int chunk = cell / (kTileRows * kTileChunk), rem = cell % (kTileRows * kTileChunk);
-                const int r = rem / kTileChunk, c = rem % kTileChunk;
-                *reinterpret_cast<int4 *>(s_pos + r * pos_stride + chunk * kTileChunk + c) = __ldg(gp + i);
-            }
+            for (int i = threadIdx.x; i < pieces; i += blockDim.x) reinterpret_cast<int4 *>(s_pos)[i] = __ldg(gp + i);
         }
         __syncthreads();
         const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
@@ -493,13 +486,12 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                         const int c = cb + nt * 8 + 2 * t;
                         const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c);
                         const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c);
-                        const int2 pos_lo = __ldg(reinterpret_cast<const int2 *>(chunk_pos + g * kTileChunk + (c - c0)));
-                        const int2 pos_hi = __ldg(reinterpret_cast<const int2 *>(chunk_pos + (g + 8) * kTileChunk + (c - c0)));
+                        const int4 pos4 = __ldg(reinterpret_cast<const int4 *>(chunk_pos) + (half * 4 + nt) * 32 + lane);
                         const float tab[4] = {__half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]),
                                               __half2float(s_tab[g * tab_stride + (i_lo >> 16)]),
                                               __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]),
                                               __half2float(s_tab[(g + 8) * tab_stride + (i_hi >> 16)])};
-                        const int pos[4] = {pos_lo.x, pos_lo.y, pos_hi.x, pos_hi.y};
+                        const int pos[4] = {pos4.x, pos4.y, pos4.z, pos4.w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));

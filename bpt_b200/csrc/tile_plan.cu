@@ -362,7 +362,15 @@ extern "C" int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t
             }
         }
     }
-    if (cell_pos && !p->cellpos.empty()) std::memcpy(cell_pos, p->cellpos.data(), p->cellpos.size() * sizeof(int32_t));
+    if (cell_pos && !p->cellpos.empty()) {
+        // Fragment order (kCellPosIndex): the 16 payloads an mma lane needs per 32 columns are four
+        // 16-byte pieces, and a warp's pieces of one column group are 512 contiguous bytes.
+        const size_t chunk_cells = static_cast<size_t>(kTileRows) * kTileChunk;
+        for (size_t base = 0; base + chunk_cells <= p->cellpos.size(); base += chunk_cells)
+            for (int r = 0; r < kTileRows; ++r)
+                for (int c = 0; c < kTileChunk; ++c)
+                    cell_pos[base + cell_pos_index(r, c)] = p->cellpos[base + static_cast<size_t>(r) * kTileChunk + c];
+    }
     if (split_rows && !p->split.empty()) std::memcpy(split_rows, p->split.data(), p->split.size() * sizeof(int32_t));
     if (row_items && !p->simt.empty()) std::memcpy(row_items, p->simt.data(), p->simt.size() * sizeof(int32_t));
     return BPT_OK;

@@ -34,6 +34,14 @@ constexpr int kMbTq = 50;          // edge types [0, tq) occur (multiple of 8)
 constexpr int kMbQrSlot = 51;      // >= 0: needs the per-row relative-position table, in this shared-memory
                                    // slot; -1: every row's edges share one type, so the term is a per-row
                                    // constant that cancels in the softmax and only shifts lse
+// Exported cell payloads (edge positions) are stored per 64-column chunk in the order the mma
+// lanes consume them rather than row by row: cell (r, c) of a chunk sits at
+//   (((c / 32) * 4 + (c % 32) / 8) * 32 + lane) * 4 + (r / 8) * 2 + (c & 1),   lane = (r % 8) * 4 + (c % 8) / 2,
+// so lane (g, t) finds {(g, c), (g, c+1), (g+8, c), (g+8, c+1)} for c = 32 half + 8 nt + 2t in one
+// 16-byte piece, and the 32 lanes' pieces of one (half, nt) are contiguous.
+__host__ __device__ constexpr int cell_pos_index(int r, int c) {
+    return (((c / 32) * 4 + (c % 32) / 8) * 32 + (r % 8) * 4 + (c % 8) / 2) * 4 + (r / 8) * 2 + (c & 1);
+}
 constexpr uint16_t kNoEdge = 0xFFFF;
 constexpr uint8_t kNoEdge8 = 0xFF;
 

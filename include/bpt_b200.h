@@ -261,7 +261,9 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
  * uint16), split_rows and row_items (4 int32 each) into host arrays of those sizes, to be
  * uploaded as they are; cell_pos (int32 per etype cell, may be NULL) is the cell's edge
  * payload: in_payload[j] of CSR entry j, or j itself when in_payload is NULL, -1 without an
- * edge.  The same planner serves the transposed problem (rows = sources): feed it the
+ * edge.  et is stored [chunk][16][64] per m-block; cell_pos holds the same cells per chunk in
+ * the order the tensor-core lanes read them: cell (r, c) of a chunk at
+ * (((c / 32) * 4 + (c % 32) / 8) * 32 + (r % 8) * 4 + (c % 8) / 2) * 4 + (r / 8) * 2 + (c & 1).  The same planner serves the transposed problem (rows = sources): feed it the
  * out-CSR with in_payload = each entry's position in the in-CSR.
  * bpt_export_in_csr / bpt_export_out_csr copy the in-CSR (indptr, src, etype; a row's entries
  * ordered by source, then by edge id) / out-CSR (indptr over n_src rows, dst, position in the

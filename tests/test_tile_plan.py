@@ -7,6 +7,15 @@ import numpy as np
 import pytest
 
 
+def _cell_pos_index(r, c):
+    """Place of cell (r, c) of a 16 x 64 chunk in the exported payload array (tile_plan.cuh)."""
+    return (((c // 32) * 4 + (c % 32) // 8) * 32 + (r % 8) * 4 + (c % 8) // 2) * 4 + (r // 8) * 2 + (c & 1)
+
+
+FRAG_ORDER = np.array([_cell_pos_index(r, c) for r in range(16) for c in range(64)])
+assert len(set(FRAG_ORDER.tolist())) == 1024
+
+
 def _plan(oracle_lib, g, min_density=0.05, max_cols=384, group_rows=64, col_block=64, simt_max_degree=0, et_bytes=2,
           max_mblocks=8, join_dense=1):
     from bpt_b200 import _lib, build
@@ -70,7 +79,8 @@ def test_plan_covers_every_edge_once(oracle_lib, spec, kw):
         for m in p["mblocks"][mb_first:mb_first + mb_count]:
             rows, slot, row_et, eoff, mask, tq, qr = m[0:16], m[16:32], m[32:48], m[48], m[49], m[50], m[51]
             cells = p["et"][eoff:eoff + 16 * ncp].reshape(ncp // 64, 16, 64)
-            cpos = p["cellpos"][eoff:eoff + 16 * ncp].reshape(ncp // 64, 16, 64)
+            # positions are exported per chunk in mma-fragment order: undo it
+            cpos = p["cellpos"][eoff:eoff + 16 * ncp].reshape(ncp // 64, 1024)[:, FRAG_ORDER].reshape(ncp // 64, 16, 64)
             assert np.array_equal(cpos >= 0, cells != none)
             valid = rows[rows >= 0]
             assert np.all(np.diff(valid) > 0)

@@ -29,15 +29,20 @@ __global__ void gather_kernel(const int32_t *__restrict__ idx, const int32_t *__
 }
 
 // row_uniform[r] = 1 when the row's incoming edges all have one type (or it has none).
+// One warp per row; the lanes stride over the row's edges.
 __global__ void row_uniform_kernel(const int32_t *__restrict__ indptr, const int32_t *__restrict__ in_etype,
                                    int64_t n_rows, int32_t *__restrict__ row_uniform) {
-    const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t r = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
     if (r >= n_rows) return;
     const int beg = indptr[r], end = indptr[r + 1];
-    int uniform = 1;
-    for (int j = beg + 1; j < end; ++j)
-        if (in_etype[j] != in_etype[beg]) { uniform = 0; break; }
-    row_uniform[r] = uniform;
+    const int first = beg < end ? in_etype[beg] : 0;
+    bool same = true;
+    for (int j0 = beg; j0 < end && same; j0 += 32) {
+        const int j = j0 + lane;
+        same = __all_sync(0xffffffffu, j >= end || in_etype[j] == first);
+    }
+    if (lane == 0) row_uniform[r] = same ? 1 : 0;
 }
 
 // Bucket key of every edge (edge-id order): its type, or n_etypes when its destination row is uniform.
@@ -188,7 +193,7 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     }
     // buckets by edge type; edges into uniform rows (zero gradient of the type table) go last
     if (n_nodes > 0) {
-        row_uniform_kernel<<<static_cast<unsigned>((n_nodes + 255) / 256), 256, 0, stream>>>(
+        row_uniform_kernel<<<static_cast<unsigned>((n_nodes * 32 + 255) / 256), 256, 0, stream>>>(
             p.in_indptr, p.in_etype, n_nodes, p.row_uniform);
         BPT_LAUNCH_CHECK();
     }

@@ -72,7 +72,7 @@ GRAPHS = {
 
 @pytest.mark.parametrize("graph", list(GRAPHS))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hd", [(8, 64), (6, 50), (3, 32), (2, 128), (20, 16)])
+@pytest.mark.parametrize("hd", [(8, 64), (12, 64), (6, 50), (3, 32), (2, 128), (20, 16)])
 def test_fused_matches_oracle(oracle_lib, graph, dtype, hd):
     H, D = hd
     if graph != "bpt_batch" and hd not in ((8, 64), (6, 50)):
@@ -204,3 +204,18 @@ def test_tensor_core_backward_matches_cuda_core_backward(oracle_lib):
     b = attention_backward(plan, q3, k3, v3, None, 0.125, lse3, d3, tensor_cores=False)
     for x, y in zip(a[:3], b[:3]):
         assert rel_err(x.float().cpu(), y.float().cpu()) < 1e-2
+
+
+def test_tensor_core_path_with_more_than_255_edge_types(oracle_lib):
+    """step = 14 gives edge types up to 318: 16-bit cells in the tile plan, and the gradients of
+    the relative-position table leave the per-row type table for the per-edge CUDA-core kernels.
+    Checked against the fp64 oracle, with 12 heads (more heads than warps in a block)."""
+    g = oracle_lib.batch_graphs([oracle_lib.binary_partition(600, False, 14, 10),
+                                 oracle_lib.binary_partition(130, True, 14, 10)])
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    assert T > 256
+    q, k, v, ak, d_o = _inputs(N, 12, 64, T, torch.bfloat16, 13)
+    want = _oracle(oracle_lib, g["src"], g["dst"], g["etype"], N, q, k, v, ak, d_o, 0.125)
+    plan, *got = _run_gpu(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
+    assert plan.tiles is not None and plan.tiles.et_bytes == 2
+    _compare(got, want, TOL[torch.bfloat16])

@@ -221,12 +221,13 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
 // One block per m-block of the forward's tile plan, one warp per head.  With lse from the forward
 // and delta = <dO, O> per row, every cell's gradient is local:
 //     p = exp2(s - lse),  dp = <dO[row], v[col]>,  dS = scale * p * (dp - delta).
-// Per 64 columns the warp stages their K rows once in swizzled shared memory (cp.async); per 32
-// columns it computes dP = dO V^T (V rows gathered straight into B fragments, head dimension
-// permuted like dO's), S = Q K^T (ldmatrix B fragments), looks the relative-position term and
-// the edge mask up in the same fp16 table as the forward, scatters {p, dS} as two bf16 to the
-// per-edge scratch (in-CSR order, for the source-side kernel and the gradient of the type table) and
-// accumulates dQ += dS K (ldmatrix.trans B fragments).  The relative-position part of dQ is
+// Per 16 columns the warp stages their K and V rows in swizzled shared memory (cp.async, two
+// buffers: the next step's rows travel while this step's products run), computes
+// dP = dO V^T and S = Q K^T (ldmatrix B fragments), looks the relative-position term and the
+// edge mask up in the same fp16 table as the forward, scatters {p, dS} as two bf16 to the
+// per-edge scratch ([head][in-CSR position], for the source-side kernel and the gradient of
+// the type table) and accumulates dQ += dS K (ldmatrix.trans B fragments).  The
+// relative-position part of dQ is
 // added afterwards by a CUDA-core kernel.
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -244,21 +245,14 @@ __device__ __forceinline__ void load_a_row(const __nv_bfloat16 *__restrict__ row
         w[2 * s + 1] = __ldg(p + 8 * s + 4 + t);
     }
 }
-// Permuted share of a row for products whose two operands are both read this way: the 16-byte
-// pieces at elements [8t, 8t+8) and [32+8t, 32+8t+8).
-__device__ __forceinline__ void load_row_frag(const __nv_bfloat16 *__restrict__ row, int t, uint32_t (&w)[8]) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(row + 8 * t));
-    const uint4 b = __ldg(reinterpret_cast<const uint4 *>(row + 32 + 8 * t));
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-}
-
 template <typename ET> struct EtTraits;
 template <> struct EtTraits<uint8_t> { static constexpr uint32_t kNone = kNoEdge8; };
 template <> struct EtTraits<uint16_t> { static constexpr uint32_t kNone = kNoEdge; };
 
 constexpr int kIdxPad = 8;
-constexpr int kKStageBytes = kTileChunk * kRowBytes;  // 8 KB: K rows of 64 columns
+constexpr int kDqStep = 16;                            // columns per pipeline step of the dQ tile kernel
+constexpr int kDqBufBytes = 2 * kDqStep * kRowBytes;   // one buffer: K rows then V rows of a step (4 KB)
+constexpr int kKStageBytes = 2 * kDqBufBytes;          // per warp: two buffers
 
 struct DqParams {
     const int32_t *groups, *mblocks, *cols, *cellpos;
@@ -308,14 +302,17 @@ attn_backward_dq_tile_kernel(const DqParams p) {
         }
     }
     cp_async_commit();
-    // K rows of head h for the 64 columns from c0 -> the warp's stage
-    auto issue_k = [&](int h, int c0) {
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
+    const int n_steps = ncols_pad / kDqStep;
+    // K and V rows of head h for the 16 columns of step j -> buffer b of the warp (K rows, then V rows)
+    auto issue_kv = [&](int h, int j, int b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
             const int id = i * 32 + lane;
             const int r = id >> 3, piece = id & 7;
-            cp_async16(s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4),
-                       p.k + (static_cast<int64_t>(s_cols[c0 + r]) * H + h) * kHeadDim + piece * 8);
+            const int64_t off = (static_cast<int64_t>(s_cols[j * kDqStep + r]) * H + h) * kHeadDim + piece * 8;
+            const uint32_t dst = s_k + b * kDqBufBytes + r * kRowBytes + ((piece ^ (r & 7)) << 4);
+            cp_async16(dst, p.k + off);
+            cp_async16(dst + kDqBufBytes / 2, p.v + off);
         }
     };
     for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
@@ -334,11 +331,11 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             const int64_t off_hi = (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim;
             load_a_row(p.q + off_lo, t, q_lo);
             load_a_row(p.q + off_hi, t, q_hi);
-            load_row_frag(p.d_o + off_lo, t, do_lo);
-            load_row_frag(p.d_o + off_hi, t, do_hi);
+            load_a_row(p.d_o + off_lo, t, do_lo);
+            load_a_row(p.d_o + off_hi, t, do_hi);
             uint32_t o_lo[8], o_hi[8];
-            load_row_frag(p.o + off_lo, t, o_lo);
-            load_row_frag(p.o + off_hi, t, o_hi);
+            load_a_row(p.o + off_lo, t, o_lo);
+            load_a_row(p.o + off_hi, t, o_hi);
             lse2_lo = row_lo < 0 ? 0.f : p.lse[static_cast<int64_t>(row_lo) * H + h];
             lse2_hi = row_hi < 0 ? 0.f : p.lse[static_cast<int64_t>(row_hi) * H + h];
             float a = 0.f, b = 0.f;
@@ -361,11 +358,17 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
         };
         __syncthreads();
-        // The first head's K rows and operand rows start travelling before the cells are staged.
-        int primed_c0 = -1;
-        if (warp < H && chunk_mask != 0u) {
-            primed_c0 = (__ffs(chunk_mask) - 1) * kTileChunk;
-            if (primed_c0 < ncols_pad) issue_k(warp, primed_c0); else primed_c0 = -1;
+        // first step after j whose 64-column chunk has an edge in this m-block; n_steps if none
+        auto next_step = [&](int j) {
+            ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 2)) & 1u)) ++j;
+            return j;
+        };
+        // The first head's first rows and operand rows start travelling before the cells are staged.
+        int primed_step = -1;
+        if (warp < H) {
+            primed_step = next_step(-1);
+            if (primed_step < n_steps) issue_kv(warp, primed_step, 0);
         }
         cp_async_commit();
         if (warp < H) load_head(warp);
@@ -441,83 +444,85 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             for (int i = 0; i < 8; ++i) { acc[i][0] = 0.f; acc[i][1] = 0.f; acc[i][2] = 0.f; acc[i][3] = 0.f; }
             uint32_t *__restrict__ ps_h = p.PS + static_cast<int64_t>(h) * p.n_edges;
 
-            for (int c0 = 0; c0 < ncols_pad; c0 += kTileChunk) {
-                if (!((chunk_mask >> (c0 / kTileChunk)) & 1u)) continue;
-                if (!(h == warp && c0 == primed_c0)) issue_k(h, c0);
+            // Two buffers for K and two for V, 16 columns each: the next step's rows travel while
+            // this step's three products run.  One cp.async group per iteration, possibly empty.
+            int j = primed_step;
+            if (j < 0) {
+                j = next_step(-1);
+                if (j < n_steps) issue_kv(h, j, 0);
                 cp_async_commit();
-                const int32_t *chunk_pos = cell_pos + static_cast<int64_t>(c0 / kTileChunk) * kTileRows * kTileChunk;
+            }
+            primed_step = -1;
+            int buf = 0;
+            while (j < n_steps) {
+                const int nj = next_step(j);
+                if (nj < n_steps) issue_kv(h, nj, buf ^ 1);
+                cp_async_commit();
+                cp_async_wait_one();  // this step's rows have landed; the newest group is the next step's
+                __syncwarp();
+                const uint32_t k_buf = s_k + buf * kDqBufBytes, v_buf = k_buf + kDqBufBytes / 2;
+                // dP = dO V^T and S = Q K^T for 2 column groups of 8
+                float dp[2][4], s[2][4];
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int cb = c0 + half * kHalf;
-                    // dP = dO V^T for 4 column groups of 8 (V rows straight from global memory)
-                    float dp[4][4];
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int r = nt * 8 + (lane & 7), pc = lane >> 3;
+                    const uint32_t off0 = r * kRowBytes + ((pc ^ (r & 7)) << 4);
+                    const uint32_t off1 = r * kRowBytes + (((pc + 4) ^ (r & 7)) << 4);
+                    uint32_t b0[4], b1[4];
+                    ldmatrix_x4(b0, v_buf + off0);
+                    ldmatrix_x4(b1, v_buf + off1);
+                    dp[nt][0] = 0.f; dp[nt][1] = 0.f; dp[nt][2] = 0.f; dp[nt][3] = 0.f;
+                    mma_bf16(dp[nt], do_lo[0], do_hi[0], do_lo[1], do_hi[1], b0[0], b0[1]);
+                    mma_bf16(dp[nt], do_lo[2], do_hi[2], do_lo[3], do_hi[3], b0[2], b0[3]);
+                    mma_bf16(dp[nt], do_lo[4], do_hi[4], do_lo[5], do_hi[5], b1[0], b1[1]);
+                    mma_bf16(dp[nt], do_lo[6], do_hi[6], do_lo[7], do_hi[7], b1[2], b1[3]);
+                    ldmatrix_x4(b0, k_buf + off0);
+                    ldmatrix_x4(b1, k_buf + off1);
+                    s[nt][0] = 0.f; s[nt][1] = 0.f; s[nt][2] = 0.f; s[nt][3] = 0.f;
+                    mma_bf16(s[nt], q_lo[0], q_hi[0], q_lo[1], q_hi[1], b0[0], b0[1]);
+                    mma_bf16(s[nt], q_lo[2], q_hi[2], q_lo[3], q_hi[3], b0[2], b0[3]);
+                    mma_bf16(s[nt], q_lo[4], q_hi[4], q_lo[5], q_hi[5], b1[0], b1[1]);
+                    mma_bf16(s[nt], q_lo[6], q_hi[6], q_lo[7], q_hi[7], b1[2], b1[3]);
+                }
+                // probabilities, per-edge scratch, dS (kept in s)
 #pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        uint32_t b[8];
-                        load_row_frag(p.v + (static_cast<int64_t>(s_cols[cb + nt * 8 + g]) * H + h) * kHeadDim, t, b);
-                        dp[nt][0] = 0.f; dp[nt][1] = 0.f; dp[nt][2] = 0.f; dp[nt][3] = 0.f;
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int c = j * kDqStep + nt * 8 + 2 * t;
+                    const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c);
+                    const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c);
+                    // positions in lane order (cell_pos_index): column group 2j + nt of the m-block
+                    const int4 pos4 = __ldg(reinterpret_cast<const int4 *>(cell_pos) + (j * 2 + nt) * 32 + lane);
+                    const float tab[4] = {__half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]),
+                                          __half2float(s_tab[g * tab_stride + (i_lo >> 16)]),
+                                          __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]),
+                                          __half2float(s_tab[(g + 8) * tab_stride + (i_hi >> 16)])};
+                    const int pos[4] = {pos4.x, pos4.y, pos4.z, pos4.w};
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks)
-                            mma_bf16(dp[nt], do_lo[2 * ks], do_hi[2 * ks], do_lo[2 * ks + 1], do_hi[2 * ks + 1], b[2 * ks],
-                                     b[2 * ks + 1]);
-                    }
-                    if (half == 0) {
-                        cp_async_wait_all();
-                        __syncwarp();
-                    }
-                    // S = Q K^T from the staged K rows
-                    float s[4][4];
-#pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        s[nt][0] = 0.f; s[nt][1] = 0.f; s[nt][2] = 0.f; s[nt][3] = 0.f;
-                        const int r = half * kHalf + nt * 8 + (lane & 7);
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            uint32_t b[4];
-                            const int piece = 4 * j + (lane >> 3);
-                            ldmatrix_x4(b, s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4));
-                            mma_bf16(s[nt], q_lo[4 * j], q_hi[4 * j], q_lo[4 * j + 1], q_hi[4 * j + 1], b[0], b[1]);
-                            mma_bf16(s[nt], q_lo[4 * j + 2], q_hi[4 * j + 2], q_lo[4 * j + 3], q_hi[4 * j + 3], b[2], b[3]);
-                        }
-                    }
-                    // probabilities, per-edge scratch, dS (kept in s)
-#pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        const int c = cb + nt * 8 + 2 * t;
-                        const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c);
-                        const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c);
-                        const int4 pos4 = __ldg(reinterpret_cast<const int4 *>(chunk_pos) + (half * 4 + nt) * 32 + lane);
-                        const float tab[4] = {__half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]),
-                                              __half2float(s_tab[g * tab_stride + (i_lo >> 16)]),
-                                              __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]),
-                                              __half2float(s_tab[(g + 8) * tab_stride + (i_hi >> 16)])};
-                        const int pos[4] = {pos4.x, pos4.y, pos4.z, pos4.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
-                            s[nt][i] = p.scale * pr * (dp[nt][i] - (i < 2 ? delta_lo : delta_hi));
-                            if (pos[i] >= 0) ps_h[pos[i]] = pack_bf16(pr, s[nt][i]);
-                        }
-                    }
-                    // dQ += dS K
-#pragma unroll
-                    for (int ks = 0; ks < 2; ++ks) {
-                        const uint32_t a0 = pack_bf16(s[2 * ks][0], s[2 * ks][1]), a1 = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-                        const uint32_t a2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-                        const uint32_t a3 = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-                        const int r = half * kHalf + ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-#pragma unroll
-                        for (int dn = 0; dn < 8; dn += 2) {
-                            const int piece = dn + (lane >> 4);
-                            uint32_t b[4];
-                            ldmatrix_x4_trans(b, s_k + r * kRowBytes + ((piece ^ (r & 7)) << 4));
-                            mma_bf16(acc[dn], a0, a1, a2, a3, b[0], b[1]);
-                            mma_bf16(acc[dn + 1], a0, a1, a2, a3, b[2], b[3]);
-                        }
+                    for (int i = 0; i < 4; ++i) {
+                        const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
+                        s[nt][i] = p.scale * pr * (dp[nt][i] - (i < 2 ? delta_lo : delta_hi));
+                        if (pos[i] >= 0) ps_h[pos[i]] = pack_bf16(pr, s[nt][i]);
                     }
                 }
-                __syncwarp();  // the K stage is rewritten by the next step
+                // dQ += dS K
+                {
+                    const uint32_t a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
+                    const uint32_t a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
+                    const int r = ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+                    for (int dn = 0; dn < 8; dn += 2) {
+                        const int piece = dn + (lane >> 4);
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, k_buf + r * kRowBytes + ((piece ^ (r & 7)) << 4));
+                        mma_bf16(acc[dn], a0, a1, a2, a3, b[0], b[1]);
+                        mma_bf16(acc[dn + 1], a0, a1, a2, a3, b[2], b[3]);
+                    }
+                }
+                __syncwarp();  // these buffers are refilled by the step after next
+                j = nj;
+                buf ^= 1;
             }
+            cp_async_wait_all();
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = half ? row_hi : row_lo;

@@ -577,13 +577,24 @@ build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__
         const bool valid = j < end;
         const int type = valid ? in_etype[j] : -1 - lane;  // idle lanes get distinct keys
         const bool distinct = __all_sync(0xffffffffu, __match_any_sync(0xffffffffu, type) == (1u << lane));
-        for (int h = 0; h < H; ++h) {
-            const float ds = valid ? __uint_as_float(PS[static_cast<int64_t>(h) * n_edges + j] & 0xffff0000u) : 0.f;
+        for (int h0 = 0; h0 < H; h0 += 8) {
+            float ds[8];  // the loads of eight heads travel together
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                ds[u] = valid && h0 + u < H
+                            ? __uint_as_float(__ldg(PS + static_cast<int64_t>(h0 + u) * n_edges + j) & 0xffff0000u)
+                            : 0.f;
             if (distinct) {
-                if (valid) g[h * tq + type] += ds;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (valid && h0 + u < H) g[(h0 + u) * tq + type] += ds[u];
             } else {
                 for (int i = 0; i < 32; ++i) {
-                    if (lane == i && valid) g[h * tq + type] += ds;
+                    if (lane == i && valid) {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (h0 + u < H) g[(h0 + u) * tq + type] += ds[u];
+                    }
                     __syncwarp();
                 }
             }

@@ -454,9 +454,21 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             }
             primed_step = -1;
             int buf = 0;
+            // cell positions in lane order (cell_pos_index), fetched one step ahead: column groups 2j, 2j+1
+            const int4 *pos_base = reinterpret_cast<const int4 *>(cell_pos) + lane;
+            int4 pos_cur[2] = {make_int4(-1, -1, -1, -1), make_int4(-1, -1, -1, -1)};
+            if (j < n_steps) {
+                pos_cur[0] = __ldg(pos_base + (j * 2) * 32);
+                pos_cur[1] = __ldg(pos_base + (j * 2 + 1) * 32);
+            }
             while (j < n_steps) {
                 const int nj = next_step(j);
-                if (nj < n_steps) issue_kv(h, nj, buf ^ 1);
+                int4 pos_next[2] = {pos_cur[0], pos_cur[1]};
+                if (nj < n_steps) {
+                    issue_kv(h, nj, buf ^ 1);
+                    pos_next[0] = __ldg(pos_base + (nj * 2) * 32);
+                    pos_next[1] = __ldg(pos_base + (nj * 2 + 1) * 32);
+                }
                 cp_async_commit();
                 cp_async_wait_one();  // this step's rows have landed; the newest group is the next step's
                 __syncwarp();
@@ -490,8 +502,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                     const int c = j * kDqStep + nt * 8 + 2 * t;
                     const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c);
                     const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c);
-                    // positions in lane order (cell_pos_index): column group 2j + nt of the m-block
-                    const int4 pos4 = __ldg(reinterpret_cast<const int4 *>(cell_pos) + (j * 2 + nt) * 32 + lane);
+                    const int4 pos4 = pos_cur[nt];
                     const float tab[4] = {__half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]),
                                           __half2float(s_tab[g * tab_stride + (i_lo >> 16)]),
                                           __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]),
@@ -519,6 +530,8 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                     }
                 }
                 __syncwarp();  // these buffers are refilled by the step after next
+                pos_cur[0] = pos_next[0];
+                pos_cur[1] = pos_next[1];
                 j = nj;
                 buf ^= 1;
             }

@@ -74,12 +74,12 @@ __global__ void attn_forward_merge_kernel(const int4 *__restrict__ split_rows, i
             const float *src = part_o + static_cast<int64_t>(first + s0) * HD + c;
             float a = acc[u] * s_f[head];
             int s = 0;
-            for (; s + 8 <= nb; s += 8) {
-                float x[8];
+            for (; s + 16 <= nb; s += 16) {
+                float x[16];
 #pragma unroll
-                for (int v = 0; v < 8; ++v) x[v] = src[static_cast<int64_t>(s + v) * HD];
+                for (int v = 0; v < 16; ++v) x[v] = src[static_cast<int64_t>(s + v) * HD];
 #pragma unroll
-                for (int v = 0; v < 8; ++v) a = fmaf(x[v], s_w[(s + v) * H + head], a);
+                for (int v = 0; v < 16; ++v) a = fmaf(x[v], s_w[(s + v) * H + head], a);
             }
             for (; s < nb; ++s) a = fmaf(src[static_cast<int64_t>(s) * HD], s_w[s * H + head], a);
             acc[u] = a;
@@ -98,9 +98,10 @@ __global__ void attn_forward_merge_kernel(const int4 *__restrict__ split_rows, i
     }
 }
 
-// Block size and shared memory of the merge kernel.  Needs H <= threads and H*D <= 8*threads.
+// Block size and shared memory of the merge kernel: one output column per thread where that fits
+// (a long row's slots are walked once, not once per column).  Needs H <= threads and H*D <= 8*threads.
 inline int merge_threads(int H, int D) {
-    int t = (H * D + 7) / 8;
+    int t = H * D;
     t = t < H ? H : t;
     t = (t + 31) / 32 * 32;
     return t < 128 ? 128 : (t > 1024 ? 1024 : t);
@@ -116,7 +117,7 @@ int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_
 
 struct PlanView;
 // Defined in fused_simt.cu: dQ += relative-position part, and d embed_ak (with its split-row merge),
-// from the per-edge scratch PS (in-CSR order, one word {bf16 p, bf16 dS} per (edge, head)); bf16
+// from the per-edge scratch PS ([head][in-CSR position], one word {bf16 p, bf16 dS} each); bf16
 // storage.  part_dak: counts[7] * D floats.
 int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, const void *q, const void *ak,
                                   const uint32_t *PS, void *dq, float *dak, float *part_dak, int H, int D,

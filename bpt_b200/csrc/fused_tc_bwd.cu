@@ -631,6 +631,12 @@ cublasHandle_t cublas_handle() {
     return handles[dev];
 }
 
+// Block size of dkv_sum_merge_kernel: one column per thread where that fits.
+inline int sum_merge_threads(int columns) {
+    const int t = (columns + 31) / 32 * 32;
+    return t < 128 ? 128 : (t > 1024 ? 1024 : t);
+}
+
 // out0[row] | out1[row] = sum over the row's slots, in slot order, of the slot's two halves.
 // (out1 == nullptr: a slot holds one array of `width` values.)
 __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_split, const float *__restrict__ part,
@@ -644,12 +650,12 @@ __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_
         const float *src = part + static_cast<int64_t>(first) * stride + c;
         float acc = 0.f;
         int s = 0;
-        for (; s + 8 <= count; s += 8) {
-            float x[8];
+        for (; s + 16 <= count; s += 16) {
+            float x[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) x[u] = src[static_cast<int64_t>(s + u) * stride];
+            for (int u = 0; u < 16; ++u) x[u] = src[static_cast<int64_t>(s + u) * stride];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) acc += x[u];
+            for (int u = 0; u < 16; ++u) acc += x[u];
         }
         for (; s < count; ++s) acc += src[static_cast<int64_t>(s) * stride];
         if (c < width) out0[static_cast<int64_t>(row) * width + c] = __float2bfloat16_rn(acc);
@@ -696,7 +702,7 @@ int run_dkv(const bpt_tile_plan_t *tp, const uint32_t *PS, int64_t n_edges, cons
     attn_backward_dkv_tile_kernel<<<static_cast<unsigned>(tp->n_groups), kWarps * 32, smem, stream>>>(p);
     BPT_LAUNCH_CHECK();
     if (tp->n_split > 0) {
-        dkv_sum_merge_kernel<<<static_cast<unsigned>(tp->n_split), 256, 0, stream>>>(
+        dkv_sum_merge_kernel<<<static_cast<unsigned>(tp->n_split), sum_merge_threads(2 * h * kHeadDim), 0, stream>>>(
             reinterpret_cast<const int4 *>(tp->split_rows), static_cast<int>(tp->n_split), part, h * kHeadDim, p.dk, p.dv);
         BPT_LAUNCH_CHECK();
     }
@@ -795,7 +801,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
                       : launch_dq_kernel<uint16_t, false>(p, dst_tiles->n_groups, smem, stream);
         if (rc) return rc;
         if (dst_tiles->n_split > 0) {
-            dkv_sum_merge_kernel<<<static_cast<unsigned>(dst_tiles->n_split), 256, 0, stream>>>(
+            dkv_sum_merge_kernel<<<static_cast<unsigned>(dst_tiles->n_split), sum_merge_threads(h * kHeadDim), 0, stream>>>(
                 reinterpret_cast<const int4 *>(dst_tiles->split_rows), static_cast<int>(dst_tiles->n_split), part_dq,
                 h * kHeadDim, static_cast<__nv_bfloat16 *>(dq), nullptr);
             BPT_LAUNCH_CHECK();

@@ -46,6 +46,9 @@ def parse():
                          "--seq-len tokens, destination nodes split over the ranks, K/V all-gathered (strong scaling)")
     ap.add_argument("--exchange", default="halo", choices=["halo", "allgather"],
                     help="seqshard mode: send only the remote K/V rows a shard reads (halo) or all-gather K/V")
+    ap.add_argument("--graph", action="store_true",
+                    help="seqshard mode on ONE GPU: capture the step in a CUDA graph and time its replay "
+                         "(with more ranks the step holds NCCL collectives and is timed eagerly)")
     ap.add_argument("--workload", default="attention", choices=["attention", "lm"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
                          "forward, batch 8 x 8192 tokens per rank, tokens/s")
@@ -197,7 +200,8 @@ def run_seqshard(a):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
     src, dst, et = g.edges_device()
@@ -244,10 +248,27 @@ def run_seqshard(a):
     for _ in range(max(a.warmup, 3)):
         step()
     barrier()
+    run_step, graph_note = step, None
+    if a.graph and world > 1:
+        # A captured step that holds NCCL collectives did not complete on two ranks here (the run was
+        # ended by its time limit), so steps with collectives are issued eagerly.
+        graph_note = "not used: the step holds NCCL collectives"
+    elif a.graph:
+        # One step (tile kernels, GEMMs, index kernels) as a CUDA graph: its launches are issued by one call.
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph):
+                step()
+            run_step, graph_note = graph.replay, "step replayed from a CUDA graph"
+            for _ in range(3):
+                run_step()
+        except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+            graph_note = "capture failed: %s" % str(exc)[:160]
+        barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(a.steps):
-        step()
+        run_step()
     stop.record()
     barrier()
     ms = start.elapsed_time(stop) / a.steps
@@ -257,6 +278,7 @@ def run_seqshard(a):
         ms = t.item()
     if rank == 0:
         print(json.dumps({
+            "cuda_graph": graph_note,
             "metric": "bpt_attention_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": a.dtype, "data": "synthetic",

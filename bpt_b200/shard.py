@@ -233,6 +233,38 @@ def halo_return(shard, g_ext, group=None):
     return g_own
 
 
+def halo_exchange_pair(shard, a, b, group=None):
+    """halo_exchange of two tensors of one shape with ONE all-to-all (K and V travel together)."""
+    import torch.distributed as dist
+    if shard.world == 1:
+        return a, b
+    send = torch.stack([a.index_select(0, shard.send_all), b.index_select(0, shard.send_all)], 1)
+    recv = a.new_empty((shard.n_halo, 2) + tuple(a.shape[1:]))
+    dist.all_to_all_single(recv, send, output_split_sizes=shard.recv_counts, input_split_sizes=shard.send_counts,
+                           group=group)
+    return torch.cat([a, recv[:, 0]], 0), torch.cat([b, recv[:, 1]], 0)
+
+
+def halo_return_pair(shard, ga_ext, gb_ext, group=None):
+    """halo_return of two gradients with ONE all-to-all; same fixed summation order."""
+    import torch.distributed as dist
+    if shard.world == 1:
+        return ga_ext, gb_ext
+    ga_own, gb_own = ga_ext[: shard.n_owned].clone(), gb_ext[: shard.n_owned].clone()
+    send = torch.stack([ga_ext[shard.n_owned:], gb_ext[shard.n_owned:]], 1)
+    recv = ga_ext.new_empty((int(shard.send_all.numel()), 2) + tuple(ga_ext.shape[1:]))
+    dist.all_to_all_single(recv, send, output_split_sizes=shard.send_counts, input_split_sizes=shard.recv_counts,
+                           group=group)
+    off = 0
+    for idx in shard.send_idx:
+        n = int(idx.numel())
+        if n:
+            ga_own[idx] += recv[off:off + n, 0]
+            gb_own[idx] += recv[off:off + n, 1]
+        off += n
+    return ga_own, gb_own
+
+
 class _HaloKV(torch.autograd.Function):
     @staticmethod
     def forward(ctx, shard, x):
@@ -296,7 +328,7 @@ class _StraddleAttention(torch.autograd.Function):
             from .attention import attention_forward, tensor_core_eligible
             if not tensor_core_eligible(q, embed_ak):
                 raise RuntimeError("halo_attention with split straddlers needs bf16 tensors with head dim 64")
-        k_e, v_e = halo_exchange(shard, k.contiguous()), halo_exchange(shard, v.contiguous())
+        k_e, v_e = halo_exchange_pair(shard, k.contiguous(), v.contiguous())
         q_loc = _local_rows(shard, q)
         o_loc, lse_loc = attention_forward(plan, q_loc, k_e, v_e, embed_ak, scale)
         if shard.n_strad:
@@ -336,7 +368,7 @@ class _StraddleAttention(torch.autograd.Function):
         if shard.n_strad and shard.world > 1:
             dist.all_reduce(dq_s)                       # every rank's share of the straddlers' dQ
         dq = _own_rows(shard, dq_loc, dq_s)
-        dk, dv = halo_return(shard, dk_e), halo_return(shard, dv_e)
+        dk, dv = halo_return_pair(shard, dk_e, dv_e)
         return None, None, dq, dk, dv, (dak.to(ak.dtype) if dak is not None else None), None
 
 

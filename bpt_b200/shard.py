@@ -148,6 +148,20 @@ class SequenceShard:
         self.send_counts = [int(t.numel()) for t in self.send_idx]
         self.send_all = torch.cat(self.send_idx) if self.send_idx else torch.zeros(0, dtype=torch.int64, device=dev)
         self.n_ext = self.n_owned + self.n_halo
+        # Table for the way back (halo_return): row i of ret_mat lists the positions in send_all that
+        # name own row ret_rows[i], in peer order, padded with n_send (an all-zero row appended to what
+        # was received).  The returned gradients are then summed with a handful of launches instead of
+        # three per peer, still in a fixed order.
+        n_send = int(self.send_all.numel())
+        order = torch.argsort(self.send_all, stable=True)
+        self.ret_rows, counts = torch.unique_consecutive(self.send_all[order], return_counts=True)
+        n_t = int(self.ret_rows.numel())
+        width = int(counts.max()) if n_t else 0
+        self.ret_mat = torch.full((n_t, width), n_send, dtype=torch.int64, device=dev)
+        if n_t:
+            starts = torch.cumsum(counts, 0) - counts
+            group = torch.repeat_interleave(torch.arange(n_t, device=dev), counts)
+            self.ret_mat[group, torch.arange(n_send, device=dev) - starts[group]] = order
         return self
 
     def pad_rows(self, x):
@@ -212,24 +226,26 @@ def halo_exchange(shard, x, group=None):
     return torch.cat([x, recv], 0)
 
 
+def _wide(x):
+    """16-bit floats are summed in fp32."""
+    return x.float() if x.dtype in (torch.bfloat16, torch.float16) else x
+
+
 def halo_return(shard, g_ext, group=None):
     """Gradient of halo_exchange: sends the halo rows' gradients back to their owners and adds
-    them to the owners' rows, peer by peer in rank order (rows of one peer are distinct, so
-    every sum has a fixed order)."""
+    them to the owners' rows; a row named by several peers gets their contributions summed in
+    fp32 in peer order (shard.ret_mat), so every sum has a fixed order."""
     import torch.distributed as dist
     if shard.world == 1:
         return g_ext
     g_own = g_ext[: shard.n_owned].clone()
     send = g_ext[shard.n_owned:].contiguous()
-    recv = g_ext.new_empty((int(shard.send_all.numel()),) + tuple(g_ext.shape[1:]))
-    dist.all_to_all_single(recv, send, output_split_sizes=shard.send_counts, input_split_sizes=shard.recv_counts,
-                           group=group)
-    off = 0
-    for idx in shard.send_idx:
-        n = int(idx.numel())
-        if n:
-            g_own[idx] += recv[off:off + n]
-        off += n
+    n_send = int(shard.send_all.numel())
+    recv = g_ext.new_zeros((n_send + 1,) + tuple(g_ext.shape[1:]))     # last row stays zero: the table's padding
+    dist.all_to_all_single(recv[:n_send], send, output_split_sizes=shard.send_counts,
+                           input_split_sizes=shard.recv_counts, group=group)
+    if shard.ret_rows.numel():
+        g_own[shard.ret_rows] += _wide(recv[shard.ret_mat]).sum(1).to(g_own.dtype)
     return g_own
 
 
@@ -252,16 +268,14 @@ def halo_return_pair(shard, ga_ext, gb_ext, group=None):
         return ga_ext, gb_ext
     ga_own, gb_own = ga_ext[: shard.n_owned].clone(), gb_ext[: shard.n_owned].clone()
     send = torch.stack([ga_ext[shard.n_owned:], gb_ext[shard.n_owned:]], 1)
-    recv = ga_ext.new_empty((int(shard.send_all.numel()), 2) + tuple(ga_ext.shape[1:]))
-    dist.all_to_all_single(recv, send, output_split_sizes=shard.send_counts, input_split_sizes=shard.recv_counts,
-                           group=group)
-    off = 0
-    for idx in shard.send_idx:
-        n = int(idx.numel())
-        if n:
-            ga_own[idx] += recv[off:off + n, 0]
-            gb_own[idx] += recv[off:off + n, 1]
-        off += n
+    n_send = int(shard.send_all.numel())
+    recv = ga_ext.new_zeros((n_send + 1, 2) + tuple(ga_ext.shape[1:]))  # last row stays zero: the table's padding
+    dist.all_to_all_single(recv[:n_send], send, output_split_sizes=shard.send_counts,
+                           input_split_sizes=shard.recv_counts, group=group)
+    if shard.ret_rows.numel():
+        total = _wide(recv[shard.ret_mat]).sum(1).to(ga_own.dtype)      # (targets, 2, ...)
+        ga_own[shard.ret_rows] += total[:, 0]
+        gb_own[shard.ret_rows] += total[:, 1]
     return ga_own, gb_own
 
 

@@ -101,3 +101,32 @@ def batch_graphs(graphs, dtype=torch.int32):
         n0, n1 = node_offsets[b], node_offsets[b + 1]
         g.fill_into(n0, src[e0:e1], dst[e0:e1], etype[e0:e1], pos[n0:n1])
     return BatchedGraph(src, dst, etype, pos, node_offsets, edge_offsets, [g.length for g in graphs])
+
+
+def inter_graph(src_ranges, dst_ranges, device=None, dtype=torch.int32):
+    """Sentence-aligned cross graph (graph/mt.py:318-321, graph/nli.py:84-87): every node of the
+    i-th source range sends an edge to every node of the i-th destination range.  Ranges are
+    (first id, count) pairs; returns (src, dst) device tensors with the reference's edge order
+    (source slow, destination fast inside a block)."""
+    if len(src_ranges) != len(dst_ranges):
+        raise ValueError("inter_graph: as many source ranges as destination ranges")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bpt_b200.csr.inter_graph needs a CUDA device (there is no CPU path)")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    blocks, offsets = [], [0]
+    for (s0, ns), (d0, nd) in zip(src_ranges, dst_ranges):
+        if ns < 0 or nd < 0:
+            raise ValueError("inter_graph: negative range length")
+        blocks.append((int(s0), int(ns), int(d0), int(nd)))
+        offsets.append(offsets[-1] + int(ns) * int(nd))
+    n_edges = offsets[-1]
+    src = torch.empty(n_edges, dtype=dtype, device=dev)
+    dst = torch.empty(n_edges, dtype=dtype, device=dev)
+    if n_edges:
+        with torch.cuda.device(dev):
+            b = torch.tensor(blocks, dtype=torch.int64).to(dev)
+            o = torch.tensor(offsets, dtype=torch.int64).to(dev)
+            _lib.check(_lib.lib().bpt_dense_blocks_fill(b.data_ptr(), o.data_ptr(), len(blocks), n_edges,
+                                                        src.element_size(), src.data_ptr(), dst.data_ptr(),
+                                                        _lib.stream()))
+    return src, dst

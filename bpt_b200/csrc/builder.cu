@@ -588,3 +588,45 @@ extern "C" int bpt_oas_fill(int64_t length, int64_t stride, int64_t c, const int
     BPT_LAUNCH_CHECK();
     return BPT_OK;
 }
+
+// ---- sentence-aligned cross graph ----
+namespace bpt {
+namespace {
+// Edge e lies in the block b with edge_offsets[b] <= e < edge_offsets[b+1]; inside the block the
+// source is the slow index: (e - offset) / n_dst-th source, (e - offset) % n_dst-th destination,
+// which is np.repeat(src_ids, n_dst) against np.tile(dst_ids, n_src) of graph/mt.py:318-321.
+template <typename IT>
+__global__ void dense_blocks_fill_kernel(const int64_t *__restrict__ blocks, const int64_t *__restrict__ edge_offsets,
+                                         int64_t n_blocks, int64_t n_edges, IT *__restrict__ src, IT *__restrict__ dst) {
+    const int64_t e = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (e >= n_edges) return;
+    int64_t lo = 0, hi = n_blocks;  // last block whose offset is <= e
+    while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (edge_offsets[mid] <= e) lo = mid; else hi = mid;
+    }
+    const int64_t *b = blocks + lo * 4;
+    const int64_t local = e - edge_offsets[lo], n_dst = b[3];
+    src[e] = static_cast<IT>(b[0] + local / n_dst);
+    dst[e] = static_cast<IT>(b[2] + local % n_dst);
+}
+}  // namespace
+}  // namespace bpt
+
+extern "C" int bpt_dense_blocks_fill(const int64_t *blocks, const int64_t *edge_offsets, int64_t n_blocks,
+                                     int64_t n_edges, int index_bytes, void *src, void *dst, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(n_blocks >= 0 && n_edges >= 0, "dense_blocks_fill: negative size");
+    BPT_CHECK_ARG(index_bytes == 4 || index_bytes == 8, "dense_blocks_fill: index_bytes must be 4 or 8");
+    if (n_edges == 0) return BPT_OK;
+    BPT_CHECK_ARG(n_blocks >= 1 && blocks && edge_offsets && src && dst, "dense_blocks_fill: null argument");
+    cudaStream_t stream = as_stream(stream_);
+    const unsigned grid = static_cast<unsigned>((n_edges + 255) / 256);
+    if (index_bytes == 4)
+        dense_blocks_fill_kernel<int32_t><<<grid, 256, 0, stream>>>(blocks, edge_offsets, n_blocks, n_edges,
+                                                                    static_cast<int32_t *>(src), static_cast<int32_t *>(dst));
+    else
+        dense_blocks_fill_kernel<int64_t><<<grid, 256, 0, stream>>>(blocks, edge_offsets, n_blocks, n_edges,
+                                                                    static_cast<int64_t *>(src), static_cast<int64_t *>(dst));
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}

@@ -4,7 +4,11 @@
 without bias, embed_ak of MAX_ETYPE rows, post-LN, FFN) under the same names, so a reference
 state dict loads; its forward (attention.py:54-81) takes the node features and an
 `AttentionPlan` instead of a DGL graph + CSR tuple and replaces the four-operator chain by
-the fused call.  `BPTLanguageModel` is the decoder-only use of
+the fused call.  `BPTMemBlock` (attention.py:84-172) adds attention to an encoder memory over the
+sentence-aligned cross graph; the fused call takes distinct destination and source node sets, so
+the reference's zero padding of the smaller side (attention.py:148-149, model.py:90-93) is not
+needed.  `BPTEncoderDecoder` is the forward of BinaryPartitionEncoderDecoder
+(modules/model.py:22-106) with relative positions.  `BPTLanguageModel` is the decoder-only use of
 BinaryPartitionTransformer.forward (modules/model.py:240-280): token embedding on the leaves,
 zeros on span nodes, `n_layers` blocks over all nodes, log-softmax generator on the leaves.
 Projections, LayerNorm and the FFN are torch operators, as in the reference.
@@ -68,6 +72,55 @@ class BPTBlock(nn.Module):
         return self.norm_inter(h + self.ffn(h))
 
 
+class BPTMemBlock(nn.Module):
+    """modules/attention.py:84-172: self-attention over the node's own graph, then attention from
+    every node to the memory nodes its cross graph names (no relative-position term there), then
+    the FFN.  Parameter names and shapes follow the reference (lists of two for the two
+    attentions), so a reference state dict loads."""
+    MAX_ETYPE = 1000
+
+    def __init__(self, dim_model, h, dim_ff, rel_pos=False, drop_h=0.1, drop_a=0.0, activation="relu"):
+        super().__init__()
+        if drop_a != 0.0:
+            raise ValueError("dropout on attention weights is not available in the fused call; "
+                             "use bpt_b200.op (the operator chain) for drop_a > 0")
+        self.dim_model, self.h, self.dim_ff = dim_model, h, dim_ff
+        self.d_k = dim_model // h
+        self.rel_pos = rel_pos
+        self.drop_h = nn.ModuleList([nn.Dropout(drop_h) for _ in range(2)])
+        self.norm_in = nn.ModuleList([nn.LayerNorm(dim_model) for _ in range(2)])
+        self.norm_inter = nn.LayerNorm(dim_model)
+        self.proj_q = nn.ModuleList([nn.Linear(dim_model, self.d_k * h, bias=False) for _ in range(2)])
+        self.proj_k = nn.ModuleList([nn.Linear(dim_model, self.d_k * h, bias=False) for _ in range(2)])
+        self.proj_v = nn.ModuleList([nn.Linear(dim_model, self.d_k * h, bias=False) for _ in range(2)])
+        self.proj_o = nn.ModuleList([nn.Linear(self.d_k * h, dim_model, bias=False) for _ in range(2)])
+        if rel_pos:
+            self.embed_ak = nn.Embedding(self.MAX_ETYPE, self.d_k)
+        self.ffn = nn.Sequential(PositionwiseFeedForward(dim_model, dim_ff, dropout=drop_h, activation=activation),
+                                 nn.Dropout(drop_h))
+
+    def reset_parameters(self):  # modules/attention.py:111-114
+        for p in self.parameters():
+            if p.dim() > 1:
+                nn.init.xavier_uniform_(p)
+
+    def forward(self, h, plan, mem, plan_inter):
+        """h: (N, dim_model) node features; plan: AttentionPlan of the nodes' own graph; mem:
+        (M, dim_model) memory node features; plan_inter: AttentionPlan(src in [0, M), dst in [0, N),
+        None, N, n_src=M) of the cross graph.  Nodes without a cross edge get a zero attention
+        result, as in the reference."""
+        shape = (-1, self.h, self.d_k)
+        scale = 1.0 / math.sqrt(self.d_k)
+        ak = self.embed_ak.weight if self.rel_pos else None
+        a = bpt_attention(plan, self.proj_q[0](h).view(shape), self.proj_k[0](h).view(shape),
+                          self.proj_v[0](h).view(shape), ak, scale).view(-1, self.d_k * self.h)
+        h = self.norm_in[0](h + self.drop_h[0](self.proj_o[0](a)))                 # attention.py:131-141
+        a = bpt_attention(plan_inter, self.proj_q[1](h).view(shape), self.proj_k[1](mem).view(shape),
+                          self.proj_v[1](mem).view(shape), None, scale).view(-1, self.d_k * self.h)
+        h = self.norm_in[1](h + self.drop_h[1](self.proj_o[1](a)))                 # attention.py:151-168
+        return self.norm_inter(h + self.ffn(h))                                    # attention.py:170-171
+
+
 class Generator(nn.Module):  # modules/model.py:8-17
     def __init__(self, dim_model, n_classes):
         super().__init__()
@@ -98,3 +151,39 @@ class BPTLanguageModel(nn.Module):
         for layer in self.layers:                                              # model.py:268-269
             h = layer(h, plan)
         return self.generator(h[leaf_ids])                                      # model.py:275
+
+
+class BPTEncoderDecoder(nn.Module):
+    """Forward of BinaryPartitionEncoderDecoder (modules/model.py:22-106) with rel_pos=True:
+    `n_layers` blocks over the encoder graph, `m_layers` memory blocks over the decoder graph
+    reading the encoder's node features, generator on the read-out nodes."""
+
+    def __init__(self, vocab_sizes, dim_model, dim_ff, h, n_layers, m_layers, dropout=0.0, activation="relu"):
+        super().__init__()
+        self.embed = nn.ModuleList([nn.Embedding(v, dim_model) for v in vocab_sizes])
+        self.enc_layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
+                                                  activation=activation) for _ in range(n_layers)])
+        self.dec_layers = nn.ModuleList([BPTMemBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
+                                                     activation=activation) for _ in range(m_layers)])
+        self.generator = Generator(dim_model, vocab_sizes[-1])
+        self.norm = nn.LayerNorm(dim_model)
+        self.emb_dropout = nn.Dropout(dropout)
+
+    def _embed(self, table, tokens, leaf_ids, n_nodes):
+        x = self.norm(self.emb_dropout(table(tokens)))                              # model.py:80-83, 96-99
+        h = x.new_zeros((n_nodes, x.size(-1)))
+        h[leaf_ids] = x
+        return h
+
+    def forward(self, enc_tokens, enc_leaf_ids, enc_plan, dec_tokens, dec_leaf_ids, dec_plan, inter_plan,
+                readout_ids):
+        """Tokens in leaf order, their node ids, the three plans (inter_plan: sources = encoder
+        nodes, destinations = decoder nodes) and the decoder nodes to read out.  Returns
+        log-probabilities (len(readout_ids), vocab)."""
+        h_enc = self._embed(self.embed[0], enc_tokens, enc_leaf_ids, enc_plan.n_nodes)
+        for layer in self.enc_layers:                                              # model.py:85-86
+            h_enc = layer(h_enc, enc_plan)
+        h_dec = self._embed(self.embed[-1], dec_tokens, dec_leaf_ids, dec_plan.n_nodes)
+        for layer in self.dec_layers:                                              # model.py:101-102
+            h_dec = layer(h_dec, dec_plan, h_enc, inter_plan)
+        return self.generator(h_dec[readout_ids])                                  # model.py:104

@@ -85,6 +85,15 @@ int bpt_oas_count(int64_t length, int64_t stride, int64_t c, int64_t *leaf_offse
 int bpt_oas_fill(int64_t length, int64_t stride, int64_t c, const int64_t *leaf_offsets, int64_t v_shift,
                  int index_bytes, void *src, void *dst, void *etype, void *pos, bpt_stream_t stream);
 
+/* Sentence-aligned cross graph (decoder -> encoder memory, graph/mt.py:318-321; premise <->
+ * hypothesis, graph/nli.py:84-87): a list of dense blocks.  blocks[b] = {first source id, number
+ * of sources, first destination id, number of destinations} (device int64[n_blocks][4]; zero-size
+ * blocks are skipped by giving them equal offsets), edge_offsets[n_blocks + 1] = running sum of
+ * sources x destinations (device int64).  Edge order inside a block as in the reference: source
+ * slow, destination fast.  src/dst: device arrays of n_edges int32 or int64. */
+int bpt_dense_blocks_fill(const int64_t *blocks, const int64_t *edge_offsets, int64_t n_blocks, int64_t n_edges,
+                          int index_bytes, void *src, void *dst, bpt_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * CSR extraction.  Replaces get_csrs(), graph/base.py:71-86 (two COO->CSR conversions and
  * two partition_csr calls).  Entries of a row are in ascending edge-id order.

@@ -110,6 +110,17 @@ def openai_sparse(length, stride, c):
     return _baseline(lib().bpto_openai_sparse, length, ctypes.c_int64(stride), ctypes.c_int64(c))
 
 
+def inter_graph(src_ranges, dst_ranges):
+    """Sentence-aligned cross graph of graph/mt.py:318-321: for every pair of id ranges
+    (first, count), np.repeat(source ids, n_dst) against np.tile(destination ids, n_src),
+    concatenated in order.  Returns (src, dst) int64."""
+    rows, cols = [np.zeros(0, np.int64)], [np.zeros(0, np.int64)]
+    for (s0, ns), (d0, nd) in zip(src_ranges, dst_ranges):
+        rows.append(np.repeat(np.arange(s0, s0 + ns, dtype=np.int64), nd))
+        cols.append(np.tile(np.arange(d0, d0 + nd, dtype=np.int64), ns))
+    return np.concatenate(rows), np.concatenate(cols)
+
+
 def partition_csr(indptr, chunk_size=32):
     """partition_csr(indptr, chunk_size) of graph_builder/builder.pyx:305-321."""
     indptr = np.ascontiguousarray(indptr, np.int64)

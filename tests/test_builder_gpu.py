@@ -162,3 +162,18 @@ def test_fused_attention_on_baseline_graph(oracle_lib):
         o, _ = attention_forward(plan, q.cuda(), k.cuda(), v.cuda(), ak.cuda(), 0.125)
         err = np.abs(o.double().cpu().numpy() - want).max() / np.abs(want).max()
         assert err < tol, (dtype, err)
+
+
+def test_inter_graph_matches_reference_formula(oracle_lib):
+    """Dense sentence-aligned blocks (graph/mt.py:318-321): edge order and ids, int32 and int64,
+    with an empty block in the middle and no blocks at all."""
+    from bpt_b200 import csr as csrmod
+    src_ranges = [(0, 5), (9, 0), (20, 3), (100, 17)]
+    dst_ranges = [(3, 4), (7, 6), (40, 1), (41, 9)]
+    want = oracle_lib.inter_graph(src_ranges, dst_ranges)
+    for dtype in (torch.int32, torch.int64):
+        got = csrmod.inter_graph(src_ranges, dst_ranges, dtype=dtype)
+        assert got[0].dtype == dtype and np.array_equal(got[0].cpu().numpy(), want[0])
+        assert np.array_equal(got[1].cpu().numpy(), want[1])
+    empty = csrmod.inter_graph([], [])
+    assert empty[0].numel() == 0 and empty[1].numel() == 0

@@ -49,9 +49,10 @@ def parse():
     ap.add_argument("--graph", action="store_true",
                     help="seqshard mode on ONE GPU: capture the step in a CUDA graph and time its replay "
                          "(with more ranks the step holds NCCL collectives and is timed eagerly)")
-    ap.add_argument("--workload", default="attention", choices=["attention", "lm"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
-                         "forward, batch 8 x 8192 tokens per rank, tokens/s")
+                         "forward, batch 8 x 8192 tokens per rank, tokens/s; mt: 6+6-layer encoder-decoder "
+                         "forward over 16 documents of 64 sentences per rank, target tokens/s")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -361,6 +362,97 @@ def run_lm(a):
         dist.destroy_process_group()
 
 
+def run_mt(a):
+    """Document-level translation forward (encoder-decoder, 6 + 6 layers, d_model 512, 8 x 64, FFN 2048,
+    bf16): per rank 16 documents of 64 sentences, sentence lengths Poisson(28) clipped to [3, 100] on both
+    sides (numpy default_rng(4 + rank)); encoder graphs bidirectional, decoder graphs causal, step 4,
+    clip 3; cross-attention over sentence-aligned dense blocks.  tokens/s = target tokens of all ranks /
+    slowest rank's time."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from bpt_b200 import csr as csrmod
+    from bpt_b200.attention import AttentionPlan
+    from bpt_b200.model import BPTEncoderDecoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rng = np.random.default_rng(4 + rank)
+    docs, sents, vocab = 16, 64, 8000
+    src_len = np.clip(rng.poisson(28, (docs, sents)), 3, 100)
+    trg_len = np.clip(rng.poisson(28, (docs, sents)), 3, 100)
+    enc_cache = csrmod.GraphCache(triu=False, step=4, clip_dist=3)
+    dec_cache = csrmod.GraphCache(triu=True, step=4, clip_dist=3)
+    enc = csrmod.batch_graphs([enc_cache.get(int(n)) for n in src_len.sum(1)])
+    dec = csrmod.batch_graphs([dec_cache.get(int(n)) for n in trg_len.sum(1)])
+    src_ranges, dst_ranges = [], []
+    for d_ in range(docs):  # graph/mt.py:289-321: leaves of sentence i on one side see those on the other
+        s0, t0 = enc.node_offsets[d_], dec.node_offsets[d_]
+        for i in range(sents):
+            src_ranges.append((s0, int(src_len[d_, i])))
+            dst_ranges.append((t0, int(trg_len[d_, i])))
+            s0 += int(src_len[d_, i])
+            t0 += int(trg_len[d_, i])
+    isrc, idst = csrmod.inter_graph(src_ranges, dst_ranges)
+    enc_plan = AttentionPlan.from_batch(enc, n_etypes=MAX_ETYPE)
+    dec_plan = AttentionPlan.from_batch(dec, n_etypes=MAX_ETYPE)
+    inter_plan = AttentionPlan(isrc, idst, None, dec.n_nodes, n_src=enc.n_nodes)
+    enc_leaves, dec_leaves = enc.leaf_ids(), dec.leaf_ids()
+    torch.manual_seed(0)
+    model = BPTEncoderDecoder([vocab, vocab], 512, 2048, 8, 6, 6, dropout=0.0)
+    for p in model.parameters():
+        torch.nn.init.normal_(p, 0.0, 0.02)
+    model = model.to(dev).to(torch.bfloat16).eval()
+    n_src_tok, n_trg_tok = int(src_len.sum()), int(trg_len.sum())
+    host_enc = torch.from_numpy(rng.integers(0, vocab, n_src_tok)).pin_memory()
+    host_dec = torch.from_numpy(rng.integers(0, vocab, n_trg_tok)).pin_memory()
+
+    def step():
+        e_tok, d_tok = host_enc.to(dev, non_blocking=True), host_dec.to(dev, non_blocking=True)
+        with torch.no_grad():
+            return model(e_tok, enc_leaves, enc_plan, d_tok, dec_leaves, dec_plan, inter_plan, dec_leaves)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(a.steps):
+        out = step()
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop) / a.steps
+    tokens = torch.tensor([float(n_trg_tok)], device=dev, dtype=torch.float64)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tokens)
+        ms = t.item()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "mt_target_tokens_per_sec", "value": tokens.item() / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "bpt_encoder_decoder_forward 6+6 layers d512 8x64 ffn2048, 16 documents x 64 "
+                                   "sentences per rank, k=4, clip 3",
+                       "encoder_nodes": enc.n_nodes, "encoder_edges": enc.n_edges, "decoder_nodes": dec.n_nodes,
+                       "decoder_edges": dec.n_edges, "cross_edges": int(isrc.numel()),
+                       "source_tokens": n_src_tok, "target_tokens": n_trg_tok,
+                       "finite": bool(torch.isfinite(out.float()).all().item())}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_ours(a):
     import torch
     import torch.distributed as dist
@@ -556,6 +648,8 @@ def main():
         run_reference(a)
     elif a.workload == "lm":
         run_lm(a)
+    elif a.workload == "mt":
+        run_mt(a)
     elif a.mode == "seqshard":
         run_seqshard(a)
     else:

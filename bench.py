@@ -294,7 +294,7 @@ def run_seqshard(a):
 
 
 def run_lm(a):
-    """12-layer causal BPT character LM forward (d_model 512, 8 x 64, FFN 2048 GELU, vocab 256,
+    """12-layer causal BPT character LM forward (d_model 512, 8 x 64, FFN 2048 GELU in its tanh form, vocab 256,
     bf16 activations, fp32 softmax), batch of --seqs sequences of --seq-len tokens per rank, Zipf(1.1)
     bytes (seed 1), weights N(0, 0.02).  tokens/s = tokens of all ranks / slowest rank's time."""
     import numpy as np
@@ -316,7 +316,7 @@ def run_lm(a):
     plan = AttentionPlan.from_batch(batch, n_etypes=MAX_ETYPE)
     leaf_ids = batch.leaf_ids()
     torch.manual_seed(0)
-    model = BPTLanguageModel(256, 512, 2048, 8, 12, dropout=0.0, activation="gelu")
+    model = BPTLanguageModel(256, 512, 2048, 8, 12, dropout=0.0, activation="gelu_tanh")
     for p in model.parameters():
         torch.nn.init.normal_(p, 0.0, 0.02)
     model = model.to(dev).to(torch.bfloat16).eval()
@@ -354,7 +354,7 @@ def run_lm(a):
             "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": "bpt_lm_forward 12 layers d512 8x64 ffn2048 gelu vocab256, %dx(n=%d,k=%d,causal) "
+            "config": {"workload": "bpt_lm_forward 12 layers d512 8x64 ffn2048 gelu(tanh) vocab256, %dx(n=%d,k=%d,causal) "
                                    "per rank" % (a.seqs, a.n, a.k),
                        "nodes_per_gpu": batch.n_nodes, "edges_per_gpu_per_layer": batch.n_edges,
                        "finite": bool(torch.isfinite(out.float()).all().item())}}), flush=True)

@@ -18,7 +18,45 @@ import math
 import torch
 import torch.nn as nn
 
+from . import _lib
 from .attention import bpt_attention
+
+
+class _AddLayerNorm(torch.autograd.Function):
+    """y = LayerNorm(x + r) through bpt_add_layer_norm (one pass over memory).  The backward
+    recomputes the sum and goes through torch's layer-norm derivative."""
+
+    @staticmethod
+    def forward(ctx, x, r, weight, bias, eps):
+        y = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().bpt_add_layer_norm(x.data_ptr(), r.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                                     float(eps), y.data_ptr(), x.numel() // x.size(-1), x.size(-1),
+                                                     _lib.dtype_code(x.dtype), _lib.stream()))
+        ctx.save_for_backward(x, r, weight, bias)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, r, weight, bias = ctx.saved_tensors
+        with torch.enable_grad():
+            s = (x + r).detach().requires_grad_(True)
+            w, b = weight.detach().requires_grad_(True), bias.detach().requires_grad_(True)
+            out = nn.functional.layer_norm(s, (s.size(-1),), w, b, ctx.eps)
+            gs, gw, gb = torch.autograd.grad(out, (s, w, b), gy)
+        return gs, gs, gw, gb, None
+
+
+def add_layer_norm(x, r, norm):
+    """norm(x + r) for an nn.LayerNorm over the last dimension; fused on CUDA when the kernel's
+    shape rules hold (same dtype everywhere, last dimension a multiple of 8 up to 4096)."""
+    dim = x.size(-1)
+    if (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and dim % 8 == 0 and dim <= 4096
+            and norm.weight is not None and norm.bias is not None and norm.weight.dtype == x.dtype
+            and r.dtype == x.dtype and r.shape == x.shape and tuple(norm.normalized_shape) == (dim,)):
+        return _AddLayerNorm.apply(x.contiguous(), r.contiguous(), norm.weight, norm.bias, norm.eps)
+    return norm(x + r)
 
 
 class PositionwiseFeedForward(nn.Module):  # modules/attention.py:8-19
@@ -27,9 +65,19 @@ class PositionwiseFeedForward(nn.Module):  # modules/attention.py:8-19
         self.w_1 = nn.Linear(dim_model, dim_ff)
         self.w_2 = nn.Linear(dim_ff, dim_model)
         self.dropout = nn.Dropout(dropout)
-        self.act = torch.relu if activation == "relu" else nn.functional.gelu
+        if activation not in ("relu", "gelu", "gelu_tanh"):
+            raise ValueError("activation must be relu, gelu or gelu_tanh")
+        self.activation = activation
+        self.act = {"relu": torch.relu, "gelu": nn.functional.gelu,
+                    "gelu_tanh": lambda t: nn.functional.gelu(t, approximate="tanh")}[activation]
 
     def forward(self, x):
+        if (x.is_cuda and x.dim() == 2 and self.activation != "gelu" and not torch.is_grad_enabled()
+                and not (self.training and self.dropout.p > 0) and x.dtype == self.w_1.weight.dtype):
+            # inference: bias and activation ride in the GEMM's epilogue (relu, or gelu in its tanh form)
+            hidden = torch._addmm_activation(self.w_1.bias, x, self.w_1.weight.t(),
+                                             use_gelu=self.activation == "gelu_tanh")
+            return self.w_2(hidden)
         return self.w_2(self.dropout(self.act(self.w_1(x))))
 
 
@@ -68,8 +116,8 @@ class BPTBlock(nn.Module):
         v = self.proj_v(h).view(-1, self.h, self.d_k)
         ak = self.embed_ak.weight if self.rel_pos else None
         a = bpt_attention(plan, q, k, v, ak, 1.0 / math.sqrt(self.d_k)).view(-1, self.d_k * self.h)
-        h = self.norm_in(h + self.drop_h(self.proj_o(a)))
-        return self.norm_inter(h + self.ffn(h))
+        h = add_layer_norm(h, self.drop_h(self.proj_o(a)), self.norm_in)
+        return add_layer_norm(h, self.ffn(h), self.norm_inter)
 
 
 class BPTMemBlock(nn.Module):
@@ -114,11 +162,11 @@ class BPTMemBlock(nn.Module):
         ak = self.embed_ak.weight if self.rel_pos else None
         a = bpt_attention(plan, self.proj_q[0](h).view(shape), self.proj_k[0](h).view(shape),
                           self.proj_v[0](h).view(shape), ak, scale).view(-1, self.d_k * self.h)
-        h = self.norm_in[0](h + self.drop_h[0](self.proj_o[0](a)))                 # attention.py:131-141
+        h = add_layer_norm(h, self.drop_h[0](self.proj_o[0](a)), self.norm_in[0])  # attention.py:131-141
         a = bpt_attention(plan_inter, self.proj_q[1](h).view(shape), self.proj_k[1](mem).view(shape),
                           self.proj_v[1](mem).view(shape), None, scale).view(-1, self.d_k * self.h)
-        h = self.norm_in[1](h + self.drop_h[1](self.proj_o[1](a)))                 # attention.py:151-168
-        return self.norm_inter(h + self.ffn(h))                                    # attention.py:170-171
+        h = add_layer_norm(h, self.drop_h[1](self.proj_o[1](a)), self.norm_in[1])  # attention.py:151-168
+        return add_layer_norm(h, self.ffn(h), self.norm_inter)                     # attention.py:170-171
 
 
 class Generator(nn.Module):  # modules/model.py:8-17

@@ -367,6 +367,17 @@ int bpt_attn_forward_static(const void *plan, const int32_t *counts_host, int64_
                             const void *v, const void *ak, double scale, void *o, float *lse,
                             int h, int d, int dtype, bpt_stream_t stream);
 
+/* ------------------------------------------------------------------------------------
+ * y = LayerNorm(x + r) over the last dimension in one pass (r may be NULL: plain LayerNorm).
+ * The blocks of modules/attention.py end each half with norm(h + sublayer(h))
+ * (attention.py:79-81, 141, 168-171); the reference spells it with torch operators.
+ * x, r, y: (n_rows, dim) of `dtype` (BPT_F32, BPT_BF16, BPT_F16), gamma, beta: (dim) of the same
+ * type (either may be NULL), all 16-byte aligned; dim a multiple of 8, at most 4096.  Statistics in
+ * fp32, biased variance, as torch.nn.LayerNorm.
+ * ---------------------------------------------------------------------------------- */
+int bpt_add_layer_norm(const void *x, const void *r, const void *gamma, const void *beta, double eps, void *y,
+                       int64_t n_rows, int dim, int dtype, bpt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

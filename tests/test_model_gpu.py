@@ -103,3 +103,48 @@ def test_mem_block_equals_operator_chain_block(oracle_lib):
         logp = model(enc_tok, enc.leaf_ids(), enc_plan, dec_tok, dec.leaf_ids(), plan, plan_inter, dec.leaf_ids())
     assert logp.shape == (sum(dec_len), 120)
     assert torch.allclose(logp.float().exp().sum(-1), torch.ones(sum(dec_len), device="cuda"), atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2), (torch.float16, 4e-3)])
+def test_add_layer_norm_matches_torch(dtype, tol):
+    """bpt_add_layer_norm against torch.nn.functional.layer_norm of the sum computed in fp32, over
+    the dimension sizes the kernel's register tiling switches on, and its gradients."""
+    from bpt_b200.model import add_layer_norm
+    torch.manual_seed(3)
+    for dim, rows in ((8, 5), (512, 1000), (520, 33), (1024, 17), (4096, 9)):
+        norm = torch.nn.LayerNorm(dim).cuda()
+        with torch.no_grad():
+            norm.weight.normal_(1.0, 0.2)
+            norm.bias.normal_(0.0, 0.2)
+        norm = norm.to(dtype)
+        x = (torch.randn(rows, dim, device="cuda") * 2 + 0.5).to(dtype).requires_grad_(True)
+        r = torch.randn(rows, dim, device="cuda").to(dtype).requires_grad_(True)
+        y = add_layer_norm(x, r, norm)
+        want = torch.nn.functional.layer_norm(x.float() + r.float(), (dim,), norm.weight.float(), norm.bias.float(),
+                                              norm.eps)
+        assert y.dtype == dtype and rel_err(y.detach().float().cpu(), want.detach().cpu()) < tol
+        gy = torch.randn(rows, dim, device="cuda").to(dtype)
+        y.backward(gy)
+        got = [t.grad.float().cpu() for t in (x, r, norm.weight, norm.bias)]
+        xr, rr = x.detach().float().requires_grad_(True), r.detach().float().requires_grad_(True)
+        w, b = norm.weight.detach().float().requires_grad_(True), norm.bias.detach().float().requires_grad_(True)
+        torch.nn.functional.layer_norm(xr + rr, (dim,), w, b, norm.eps).backward(gy.float())
+        for a, e in zip(got, (xr.grad, rr.grad, w.grad, b.grad)):
+            assert rel_err(a, e.cpu()) < max(tol, 1e-4)
+    # shapes outside the kernel's rules fall back to torch
+    norm = torch.nn.LayerNorm(300).cuda().to(dtype)
+    x = torch.randn(7, 300, device="cuda").to(dtype)
+    assert torch.equal(add_layer_norm(x, x, norm), norm(x + x))
+
+
+def test_feed_forward_epilogue_path_matches_plain_path():
+    """Inference runs bias + activation in the GEMM epilogue; it must agree with the plain path."""
+    from bpt_b200.model import PositionwiseFeedForward
+    torch.manual_seed(4)
+    for act in ("relu", "gelu_tanh"):
+        ffn = PositionwiseFeedForward(128, 512, dropout=0.0, activation=act).cuda().eval()
+        x = torch.randn(300, 128, device="cuda")
+        plain = ffn(x)                      # grad mode on: plain path
+        with torch.no_grad():
+            fused = ffn(x)
+        assert rel_err(fused.cpu(), plain.detach().cpu()) < 1e-5

@@ -149,10 +149,11 @@ attn_forward_tile_kernel(const TcParams p) {
         const int tq = use_qr ? mb[kMbTq] : 0;            // table entry tq (or 1) is the -inf entry
         const uint32_t none_idx = use_qr ? tq : 1;
         const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
-        // first step after j whose 64-column chunk has an edge in this m-block; n_steps if none
+        // first step after j with an edge in this m-block (one mask bit per 32 columns); n_steps if none
+        static_assert(kStep == kMaskCols, "the forward's pipeline step is the mask's granularity");
         auto next_step = [&](int j) {
             ++j;
-            while (j < n_steps && !((chunk_mask >> (j >> 1)) & 1u)) ++j;
+            while (j < n_steps && !((chunk_mask >> j) & 1u)) ++j;
             return j;
         };
         __syncthreads();  // previous m-block's indices are no longer read; s_cols is visible
@@ -432,7 +433,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
     BPT_CHECK_ARG(n_groups == 0 || (groups && mblocks), "attn_forward_tc: null plan arrays");
     BPT_CHECK_ARG(max_cols_pad == 0 || (cols && et), "attn_forward_tc: null plan arrays");
     BPT_CHECK_ARG(et_bytes == 1 || et_bytes == 2, "attn_forward_tc: et_bytes must be 1 or 2");
-    BPT_CHECK_ARG(max_cols_pad % kTileChunk == 0 && max_cols_pad <= kMaxChunks * kTileChunk && t_max % 8 == 0 &&
+    BPT_CHECK_ARG(max_cols_pad % kTileChunk == 0 && max_cols_pad <= kMaxMaskBits * kMaskCols && t_max % 8 == 0 &&
                       n_etypes >= 1 && max_mblocks >= 0 && max_mblocks <= kMaxMBlocks && max_qr_slots >= 0,
                   "attn_forward_tc: bad plan sizes");
     BPT_CHECK_ARG(n_groups < (int64_t(1) << 31) && n_row_items < (int64_t(1) << 31) && h <= 65535,

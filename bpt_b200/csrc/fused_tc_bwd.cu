@@ -100,10 +100,11 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
     for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
         const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
         const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
-        // first step after j whose 64-column chunk has a cell in this m-block; n_steps if none
+        // first step after j with a cell in this m-block (one mask bit per 32 columns, two steps); n_steps if none
+        static_assert(kMaskCols == 2 * kDkvStep, "two pipeline steps per mask bit");
         auto next_step = [&](int j) {
             ++j;
-            while (j < n_steps && !((chunk_mask >> (j >> 2)) & 1u)) ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 1)) & 1u)) ++j;
             return j;
         };
         // packed {p, dS} words of this lane's 8 cells of step j: rows g / g+8, destinations 8nt + 2t, +1
@@ -358,10 +359,11 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
         };
         __syncthreads();
-        // first step after j whose 64-column chunk has an edge in this m-block; n_steps if none
+        // first step after j with an edge in this m-block (one mask bit per 32 columns, two steps); n_steps if none
+        static_assert(kMaskCols == 2 * kDqStep, "two pipeline steps per mask bit");
         auto next_step = [&](int j) {
             ++j;
-            while (j < n_steps && !((chunk_mask >> (j >> 2)) & 1u)) ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 1)) & 1u)) ++j;
             return j;
         };
         // The first head's first rows and operand rows start travelling before the cells are staged.
@@ -675,7 +677,7 @@ int check_tile_plan(const char *name, const bpt_tile_plan_t *tp, bool need_et, b
     BPT_CHECK_ARG(tp->n_groups >= 0 && tp->n_split >= 0 && tp->n_slots >= 0 && tp->n_groups < (int64_t(1) << 31),
                   "%s: bad tile plan sizes", name);
     BPT_CHECK_ARG(tp->n_groups == 0 || (tp->groups && tp->mblocks), "%s: null tile plan arrays", name);
-    BPT_CHECK_ARG(tp->max_cols_pad % kTileChunk == 0 && tp->max_cols_pad <= kMaxChunks * kTileChunk && tp->t_max % 8 == 0,
+    BPT_CHECK_ARG(tp->max_cols_pad % kTileChunk == 0 && tp->max_cols_pad <= kMaxMaskBits * kMaskCols && tp->t_max % 8 == 0,
                   "%s: bad tile plan sizes", name);
     BPT_CHECK_ARG(tp->max_cols_pad == 0 || tp->cols, "%s: null tile plan arrays", name);
     if (need_et) BPT_CHECK_ARG(tp->max_cols_pad == 0 || (tp->et && (tp->et_bytes == 1 || tp->et_bytes == 2)), "%s: tile plan without edge types", name);

@@ -131,7 +131,7 @@ void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr,
                     const size_t cell = base + (static_cast<size_t>(chunk) * kTileRows + r) * kTileChunk + (c % kTileChunk);
                     plan.et[cell] = static_cast<uint16_t>(e.etype);
                     plan.cellpos[cell] = e.pos;
-                    mask |= 1u << chunk;
+                    mask |= 1u << (c / kMaskCols);
                     if (e.etype > max_et) max_et = e.etype;
                     ++cnt;
                     ++p;
@@ -164,7 +164,7 @@ extern "C" void *bpt_tile_plan_create(const int32_t *in_indptr, const int32_t *i
                                       int group_rows, int col_block, int simt_max_degree, int max_mblocks,
                                       int join_dense) {
     if (!in_indptr || (n_edges > 0 && !in_src) || n_nodes < 0 || n_edges < 0 || max_cols < kTileChunk ||
-        max_cols > kMaxChunks * kTileChunk || col_block < 1 || group_rows < kTileRows ||
+        max_cols > kMaxMaskBits * kMaskCols || col_block < 1 || group_rows < kTileRows ||
         group_rows % kTileRows != 0 || max_mblocks < 1 || max_mblocks > kMaxMBlocks ||
         group_rows / kTileRows > max_mblocks) {
         fail(BPT_ERR_INVALID, "tile_plan_create: bad arguments");

@@ -13,7 +13,8 @@ namespace bpt {
 constexpr int kTileRows = 16;     // destination rows per m-block (one mma M block)
 constexpr int kTileChunk = 64;    // source columns per pipeline step; column counts are padded to it
 constexpr int kMaxMBlocks = 8;    // m-blocks (warps) per group at most
-constexpr int kMaxChunks = 32;    // chunk activity is a 32-bit mask
+constexpr int kMaskCols = 32;     // an m-block's activity mask has one bit per 32 columns
+constexpr int kMaxMaskBits = 32;  // so a group holds at most 1024 columns
 
 // group record: kGroupInts int32 words
 constexpr int kGroupInts = 8;
@@ -29,7 +30,7 @@ constexpr int kMbRowOff = 0;       // [0,16): destination row ids, -1 = unused
 constexpr int kMbSlotOff = 16;     // [16,32): partial-result slot per row, -1 = this m-block holds the whole row
 constexpr int kMbRowEtOff = 32;    // [32,48): the row's single edge type when kMbQrSlot < 0
 constexpr int kMbEtOff = 48;       // offset (in cells) of the [chunks][16][64] edge-type matrix in `et`
-constexpr int kMbChunkMask = 49;   // bit c set = some row has an edge in column chunk c
+constexpr int kMbChunkMask = 49;   // bit s set = some row has an edge in columns [32 s, 32 s + 32)
 constexpr int kMbTq = 50;          // edge types [0, tq) occur (multiple of 8)
 constexpr int kMbQrSlot = 51;      // >= 0: needs the per-row relative-position table, in this shared-memory
                                    // slot; -1: every row's edges share one type, so the term is a per-row

@@ -89,8 +89,8 @@ def test_plan_covers_every_edge_once(oracle_lib, spec, kw):
                 n_qr += 1
             else:
                 assert all(uniform[valid])
-            for ch in range(ncp // 64):
-                assert bool((int(mask) >> ch) & 1) == bool(np.any(cells[ch] != none))
+            for st in range(ncp // 32):     # one activity bit per 32 columns
+                assert bool((int(mask) >> st) & 1) == bool(np.any(cells[st // 2][:, 32 * (st % 2):32 * (st % 2) + 32] != none))
             for i in range(16):
                 row_cells = cells[:, i, :].reshape(-1)
                 if rows[i] < 0:

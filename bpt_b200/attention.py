@@ -127,7 +127,7 @@ class TilePlan:
              self.max_cols_pad, self.max_mblocks, self.max_qr_slots, self.n_row_items,
              self.n_dense_groups) = [int(x) for x in sizes]
             max_et = 0 if transposed or not E else int(extra[:E].max())
-            self.et_bytes = 1 if max_et < 255 else 2
+            self.et_bytes = 1 if max_et < 248 else 2  # 8-bit cells: types and the "no edge" table index fit a byte
             groups = np.empty(max(self.n_groups * 8, 1), np.int32)
             mblocks = np.empty(max(self.n_mblocks * 56, 1), np.int32)
             cols = np.empty(max(n_cols, 1), np.int32)

@@ -1,8 +1,11 @@
 // Fused graph attention forward on tensor cores (bf16 storage, fp32 accumulation, head dim 64).
 //
-// One thread block per group of the tile plan (tile_plan.cuh), one warp per head.  The block
-// stages the group's column ids, the m-block's cells (as table indices) and the embed_ak rows it
-// can meet once; the warp's first K and V rows are already travelling while that happens.  For
+// A thread block works on two groups of the tile plan (tile_plan.cuh) at once, four warps each; a
+// warp takes heads w, w + 4, ... of its group.  (Two groups per block keep four independent
+// chains of dependent loads in flight per SM at the same register and shared-memory budget, and
+// share one copy of the embed_ak rows.)  The four warps stage the group's column ids and the
+// m-block's cells (as table indices) once; the warp's first K and V rows are already travelling
+// while that happens.  For
 // each m-block of the group (<=16 destination rows x the group's column list) and each active
 // 32-column step a warp
 //   1. takes the step's K rows from its K buffer (cp.async, swizzled; ldmatrix B fragments),
@@ -78,8 +81,32 @@ template <typename ET> struct EtTraits;
 template <> struct EtTraits<uint8_t> { static constexpr uint32_t kNone = kNoEdge8; };
 template <> struct EtTraits<uint16_t> { static constexpr uint32_t kNone = kNoEdge; };
 
-constexpr int kWarps = 8;
-constexpr int kEtPad = 8;  // uint16 padding per staged index row (spreads the 8 row groups over the banks)
+constexpr int kTileWarps = 4;       // warps that share one tile (group); a warp takes heads w, w + 4, ...
+constexpr int kTilesPerBlock = 2;   // a block works on two tiles at once, four warps each
+constexpr int kWarps = kTileWarps * kTilesPerBlock;
+constexpr int kEtPad = 8;  // padding per staged index row (spreads the 8 row groups over the banks)
+// Staged table indices are as wide as the plan's cells; with 8-bit cells the -inf entry's index
+// (the m-block's type count, at most kMaxTypes8) still fits.
+constexpr int kMaxTypes8 = 248;
+
+// Two neighbouring staged table indices (8- or 16-bit) in one shared-memory load.
+__device__ __forceinline__ void load_idx_pair(const uint8_t *p, uint32_t &a, uint32_t &b) {
+    const uint32_t v = *reinterpret_cast<const uint16_t *>(p);
+    a = v & 0xffu;
+    b = v >> 8;
+}
+__device__ __forceinline__ void load_idx_pair(const uint16_t *p, uint32_t &a, uint32_t &b) {
+    const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+    a = v & 0xffffu;
+    b = v >> 16;
+}
+// Barrier among the four warps of one tile (ids 1 and 2; 0 is the block's).
+__device__ __forceinline__ void tile_barrier(int tile_in_block) {
+    if (tile_in_block == 0)
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kTileWarps * 32) : "memory");
+    else
+        asm volatile("bar.sync 2, %0;\n" ::"n"(kTileWarps * 32) : "memory");
+}
 
 struct TcParams {
     const int32_t *groups, *mblocks, *cols;
@@ -88,6 +115,7 @@ struct TcParams {
     __nv_bfloat16 *o;
     float *lse, *part_o, *part_ml;
     int n_etypes, H, max_cols_pad, t_max;
+    int64_t n_groups;
     float scale;
 };
 
@@ -95,20 +123,41 @@ template <typename ET, bool kHasBias>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 attn_forward_tile_kernel(const TcParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: K and V buffers (one pair per warp, 8 KB) | column ids | table indices of the m-block |
-    // tables (fp16, one per warp) | embed_ak rows
-    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKvStageBytes);
-    uint16_t *s_idx = reinterpret_cast<uint16_t *>(s_cols + p.max_cols_pad);
+    // layout: K and V buffers (one pair per warp, 8 KB) | column ids (per tile) | table indices of the
+    // m-block (per tile) | tables (fp16, one per warp) | embed_ak rows (shared by both tiles)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tib = warp / kTileWarps, wl = warp % kTileWarps;  // tile in block, warp in tile
+    const int tid = threadIdx.x % (kTileWarps * 32);             // thread in tile
+    constexpr int kTileThreads = kTileWarps * 32;
     const int idx_stride = p.max_cols_pad + kEtPad;
-    __half *s_tab_all = reinterpret_cast<__half *>(s_idx + kTileRows * idx_stride);
+    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKvStageBytes) + tib * p.max_cols_pad;
+    ET *s_idx_all = reinterpret_cast<ET *>(reinterpret_cast<int32_t *>(smem + kWarps * kKvStageBytes) +
+                                           kTilesPerBlock * p.max_cols_pad);
+    ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
+    __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
     const int tab_stride = p.t_max + 8;  // t_max types + the -inf entry, padded; >= 8
     // embed_ak rows [0, t_max), staged once per block (16-byte aligned: every region before it is)
     const uint32_t s_ak_addr = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
 
-    const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
+    if (kHasBias) {
+        for (int i = threadIdx.x; i < p.t_max * 8; i += blockDim.x) {
+            const int r = i >> 3, piece = i & 7;
+            const int type = r < p.n_etypes ? r : p.n_etypes - 1;
+            cp_async16(s_ak_addr + r * kRowBytes + ((piece ^ (r & 7)) << 4),
+                       p.ak + static_cast<int64_t>(type) * kHeadDim + piece * 8);
+        }
+    }
+    cp_async_commit();
+    const int64_t tile = static_cast<int64_t>(blockIdx.x) * kTilesPerBlock + tib;
+    const int32_t *grp = p.groups + (tile < p.n_groups ? tile : 0) * kGroupInts;
+    const int n_mblocks = tile < p.n_groups ? grp[kGroupMbCount] : 0;
+    if (n_mblocks == 0) {  // no tile for this half of the block: only keep the block's one barrier
+        cp_async_wait<0>();
+        __syncthreads();
+        return;
+    }
     const int ncols_pad = grp[kGroupNcolsPad];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int H = p.H;
     const uint32_t s_k_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kKvStageBytes));
@@ -120,17 +169,8 @@ attn_forward_tile_kernel(const TcParams p) {
 
     {
         const int32_t *gc = p.cols + grp[kGroupColOff];
-        for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
+        for (int i = tid; i < ncols_pad; i += kTileThreads) s_cols[i] = gc[i];
     }
-    if (kHasBias) {
-        for (int i = threadIdx.x; i < p.t_max * 8; i += blockDim.x) {
-            const int r = i >> 3, piece = i & 7;
-            const int type = r < p.n_etypes ? r : p.n_etypes - 1;
-            cp_async16(s_ak_addr + r * kRowBytes + ((piece ^ (r & 7)) << 4),
-                       p.ak + static_cast<int64_t>(type) * kHeadDim + piece * 8);
-        }
-    }
-    cp_async_commit();
 
     // 32 rows of K or V of head h for step j -> the warp's buffer (16-byte pieces, piece index XOR (row & 7))
     auto issue_rows = [&](uint32_t dst, const __nv_bfloat16 *__restrict__ base, int h, int j) {
@@ -143,7 +183,7 @@ attn_forward_tile_kernel(const TcParams p) {
         }
     };
 
-    for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
+    for (int mbi = 0; mbi < n_mblocks; ++mbi) {
         const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
         const bool use_qr = kHasBias && mb[kMbQrSlot] >= 0;
         const int tq = use_qr ? mb[kMbTq] : 0;            // table entry tq (or 1) is the -inf entry
@@ -156,20 +196,20 @@ attn_forward_tile_kernel(const TcParams p) {
             while (j < n_steps && !((chunk_mask >> j) & 1u)) ++j;
             return j;
         };
-        __syncthreads();  // previous m-block's indices are no longer read; s_cols is visible
+        tile_barrier(tib);  // previous m-block's indices are no longer read; s_cols is visible
         // The warp's first K and V rows start travelling now; the cells, Q and the table follow
         // while they are in flight.
         int primed_step = -1;
-        if (warp < H) primed_step = next_step(-1);
-        if (primed_step >= 0 && primed_step < n_steps) issue_rows(s_k_addr, p.k, warp, primed_step);
+        if (wl < H) primed_step = next_step(-1);
+        if (primed_step >= 0 && primed_step < n_steps) issue_rows(s_k_addr, p.k, wl, primed_step);
         cp_async_commit();
-        if (primed_step >= 0 && primed_step < n_steps) issue_rows(s_v_addr, p.v, warp, primed_step);
+        if (primed_step >= 0 && primed_step < n_steps) issue_rows(s_v_addr, p.v, wl, primed_step);
         cp_async_commit();
         const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
         uint32_t q_lo[8], q_hi[8];
-        if (warp < H) {
-            load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + warp) * kHeadDim, t, q_lo);
-            load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + warp) * kHeadDim, t, q_hi);
+        if (wl < H) {
+            load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + wl) * kHeadDim, t, q_lo);
+            load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + wl) * kHeadDim, t, q_hi);
         }
         {
             // stage the m-block's cells as table indices: edge type, or the -inf entry; 16 bytes of
@@ -177,23 +217,27 @@ attn_forward_tile_kernel(const TcParams p) {
             constexpr int kCellsPerPiece = 16 / static_cast<int>(sizeof(ET));
             const uint4 *ge = reinterpret_cast<const uint4 *>(et_base + mb[kMbEtOff]);
             const int pieces = kTileRows * ncols_pad / kCellsPerPiece;
-            for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+            for (int i = tid; i < pieces; i += kTileThreads) {
                 const int cell = i * kCellsPerPiece;
                 const int chunk = cell / (kTileRows * kTileChunk), rem = cell % (kTileRows * kTileChunk);
                 const int r = rem / kTileChunk, c = rem % kTileChunk;
                 const uint4 raw = __ldg(ge + i);
                 const ET *e = reinterpret_cast<const ET *>(&raw);
-                uint16_t *dst = s_idx + r * idx_stride + chunk * kTileChunk + c;
+                ET *dst = s_idx + r * idx_stride + chunk * kTileChunk + c;
 #pragma unroll
                 for (int u = 0; u < kCellsPerPiece; ++u)
-                    dst[u] = static_cast<uint16_t>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
+                    dst[u] = static_cast<ET>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
             }
         }
-        cp_async_wait<2>();  // embed_ak rows have landed (the two newest groups are the first K and V)
-        __syncthreads();
+        if (mbi == 0) {
+            cp_async_wait<2>();  // embed_ak rows have landed (the two newest groups are the first K and V)
+            __syncthreads();     // the block's one barrier: both tiles' threads staged embed_ak
+        } else {
+            tile_barrier(tib);
+        }
 
-        for (int h = warp; h < H; h += kWarps) {
-            if (h != warp) {
+        for (int h = wl; h < H; h += kTileWarps) {
+            if (h != wl) {
                 load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim, t, q_lo);
                 load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim, t, q_hi);
             }
@@ -291,12 +335,13 @@ attn_forward_tile_kernel(const TcParams p) {
                 float cmax_lo = -INFINITY, cmax_hi = -INFINITY;
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
-                    const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c0 + nt * 8 + 2 * t);
-                    const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c0 + nt * 8 + 2 * t);
-                    s[nt][0] = fmaf(s[nt][0], sl2, __half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]));
-                    s[nt][1] = fmaf(s[nt][1], sl2, __half2float(s_tab[g * tab_stride + (i_lo >> 16)]));
-                    s[nt][2] = fmaf(s[nt][2], sl2, __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]));
-                    s[nt][3] = fmaf(s[nt][3], sl2, __half2float(s_tab[(g + 8) * tab_stride + (i_hi >> 16)]));
+                    uint32_t i_lo0, i_lo1, i_hi0, i_hi1;
+                    load_idx_pair(s_idx + g * idx_stride + c0 + nt * 8 + 2 * t, i_lo0, i_lo1);
+                    load_idx_pair(s_idx + (g + 8) * idx_stride + c0 + nt * 8 + 2 * t, i_hi0, i_hi1);
+                    s[nt][0] = fmaf(s[nt][0], sl2, __half2float(s_tab[g * tab_stride + i_lo0]));
+                    s[nt][1] = fmaf(s[nt][1], sl2, __half2float(s_tab[g * tab_stride + i_lo1]));
+                    s[nt][2] = fmaf(s[nt][2], sl2, __half2float(s_tab[(g + 8) * tab_stride + i_hi0]));
+                    s[nt][3] = fmaf(s[nt][3], sl2, __half2float(s_tab[(g + 8) * tab_stride + i_hi1]));
                     cmax_lo = fmaxf(cmax_lo, fmaxf(s[nt][0], s[nt][1]));
                     cmax_hi = fmaxf(cmax_hi, fmaxf(s[nt][2], s[nt][3]));
                 }
@@ -389,9 +434,9 @@ attn_forward_tile_kernel(const TcParams p) {
     }
 }
 
-size_t tc_smem_bytes(int max_cols_pad, int t_max) {
-    return static_cast<size_t>(kWarps) * kKvStageBytes + static_cast<size_t>(max_cols_pad) * 4 +
-           static_cast<size_t>(kTileRows) * (max_cols_pad + kEtPad) * 2 +
+size_t tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
+    return static_cast<size_t>(kWarps) * kKvStageBytes + static_cast<size_t>(kTilesPerBlock) * max_cols_pad * 4 +
+           static_cast<size_t>(kTilesPerBlock) * kTileRows * (max_cols_pad + kEtPad) * et_bytes +
            static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2 + static_cast<size_t>(t_max) * kRowBytes;
 }
 
@@ -399,7 +444,8 @@ template <typename ET, bool kHasBias>
 int launch_tile_kernel(const TcParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
     BPT_CUDA(cudaFuncSetAttribute(attn_forward_tile_kernel<ET, kHasBias>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attn_forward_tile_kernel<ET, kHasBias><<<static_cast<unsigned>(n_groups), kWarps * 32, smem, stream>>>(p);
+    attn_forward_tile_kernel<ET, kHasBias><<<static_cast<unsigned>((n_groups + kTilesPerBlock - 1) / kTilesPerBlock),
+                                             kWarps * 32, smem, stream>>>(p);
     BPT_LAUNCH_CHECK();
     return BPT_OK;
 }
@@ -466,7 +512,10 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
         p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = max_cols_pad;
         p.t_max = bias ? t_max : 0;
         p.scale = static_cast<float>(scale);
-        const size_t smem = tc_smem_bytes(max_cols_pad, p.t_max);
+        p.n_groups = n_groups;
+        if (et_bytes == 1 && p.t_max > kMaxTypes8)
+            return fail(BPT_ERR_INVALID, "attn_forward_tc: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
+        const size_t smem = tc_smem_bytes(max_cols_pad, p.t_max, et_bytes);
         if (smem > 227 * 1024)
             return fail(BPT_ERR_UNSUPPORTED, "attn_forward_tc: tile plan needs %zu bytes of shared memory", smem);
         int rc;

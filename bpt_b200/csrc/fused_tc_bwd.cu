@@ -251,6 +251,31 @@ template <> struct EtTraits<uint8_t> { static constexpr uint32_t kNone = kNoEdge
 template <> struct EtTraits<uint16_t> { static constexpr uint32_t kNone = kNoEdge; };
 
 constexpr int kIdxPad = 8;
+// The destination-side kernel works on two tiles per block, four warps each (a warp takes heads
+// w, w + 4, ...): four independent chains of dependent loads per SM instead of two, one copy of the
+// embed_ak rows.  8-bit plans stage 8-bit table indices, which is what makes room for the second tile.
+constexpr int kTileWarps = 4;
+constexpr int kTilesPerBlock = 2;
+constexpr int kMaxTypes8 = 248;  // with 8-bit cells the -inf entry's index (the type count) must fit a byte
+static_assert(kTileWarps * kTilesPerBlock == kWarps, "two tiles of four warps fill the block");
+
+__device__ __forceinline__ void load_idx_pair(const uint8_t *p, uint32_t &a, uint32_t &b) {
+    const uint32_t v = *reinterpret_cast<const uint16_t *>(p);
+    a = v & 0xffu;
+    b = v >> 8;
+}
+__device__ __forceinline__ void load_idx_pair(const uint16_t *p, uint32_t &a, uint32_t &b) {
+    const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+    a = v & 0xffffu;
+    b = v >> 16;
+}
+// Barrier among the four warps of one tile (ids 1 and 2; 0 is the block's).
+__device__ __forceinline__ void tile_barrier(int tile_in_block) {
+    if (tile_in_block == 0)
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kTileWarps * 32) : "memory");
+    else
+        asm volatile("bar.sync 2, %0;\n" ::"n"(kTileWarps * 32) : "memory");
+}
 constexpr int kDqStep = 16;                            // columns per pipeline step of the dQ tile kernel
 constexpr int kDqBufBytes = 2 * kDqStep * kRowBytes;   // one buffer: K rows then V rows of a step (4 KB)
 constexpr int kKStageBytes = 2 * kDqBufBytes;          // per warp: two buffers
@@ -265,6 +290,7 @@ struct DqParams {
     float *part_dq;
     __nv_bfloat16 *dq;
     int n_etypes, H, max_cols_pad, t_max;
+    int64_t n_groups;
     float scale;
 };
 
@@ -272,29 +298,21 @@ template <typename ET, bool kHasBias>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 attn_backward_dq_tile_kernel(const DqParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: K stages (one per warp, 8 KB) | column ids | table indices of the m-block | tables (fp16, per warp) |
-    // embed_ak rows [0, t_max)
-    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKStageBytes);
-    uint16_t *s_idx = reinterpret_cast<uint16_t *>(s_cols + p.max_cols_pad);
+    // layout: K/V buffers (per warp, 8 KB) | column ids (per tile) | table indices of the m-block (per tile) |
+    // tables (fp16, per warp) | embed_ak rows [0, t_max) (shared by both tiles)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tib = warp / kTileWarps, wl = warp % kTileWarps;  // tile in block, warp in tile
+    const int tid = threadIdx.x % (kTileWarps * 32);
+    constexpr int kTileThreads = kTileWarps * 32;
     const int idx_stride = p.max_cols_pad + kIdxPad;
-    __half *s_tab_all = reinterpret_cast<__half *>(s_idx + kTileRows * idx_stride);
+    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kKStageBytes) + tib * p.max_cols_pad;
+    ET *s_idx_all = reinterpret_cast<ET *>(reinterpret_cast<int32_t *>(smem + kWarps * kKStageBytes) +
+                                           kTilesPerBlock * p.max_cols_pad);
+    ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
+    __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
     const int tab_stride = p.t_max + 8;
     const uint32_t s_ak = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
-
-    const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
-    const int ncols_pad = grp[kGroupNcolsPad];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int H = p.H;
-    const uint32_t s_k = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kKStageBytes));
-    __half *s_tab = s_tab_all + static_cast<int64_t>(warp) * kTileRows * tab_stride;
-    const float sl2 = p.scale * kLog2e;
-    const ET *et_base = static_cast<const ET *>(p.et);
-    {
-        const int32_t *gc = p.cols + grp[kGroupColOff];
-        for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
-    }
     if (kHasBias) {
         for (int i = threadIdx.x; i < p.t_max * 8; i += blockDim.x) {
             const int r = i >> 3, piece = i & 7;
@@ -303,6 +321,25 @@ attn_backward_dq_tile_kernel(const DqParams p) {
         }
     }
     cp_async_commit();
+    const int64_t tile = static_cast<int64_t>(blockIdx.x) * kTilesPerBlock + tib;
+    const int32_t *grp = p.groups + (tile < p.n_groups ? tile : 0) * kGroupInts;
+    const int n_mblocks = tile < p.n_groups ? grp[kGroupMbCount] : 0;
+    if (n_mblocks == 0) {  // no tile for this half of the block: only keep the block's one barrier
+        cp_async_wait_all();
+        __syncthreads();
+        return;
+    }
+    const int ncols_pad = grp[kGroupNcolsPad];
+    const int g = lane >> 2, t = lane & 3;
+    const int H = p.H;
+    const uint32_t s_k = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kKStageBytes));
+    __half *s_tab = s_tab_all + static_cast<int64_t>(warp) * kTileRows * tab_stride;
+    const float sl2 = p.scale * kLog2e;
+    const ET *et_base = static_cast<const ET *>(p.et);
+    {
+        const int32_t *gc = p.cols + grp[kGroupColOff];
+        for (int i = tid; i < ncols_pad; i += kTileThreads) s_cols[i] = gc[i];
+    }
     const int n_steps = ncols_pad / kDqStep;
     // K and V rows of head h for the 16 columns of step j -> buffer b of the warp (K rows, then V rows)
     auto issue_kv = [&](int h, int j, int b) {
@@ -316,7 +353,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             cp_async16(dst + kDqBufBytes / 2, p.v + off);
         }
     };
-    for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
+    for (int mbi = 0; mbi < n_mblocks; ++mbi) {
         const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
         const bool use_qr = kHasBias && mb[kMbQrSlot] >= 0;
         const int tq = use_qr ? mb[kMbTq] : 0;
@@ -358,7 +395,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             lse2_lo = lse2_lo == -INFINITY ? 0.f : lse2_lo * kLog2e;
             lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
         };
-        __syncthreads();
+        tile_barrier(tib);  // previous m-block's indices are no longer read; s_cols is visible
         // first step after j with an edge in this m-block (one mask bit per 32 columns, two steps); n_steps if none
         static_assert(kMaskCols == 2 * kDqStep, "two pipeline steps per mask bit");
         auto next_step = [&](int j) {
@@ -368,33 +405,37 @@ attn_backward_dq_tile_kernel(const DqParams p) {
         };
         // The first head's first rows and operand rows start travelling before the cells are staged.
         int primed_step = -1;
-        if (warp < H) {
+        if (wl < H) {
             primed_step = next_step(-1);
-            if (primed_step < n_steps) issue_kv(warp, primed_step, 0);
+            if (primed_step < n_steps) issue_kv(wl, primed_step, 0);
         }
         cp_async_commit();
-        if (warp < H) load_head(warp);
+        if (wl < H) load_head(wl);
         {
             constexpr int kCellsPerPiece = 16 / static_cast<int>(sizeof(ET));
             const uint4 *ge = reinterpret_cast<const uint4 *>(et_base + mb[kMbEtOff]);
             const int pieces = kTileRows * ncols_pad / kCellsPerPiece;
-            for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+            for (int i = tid; i < pieces; i += kTileThreads) {
                 const int cell = i * kCellsPerPiece;
                 const int chunk = cell / (kTileRows * kTileChunk), rem = cell % (kTileRows * kTileChunk);
                 const int r = rem / kTileChunk, c = rem % kTileChunk;
                 const uint4 raw = __ldg(ge + i);
                 const ET *e = reinterpret_cast<const ET *>(&raw);
-                uint16_t *dst = s_idx + r * idx_stride + chunk * kTileChunk + c;
+                ET *dst = s_idx + r * idx_stride + chunk * kTileChunk + c;
 #pragma unroll
                 for (int u = 0; u < kCellsPerPiece; ++u)
-                    dst[u] = static_cast<uint16_t>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
+                    dst[u] = static_cast<ET>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
             }
         }
-        cp_async_wait_one();  // embed_ak rows have landed; the newest group is the first K
-        __syncthreads();
+        if (mbi == 0) {
+            cp_async_wait_one();  // embed_ak rows have landed; the newest group is the first K and V
+            __syncthreads();      // the block's one barrier: both tiles' threads staged embed_ak
+        } else {
+            tile_barrier(tib);
+        }
 
-        for (int h = warp; h < H; h += kWarps) {
-            if (h != warp) load_head(h);
+        for (int h = wl; h < H; h += kTileWarps) {
+            if (h != wl) load_head(h);
             if (use_qr) {
                 for (int nt = 0; nt < tq; nt += 8) {
                     const int r = nt + (lane & 7), pc = lane >> 3;
@@ -502,13 +543,14 @@ attn_backward_dq_tile_kernel(const DqParams p) {
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     const int c = j * kDqStep + nt * 8 + 2 * t;
-                    const uint32_t i_lo = *reinterpret_cast<const uint32_t *>(s_idx + g * idx_stride + c);
-                    const uint32_t i_hi = *reinterpret_cast<const uint32_t *>(s_idx + (g + 8) * idx_stride + c);
+                    uint32_t i_lo0, i_lo1, i_hi0, i_hi1;
+                    load_idx_pair(s_idx + g * idx_stride + c, i_lo0, i_lo1);
+                    load_idx_pair(s_idx + (g + 8) * idx_stride + c, i_hi0, i_hi1);
                     const int4 pos4 = pos_cur[nt];
-                    const float tab[4] = {__half2float(s_tab[g * tab_stride + (i_lo & 0xffffu)]),
-                                          __half2float(s_tab[g * tab_stride + (i_lo >> 16)]),
-                                          __half2float(s_tab[(g + 8) * tab_stride + (i_hi & 0xffffu)]),
-                                          __half2float(s_tab[(g + 8) * tab_stride + (i_hi >> 16)])};
+                    const float tab[4] = {__half2float(s_tab[g * tab_stride + i_lo0]),
+                                          __half2float(s_tab[g * tab_stride + i_lo1]),
+                                          __half2float(s_tab[(g + 8) * tab_stride + i_hi0]),
+                                          __half2float(s_tab[(g + 8) * tab_stride + i_hi1])};
                     const int pos[4] = {pos4.x, pos4.y, pos4.z, pos4.w};
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -715,7 +757,8 @@ template <typename ET, bool kHasBias>
 int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
     BPT_CUDA(cudaFuncSetAttribute(attn_backward_dq_tile_kernel<ET, kHasBias>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attn_backward_dq_tile_kernel<ET, kHasBias><<<static_cast<unsigned>(n_groups), kWarps * 32, smem, stream>>>(p);
+    attn_backward_dq_tile_kernel<ET, kHasBias><<<static_cast<unsigned>((n_groups + kTilesPerBlock - 1) / kTilesPerBlock),
+                                                 kWarps * 32, smem, stream>>>(p);
     BPT_LAUNCH_CHECK();
     return BPT_OK;
 }
@@ -788,8 +831,12 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = dst_tiles->max_cols_pad;
         p.t_max = bias ? dst_tiles->t_max : 0;
         p.scale = sc;
-        const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes + static_cast<size_t>(p.max_cols_pad) * 4 +
-                            static_cast<size_t>(kTileRows) * (p.max_cols_pad + kIdxPad) * 2 +
+        p.n_groups = dst_tiles->n_groups;
+        if (dst_tiles->et_bytes == 1 && p.t_max > kMaxTypes8)
+            return fail(BPT_ERR_INVALID, "attn_backward_tc: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
+        const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes +
+                            static_cast<size_t>(kTilesPerBlock) * p.max_cols_pad * 4 +
+                            static_cast<size_t>(kTilesPerBlock) * kTileRows * (p.max_cols_pad + kIdxPad) * dst_tiles->et_bytes +
                             static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2 +
                             static_cast<size_t>(p.t_max) * kRowBytes;
         if (smem > 227 * 1024)

@@ -49,10 +49,12 @@ def parse():
     ap.add_argument("--graph", action="store_true",
                     help="seqshard mode on ONE GPU: capture the step in a CUDA graph and time its replay "
                          "(with more ranks the step holds NCCL collectives and is timed eagerly)")
-    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt", "chain"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
                          "forward, batch 8 x 8192 tokens per rank, tokens/s; mt: 6+6-layer encoder-decoder "
-                         "forward over 16 documents of 64 sentences per rank, target tokens/s")
+                         "forward over 16 documents of 64 sentences per rank, target tokens/s; chain: the same "
+                         "layer as `attention` through the reference's four separate operators (modules/op.py), "
+                         "forward + backward")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -453,6 +455,56 @@ def run_mt(a):
         dist.destroy_process_group()
 
 
+def run_chain(a):
+    """The layer of the headline workload spelled as the reference spells it (modules/attention.py:56-77):
+    embed_ak(etype) gathered to (E, d), masked_mm + node_mul_edge, sparse_softmax, vec_spmm, and autograd
+    through them -- on this library's deterministic operator kernels.  One GPU; edges/s."""
+    import torch
+    from bpt_b200 import csr as csrmod, graphbuilder, op
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
+    batch = csrmod.batch_graphs([g] * a.seqs)
+    N, E = batch.n_nodes, batch.n_edges
+    out_csr, in_csr, ROW, INDPTR_R, COL, INDPTR_C = csrmod.get_csrs(batch.src, batch.dst, N)
+    gen = torch.Generator(device="cpu").manual_seed(2)
+    q, k, v = [(torch.randn(N, H, D, generator=gen) * 0.125).to(dtype).to(dev).requires_grad_(True) for _ in range(3)]
+    d_o = torch.randn(N, H, D, generator=gen).to(dtype).to(dev)
+    table = (torch.randn(MAX_ETYPE, D, generator=gen) * 0.125).to(dtype).to(dev).requires_grad_(True)
+    etype = batch.etype.long()
+    scale = 1.0 / math.sqrt(D)
+
+    def step():
+        for t_ in (q, k, v, table):
+            t_.grad = None
+        ak = torch.nn.functional.embedding(etype, table)                       # attention.py:56-57
+        e = op.masked_mm(ROW, INDPTR_R, out_csr[2], out_csr[1], COL, INDPTR_C, in_csr[2], in_csr[1], k, q)
+        e_rel = op.node_mul_edge(COL, INDPTR_C, in_csr[2], q, ak)
+        p_ = op.sparse_softmax(COL, INDPTR_C, in_csr[2], (e_rel + e) * scale)
+        o = op.vec_spmm(COL, INDPTR_C, in_csr[2], in_csr[1], ROW, INDPTR_R, out_csr[2], out_csr[1], p_, v)
+        o.backward(d_o)
+        return o
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(a.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / a.steps
+    print(json.dumps({
+        "metric": "bpt_attention_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": a.dtype, "data": "synthetic",
+        "config": {"workload": "operator chain (masked_mm, node_mul_edge, sparse_softmax, vec_spmm) fwd+bwd, "
+                               + workload_name(a), "nodes": N, "edges": E}}), flush=True)
+
+
 def run_ours(a):
     import torch
     import torch.distributed as dist
@@ -650,6 +702,8 @@ def main():
         run_lm(a)
     elif a.workload == "mt":
         run_mt(a)
+    elif a.workload == "chain":
+        run_chain(a)
     elif a.mode == "seqshard":
         run_seqshard(a)
     else:

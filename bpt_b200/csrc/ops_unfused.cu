@@ -72,27 +72,65 @@ __global__ void edge_dot_kernel(const int64_t *__restrict__ row, const int64_t *
 // out[r, j] = sum_k W[eid[k], j / d] * X[...], k over the whole row, j in [0, h*d):
 //   kEdgeX == false: X = Xn[indices[k], j]      (vector_spmm fwd, its dx, maskedmm_csr bwd)
 //   kEdgeX == true:  X = Xe[eid[k], j % d]      (node_mul_edge bwd, dA)
+// The block of the row's first chunk owns the row.  Its kRowWarps warps take the row's entries
+// round-robin (warp w: entries w, w + kRowWarps, ...), each lane summing kRowCols columns 32 apart,
+// so a row of thousands of entries (a span node near the root) is walked by eight warps with
+// several independent loads in flight instead of one thread per column walking it alone.  The
+// warps' partial sums meet in shared memory and are added in warp order: one writer per output
+// element, fixed order.  Rows wider than 32 * kRowCols columns take several passes.
+constexpr int kRowWarps = 8;
+constexpr int kRowCols = 8;
+
 template <typename T, bool kEdgeX>
-__global__ void row_sum_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indptr,
-                               const int64_t *__restrict__ eid, const int64_t *__restrict__ indices,
-                               int64_t n_chunks, const T *__restrict__ W, const T *__restrict__ X,
-                               T *__restrict__ out, int h, int d) {
+__global__ void __launch_bounds__(kRowWarps * 32)
+row_sum_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indptr,
+               const int64_t *__restrict__ eid, const int64_t *__restrict__ indices,
+               int64_t n_chunks, const T *__restrict__ W, const T *__restrict__ X,
+               T *__restrict__ out, int h, int d) {
     using acc_t = typename Acc<T>::type;
+    __shared__ acc_t s_part[kRowWarps][32 * kRowCols];
     int64_t r, beg, end;
     if (!row_range(row, indptr, n_chunks, blockIdx.x, r, beg, end)) return;
     const int hd = h * d;
-    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
-        const int hh = j / d, dd = j - hh * d;
-        acc_t sum = 0;
-        for (int64_t k = beg; k < end; ++k) {
-            const int64_t e = eid[k];
-            const acc_t w = to_acc(W[e * h + hh]);
-            const acc_t x = kEdgeX ? to_acc(X[e * d + dd]) : to_acc(X[indices[k] * hd + j]);
-            sum += w * x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int col0 = 0; col0 < hd; col0 += 32 * kRowCols) {
+        acc_t acc[kRowCols];
+        int hh[kRowCols];
+#pragma unroll
+        for (int u = 0; u < kRowCols; ++u) {
+            acc[u] = 0;
+            const int j = col0 + lane + 32 * u;
+            hh[u] = j < hd ? j / d : -1;
         }
-        out[r * hd + j] = from_acc<T>(sum);
+#pragma unroll 4
+        for (int64_t k = beg + warp; k < end; k += kRowWarps) {
+            const int64_t e = eid[k];
+            const T *w_row = W + e * h;
+            const T *x_row = kEdgeX ? X + e * d : X + indices[k] * hd;
+#pragma unroll
+            for (int u = 0; u < kRowCols; ++u) {
+                if (hh[u] < 0) continue;
+                const int j = col0 + lane + 32 * u;
+                const acc_t x = kEdgeX ? to_acc(x_row[j - hh[u] * d]) : to_acc(x_row[j]);
+                acc[u] += to_acc(w_row[hh[u]]) * x;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kRowCols; ++u) s_part[warp][lane + 32 * u] = acc[u];
+        __syncthreads();
+        {
+            const int j = col0 + threadIdx.x;  // kRowWarps * 32 threads = 32 * kRowCols columns
+            if (j < hd) {
+                acc_t sum = 0;
+#pragma unroll
+                for (int w = 0; w < kRowWarps; ++w) sum += s_part[w][threadIdx.x];
+                out[r * hd + j] = from_acc<T>(sum);
+            }
+        }
+        __syncthreads();
     }
 }
+static_assert(kRowWarps * 32 == 32 * kRowCols, "one thread per column of a pass in the final sum");
 
 // node_mul_edge backward, dB[eid[k], dd] = sum_hh dy[eid[k], hh] * A[row, hh, dd]
 template <typename T>
@@ -193,11 +231,6 @@ int check_common(const char *name, const void *row, const void *indptr, int64_t 
     return BPT_OK;
 }
 
-int row_threads(int hd) {
-    int t = (hd + 31) / 32 * 32;
-    return t > 256 ? 256 : t;
-}
-
 template <typename T, bool kPerHead>
 int launch_edge_dot(const int64_t *row, const int64_t *indptr, const int64_t *eid, const int64_t *indices,
                     int64_t n_chunks, const void *A, const void *B, void *y, int h, int d,
@@ -218,7 +251,7 @@ int launch_row_sum(const int64_t *row, const int64_t *indptr, const int64_t *eid
                    int d, cudaStream_t stream) {
     BPT_CUDA(cudaMemsetAsync(out, 0, sizeof(T) * static_cast<size_t>(n_rows_out) * h * d, stream));
     if (n_chunks == 0) return BPT_OK;
-    row_sum_kernel<T, kEdgeX><<<static_cast<unsigned>(n_chunks), row_threads(h * d), 0, stream>>>(
+    row_sum_kernel<T, kEdgeX><<<static_cast<unsigned>(n_chunks), kRowWarps * 32, 0, stream>>>(
         row, indptr, eid, indices, n_chunks, static_cast<const T *>(W), static_cast<const T *>(X),
         static_cast<T *>(out), h, d);
     BPT_LAUNCH_CHECK();

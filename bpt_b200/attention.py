@@ -174,8 +174,19 @@ class TilePlan:
         return ws
 
 
-def tensor_core_eligible(q, embed_ak):
-    return q.dtype == torch.bfloat16 and q.size(-1) == 64
+MAX_BLOCK_SMEM = 227 * 1024  # shared memory one thread block can have on this GPU
+
+
+def tensor_core_eligible(q, embed_ak, plan=None):
+    """bf16 with head dim 64; and, when the plan is given, a tile plan whose per-head tables fit
+    in shared memory (graphs with many hundreds of edge types stay on the CUDA-core kernels)."""
+    if not (q.dtype == torch.bfloat16 and q.size(-1) == 64):
+        return False
+    if plan is None:
+        return True
+    tp = plan.tile_plan()
+    need = _lib.lib().bpt_attn_tc_smem_bytes(tp.max_cols_pad, tp.t_max if embed_ak is not None else 0, tp.et_bytes)
+    return 0 < need <= MAX_BLOCK_SMEM
 
 
 def attention_forward_tc(plan, q, k, v, embed_ak, scale):
@@ -205,7 +216,7 @@ def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
     """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype.
     bf16 with head dim 64 runs on the tensor-core kernel unless tensor_cores=False."""
     if tensor_cores is None:
-        tensor_cores = tensor_core_eligible(q, embed_ak)
+        tensor_cores = tensor_core_eligible(q, embed_ak, plan)
     if tensor_cores:
         return attention_forward_tc(plan, q, k, v, embed_ak, scale)
     _lib.require_cuda(q, k, v)
@@ -259,7 +270,7 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
     _lib.require_cuda(q, k, v, lse, d_o)
     N, h, d = q.shape
     if tensor_cores is None:
-        tensor_cores = o is not None and tensor_core_eligible(q, embed_ak)
+        tensor_cores = o is not None and tensor_core_eligible(q, embed_ak, plan)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dak = None
     if embed_ak is not None:

@@ -455,6 +455,11 @@ int launch_tile_kernel(const TcParams &p, int64_t n_groups, size_t smem, cudaStr
 
 using namespace bpt;
 
+extern "C" size_t bpt_attn_tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
+    if (max_cols_pad < 0 || t_max < 0 || (et_bytes != 1 && et_bytes != 2)) return 0;
+    return tc_smem_bytes(max_cols_pad, t_max, et_bytes);
+}
+
 extern "C" size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h) {
     if (n_slots < 0 || h < 1) return 0;
     const size_t s = static_cast<size_t>(n_slots);

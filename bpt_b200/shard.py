@@ -340,8 +340,9 @@ class _StraddleAttention(torch.autograd.Function):
             attention_forward = _KERNELS[0]
         else:
             from .attention import attention_forward, tensor_core_eligible
-            if not tensor_core_eligible(q, embed_ak):
-                raise RuntimeError("halo_attention with split straddlers needs bf16 tensors with head dim 64")
+            if not tensor_core_eligible(q, embed_ak, plan):
+                raise RuntimeError("halo_attention with split straddlers needs bf16 tensors with head dim 64 "
+                                   "and a tile plan that fits in shared memory")
         k_e, v_e = halo_exchange_pair(shard, k.contiguous(), v.contiguous())
         q_loc = _local_rows(shard, q)
         o_loc, lse_loc = attention_forward(plan, q_loc, k_e, v_e, embed_ak, scale)

@@ -305,6 +305,13 @@ typedef struct {
     int32_t et_bytes, max_cols_pad, t_max, reserved;
 } bpt_tile_plan_t;
 
+/* Shared memory per block that the tile kernels of bpt_attn_forward_tc / bpt_attn_backward_tc need
+ * for a tile plan with these sizes (t_max = 0 without embed_ak).  A plan whose need exceeds the
+ * 227 KB a block can have (very many edge types: the per-head tables grow with t_max) is refused
+ * by those calls with BPT_ERR_UNSUPPORTED; callers ask here first and use bpt_attn_forward /
+ * bpt_attn_backward instead.  Host-only, no CUDA call. */
+size_t bpt_attn_tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes);
+
 size_t bpt_attn_forward_tc_workspace_bytes(int64_t n_slots, int h);
 
 /* groups, mblocks, cols, et, split_rows, row_items: device copies of the exported arrays;

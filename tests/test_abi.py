@@ -61,3 +61,13 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower() or f == "build.py", os.path.join(dirpath, f)
+
+
+def test_tile_kernel_shared_memory_query():
+    """bpt_attn_tc_smem_bytes is host-only: the headline plan fits twice per SM, a plan with
+    ~900 edge types (step = 64) does not fit a block at all, bad arguments give 0."""
+    from bpt_b200 import _lib
+    L = _lib.lib()
+    assert 0 < L.bpt_attn_tc_smem_bytes(384, 72, 1) <= 113 * 1024
+    assert L.bpt_attn_tc_smem_bytes(384, 904, 2) > 227 * 1024
+    assert L.bpt_attn_tc_smem_bytes(384, 72, 3) == 0 and L.bpt_attn_tc_smem_bytes(-64, 72, 1) == 0

@@ -219,3 +219,19 @@ def test_tensor_core_path_with_more_than_255_edge_types(oracle_lib):
     plan, *got = _run_gpu(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
     assert plan.tiles is not None and plan.tiles.et_bytes == 2
     _compare(got, want, TOL[torch.bfloat16])
+
+
+def test_many_edge_types_fall_back_to_cuda_cores(oracle_lib):
+    """step = 64, clip 6 (the reference's configs/enwik8-8192.yml) gives ~900 edge types: the tile
+    kernels' per-head tables no longer fit in shared memory, so bf16 x 64 runs on the CUDA-core
+    kernels instead of failing, and still matches the oracle."""
+    from bpt_b200.attention import AttentionPlan, tensor_core_eligible
+    g = oracle_lib.binary_partition(700, True, 64, 6)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    assert T > 700
+    q, k, v, ak, d_o = _inputs(N, 8, 64, T, torch.bfloat16, 17)
+    want = _oracle(oracle_lib, g["src"], g["dst"], g["etype"], N, q, k, v, ak, d_o, 0.125)
+    plan, *got = _run_gpu(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
+    assert not tensor_core_eligible(q.cuda(), ak.cuda(), plan)
+    assert tensor_core_eligible(q.cuda(), None, plan)      # without the relative-position tables it fits
+    _compare(got, want, TOL[torch.bfloat16])

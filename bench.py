@@ -49,10 +49,12 @@ def parse():
     ap.add_argument("--graph", action="store_true",
                     help="seqshard mode on ONE GPU: capture the step in a CUDA graph and time its replay "
                          "(with more ranks the step holds NCCL collectives and is timed eagerly)")
-    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt", "chain"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt", "cls", "chain"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
                          "forward, batch 8 x 8192 tokens per rank, tokens/s; mt: 6+6-layer encoder-decoder "
-                         "forward over 16 documents of 64 sentences per rank, target tokens/s; chain: the same "
+                         "forward over 16 documents of 64 sentences per rank, target tokens/s; cls: 5-layer fp32 "
+                         "classifier (d_model 300, 6 x 50) over 32 variable-length sequences per rank, forward + "
+                         "backward with the graph, CSRs and plans rebuilt every step, sequences/s; chain: the same "
                          "layer as `attention` through the reference's four separate operators (modules/op.py), "
                          "forward + backward")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -455,6 +457,88 @@ def run_mt(a):
         dist.destroy_process_group()
 
 
+def run_cls(a):
+    """Variable-length classification step (5 layers, d_model 300, 6 heads x 50, FFN 600, fp32, causal
+    k = 4 graphs with clip 5 as configs/imdb-4.yml): 32 sequences per rank and step with lengths
+    clip(round(lognormal(5.3, 0.6)), 10, 2500) drawn anew every step (numpy default_rng(3 + rank)), so the
+    timed step includes batching the graphs and building the attention plan, then forward, loss and
+    backward.  Mean-pooled leaves feed a 2-way head.  sequences/s = sequences of all ranks / slowest rank."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from bpt_b200 import csr as csrmod
+    from bpt_b200.attention import AttentionPlan
+    from bpt_b200.model import BPTClassifier
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rng = np.random.default_rng(3 + rank)
+    batch_size, vocab = 32, 50000
+    cache = csrmod.GraphCache(triu=True, step=4, clip_dist=5)
+    torch.manual_seed(0)
+    model = BPTClassifier(vocab, 300, 600, 6, 5, 2, dropout=0.0, readout="mean").to(dev)
+    n_steps = max(a.warmup, 3) + a.steps
+    all_lengths = np.clip(np.round(rng.lognormal(5.3, 0.6, (n_steps, batch_size))), 10, 2500).astype(np.int64)
+    for n in np.unique(all_lengths):       # a training run meets every length again and again: graphs are cached
+        cache.get(int(n))
+    labels = torch.from_numpy(rng.integers(0, 2, (n_steps, batch_size))).to(dev)
+    tokens_host = [torch.from_numpy(rng.integers(0, vocab, int(l.sum()))).pin_memory() for l in all_lengths]
+    stats = {"tokens": 0, "edges": 0}
+
+    def step(i):
+        lengths = all_lengths[i]
+        batch = csrmod.batch_graphs([cache.get(int(n)) for n in lengths])      # graph/text_classification.py:36-67
+        plan = AttentionPlan.from_batch(batch, n_etypes=MAX_ETYPE)
+        tokens = tokens_host[i].to(dev, non_blocking=True)
+        logp = model(tokens, batch.leaf_ids(), plan, batch.root_ids(), torch.from_numpy(lengths).to(dev))
+        loss = torch.nn.functional.nll_loss(logp, labels[i])
+        model.zero_grad(set_to_none=True)
+        loss.backward()
+        stats["tokens"] += int(lengths.sum())
+        stats["edges"] += batch.n_edges
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    w = max(a.warmup, 3)
+    for i in range(w):
+        step(i)
+    barrier()
+    stats = {"tokens": 0, "edges": 0}
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(w, n_steps):
+        loss = step(i)
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop) / a.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "cls_sequences_per_sec", "value": world * batch_size / (ms * 1e-3), "unit": "sequences/s",
+            "n_gpus": world, "steps": a.steps, "warmup": w, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": "bpt_classifier_train_step 5 layers d300 6x50 ffn600 fp32, 32 variable-length "
+                                   "sequences per rank (lognormal 5.3/0.6 in [10, 2500]), k=4 causal, graph batch and "
+                                   "plan rebuilt every step",
+                       "tokens_per_step_rank0": stats["tokens"] // a.steps,
+                       "edges_per_step_rank0": stats["edges"] // a.steps,
+                       "finite_loss": bool(torch.isfinite(loss).item())}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_chain(a):
     """The layer of the headline workload spelled as the reference spells it (modules/attention.py:56-77):
     embed_ak(etype) gathered to (E, d), masked_mm + node_mul_edge, sparse_softmax, vec_spmm, and autograd
@@ -702,6 +786,8 @@ def main():
         run_lm(a)
     elif a.workload == "mt":
         run_mt(a)
+    elif a.workload == "cls":
+        run_cls(a)
     elif a.workload == "chain":
         run_chain(a)
     elif a.mode == "seqshard":

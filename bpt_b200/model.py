@@ -201,6 +201,44 @@ class BPTLanguageModel(nn.Module):
         return self.generator(h[leaf_ids])                                      # model.py:275
 
 
+class BPTClassifier(nn.Module):
+    """The sequence classifier use of BinaryPartitionTransformer (modules/model.py:197-280 as
+    driven by graph/text_classification.py): blocks over all nodes, then one vector per sequence
+    into a linear head.  readout="root" reads each sequence's root node as the reference does
+    (text_classification.py:48,77); readout="mean" averages the sequence's leaves."""
+
+    def __init__(self, vocab_size, dim_model, dim_ff, h, n_layers, n_classes, dropout=0.0, activation="relu",
+                 readout="root"):
+        super().__init__()
+        if readout not in ("root", "mean"):
+            raise ValueError("readout must be root or mean")
+        self.readout = readout
+        self.embed = nn.Embedding(vocab_size, dim_model)
+        self.layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
+                                              activation=activation) for _ in range(n_layers)])
+        self.generator = Generator(dim_model, n_classes)
+        self.norm = nn.LayerNorm(dim_model)
+        self.emb_dropout = nn.Dropout(dropout)
+
+    def forward(self, tokens, leaf_ids, plan, root_ids, lengths=None):
+        """tokens: (n_leaves,) in leaf order; root_ids: (B,) node id of every sequence's root;
+        lengths: (B,) leaves per sequence (needed for readout="mean"; leaves of a sequence are
+        contiguous in `tokens`).  Returns log-probabilities (B, n_classes)."""
+        x = self.norm(self.emb_dropout(self.embed(tokens)))
+        h = x.new_zeros((plan.n_nodes, x.size(-1)))
+        h[leaf_ids] = x
+        for layer in self.layers:
+            h = layer(h, plan)
+        if self.readout == "root":
+            pooled = h[root_ids]
+        else:
+            seq = torch.repeat_interleave(torch.arange(lengths.numel(), device=h.device), lengths)
+            pooled = torch.zeros((lengths.numel(), h.size(-1)), dtype=h.dtype, device=h.device)
+            pooled.index_add_(0, seq, h[leaf_ids])
+            pooled = pooled / lengths.to(h.dtype).unsqueeze(1)
+        return self.generator(pooled)
+
+
 class BPTEncoderDecoder(nn.Module):
     """Forward of BinaryPartitionEncoderDecoder (modules/model.py:22-106) with rel_pos=True:
     `n_layers` blocks over the encoder graph, `m_layers` memory blocks over the decoder graph

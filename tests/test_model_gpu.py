@@ -148,3 +148,26 @@ def test_feed_forward_epilogue_path_matches_plain_path():
         with torch.no_grad():
             fused = ffn(x)
         assert rel_err(fused.cpu(), plain.detach().cpu()) < 1e-5
+
+
+def test_classifier_readouts():
+    """Variable-length batch (D = 50 per head, fp32: the CUDA-core kernels): the root read-out takes each
+    sequence's last node, the mean read-out equals the mean of the sequence's leaves; gradients flow."""
+    from bpt_b200 import csr as csrmod
+    from bpt_b200.attention import AttentionPlan
+    from bpt_b200.model import BPTClassifier
+    torch.manual_seed(5)
+    lengths = [10, 57, 128, 301]
+    cache = csrmod.GraphCache(triu=True, step=4, clip_dist=5)
+    batch = csrmod.batch_graphs([cache.get(n) for n in lengths])
+    plan = AttentionPlan.from_batch(batch, n_etypes=1000)
+    tokens = torch.randint(0, 500, (sum(lengths),), device="cuda")
+    lens = torch.tensor(lengths, device="cuda")
+    for readout in ("root", "mean"):
+        model = BPTClassifier(500, 300, 600, 6, 2, 2, readout=readout).cuda()
+        logp = model(tokens, batch.leaf_ids(), plan, batch.root_ids(), lens)
+        assert logp.shape == (4, 2)
+        assert torch.allclose(logp.exp().sum(-1), torch.ones(4, device="cuda"), atol=1e-5)
+        torch.nn.functional.nll_loss(logp, torch.tensor([0, 1, 1, 0], device="cuda")).backward()
+        assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+    assert batch.root_ids().tolist() == [o - 1 for o in batch.node_offsets[1:]]

@@ -83,6 +83,16 @@ def test_operators_forward_backward(oracle_lib, kind, dtype, hd):
         x_ref, x_gpu = pair(eshape, 6, 2.0)
         y_ref = ops_torch.sparse_softmax(crw, cip, ced, x_ref, n_rows=N)
         y_gpu = op.sparse_softmax(rw, ip, ed, x_gpu)
+        if not rel_err(y_gpu.detach().double().cpu(), y_ref.detach()) < tol:
+            # say which side moved before failing: rerun both and compare bitwise
+            yg, yr = y_gpu.detach().double().cpu(), y_ref.detach()
+            diff = (yg - yr).abs()
+            yg2 = op.sparse_softmax(rw, ip, ed, x_gpu).detach().double().cpu()
+            yr2 = ops_torch.sparse_softmax(crw, cip, ced, x_ref.detach(), n_rows=N)
+            print("sparse_softmax mismatch: %d entries above 1e-13, max %.3e at %s; GPU rerun identical: %s, "
+                  "CPU rerun identical: %s, CPU threads %d" % (
+                      int((diff > 1e-13).sum()), diff.max().item(), torch.nonzero(diff == diff.max())[:1].tolist(),
+                      torch.equal(yg2, yg), torch.equal(yr2, yr), torch.get_num_threads()))
         assert rel_err(y_gpu.detach().double().cpu(), y_ref.detach()) < tol
         y_ref.backward(dy.double())
         y_gpu.backward(dy.cuda())

@@ -235,3 +235,38 @@ def test_many_edge_types_fall_back_to_cuda_cores(oracle_lib):
     assert not tensor_core_eligible(q.cuda(), ak.cuda(), plan)
     assert tensor_core_eligible(q.cuda(), None, plan)      # without the relative-position tables it fits
     _compare(got, want, TOL[torch.bfloat16])
+
+
+def test_largest_sweep_size_properties():
+    """n = 65536, k = 8 (N = 131071, E = 13,239,926), bf16 x 8 x 64: the largest cell of the scaling sweep,
+    too big for the CPU oracle in a test, checked through identities that hold at any size:
+      - attention weights of a row sum to one: with v = 1 the output is 1;
+      - O is linear in V with the weights the backward uses:  <dO, O> = <V, dV>;
+      - scores are bilinear:  <Q, dQ> = <K, dK> + <embed_ak, d embed_ak>."""
+    from bpt_b200 import graphbuilder
+    from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
+    gb = graphbuilder.BinaryPartition(65536, False, 8, 10)
+    assert gb.number_of_nodes == 131071 and gb.number_of_edges == 13239926
+    src, dst, et = gb.edges_device()
+    N, T = gb.number_of_nodes, 1000
+    plan = AttentionPlan(src, dst, et, N, n_etypes=T)
+    gen = torch.Generator().manual_seed(2)
+    q, k, v = [(torch.randn(N, 8, 64, generator=gen) * 0.125).bfloat16().cuda() for _ in range(3)]
+    ak = (torch.randn(T, 64, generator=gen) * 0.125).bfloat16().cuda()
+    d_o = torch.randn(N, 8, 64, generator=gen).bfloat16().cuda()
+    o, lse = attention_forward(plan, q, k, v, ak, 0.125)
+    assert plan.tiles is not None and torch.isfinite(lse).all()
+    dq, dk, dv, dak = attention_backward(plan, q, k, v, ak, 0.125, lse, d_o, o=o)
+    o1, _ = attention_forward(plan, q, k, torch.ones_like(v), ak, 0.125)
+    assert rel_err(o1.float().cpu(), torch.ones(N, 8, 64)) < 1e-2
+
+    def inner(a, b):
+        return (a.double() * b.double()).sum().item()
+
+    def scale_of(a, b):
+        return (a.double() * b.double()).abs().sum().item()
+
+    lhs, rhs = inner(d_o, o), inner(v, dv)
+    assert abs(lhs - rhs) < 1e-2 * scale_of(d_o, o), (lhs, rhs)
+    lhs, rhs = inner(q, dq), inner(k, dk) + inner(ak, dak)
+    assert abs(lhs - rhs) < 1e-2 * (scale_of(q, dq) + scale_of(k, dk)), (lhs, rhs)

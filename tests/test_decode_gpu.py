@@ -1,0 +1,62 @@
+"""Incremental decoding (bpt_b200/decode.py) against the full forward of the encoder-decoder:
+a causal binary-partition graph lets the nodes of position t be computed from positions <= t, so
+feeding the target tokens step by step must give the log-probabilities of the one-shot forward
+(fp32, CUDA-core kernels, 1e-4), and greedy decoding must be a fixed point of the full forward."""
+import pytest
+import torch
+
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup():
+    from bpt_b200 import csr as csrmod, graphbuilder
+    from bpt_b200.attention import AttentionPlan
+    from bpt_b200.model import BPTEncoderDecoder
+    torch.manual_seed(7)
+    enc_len, dec_len = [23, 40], [17, 9]
+    enc = csrmod.batch_graphs([graphbuilder.BinaryPartition(n, False, 2, 3) for n in enc_len])
+    dec = csrmod.batch_graphs([graphbuilder.BinaryPartition(n, True, 2, 3) for n in dec_len])
+    src_ranges = [(enc.node_offsets[i], enc_len[i]) for i in range(2)]
+    dst_ranges = [(dec.node_offsets[i], dec_len[i]) for i in range(2)]
+    isrc, idst = csrmod.inter_graph(src_ranges, dst_ranges)
+    model = BPTEncoderDecoder([50, 60], 64, 128, 4, 2, 2).cuda().eval()
+    enc_plan = AttentionPlan.from_batch(enc, n_etypes=1000)
+    dec_plan = AttentionPlan.from_batch(dec, n_etypes=1000)
+    inter_plan = AttentionPlan(isrc, idst, None, dec.n_nodes, n_src=enc.n_nodes)
+    enc_tok = torch.randint(0, 50, (sum(enc_len),), device="cuda")
+    return model, enc, dec, isrc, idst, enc_plan, dec_plan, inter_plan, enc_tok, dec_len
+
+
+def test_teacher_forced_steps_equal_full_forward():
+    from bpt_b200.decode import DecodeSchedule, teacher_forced
+    model, enc, dec, isrc, idst, enc_plan, dec_plan, inter_plan, enc_tok, dec_len = _setup()
+    dec_tok = torch.randint(0, 60, (sum(dec_len),), device="cuda")
+    with torch.no_grad():
+        want = model(enc_tok, enc.leaf_ids(), enc_plan, dec_tok, dec.leaf_ids(), dec_plan, inter_plan, dec.leaf_ids())
+    sched = DecodeSchedule(dec, isrc, idst, enc.n_nodes)
+    assert sched.n_steps == max(dec_len) and sum(r.numel() for r in sched.rows) == dec.n_nodes
+    per_seq = list(torch.split(dec_tok, dec_len))
+    got = teacher_forced(model, sched, enc_tok, enc.leaf_ids(), enc_plan, per_seq)
+    assert got.shape == want.shape
+    assert rel_err(got.cpu(), want.cpu()) < 1e-4
+
+
+def test_greedy_decoding_is_a_fixed_point_of_the_full_forward():
+    from bpt_b200.decode import DecodeSchedule, greedy
+    model, enc, dec, isrc, idst, enc_plan, dec_plan, inter_plan, enc_tok, dec_len = _setup()
+    sched = DecodeSchedule(dec, isrc, idst, enc.n_nodes)
+    first = torch.tensor([1, 2], device="cuda")
+    out = greedy(model, sched, enc_tok, enc.leaf_ids(), enc_plan, first)         # (n_steps, n_seq)
+    assert out.shape == (max(dec_len), 2)
+    for b, n in enumerate(dec_len):
+        assert bool((out[:n, b] >= 0).all()) and bool((out[n:, b] == -1).all())
+    # the decoder inputs of greedy decoding: the first token, then each step's arg-max
+    inputs = torch.cat([torch.cat([first[b:b + 1], out[:n - 1, b]]) for b, n in enumerate(dec_len)])
+    with torch.no_grad():
+        logp = model(enc_tok, enc.leaf_ids(), enc_plan, inputs, dec.leaf_ids(), dec_plan, inter_plan, dec.leaf_ids())
+    want = torch.cat([out[:n, b] for b, n in enumerate(dec_len)])
+    top2 = logp.topk(2, -1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 1e-3      # positions where the arg-max is not a near tie
+    assert bool((logp.argmax(-1)[clear] == want[clear]).all())

@@ -177,6 +177,27 @@ class TilePlan:
 MAX_BLOCK_SMEM = 227 * 1024  # shared memory one thread block can have on this GPU
 
 
+def _check_inputs(plan, q, k, v, embed_ak):
+    """Shape, dtype and device rules shared by every entry of the fused call, checked before any path
+    is chosen: q (n_nodes, h, d); k, v (n_src, h, d) of q's dtype; embed_ak (>= n_etypes, d) of q's dtype
+    (the kernels read it as q's element type and index it with every edge type of the plan)."""
+    _lib.require_cuda(q, k, v)
+    if q.dim() != 3:
+        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d)")
+    N, h, d = q.shape
+    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
+        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError("bpt_attention: q, k and v must have one dtype")
+    if embed_ak is not None:
+        _lib.require_cuda(embed_ak)
+        if (embed_ak.dim() != 2 or embed_ak.dtype != q.dtype or embed_ak.size(0) < plan.n_etypes
+                or embed_ak.size(1) != d):
+            raise RuntimeError("bpt_attention: embed_ak must be (>= n_etypes = %d, d = %d) of the dtype of q (%s); "
+                               "got %s of %s" % (plan.n_etypes, d, q.dtype, tuple(embed_ak.shape), embed_ak.dtype))
+    return N, h, d
+
+
 def tensor_core_eligible(q, embed_ak, plan=None):
     """bf16 with head dim 64; and, when the plan is given, a tile plan whose per-head tables fit
     in shared memory (graphs with many hundreds of edge types stay on the CUDA-core kernels)."""
@@ -191,13 +212,8 @@ def tensor_core_eligible(q, embed_ak, plan=None):
 
 def attention_forward_tc(plan, q, k, v, embed_ak, scale):
     """Forward through bpt_attn_forward_tc (bf16, head dim 64). Returns (o, lse)."""
-    _lib.require_cuda(q, k, v)
-    if embed_ak is not None:
-        _lib.require_cuda(embed_ak)
+    N, h, d = _check_inputs(plan, q, k, v, embed_ak)
     tp = plan.tile_plan()
-    N, h, d = q.shape
-    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
-        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
@@ -215,18 +231,11 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale):
 def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
     """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype.
     bf16 with head dim 64 runs on the tensor-core kernel unless tensor_cores=False."""
+    N, h, d = _check_inputs(plan, q, k, v, embed_ak)
     if tensor_cores is None:
         tensor_cores = tensor_core_eligible(q, embed_ak, plan)
     if tensor_cores:
         return attention_forward_tc(plan, q, k, v, embed_ak, scale)
-    _lib.require_cuda(q, k, v)
-    if embed_ak is not None:
-        _lib.require_cuda(embed_ak)
-        if embed_ak.dtype != q.dtype or embed_ak.size(0) < plan.n_etypes or embed_ak.size(1) != q.size(-1):
-            raise RuntimeError("bpt_attention: embed_ak must be (>= n_etypes, d) of the dtype of q")
-    N, h, d = q.shape
-    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
-        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
@@ -245,15 +254,16 @@ def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=N
     wrapper allocates nothing either.  Graphs whose split rows need more scratch than the
     built-in array raise; use attention_forward for those.  Calls on one GPU share that array
     and must not overlap in time."""
-    _lib.require_cuda(q, k, v)
-    if embed_ak is not None:
-        _lib.require_cuda(embed_ak)
-    N, h, d = q.shape
-    if N != plan.n_nodes or k.shape != (plan.n_src, h, d) or v.shape != k.shape:
-        raise RuntimeError("bpt_attention: q must be (n_nodes, h, d) and k, v (n_src, h, d)")
+    N, h, d = _check_inputs(plan, q, k, v, embed_ak)
     o = torch.empty_like(q) if out is None else out
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device) if lse_out is None else lse_out
     _lib.require_cuda(o, lse)
+    # caller-supplied outputs go to the library as raw pointers: a wrong shape or dtype would be an
+    # out-of-bounds device write
+    if o.shape != q.shape or o.dtype != q.dtype or o.device != q.device:
+        raise RuntimeError("bpt_attention: out must have the shape, dtype and device of q")
+    if lse.shape != (N, h) or lse.dtype != torch.float32 or lse.device != q.device:
+        raise RuntimeError("bpt_attention: lse_out must be float32 (n_nodes, h) on the device of q")
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().bpt_attn_forward_static(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                                       _lib.ptr(embed_ak), float(scale), o.data_ptr(),
@@ -267,8 +277,12 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
     bf16 with head dim 64 runs on the tensor-core kernels when the forward's output `o` is given
     (they take delta = <dO, O> from it) unless tensor_cores=False."""
     d_o = d_o.contiguous()
-    _lib.require_cuda(q, k, v, lse, d_o)
-    N, h, d = q.shape
+    N, h, d = _check_inputs(plan, q, k, v, embed_ak)
+    _lib.require_cuda(lse, d_o)
+    if d_o.shape != q.shape or d_o.dtype != q.dtype:
+        raise RuntimeError("bpt_attention: d_o must have the shape and dtype of q")
+    if lse.shape != (N, h) or lse.dtype != torch.float32:
+        raise RuntimeError("bpt_attention: lse must be float32 (n_nodes, h)")
     if tensor_cores is None:
         tensor_cores = o is not None and tensor_core_eligible(q, embed_ak, plan)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)

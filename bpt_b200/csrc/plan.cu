@@ -22,6 +22,18 @@ __global__ void permute_in_kernel(const int32_t *__restrict__ in_rank, const int
     inpos_of_eid[e] = static_cast<int32_t>(p);
 }
 
+// flags[0..2] = 1 when some src is outside [0, n_src), some dst outside [0, n_nodes), some etype
+// outside [0, n_etypes).  Everything downstream indexes with these values.
+__global__ void range_check_kernel(const int32_t *__restrict__ src, const int32_t *__restrict__ dst,
+                                   const int32_t *__restrict__ etype, int64_t n_edges, int64_t n_src,
+                                   int64_t n_nodes, int n_etypes, int32_t *__restrict__ flags) {
+    const int64_t e = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (e >= n_edges) return;
+    if (src[e] < 0 || src[e] >= n_src) flags[0] = 1;
+    if (dst[e] < 0 || dst[e] >= n_nodes) flags[1] = 1;
+    if (etype && (etype[e] < 0 || etype[e] >= n_etypes)) flags[2] = 1;
+}
+
 __global__ void gather_kernel(const int32_t *__restrict__ idx, const int32_t *__restrict__ table,
                               int64_t n, int32_t *__restrict__ out) {
     const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
@@ -142,7 +154,7 @@ extern "C" size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_src, 
     int64_t rows = n_nodes > n_etypes + 1 ? n_nodes : n_etypes + 1;
     rows = rows > n_src ? rows : n_src;
     const size_t e = static_cast<size_t>(n_edges > 0 ? n_edges : 1);
-    return 5 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 3 * work_ws_bytes(rows) + 1024;
+    return 5 * align_up(e * 4, 256) + bpt_coo_to_csr_workspace_bytes(n_edges, rows) + 256 + 3 * work_ws_bytes(rows) + 1024;
 }
 
 extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
@@ -168,8 +180,25 @@ extern "C" int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const
     rows = rows > n_src ? rows : n_src;
     const size_t csr_ws_bytes = bpt_coo_to_csr_workspace_bytes(n_edges, rows);
     char *csr_ws = ws.take<char>(csr_ws_bytes);
+    int32_t *range_flags = ws.take<int32_t>(4);
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_plan_build: workspace too small");
     const unsigned eb = static_cast<unsigned>((n_edges + 255) / 256);
+
+    // Every later kernel indexes with src, dst and etype, so an id out of range is refused here (the
+    // reference's nn.Embedding raises on an edge type beyond its table, modules/attention.py:57).
+    if (n_edges > 0) {
+        int32_t bad[4] = {0, 0, 0, 0};
+        BPT_CUDA(cudaMemsetAsync(range_flags, 0, 4 * sizeof(int32_t), stream));
+        range_check_kernel<<<eb, 256, 0, stream>>>(src, dst, etype, n_edges, n_src, n_nodes, n_etypes, range_flags);
+        BPT_LAUNCH_CHECK();
+        BPT_CUDA(cudaMemcpyAsync(bad, range_flags, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+        BPT_CUDA(cudaStreamSynchronize(stream));
+        if (bad[0] || bad[1] || bad[2])
+            return fail(BPT_ERR_INVALID, "attn_plan_build: %s%s%sout of range (n_src %lld, n_nodes %lld, n_etypes %d)",
+                        bad[0] ? "a source id, " : "", bad[1] ? "a destination id, " : "",
+                        bad[2] ? "an edge type, " : "", static_cast<long long>(n_src),
+                        static_cast<long long>(n_nodes), n_etypes);
+    }
 
     // out-CSR (rows = sources, edge-id order inside a row)
     if (int rc = bpt_coo_to_csr(src, dst, n_edges, n_src, 4, p.out_indptr, p.out_dst, eid_by_src, csr_ws,

@@ -209,7 +209,9 @@ int bpt_vector_spmm_backward(const int64_t *row, const int64_t *indptr, const in
  * (src, dst, etype: int32, edge id = position), holding the int32 in-CSR, out-CSR, per-type
  * buckets and the work lists the kernels walk.  counts_host[12] (host memory, filled by
  * bpt_attn_plan_build, which waits for the stream) must be passed back to the other calls.
- * etype may be NULL (all edges type 0); every etype must be < n_etypes.
+ * etype may be NULL (all edges type 0); every etype must be < n_etypes, every src < n_src and every
+ * dst < n_nodes: bpt_attn_plan_build checks all three on the device first and returns
+ * BPT_ERR_INVALID, with nothing built, when one is out of range.
  * Destinations and sources may be different node sets: dst ids index n_nodes rows (q, o, lse,
  * dq), src ids index n_src rows (k, v, dk, dv).  Self-attention has n_src == n_nodes; the
  * reference's cross-attention (BPTMemBlock, modules/attention.py:144-168) and a shard of a long

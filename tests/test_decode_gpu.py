@@ -10,7 +10,7 @@ from helpers import rel_err
 pytestmark = pytest.mark.gpu
 
 
-def _setup():
+def _setup(dim=64, heads=4, dtype=torch.float32):
     from bpt_b200 import csr as csrmod, graphbuilder
     from bpt_b200.attention import AttentionPlan
     from bpt_b200.model import BPTEncoderDecoder
@@ -21,7 +21,7 @@ def _setup():
     src_ranges = [(enc.node_offsets[i], enc_len[i]) for i in range(2)]
     dst_ranges = [(dec.node_offsets[i], dec_len[i]) for i in range(2)]
     isrc, idst = csrmod.inter_graph(src_ranges, dst_ranges)
-    model = BPTEncoderDecoder([50, 60], 64, 128, 4, 2, 2).cuda().eval()
+    model = BPTEncoderDecoder([50, 60], dim, 2 * dim, heads, 2, 2).cuda().to(dtype).eval()
     enc_plan = AttentionPlan.from_batch(enc, n_etypes=1000)
     dec_plan = AttentionPlan.from_batch(dec, n_etypes=1000)
     inter_plan = AttentionPlan(isrc, idst, None, dec.n_nodes, n_src=enc.n_nodes)
@@ -41,6 +41,25 @@ def test_teacher_forced_steps_equal_full_forward():
     got = teacher_forced(model, sched, enc_tok, enc.leaf_ids(), enc_plan, per_seq)
     assert got.shape == want.shape
     assert rel_err(got.cpu(), want.cpu()) < 1e-4
+
+
+def test_teacher_forced_steps_equal_full_forward_bf16_tile_kernels():
+    """The same in bf16 with head dim 64: the full forward and every per-step plan run on the tensor-core
+    tile kernels; both are compared with the fp32 full forward of the same (bf16-rounded) weights at the
+    bf16 bar of 2e-2 on the log-probabilities."""
+    from bpt_b200.decode import DecodeSchedule, teacher_forced
+    model, enc, dec, isrc, idst, enc_plan, dec_plan, inter_plan, enc_tok, dec_len = _setup(256, 4, torch.bfloat16)
+    dec_tok = torch.randint(0, 60, (sum(dec_len),), device="cuda")
+    sched = DecodeSchedule(dec, isrc, idst, enc.n_nodes)
+    per_seq = list(torch.split(dec_tok, dec_len))
+    with torch.no_grad():
+        full = model(enc_tok, enc.leaf_ids(), enc_plan, dec_tok, dec.leaf_ids(), dec_plan, inter_plan, dec.leaf_ids())
+        got = teacher_forced(model, sched, enc_tok, enc.leaf_ids(), enc_plan, per_seq)
+        assert dec_plan.tiles is not None and sched.self_plans[-1].tiles is not None, "not on the tile kernels"
+        want = model.float()(enc_tok, enc.leaf_ids(), enc_plan, dec_tok, dec.leaf_ids(), dec_plan, inter_plan,
+                             dec.leaf_ids())
+    assert rel_err(full.float().cpu(), want.cpu()) < 2e-2
+    assert rel_err(got.float().cpu(), want.cpu()) < 2e-2
 
 
 def test_greedy_decoding_is_a_fixed_point_of_the_full_forward():

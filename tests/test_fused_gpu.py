@@ -270,3 +270,28 @@ def test_largest_sweep_size_properties():
     assert abs(lhs - rhs) < 1e-2 * scale_of(d_o, o), (lhs, rhs)
     lhs, rhs = inner(q, dq), inner(k, dk) + inner(ak, dak)
     assert abs(lhs - rhs) < 1e-2 * (scale_of(q, dq) + scale_of(k, dk)), (lhs, rhs)
+
+
+def test_input_checks_run_before_the_path_is_chosen(oracle_lib):
+    """embed_ak of another dtype (nn.Embedding weights under autocast), a table shorter than the plan's
+    n_etypes, and an edge type beyond n_etypes must raise on every path, the tensor-core one included."""
+    from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
+    g = oracle_lib.binary_partition(64, False, 2, 10)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    src, dst, et = [torch.from_numpy(g[n]).cuda() for n in ("src", "dst", "etype")]
+    plan = AttentionPlan(src, dst, et, N, n_etypes=T)
+    q = torch.randn(N, 8, 64, device="cuda").to(torch.bfloat16)
+    ak32 = torch.randn(T, 64, device="cuda")
+    with pytest.raises(RuntimeError, match="embed_ak"):
+        attention_forward(plan, q, q, q, ak32, 0.125)
+    with pytest.raises(RuntimeError, match="embed_ak"):
+        attention_forward(plan, q, q, q, ak32.to(torch.bfloat16)[: T - 1].contiguous(), 0.125)
+    o, lse = attention_forward(plan, q, q, q, ak32.to(torch.bfloat16), 0.125)
+    with pytest.raises(RuntimeError, match="embed_ak"):
+        attention_backward(plan, q, q, q, ak32, 0.125, lse, q, o=o)
+    with pytest.raises(RuntimeError, match="embed_ak"):
+        attention_backward(plan, q, q, q, ak32.to(torch.bfloat16)[: T - 1].contiguous(), 0.125, lse, q, o=o)
+    with pytest.raises(RuntimeError, match="out of range"):
+        AttentionPlan(src, dst, et, N, n_etypes=T - 1)
+    with pytest.raises(RuntimeError, match="out of range"):
+        AttentionPlan(src, dst, et, N - 1, n_etypes=T)

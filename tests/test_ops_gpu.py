@@ -32,6 +32,22 @@ def _to(csr, device):
     return [[f(a) for a in csr[0]], [f(a) for a in csr[1]], f(csr[2]), f(csr[3]), f(csr[4]), f(csr[5])]
 
 
+def _softmax_longdouble(row, indptr, eid, x, n_rows):
+    """Edge softmax over the CSR rows in numpy long double (80-bit on x86): the tie-breaker between the
+    fp64 kernel and the fp64 torch restatement."""
+    r = ops_torch._expand_rows(row, indptr).numpy()
+    e = eid.numpy()
+    xs = x[e].astype(np.longdouble)
+    m = np.full((n_rows,) + xs.shape[1:], -np.inf, dtype=np.longdouble)
+    np.maximum.at(m, r, xs)
+    ex = np.exp(xs - m[r])
+    ssum = np.zeros_like(m)
+    np.add.at(ssum, r, ex)
+    y = np.zeros(x.shape, dtype=np.longdouble)
+    y[e] = ex / ssum[r]
+    return y.astype(np.float64)
+
+
 def _rand(shape, seed, dtype):
     g = torch.Generator().manual_seed(seed)
     return torch.randn(*shape, generator=g, dtype=torch.float64).to(dtype)
@@ -84,25 +100,25 @@ def test_operators_forward_backward(oracle_lib, kind, dtype, hd):
         y_ref = ops_torch.sparse_softmax(crw, cip, ced, x_ref, n_rows=N)
         y_gpu = op.sparse_softmax(rw, ip, ed, x_gpu)
         err = rel_err(y_gpu.detach().double().cpu(), y_ref.detach())
-        if not err < tol:
-            # say which side moved: rerun both and compare bitwise
-            yg, yr = y_gpu.detach().double().cpu(), y_ref.detach()
-            diff = (yg - yr).abs()
-            yg2 = op.sparse_softmax(rw, ip, ed, x_gpu).detach().double().cpu()
-            yr2 = ops_torch.sparse_softmax(crw, cip, ced, x_ref.detach(), n_rows=N)
-            print("sparse_softmax mismatch: %d entries above 1e-13, max %.3e at %s; GPU rerun identical: %s, "
-                  "CPU rerun identical: %s, CPU threads %d" % (
-                      int((diff > 1e-13).sum()), diff.max().item(), torch.nonzero(diff == diff.max())[:1].tolist(),
-                      torch.equal(yg2, yg), torch.equal(yr2, yr), torch.get_num_threads()))
-        # In fp64 this comparison has shown an isolated 5e-10 in the first process started on a machine
-        # (about one run in six, never in a later process), cause not identified: kernel and restatement
-        # are each deterministic when rerun.  fp64 is here to tell double from single precision arithmetic
-        # (1e-7), so the bar for this one comparison is 1e-9; anything above 1e-12 is reported above.
-        assert err < (1e-9 if dtype == torch.float64 else tol)
+        restatement_moved = False
+        if dtype == torch.float64 and not err < tol:
+            # The torch restatement runs on whatever vector math library the host's torch build picks;
+            # an isolated 5e-10 between it and the kernel was seen in some first processes on a
+            # machine, with both sides bitwise stable when rerun.  A third opinion in extended
+            # precision (numpy long double, exp and sums) decides: the kernel must be within 1e-12 of it.
+            truth = _softmax_longdouble(crw, cip, ced, x_ref.detach().numpy(), N)
+            err_gpu = rel_err(y_gpu.detach().double().cpu().numpy(), truth)
+            err_cpu = rel_err(y_ref.detach().numpy(), truth)
+            print("sparse_softmax fp64: kernel vs torch restatement %.3e; kernel vs long double %.3e; "
+                  "torch restatement vs long double %.3e (CPU threads %d)" % (err, err_gpu, err_cpu,
+                                                                              torch.get_num_threads()))
+            err, restatement_moved = err_gpu, err_cpu > tol
+        assert err < tol
         y_ref.backward(dy.double())
         y_gpu.backward(dy.cuda())
         # graph_kernel/test.py:239 relaxes softmax gradients to rtol 1e-3 in fp32; we keep 10x the forward bar
-        assert rel_err(x_gpu.grad.double().cpu(), x_ref.grad) < 10 * (1e-9 if dtype == torch.float64 else tol)
+        # (when the restatement's forward was the side that moved, its gradient carries that error)
+        assert rel_err(x_gpu.grad.double().cpu(), x_ref.grad) < (1e-8 if restatement_moved else 10 * tol)
 
     # vec_spmm over the in-CSR with the out-CSR as its transpose (attention.py:74-77)
     (w_ref, w_gpu), (x_ref, x_gpu) = pair(eshape, 7, 0.2), pair(nshape, 8)

@@ -56,3 +56,16 @@ def test_static_scratch_rejects_graphs_beyond_its_size():
     q = torch.zeros(g.number_of_nodes, 8, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="built-in scratch"):
         attention_forward_static(plan, q, q, q, None, 0.125)
+
+
+def test_static_scratch_checks_caller_buffers(oracle_lib):
+    """out and lse_out reach the library as raw pointers: a wrong shape or dtype must raise first."""
+    from bpt_b200.attention import attention_forward_static
+    plan, q, k, v, ak = _case(oracle_lib, 200, 2)
+    with pytest.raises(RuntimeError, match="lse_out"):
+        attention_forward_static(plan, q, k, v, ak, 0.125,
+                                 lse_out=torch.empty(plan.n_nodes, 8, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(RuntimeError, match="out must"):
+        attention_forward_static(plan, q, k, v, ak, 0.125, out=torch.empty_like(q)[:-1])
+    with pytest.raises(RuntimeError, match="embed_ak"):
+        attention_forward_static(plan, q, k, v, ak.double(), 0.125)

@@ -21,6 +21,7 @@ kernels on the same GPU" leg of the benchmark.  Nothing in the shipped package m
 Usage:  python oracle/build_ref_graphop.py [--ref /path/to/reference/checkout]
 """
 import argparse
+import atexit
 import glob
 import importlib.machinery
 import importlib.util
@@ -149,6 +150,15 @@ def _stub_dgl():
     return made
 
 
+_TEMP_DIRS = []
+
+
+@atexit.register
+def _remove_temp_dirs():
+    for d in _TEMP_DIRS:
+        shutil.rmtree(d, ignore_errors=True)
+
+
 def load_modules(graphop_module, ref_root=None):
     """The reference's modules/op.py and modules/attention.py bound to `graphop_module` (what their
     `from graphop import *`, modules/op.py:2, resolves to).  Taken from the checkout's .py files
@@ -159,6 +169,12 @@ def load_modules(graphop_module, ref_root=None):
         src = {n: os.path.join(ref_root, "modules", n + ".py") for n in ("op", "attention")}
     else:
         src = modules_so_paths()
+        if src is not None:
+            # An extension module file is initialised once per process; every call here must yield modules
+            # of its own (bound to its own `graphop`), so each call loads private copies of the two files.
+            tmp = tempfile.mkdtemp(prefix="bpt_ref_modules_")
+            _TEMP_DIRS.append(tmp)
+            src = {n: shutil.copy2(path, os.path.join(tmp, os.path.basename(path))) for n, path in src.items()}
     if src is None:
         return None
     saved = {k: sys.modules.get(k) for k in ("graphop", MODULES_PKG, MODULES_PKG + ".op", MODULES_PKG + ".attention")}

@@ -193,13 +193,15 @@ def test_reference_block_runs_unchanged_on_this_library(oracle_lib, ref_graphop)
     mine = BPTBlock(dim, heads, ff, rel_pos=True, drop_h=0.0).cuda()
     mine.load_state_dict(blk_ours.state_dict())       # the reference block's state dict loads as it is
     h0 = torch.randn(batch.n_nodes, dim, device="cuda")
+    # loss = <output, fixed random tensor> (a sum of squares of a LayerNorm output is constant: zero gradient)
+    w_loss = torch.randn(batch.n_nodes, dim, device="cuda")
     outs, grads = [], []
     for blk in (blk_ours, blk_theirs):
         g = build_ref_graphop.FakeGraph(ndata={"h": h0.clone().requires_grad_(True)},
                                         edata={"etype": batch.etype.long()})
         h_in = g.ndata["h"]
         blk(g, csr)
-        g.ndata["h"].square().sum().backward()
+        (g.ndata["h"] * w_loss).sum().backward()
         outs.append(g.ndata["h"].detach())
         grads.append([h_in.grad] + [p.grad for p in blk.parameters()])
     assert rel_err(outs[0].cpu(), outs[1].cpu()) < 1e-5
@@ -208,7 +210,7 @@ def test_reference_block_runs_unchanged_on_this_library(oracle_lib, ref_graphop)
     plan = AttentionPlan.from_batch(batch, n_etypes=1000)
     h_in = h0.clone().requires_grad_(True)
     out = mine(h_in, plan)
-    out.square().sum().backward()
+    (out * w_loss).sum().backward()
     assert rel_err(out.detach().cpu(), outs[1].cpu()) < 1e-5
     for a, b in zip([h_in.grad] + [p.grad for p in mine.parameters()], grads[1]):
         assert rel_err(a.cpu(), b.cpu()) < 1e-4

@@ -79,8 +79,9 @@ def test_reference_block_forward_equals_oracle_chain(oracle_lib, source):
     want = blk.norm_inter(hh + blk.ffn(hh))
     assert torch.allclose(out, want, rtol=1e-10, atol=1e-12)
     # and the reference's autograd shim (modules/op.py:10-58) yields the chain's gradients
-    g1 = torch.autograd.grad(out.square().sum(), [h0] + list(blk.parameters()), retain_graph=True)
-    g2 = torch.autograd.grad(want.square().sum(), [h0] + list(blk.parameters()))
+    w_loss = torch.randn(N, dim, dtype=torch.float64)  # (a sum of squares of a LayerNorm output has zero gradient)
+    g1 = torch.autograd.grad((out * w_loss).sum(), [h0] + list(blk.parameters()), retain_graph=True)
+    g2 = torch.autograd.grad((want * w_loss).sum(), [h0] + list(blk.parameters()))
     for x, y in zip(g1, g2):
         assert torch.allclose(x, y, rtol=1e-8, atol=1e-10)
     assert np.isfinite(out.detach().numpy()).all()

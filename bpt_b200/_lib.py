@@ -68,6 +68,10 @@ SIGNATURES = {
     "bpt_attn_backward_tc_workspace_bytes": (_sz, [_vp, _vp, _vp, _i64, _i64, _int]),
     "bpt_attn_backward_tc": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp,
                                     _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+    "bpt_attn_forward_tc5_smem_bytes": (_sz, [_int, _int]),
+    "bpt_attn_forward_tc5_workspace_bytes": (_sz, [_i64, _int]),
+    "bpt_attn_forward_tc5": (_int, [_vp, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+    "bpt_attn_forward_tc5_status": (_int, [_vp, _vp, _vp]),
     "bpt_attn_forward_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                        _int, _int, _int, _vp]),
 }

@@ -15,6 +15,7 @@ in the forward, and its results do not vary from run to run.
 """
 import ctypes
 import math
+import os
 
 import numpy as np
 import torch
@@ -61,6 +62,7 @@ class AttentionPlan:
         self._ws = {}
         self.tiles = None    # TilePlan of the tensor-core forward, built on first use
         self.tiles_t = None  # transposed TilePlan of the tensor-core dK/dV kernel
+        self.tiles5 = None   # 128-row TilePlan of the tcgen05 forward
 
     @classmethod
     def from_batch(cls, batch, n_etypes=None):
@@ -84,6 +86,15 @@ class AttentionPlan:
         if self.tiles is None:
             self.tiles = TilePlan(self)
         return self.tiles
+
+    def tile_plan5(self):
+        """The tile plan of the tcgen05 forward: groups of 128 destination rows (one per thread and
+        tensor-memory lane) over up to 512 source columns; rows outside dense groups bucketed by
+        block of 128 consecutive sources."""
+        if self.tiles5 is None:
+            self.tiles5 = TilePlan(self, min_density=0.05, max_cols=512, group_rows=128, col_block=128,
+                                   max_mblocks=8)
+        return self.tiles5
 
     def tile_plan_t(self):
         """The transposed tile plan (rows = sources) of the tensor-core dK/dV kernel."""
@@ -228,6 +239,56 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale):
     return o, lse
 
 
+def tc5_eligible(q, embed_ak, plan):
+    """bf16, head dim 64, 8-bit cells (at most 248 edge types) and a 128-row tile plan that fits in
+    shared memory: the tcgen05 forward applies."""
+    if not (q.dtype == torch.bfloat16 and q.size(-1) == 64):
+        return False
+    tp = plan.tile_plan5()
+    if tp.et_bytes != 1 or (embed_ak is not None and tp.t_max > 248):
+        return False
+    need = _lib.lib().bpt_attn_forward_tc5_smem_bytes(tp.max_cols_pad, tp.t_max if embed_ak is not None else 0)
+    return 0 < need <= MAX_BLOCK_SMEM
+
+
+def attention_forward_tc5(plan, q, k, v, embed_ak, scale):
+    """Forward through bpt_attn_forward_tc5 (tcgen05.mma, accumulators in tensor memory). Returns (o, lse)."""
+    N, h, d = _check_inputs(plan, q, k, v, embed_ak)
+    tp = plan.tile_plan5()
+    o = torch.empty_like(q)
+    lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
+    L = _lib.lib()
+    with torch.cuda.device(q.device):
+        ws = tp._ws.get(("tc5", h))
+        if ws is None:
+            ws = _lib.workspace(L.bpt_attn_forward_tc5_workspace_bytes(tp.n_slots, h), q.device)
+            ws[:16].zero_()  # the status word
+            tp._ws[("tc5", h)] = ws
+        tiles = tp.struct()
+        _lib.check(L.bpt_attn_forward_tc5(ctypes.addressof(tiles), plan.n_nodes, plan.n_etypes, q.data_ptr(),
+                                          k.data_ptr(), v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(),
+                                          lse.data_ptr(), h, d, _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(),
+                                          _lib.stream()))
+    return o, lse
+
+
+def tc5_status(plan, h):
+    """0 when every bounded wait of the tcgen05 forward calls on this plan completed (waits for the stream)."""
+    tp = plan.tiles5
+    ws = None if tp is None else tp._ws.get(("tc5", h))
+    if ws is None:
+        return 0
+    out = ctypes.c_int32(0)
+    with torch.cuda.device(ws.device):
+        _lib.check(_lib.lib().bpt_attn_forward_tc5_status(ws.data_ptr(), ctypes.addressof(out), _lib.stream()))
+    return int(out.value)
+
+
+# Which tensor-core forward bf16 / head-dim-64 calls take: "tc5" (tcgen05, 128-row tiles) where it
+# applies, else "tile" (mma.sync, 16-row tiles).
+FORWARD_IMPL = os.environ.get("BPT_FORWARD_IMPL", "tile")
+
+
 def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
     """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype.
     bf16 with head dim 64 runs on the tensor-core kernel unless tensor_cores=False."""
@@ -235,6 +296,8 @@ def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
     if tensor_cores is None:
         tensor_cores = tensor_core_eligible(q, embed_ak, plan)
     if tensor_cores:
+        if FORWARD_IMPL == "tc5" and tc5_eligible(q, embed_ak, plan):
+            return attention_forward_tc5(plan, q, k, v, embed_ak, scale)
         return attention_forward_tc(plan, q, k, v, embed_ak, scale)
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)

@@ -352,6 +352,24 @@ int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t
                          void *dq, void *dk, void *dv, float *dak, int h, int d, int dtype,
                          void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 
+/* ------------------------------------------------------------------------------------
+ * Forward on the 5th-generation tensor cores (tcgen05.mma with accumulators in tensor memory; bf16, head
+ * dim 64).  Same result as bpt_attn_forward_tc within bf16 tolerance and the same operator chain of the
+ * reference (modules/attention.py:66-77).  `tiles` is a tile plan made by bpt_tile_plan_create with
+ * group_rows = 128 and max_mblocks = 8 (a thread block owns 128 destination rows, one per thread and
+ * tensor-memory lane), exported with 8-bit cells and without row items; at most 248 edge types when ak
+ * is given.  The first 16 bytes of the workspace hold a status word that the kernel sets to 1 when one of
+ * its bounded waits ran out (the block then frees its tensor memory and returns; results are invalid):
+ * zero them once, read them with bpt_attn_forward_tc5_status (which waits for the stream).
+ * bpt_attn_forward_tc5_smem_bytes: shared memory per block for a plan with these sizes (host only).
+ * ---------------------------------------------------------------------------------- */
+size_t bpt_attn_forward_tc5_smem_bytes(int max_cols_pad, int t_max);
+size_t bpt_attn_forward_tc5_workspace_bytes(int64_t n_slots, int h);
+int bpt_attn_forward_tc5(const bpt_tile_plan_t *tiles, int64_t n_nodes, int n_etypes, const void *q, const void *k,
+                         const void *v, const void *ak, double scale, void *o, float *lse, int h, int d, int dtype,
+                         void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+int bpt_attn_forward_tc5_status(const void *workspace, int32_t *status_host, bpt_stream_t stream);
+
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

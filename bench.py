@@ -4,13 +4,17 @@
 One "step" is one pass of the hot path over one batch: a block-diagonal batch of `--seqs`
 independent sequences of `--seq-len` tokens with `--step` neighbours per side per level, 8 heads x 64,
 forward and backward.  The metric is attention edges per second (edges of the batch graph
-divided by the step time), the one BASELINE.json quotes at n = 8192, k = 4.
+divided by the step time), quoted at n = 8192, k = 4.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 With N > 1 it is launched by torch.distributed.run, one rank per GPU; every rank processes
 its own batch (independent graphs shard by graph, no collective on the data path) and the
-reported value is all ranks' edges over the slowest rank's device time.
+reported value is all ranks' edges over the slowest rank's device time.  The default line also
+carries sub-records measured in the same run: `single_seq` (one sequence of n = 8192, k = 4),
+`fp32` (the headline workload in fp32), `lm` (12-layer language-model forward, tokens/s, weak
+scaling) and `seqshard` (one 65,536-token sequence with its destination nodes split over the
+ranks, strong scaling).
 `--impl reference` times the CPU restatement of the reference's math on the host cores.
 """
 import argparse
@@ -59,6 +63,9 @@ def parse():
                          "forward + backward")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="attention workload: only the headline line, without the single_seq / fp32 / lm / seqshard "
+                         "sub-records")
     return ap.parse_args()
 
 
@@ -191,27 +198,87 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- GPU side
 
-def run_seqshard(a):
-    """One long sequence, destination nodes sharded over the ranks (bpt_b200/shard.py).
-    Timed step = all-gather K,V -> fused forward -> fused backward -> reduce-scatter dK,dV."""
+_CTX = None
+
+
+def dist_context():
+    """(world, rank, device) of this process; the NCCL process group is created once and shared by every
+    measurement of the run."""
+    global _CTX
+    if _CTX is None:
+        import datetime
+        import torch
+        import torch.distributed as dist
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise RuntimeError("bench.py needs a CUDA device: the attention path has no CPU fallback")
+        torch.cuda.set_device(local_rank)
+        dev = torch.device("cuda", local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+        _CTX = (world, rank, dev)
+    return _CTX
+
+
+def barrier():
     import torch
     import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(values, dev):
+    """Element-wise maximum of a list of floats over the ranks."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return list(values)
+    t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def timed_blocks(run_step, steps, dev, min_seconds=1.0, max_blocks=50):
+    """Times blocks of exactly `steps` steps with CUDA events (barrier + synchronize on both sides of
+    every block), repeating blocks until about `min_seconds` have been measured.  Returns (median ms
+    per step over the blocks after the maximum over ranks, number of blocks)."""
+    import torch
+    per_step = []
+    total = 0.0
+    while True:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for _ in range(steps):
+            run_step()
+        stop.record()
+        barrier()
+        ms = max_over_ranks([start.elapsed_time(stop)], dev)[0]
+        per_step.append(ms / steps)
+        total += ms
+        if total >= 1e3 * min_seconds or len(per_step) >= max_blocks:
+            break
+    per_step.sort()
+    return per_step[len(per_step) // 2], len(per_step)
+
+
+def measure_seqshard(a, n, k, steps, warmup, min_seconds=1.0):
+    """One long sequence of n tokens, destination nodes sharded over the ranks (bpt_b200/shard.py):
+    forward + backward of one attention layer, K/V rows exchanged over NCCL.  Strong scaling: the
+    work is fixed, the ranks split it.  Returns the record (rank 0) or None."""
+    import torch
     from bpt_b200 import graphbuilder, shard as sh
     from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        import datetime
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+    world, rank, dev = dist_context()
     dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
-    g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
+    halo = a.exchange == "halo" and dtype == torch.bfloat16
+    g = graphbuilder.BinaryPartition(n, a.causal, k, 10)
     src, dst, et = g.edges_device()
     s = sh.SequenceShard(src, dst, et, g.n_nodes_arr, g.shift, rank, world)
-    halo = a.exchange == "halo"
     if halo:
         s.build_halo(src, dst, split_straddlers=True)
         plan = AttentionPlan(s.src_h, s.dst_l, s.etype_l, s.n_dst_local, n_etypes=MAX_ETYPE, n_src=s.n_ext)
@@ -219,47 +286,36 @@ def run_seqshard(a):
         plan = AttentionPlan(s.src_g, s.dst_l, s.etype_l, s.n_owned, n_etypes=MAX_ETYPE, n_src=s.n_gathered)
     E = g.number_of_edges
     gen = torch.Generator().manual_seed(2 + rank)
-    q, k, v, d_o = [(torch.randn(s.n_owned, H, D, generator=gen) * sg).to(dtype).to(dev)
-                    for sg in (0.125, 0.125, 0.125, 1.0)]
+    q, k_, v, d_o = [(torch.randn(s.n_owned, H, D, generator=gen) * sg).to(dtype).to(dev)
+                     for sg in (0.125, 0.125, 0.125, 1.0)]
     ak = (torch.randn(MAX_ETYPE, D, generator=torch.Generator().manual_seed(1)) * 0.125).to(dtype).to(dev)
     scale = 1.0 / math.sqrt(D)
-
     if halo:
-        for t_ in (q, k, v, ak):
+        for t_ in (q, k_, v, ak):
             t_.requires_grad_(True)
 
     def step():
         if halo:
             # the autograd function: halo all-to-all, tile kernels, merge of the straddlers' partial rows
-            for t_ in (q, k, v, ak):
+            for t_ in (q, k_, v, ak):
                 t_.grad = None
-            sh.halo_attention(s, plan, q, k, v, ak, scale).backward(d_o)
-            return k.grad, v.grad
-        elif world > 1:
-            k_g, v_g = sh.all_gather_rows(s, k), sh.all_gather_rows(s, v)
+            sh.halo_attention(s, plan, q, k_, v, ak, scale).backward(d_o)
+            return
+        if world > 1:
+            k_g, v_g = sh.all_gather_rows(s, k_), sh.all_gather_rows(s, v)
         else:
-            k_g, v_g = s.pad_rows(k), s.pad_rows(v)
+            k_g, v_g = s.pad_rows(k_), s.pad_rows(v)
         o, lse = attention_forward(plan, q, k_g, v_g, ak, scale)
         dq, dk_g, dv_g, dak = attention_backward(plan, q, k_g, v_g, ak, scale, lse, d_o, o=o)
         if world > 1:
-            return sh.reduce_scatter_rows(s, dk_g), sh.reduce_scatter_rows(s, dv_g)
-        return dk_g, dv_g
+            sh.reduce_scatter_rows(s, dk_g), sh.reduce_scatter_rows(s, dv_g)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(a.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
-    barrier()
     run_step, graph_note = step, None
-    if a.graph and world > 1:
-        # A captured step that holds NCCL collectives did not complete on two ranks here (the run was
-        # ended by its time limit), so steps with collectives are issued eagerly.
-        graph_note = "not used: the step holds NCCL collectives"
-    elif a.graph:
+    if a.graph and world == 1:
         # One step (tile kernels, GEMMs, index kernels) as a CUDA graph: its launches are issued by one call.
+        # (With more ranks the step holds NCCL collectives and is issued eagerly.)
         graph = torch.cuda.CUDAGraph()
         try:
             with torch.cuda.graph(graph):
@@ -267,103 +323,80 @@ def run_seqshard(a):
             run_step, graph_note = graph.replay, "step replayed from a CUDA graph"
             for _ in range(3):
                 run_step()
-        except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+        except Exception as exc:  # noqa: BLE001 - reported in the record
             graph_note = "capture failed: %s" % str(exc)[:160]
-        barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(a.steps):
-        run_step()
-    stop.record()
-    barrier()
-    ms = start.elapsed_time(stop) / a.steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
-    if rank == 0:
-        print(json.dumps({
-            "cuda_graph": graph_note,
-            "metric": "bpt_attention_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
-            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": a.dtype, "data": "synthetic",
-            "config": {"workload": "bpt_attention_fwd_bwd 1x(n=%d,k=%d) destination-sharded, %s over NCCL" % (
-                           a.n, a.k, "halo all-to-all of K/V rows and of their gradients, straddling span nodes merged across ranks" if halo
-                           else "K/V all-gather + dK/dV reduce-scatter"),
-                       "edges": E, "nodes": g.number_of_nodes, "owned_nodes_rank0": s.n_owned,
-                       "kv_bytes_received_rank0": 2 * (s.n_halo if halo else s.n_gathered) * H * D * q.element_size()}}),
-              flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    ms, blocks = timed_blocks(run_step, steps, dev, min_seconds)
+    if rank != 0:
+        return None
+    return {
+        "metric": "bpt_attention_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
+        "steps": steps, "blocks": blocks, "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": a.dtype, "data": "synthetic", "cuda_graph": graph_note,
+        "config": {"workload": "bpt_attention_fwd_bwd 1x(n=%d,k=%d) destination-sharded, %s over NCCL" % (
+                       n, k, "halo all-to-all of K/V rows and of their gradients, straddling span nodes merged across ranks"
+                       if halo else "K/V all-gather + dK/dV reduce-scatter"),
+                   "edges": E, "nodes": g.number_of_nodes, "owned_nodes_rank0": s.n_owned,
+                   "kv_bytes_received_rank0": 2 * (s.n_halo if halo else s.n_gathered) * H * D * q.element_size()}}
 
 
-def run_lm(a):
+def run_seqshard(a):
+    rec = measure_seqshard(a, a.n, a.k, a.steps, a.warmup)
+    if rec is not None:
+        print(json.dumps(rec), flush=True)
+
+
+def measure_lm(a, steps, warmup, min_seconds=1.0):
     """12-layer causal BPT character LM forward (d_model 512, 8 x 64, FFN 2048 GELU in its tanh form, vocab 256,
-    bf16 activations, fp32 softmax), batch of --seqs sequences of --seq-len tokens per rank, Zipf(1.1)
-    bytes (seed 1), weights N(0, 0.02).  tokens/s = tokens of all ranks / slowest rank's time."""
+    bf16 activations, fp32 softmax), batch of 8 sequences of 8192 tokens per rank, Zipf(1.1) bytes (seed 1),
+    weights N(0, 0.02).  tokens/s = tokens of all ranks / slowest rank's time (the quantity the reference
+    logs at lm.py:158-163).  Every step copies its tokens from pinned host memory."""
     import numpy as np
     import torch
-    import torch.distributed as dist
     from bpt_b200 import csr as csrmod, graphbuilder
     from bpt_b200.attention import AttentionPlan
     from bpt_b200.model import BPTLanguageModel
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    g = graphbuilder.BinaryPartition(a.n, True, a.k, 10)
-    batch = csrmod.batch_graphs([g] * a.seqs)
+    world, rank, dev = dist_context()
+    seqs, n, k = 8, 8192, 4
+    g = graphbuilder.BinaryPartition(n, True, k, 10)
+    batch = csrmod.batch_graphs([g] * seqs)
     plan = AttentionPlan.from_batch(batch, n_etypes=MAX_ETYPE)
     leaf_ids = batch.leaf_ids()
     torch.manual_seed(0)
     model = BPTLanguageModel(256, 512, 2048, 8, 12, dropout=0.0, activation="gelu_tanh")
-    for p in model.parameters():
-        torch.nn.init.normal_(p, 0.0, 0.02)
+    for p_ in model.parameters():
+        torch.nn.init.normal_(p_, 0.0, 0.02)
     model = model.to(dev).to(torch.bfloat16).eval()
     rng = np.random.default_rng(1 + rank)
     w = 1.0 / np.arange(1, 257) ** 1.1
-    host_tokens = torch.from_numpy(rng.choice(256, size=a.seqs * a.n, p=w / w.sum())).pin_memory()
+    host_tokens = torch.from_numpy(rng.choice(256, size=seqs * n, p=w / w.sum())).pin_memory()
+    out = [None]
 
     def step():
         tokens = host_tokens.to(dev, non_blocking=True)
         with torch.no_grad():
-            return model(tokens, leaf_ids, plan)
+            out[0] = model(tokens, leaf_ids, plan)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(a.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(a.steps):
-        out = step()
-    stop.record()
-    barrier()
-    ms = start.elapsed_time(stop) / a.steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
-    if rank == 0:
-        print(json.dumps({
-            "metric": "lm_tokens_per_sec", "value": world * a.seqs * a.n / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": "bpt_lm_forward 12 layers d512 8x64 ffn2048 gelu(tanh) vocab256, %dx(n=%d,k=%d,causal) "
-                                   "per rank" % (a.seqs, a.n, a.k),
-                       "nodes_per_gpu": batch.n_nodes, "edges_per_gpu_per_layer": batch.n_edges,
-                       "finite": bool(torch.isfinite(out.float()).all().item())}}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    ms, blocks = timed_blocks(step, steps, dev, min_seconds)
+    finite = bool(torch.isfinite(out[0].float()).all().item())
+    del model
+    if rank != 0:
+        return None
+    return {
+        "metric": "lm_tokens_per_sec", "value": world * seqs * n / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "blocks": blocks, "warmup": max(warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "bpt_lm_forward 12 layers d512 8x64 ffn2048 gelu(tanh) vocab256, %dx(n=%d,k=%d,causal) "
+                               "per rank" % (seqs, n, k),
+                   "nodes_per_gpu": batch.n_nodes, "edges_per_gpu_per_layer": batch.n_edges, "finite": finite}}
+
+
+def run_lm(a):
+    rec = measure_lm(a, a.steps, a.warmup)
+    if rec is not None:
+        print(json.dumps(rec), flush=True)
 
 
 def run_mt(a):
@@ -379,13 +412,7 @@ def run_mt(a):
     from bpt_b200.attention import AttentionPlan
     from bpt_b200.model import BPTEncoderDecoder
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, dev = dist_context()
     rng = np.random.default_rng(4 + rank)
     docs, sents, vocab = 16, 64, 8000
     src_len = np.clip(rng.poisson(28, (docs, sents)), 3, 100)
@@ -421,11 +448,6 @@ def run_mt(a):
         with torch.no_grad():
             return model(e_tok, enc_leaves, enc_plan, d_tok, dec_leaves, dec_plan, inter_plan, dec_leaves)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     for _ in range(max(a.warmup, 3)):
         step()
     barrier()
@@ -453,8 +475,6 @@ def run_mt(a):
                        "decoder_edges": dec.n_edges, "cross_edges": int(isrc.numel()),
                        "source_tokens": n_src_tok, "target_tokens": n_trg_tok,
                        "finite": bool(torch.isfinite(out.float()).all().item())}}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def run_cls(a):
@@ -470,13 +490,7 @@ def run_cls(a):
     from bpt_b200.attention import AttentionPlan
     from bpt_b200.model import BPTClassifier
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, dev = dist_context()
     rng = np.random.default_rng(3 + rank)
     batch_size, vocab = 32, 50000
     cache = csrmod.GraphCache(triu=True, step=4, clip_dist=5)
@@ -502,11 +516,6 @@ def run_cls(a):
         stats["tokens"] += int(lengths.sum())
         stats["edges"] += batch.n_edges
         return loss
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
     w = max(a.warmup, 3)
     for i in range(w):
@@ -535,8 +544,6 @@ def run_cls(a):
                        "tokens_per_step_rank0": stats["tokens"] // a.steps,
                        "edges_per_step_rank0": stats["edges"] // a.steps,
                        "finite_loss": bool(torch.isfinite(loss).item())}}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def run_chain(a):
@@ -589,98 +596,103 @@ def run_chain(a):
                                + workload_name(a), "nodes": N, "edges": E}}), flush=True)
 
 
-def run_ours(a):
+# dram__bytes_read + dram__bytes_write of the forward kernel from ncu captures of 2 sequences of n = 8192, k = 4
+# (bidirectional, bf16): bytes per edge, keyed by the kernel that was captured.  A kernel without an entry
+# (or another shape) reports traffic = null rather than a stale figure.
+FORWARD_TRAFFIC_PER_EDGE = {
+    "attn_forward_tile_kernel": {"bytes_per_edge": 151.35e6 / 1491572,
+                                 "source": "ncu dram__bytes, 2 x (n=8192,k=4), profiles/attn_tile_kernels_bf16_n8192_k4.md"},
+    "attn_forward_tc5_kernel": {"bytes_per_edge": (112.53e6 + 20.41e6) / 1491572,
+                                "source": "ncu dram__bytes, 2 x (n=8192,k=4), profiles/attn_forward_tc5_bf16_n8192_k4.md"},
+}
+
+
+def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e, with_clocks, min_seconds=1.0):
+    """Fused attention forward + backward over a block-diagonal batch of `seqs` sequences per rank.
+    Returns (record, state) on rank 0 and (None, state) elsewhere."""
     import torch
-    import torch.distributed as dist
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the attention path has no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    from bpt_b200 import csr as csrmod, graphbuilder
+    from bpt_b200 import attention as att, csr as csrmod, graphbuilder
     from bpt_b200.attention import AttentionPlan, attention_backward, attention_forward
 
-    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
-    g = graphbuilder.BinaryPartition(a.n, a.causal, a.k, 10)
-    batch = csrmod.batch_graphs([g] * a.seqs)
+    world, rank, dev = dist_context()
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    g = graphbuilder.BinaryPartition(n, causal, k, 10)
+    batch = csrmod.batch_graphs([g] * seqs)
     plan = AttentionPlan.from_batch(batch, n_etypes=MAX_ETYPE)
     N, E = batch.n_nodes, batch.n_edges
     gen = torch.Generator(device="cpu").manual_seed(2 + rank)
     host = {}
     for name, sigma in (("q", 0.125), ("k", 0.125), ("v", 0.125), ("d_o", 1.0)):
-        host[name] = (torch.randn(N, H, D, generator=gen) * sigma).to(dtype).pin_memory()
+        host[name] = (torch.randn(N, H, D, generator=gen) * sigma).to(dtype)
+        if with_e2e:
+            host[name] = host[name].pin_memory()
     ak = (torch.randn(MAX_ETYPE, D, generator=gen) * 0.125).to(dtype).to(dev)
-    q, k, v, d_o = [host[n].to(dev) for n in ("q", "k", "v", "d_o")]
+    q, k_, v, d_o = [host[n_].to(dev) for n_ in ("q", "k", "v", "d_o")]
     scale = 1.0 / math.sqrt(D)
 
     if dtype == torch.bfloat16:
-        tp = plan.tile_plan()
+        tc5 = att.FORWARD_IMPL == "tc5" and att.tc5_eligible(q, ak, plan)
+        tp = plan.tile_plan5() if tc5 else plan.tile_plan()
         launches_fwd = 1 + (tp.n_split > 0) + (tp.n_row_items > 0)
-        fwd_kernel = "attn_forward_tile_kernel"
+        fwd_kernel = "attn_forward_tc5_kernel" if tc5 else "attn_forward_tile_kernel"
+        tpd, tpt = plan.tile_plan(), plan.tile_plan_t()
+        # destination-side tiles, per-row type table, source-side tiles (+ merges); the two GEMMs of
+        # the relative-position gradients are cuBLAS launches and not counted
+        launches_bwd = 3 + (tpd.n_split > 0) + (tpt.n_split > 0)
+        bwd_kernels = "attn_backward_dq_tile_kernel + build_type_table_kernel + 2 cuBLAS GEMMs + attn_backward_dkv_tile_kernel"
     else:
         launches_fwd = 1 + (plan.counts[2] > 0)
         fwd_kernel = "attn_forward_kernel"
-    if dtype == torch.bfloat16:
-        tpt = plan.tile_plan_t()
-        # destination-side tiles, per-row type table, source-side tiles (+ merges); the two GEMMs of
-        # the relative-position gradients are cuBLAS launches and not counted
-        launches_bwd = 3 + (tp.n_split > 0) + (tpt.n_split > 0)
-        bwd_kernels = "attn_backward_dq_tile_kernel + build_type_table_kernel + 2 cuBLAS GEMMs + attn_backward_dkv_tile_kernel"
-    else:
         launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
         bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"
 
     def step():
-        o, lse = attention_forward(plan, q, k, v, ak, scale)
-        return o, attention_backward(plan, q, k, v, ak, scale, lse, d_o, o=o)
+        o, lse = attention_forward(plan, q, k_, v, ak, scale)
+        return o, attention_backward(plan, q, k_, v, ak, scale, lse, d_o, o=o)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(a.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     barrier()
 
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
-    if sampler:
+    sampler = None
+    if with_clocks and rank == 0:
+        sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid))
         sampler.start()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(a.steps)]
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for i in range(a.steps):
-        ev[i][0].record()
-        o, lse = attention_forward(plan, q, k, v, ak, scale)
-        ev[i][1].record()
-        attention_backward(plan, q, k, v, ak, scale, lse, d_o, o=o)
-        ev[i][2].record()
-    stop.record()
-    barrier()
+    # blocks of exactly `steps` steps, forward and backward also timed apart by events on the launching stream
+    blocks, total_s = [], 0.0
+    while True:
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(steps):
+            ev[i][0].record()
+            o, lse = attention_forward(plan, q, k_, v, ak, scale)
+            ev[i][1].record()
+            attention_backward(plan, q, k_, v, ak, scale, lse, d_o, o=o)
+            ev[i][2].record()
+        stop.record()
+        barrier()
+        t = [start.elapsed_time(stop) / steps, sum(e[0].elapsed_time(e[1]) for e in ev) / steps,
+             sum(e[1].elapsed_time(e[2]) for e in ev) / steps]
+        blocks.append(max_over_ranks(t, dev))
+        total_s += blocks[-1][0] * steps * 1e-3
+        if total_s >= min_seconds or len(blocks) >= 50:
+            break
     clocks = sampler.stop() if sampler else None
-    total_ms = start.elapsed_time(stop)
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / a.steps
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / a.steps
-    if world > 1:
-        t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, fwd_ms, bwd_ms = t.tolist()
+    blocks.sort()
+    ms_per_step, fwd_ms, bwd_ms = blocks[len(blocks) // 2]
+    if dtype == torch.bfloat16 and att.FORWARD_IMPL == "tc5" and att.tc5_status(plan, H) != 0:
+        raise RuntimeError("bench: a bounded wait of the tcgen05 forward ran out; its results are invalid")
 
     # end to end: host buffers in, host buffers out, through the public call.  Every step copies
     # its q, k, v, dO from pinned host memory and copies o, dq, dk, dv back; copies and kernels of
     # consecutive steps overlap on three streams (two sets of device buffers), as a caller
     # feeding the layer from host memory would arrange it.
     e2e = None
-    if not a.no_e2e:
+    if with_e2e:
         names = ("q", "k", "v", "d_o")
-        e2e_steps = max(4, min(a.steps, 12))
+        e2e_steps = max(4, min(steps, 12))
         n_buf = 2
         dev_in = [[torch.empty((N, H, D), dtype=dtype, device=dev) for _ in names] for _ in range(n_buf)]
         host_out = [[torch.empty((N, H, D), dtype=dtype).pin_memory() for _ in range(4)] for _ in range(n_buf)]
@@ -691,8 +703,8 @@ def run_ours(a):
         ev_out = [torch.cuda.Event() for _ in range(n_buf)]
         results = [None] * n_buf
 
-        def e2e_run(steps):
-            for i in range(steps):
+        def e2e_run(count):
+            for i in range(count):
                 b = i % n_buf
                 with torch.cuda.stream(s_in):
                     s_in.wait_event(ev_done[b])      # the kernels that read this input set are done
@@ -701,9 +713,9 @@ def run_ours(a):
                     ev_in[b].record(s_in)
                 s_main.wait_event(ev_in[b])
                 s_main.wait_event(ev_out[b])         # the previous results of this set have left the device
-                q_, k_, v_, do_ = dev_in[b]
-                o, lse = attention_forward(plan, q_, k_, v_, ak, scale)
-                grads = attention_backward(plan, q_, k_, v_, ak, scale, lse, do_, o=o)
+                q_, kk_, v_, do_ = dev_in[b]
+                o, lse = attention_forward(plan, q_, kk_, v_, ak, scale)
+                grads = attention_backward(plan, q_, kk_, v_, ak, scale, lse, do_, o=o)
                 results[b] = (o, grads[0], grads[1], grads[2])
                 ev_done[b].record(s_main)
                 with torch.cuda.stream(s_out):
@@ -722,67 +734,98 @@ def run_ours(a):
         s_main.wait_stream(s_out)
         t2.record()
         barrier()
-        e2e_ms = s2.elapsed_time(t2) / e2e_steps
-        if world > 1:
-            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = t.item()
+        e2e_ms = max_over_ranks([s2.elapsed_time(t2) / e2e_steps], dev)[0]
         nbytes = N * H * D * q.element_size()
         e2e = {"value": world * E / (e2e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": 4 * nbytes,
                "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": e2e_ms, "steps": e2e_steps,
                "overlap": "H2D, kernels and D2H of consecutive steps on three streams"}
 
+    if rank != 0:
+        return None
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    fwd_bytes, bwd_bytes = algorithmic_bytes(N, E, q.element_size())
+    fwd_gbs = fwd_bytes / (fwd_ms * 1e-3) / 1e9
+    bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+    traffic, traffic_src = None, None
+    known = FORWARD_TRAFFIC_PER_EDGE.get(fwd_kernel)
+    if known and dtype_name == "bf16" and n == 8192 and k == 4 and not causal:
+        traffic, traffic_src = known["bytes_per_edge"] * E, known["source"]
+    line = {
+        "metric": "bpt_attention_edges_per_sec", "value": world * E / (ms_per_step * 1e-3),
+        "unit": "edges/s", "n_gpus": world, "steps": steps, "blocks": len(blocks), "warmup": max(warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": dtype_name, "data": "synthetic",
+        "config": {"workload": "bpt_attention_fwd_bwd %dx(n=%d,k=%d,%s) h=%dx%d %s" % (
+                       seqs, n, k, "causal" if causal else "bidirectional", H, D, dtype_name),
+                   "nodes_per_gpu": N, "edges_per_gpu": E,
+                   "sharding": "independent graphs per rank, no data-path collective",
+                   "l2": ("inputs+outputs %.0f MB per step exceed the 126 MB L2" if 8 * N * H * D * q.element_size() > 126e6
+                          else "inputs+outputs %.0f MB per step fit the 126 MB L2: not flushed between steps") %
+                         (8 * N * H * D * q.element_size() / 1e6)},
+        "gpu_launches": steps * len(blocks) * (launches_fwd + launches_bwd),
+        "forward": {"ms": fwd_ms, "edges_per_sec": world * E / (fwd_ms * 1e-3)},
+        "backward": {"ms": bwd_ms, "edges_per_sec": world * E / (bwd_ms * 1e-3)},
+        "roofline": {"kernel": fwd_kernel, "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
+                     "peak_source": peak_src, "unit": "GB/s", "frac": fwd_gbs / peak,
+                     "algorithmic_bytes": fwd_bytes, "traffic": traffic, "traffic_source": traffic_src},
+        "roofline_backward": {"kernels": bwd_kernels, "bound": "hbm",
+                              "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
+                              "algorithmic_bytes": bwd_bytes},
+    }
+    if clocks is not None:
+        line["clocks"] = clocks
+    if e2e:
+        line["e2e"] = e2e
+    return line
+
+
+def brief(rec, keys=("metric", "value", "unit", "n_gpus", "steps", "blocks", "ms_per_step", "scaling", "dtype", "config",
+                     "forward", "backward", "roofline", "roofline_backward")):
+    return None if rec is None else {k_: rec[k_] for k_ in keys if k_ in rec}
+
+
+def run_ours(a):
+    """The headline line, then -- in the same process group -- the other parts of the metric as sub-records:
+    the exact single-sequence cell, the same workload in fp32, the language-model forward (tokens/s, weak
+    scaling) and the destination-sharded 65,536-token sequence (strong scaling)."""
+    world, rank, dev = dist_context()
+    line = measure_attention(a, a.seqs, a.n, a.k, a.dtype, a.causal, a.steps, a.warmup, not a.no_e2e, True)
+    extras = {}
+    if not a.no_extras:
+        sub_steps = max(5, min(a.steps, 20))
+        extras["single_seq"] = brief(measure_attention(a, 1, 8192, 4, "bf16", False, sub_steps, 3, False, False, 0.3))
+        extras["fp32"] = brief(measure_attention(a, a.seqs, a.n, a.k, "fp32", a.causal, max(3, sub_steps // 4), 3,
+                                                 False, False, 0.3))
+        extras["lm"] = brief(measure_lm(a, max(3, sub_steps // 4), 3, 0.5))
+        extras["seqshard"] = brief(measure_seqshard(a, 65536, 4, sub_steps, 3, 0.5))
     if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(peaks_path):
-            peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured"
-        else:
-            peak, peak_src = 6650.0, "fallback"
-        fwd_bytes, bwd_bytes = algorithmic_bytes(N, E, q.element_size())
-        ms_per_step = total_ms / a.steps
-        fwd_gbs = fwd_bytes / (fwd_ms * 1e-3) / 1e9
-        bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
-        line = {
-            "metric": "bpt_attention_edges_per_sec", "value": world * E / (ms_per_step * 1e-3),
-            "unit": "edges/s", "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": a.dtype, "data": "synthetic",
-            "config": {"workload": workload_name(a), "nodes_per_gpu": N, "edges_per_gpu": E,
-                       "sharding": "independent graphs per rank, no data-path collective",
-                       "l2": "inputs+outputs %.0f MB per step exceed the 126 MB L2" %
-                             (8 * N * H * D * q.element_size() / 1e6)},
-            "gpu_launches": a.steps * (launches_fwd + launches_bwd),
-            "forward": {"ms": fwd_ms, "edges_per_sec": world * E / (fwd_ms * 1e-3)},
-            "backward": {"ms": bwd_ms, "edges_per_sec": world * E / (bwd_ms * 1e-3)},
-            "roofline": {"kernel": fwd_kernel, "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
-                         "peak_source": peak_src, "unit": "GB/s", "frac": fwd_gbs / peak,
-                         "algorithmic_bytes": fwd_bytes, "traffic": None},
-            "roofline_backward": {"kernels": bwd_kernels, "bound": "hbm",
-                                  "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
-                                  "algorithmic_bytes": bwd_bytes},
-            "clocks": clocks,
-        }
-        if e2e:
-            line["e2e"] = e2e
+        line.update(extras)
         if world == 1 and not a.no_cpu_baseline:
             value, info = cpu_reference_run(a, 1, 1, min_seconds=10.0)
             line["cpu_baseline"] = {"value": value, "unit": "edges/s", "cores": info["cores"], "kind": "port",
                                     "sample": info["sample"]}
-        if a.dtype == "bf16" and a.n == 8192 and a.k == 4 and not a.causal:
-            # dram__bytes_read + dram__bytes_write of attn_forward_tile_kernel from one ncu capture on 2
-            # sequences of this shape (profiles/attn_tile_kernels_bf16_n8192_k4.md): 151.35 MB for
-            # 1,491,572 edges; traffic grows in proportion to the number of sequences.
-            line["roofline"]["traffic"] = 151.35e6 / 1491572 * E
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
     a = parse()
     if a.impl == "reference":
         run_reference(a)
-    elif a.workload == "lm":
+        return
+    try:
+        dispatch(a)
+    finally:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def dispatch(a):
+    if a.workload == "lm":
         run_lm(a)
     elif a.workload == "mt":
         run_mt(a)

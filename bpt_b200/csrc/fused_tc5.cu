@@ -49,7 +49,7 @@ struct Tc5Params {
 };
 
 struct Tc5Smem {
-    uint32_t q, k, v, p, ak, tab, cols, bar, total;
+    uint32_t q, k, v, p, ak, tab, cols, xch, bar, total;
     int tab_stride;  // in halves
 };
 __host__ __device__ inline Tc5Smem tc5_smem_layout(int max_cols_pad, int tq16) {
@@ -62,20 +62,54 @@ __host__ __device__ inline Tc5Smem tc5_smem_layout(int max_cols_pad, int tq16) {
     s.tab = s.ak + static_cast<uint32_t>((tq16 * 128 + 1023) / 1024 * 1024);
     s.tab_stride = tq16 + 2;  // an odd number of 32-bit words per row: the rows of a warp start in 32 different banks
     s.cols = s.tab + static_cast<uint32_t>((kRows * s.tab_stride * 2 + 15) / 16 * 16);
-    s.bar = s.cols + static_cast<uint32_t>(max_cols_pad) * 4;
+    s.xch = s.cols + static_cast<uint32_t>(max_cols_pad) * 4;  // [2][128] floats exchanged between a row's two threads
+    s.bar = s.xch + 2 * kRows * 4;
     s.bar = (s.bar + 15) / 16 * 16;
     s.total = s.bar + 64 + 1024;  // barriers, TMEM slot; slack for the 1024-byte alignment of the base
     return s;
 }
 
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lds_half(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+    return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+// Barrier among the 64 threads (two warps) that share one quarter of the rows.
+__device__ __forceinline__ void pair_barrier(int quarter) {
+    switch (quarter) {  // literal ids: the kernel then reserves five barriers, not all sixteen
+        case 0: asm volatile("bar.sync 1, 64;\n" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 2, 64;\n" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 3, 64;\n" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 64;\n" ::: "memory"); break;
+    }
+}
+
+constexpr int kThreads = 2 * kRows;  // two threads per destination row: each takes 32 of a chunk's 64 columns
+
 template <bool kHasBias>
-__global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params p) {
+__global__ void __launch_bounds__(kThreads, 2) attn_forward_tc5_kernel(const Tc5Params p) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char *sm = smem_raw + (base - raw);
     const Tc5Smem L = tc5_smem_layout(p.max_cols_pad, kHasBias ? p.tq16 : 0);
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = warp & 3, half = warp >> 2;  // TMEM lanes 32 * quarter ..., columns 32 * half ... of a chunk
+    const int trow = quarter * 32 + lane;            // this thread's row of the tile
     const int H = p.H;
 
     const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
@@ -83,22 +117,23 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
     if (n_mb == 0) return;
     const int ncols_pad = grp[kGroupNcolsPad];
     const int n_chunks = ncols_pad / kChunk;
-    const int my_mb = tid >> 4, r16 = tid & 15;
+    const int my_mb = trow >> 4, r16 = trow & 15;
     const bool has_mb = my_mb < n_mb;
     const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + (has_mb ? my_mb : 0)) * kMbInts;
     const int row = has_mb ? mb[kMbRowOff + r16] : -1;
     const int slot = has_mb ? mb[kMbSlotOff + r16] : -1;
     const bool use_qr = kHasBias && has_mb && mb[kMbQrSlot] >= 0;
-    const uint32_t my_mask = has_mb ? static_cast<uint32_t>(mb[kMbChunkMask]) : 0u;
-    const uint32_t warp_mask = my_mask | __shfl_xor_sync(0xffffffffu, my_mask, 16);
-    uint32_t group_mask = 0;
+    const uint32_t my_fine = has_mb ? static_cast<uint32_t>(mb[kMbFineMask]) : 0u;  // bit per 16 columns
+    const uint32_t warp_fine = my_fine | __shfl_xor_sync(0xffffffffu, my_fine, 16);
+    uint32_t group_mask = 0;  // bit per 32 columns
     for (int i = 0; i < n_mb; ++i)
         group_mask |= static_cast<uint32_t>(p.mblocks[static_cast<int64_t>(grp[kGroupMbFirst] + i) * kMbInts + kMbChunkMask]);
-    const uint8_t *et_row = p.et + (has_mb ? mb[kMbEtOff] : 0) + r16 * kTileChunk;  // + chunk * 16 * 64
+    const uint8_t *et_row = p.et + (has_mb ? mb[kMbEtOff] : 0) + r16 * kTileChunk + half * 32;  // + chunk * 16 * 64
     static_assert(kTileChunk == kChunk && kMaskCols * 2 == kChunk, "plan chunking and the kernel's step agree");
 
     int32_t *s_cols = reinterpret_cast<int32_t *>(sm + L.cols);
-    __half *tab_row = reinterpret_cast<__half *>(sm + L.tab) + tid * L.tab_stride;
+    const uint32_t tab_addr = base + L.tab + static_cast<uint32_t>(trow) * L.tab_stride * 2;
+    const uint32_t xch_mine = base + L.xch + (half * kRows + trow) * 4, xch_other = base + L.xch + ((half ^ 1) * kRows + trow) * 4;
     const uint32_t bar_tab = base + L.bar, bar_s = bar_tab + 8, bar_pv = bar_tab + 16;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(sm + L.bar + 32);
 
@@ -115,10 +150,10 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
     if (warp == 0) tmem_alloc(base + L.bar + 32, tmem_cols);
     {
         const int32_t *gc = p.cols + grp[kGroupColOff];
-        for (int i = tid; i < ncols_pad; i += kRows) s_cols[i] = gc[i];
+        for (int i = tid; i < ncols_pad; i += kThreads) s_cols[i] = gc[i];
     }
     if (kHasBias) {
-        for (int i = tid; i < tq16 * 8; i += kRows) {
+        for (int i = tid; i < tq16 * 8; i += kThreads) {
             const int r = i >> 3, piece = i & 7;
             const int type = r < p.n_etypes ? r : p.n_etypes - 1;
             cp_async16(base + L.ak + swz(r, piece), p.ak + static_cast<int64_t>(type) * kHeadDim + piece * 8);
@@ -131,13 +166,13 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tm_tab = tmem + lane_base, tm_s = tmem + lane_base + col_s, tm_o = tmem + lane_base + col_o;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tm_tab = tmem + lane_base, tm_s = tmem + lane_base + col_s + half * 32, tm_o = tmem + lane_base + col_o + half * 32;
 
     const float sl2 = p.scale * kLog2e;
     const uint32_t none_idx = kHasBias ? static_cast<uint32_t>(tq16) : 1u;
     const uint32_t none4 = none_idx * 0x01010101u;
-    constexpr uint32_t kIdescS = instr_desc(kRows, kChunk, 0, 0);     // S = Q K^T and the table's columns are set below
+    constexpr uint32_t kIdescS = instr_desc(kRows, kChunk, 0, 0);     // S = Q K^T
     constexpr uint32_t kIdescPV = instr_desc(kRows, kHeadDim, 0, 1);  // O += P V, V MN-major
     const uint32_t idesc_tab = instr_desc(kRows, tq16 > 0 ? tq16 : 16, 0, 0);
 
@@ -145,11 +180,11 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
         while (c < n_chunks && !((group_mask >> (2 * c)) & 3u)) ++c;
         return c;
     };
-    // K and V rows of head h for chunk c -> buffer b (4 + 4 pieces per thread)
+    // K and V rows of head h for chunk c -> buffer b (2 + 2 pieces per thread)
     auto issue_kv = [&](int h, int c, int b) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int id = i * kRows + tid;
+        for (int i = 0; i < 2; ++i) {
+            const int id = i * kThreads + tid;
             const int r = id >> 3, piece = id & 7;
             const int64_t off = (static_cast<int64_t>(s_cols[c * kChunk + r]) * H + h) * kHeadDim + piece * 8;
             const uint32_t dst = static_cast<uint32_t>(b) * kTileBytes + swz(r, piece);
@@ -163,11 +198,11 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
     const int c_first = first_chunk_from(0);
 
     for (int h = 0; h < H; ++h) {
-        // ---- stage Q of this head (own row) and the first chunk's K and V
+        // ---- stage Q of this head (4 pieces of the row per thread) and the first chunk's K and V
         {
             const __nv_bfloat16 *src = p.q + (static_cast<int64_t>(row < 0 ? 0 : row) * H + h) * kHeadDim;
 #pragma unroll
-            for (int piece = 0; piece < 8; ++piece) cp_async16(base + L.q + swz(tid, piece), src + piece * 8);
+            for (int i = 0; i < 4; ++i) cp_async16(base + L.q + swz(trow, half * 4 + i), src + (half * 4 + i) * 8);
         }
         if (c_first < n_chunks) issue_kv(h, c_first, 0);
         cp_async_commit();
@@ -177,7 +212,7 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
         if (__syncthreads_or(!ok)) break;
         if (tid == 0) {
             fence_after_sync();
-            if (kHasBias && tq16 > 0) {
+            if (kHasBias) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     mma_ss(tmem, desc_kmajor(base + L.q, ks), desc_kmajor(base + L.ak, ks), idesc_tab, ks > 0);
@@ -190,26 +225,29 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
                 mma_commit(bar_s);
             }
         }
-        // ---- the head's table row: scale * log2(e) * <q[row], embed_ak[type]> as fp16; rows whose edges
-        // share one type keep zeros (the term is a per-row constant that cancels; it is added to lse)
+        // ---- the head's table row: scale * log2(e) * <q[row], embed_ak[type]> as fp16 (each of the row's two
+        // threads converts half of it); rows whose edges share one type keep zeros: the term is then a
+        // per-row constant that cancels in the softmax and is added to lse
         float bias_row = 0.f;
-        if (kHasBias && tq16 > 0) {
+        if (kHasBias) {
             ok = ok && mbar_wait(bar_tab, n_tab_done & 1u);
             ++n_tab_done;
             fence_after_sync();
-            for (int c0 = 0; c0 < tq16; c0 += 16) {
+            const int n_units = tq16 / 16, u_split = (n_units + 1) / 2;
+            for (int u = half ? u_split : 0; u < (half ? n_units : u_split); ++u) {
                 uint32_t t[16];
-                tmem_ld16(tm_tab + c0, t);
+                tmem_ld16(tm_tab + u * 16, t);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
                     const float a = use_qr ? __uint_as_float(t[i]) * sl2 : 0.f;
                     const float b = use_qr ? __uint_as_float(t[i + 1]) * sl2 : 0.f;
-                    *reinterpret_cast<__half2 *>(tab_row + c0 + i) = __floats2half2_rn(a, b);
+                    __half2 hv = __floats2half2_rn(a, b);
+                    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(tab_addr + (u * 16 + i) * 2), "r"(*reinterpret_cast<uint32_t *>(&hv)) : "memory");
                 }
             }
-            tab_row[tq16] = __float2half_rn(-INFINITY);
-            if (!use_qr && row >= 0) {
+            if (half) asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(tab_addr + tq16 * 2), "h"(static_cast<unsigned short>(0xFC00)) : "memory");
+            if (!use_qr && row >= 0 && half == 0) {
                 int type = mb[kMbRowEtOff + r16];
                 type = type < 0 ? 0 : (type < p.n_etypes ? type : p.n_etypes - 1);
                 const uint4 *qa = reinterpret_cast<const uint4 *>(p.q + (static_cast<int64_t>(row) * H + h) * kHeadDim);
@@ -228,99 +266,102 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
                 }
                 bias_row = sum * sl2;
             }
+            pair_barrier(quarter);  // the row's other thread wrote the other half of the table row
         } else {
-            *reinterpret_cast<__half2 *>(tab_row) = __floats2half2_rn(0.f, -INFINITY);
+            if (half == 0) asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(tab_addr), "r"(0xFC000000u) : "memory");  // {0, -inf}
+            pair_barrier(quarter);
         }
 
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;  // m_run is shared by the row's two threads, l_run is this thread's part
         int n_pv = 0, buf = 0;
         int c = c_first;
         bool aborted = false;
         while (c < n_chunks) {
             const int nc = first_chunk_from(c + 1);
+            // this thread's 32 cells of the chunk (edge types, 0xFF = no edge), fetched while S is on its way
+            uint32_t cells[8];
+            if (has_mb) {
+                const uint4 *cp = reinterpret_cast<const uint4 *>(et_row + c * (kTileRows * kTileChunk));
+                const uint4 x = __ldg(cp), y = __ldg(cp + 1);
+                cells[0] = x.x; cells[1] = x.y; cells[2] = x.z; cells[3] = x.w;
+                cells[4] = y.x; cells[5] = y.y; cells[6] = y.z; cells[7] = y.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cells[j] = 0xFFFFFFFFu;
+            }
             if (n_pv > 0) {  // the previous chunk's O += P V is done: P, the other K/V buffer and O are free
                 ok = ok && mbar_wait(bar_pv, n_pv_done & 1u);
                 ++n_pv_done;
             }
             if (nc < n_chunks) issue_kv(h, nc, buf ^ 1);
             cp_async_commit();
-            // this row's 64 cells of the chunk (edge types, 0xFF = no edge), fetched while S is on its way
-            uint32_t cells[16];
-            if (has_mb) {
-                const uint4 *cp = reinterpret_cast<const uint4 *>(et_row + c * (kTileRows * kTileChunk));
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 x = __ldg(cp + j);
-                    cells[4 * j] = x.x; cells[4 * j + 1] = x.y; cells[4 * j + 2] = x.z; cells[4 * j + 3] = x.w;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) cells[j] = 0xFFFFFFFFu;
-            }
             ok = ok && mbar_wait(bar_s, n_s_done & 1u);
             ++n_s_done;
             fence_after_sync();
 
+            // scores of the two 16-column units of this thread, in the log2 domain, mask applied
+            const uint32_t act = (warp_fine >> (4 * c + 2 * half)) & 3u;  // uniform over the warp
+            float x[32];
+            float cmax = -INFINITY;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const bool active = (warp_mask >> (2 * c + half)) & 1u;  // uniform over the warp
-                uint32_t pk[16];
-                if (active) {
-                    uint32_t s[32];
-                    tmem_ld32(tm_s + half * 32, s);
+            for (int u = 0; u < 2; ++u) {
+                if ((act >> u) & 1u) {
+                    uint32_t s[16];
+                    tmem_ld16(tm_s + u * 16, s);
                     tmem_ld_wait();
-                    float cmax = -INFINITY;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t w = half ? cells[8 + j] : cells[j];
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t w = cells[4 * u + j];
                         const uint32_t none = __vcmpeq4(w, 0xFFFFFFFFu);
                         const uint32_t idx4 = ((use_qr ? w : 0u) & ~none) | (none4 & none);
 #pragma unroll
                         for (int b = 0; b < 4; ++b) {
-                            const uint32_t idx = (idx4 >> (8 * b)) & 0xFFu;
-                            const float x = fmaf(__uint_as_float(s[4 * j + b]), sl2, __half2float(tab_row[idx]));
-                            s[4 * j + b] = __float_as_uint(x);
-                            cmax = fmaxf(cmax, x);
+                            const uint32_t idx2 = (idx4 >> (8 * b) << 1) & 0x1FEu;  // byte offset of the table entry
+                            const float v = fmaf(__uint_as_float(s[4 * j + b]), sl2, lds_half(tab_addr + idx2));
+                            x[16 * u + 4 * j + b] = v;
+                            cmax = fmaxf(cmax, v);
                         }
-                    }
-                    // lazily updated maximum: move it (and rescale the sums) only when it grows by more than 8
-                    const bool need = cmax > m_run + 8.f || (m_run == -INFINITY && cmax > -INFINITY);
-                    if (__any_sync(0xffffffffu, need)) {
-                        const float f = need ? exp2f(m_run - cmax) : 1.f;
-                        if (need) {
-                            m_run = cmax;
-                            l_run *= f;
-                        }
-                        if (n_pv > 0) {
-#pragma unroll 1
-                            for (int part = 0; part < 2; ++part) {
-                                uint32_t o[32];
-                                tmem_ld32(tm_o + part * 32, o);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                                tmem_st32(tm_o + part * 32, o);
-                            }
-                            tmem_st_wait();
-                        }
-                    }
-                    const float ms = m_run == -INFINITY ? 0.f : m_run;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float e0 = exp2f(__uint_as_float(s[i]) - ms), e1 = exp2f(__uint_as_float(s[i + 1]) - ms);
-                        l_run += e0 + e1;
-                        __nv_bfloat162 v2 = __floats2bfloat162_rn(e0, e1);
-                        pk[i >> 1] = *reinterpret_cast<uint32_t *>(&v2);
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) pk[i] = 0u;
+                    for (int i = 0; i < 16; ++i) x[16 * u + i] = -INFINITY;
                 }
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4 *>(sm + L.p + swz(tid, half * 4 + j)) =
-                        make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
             }
+            // one maximum per row: exchange with the row's other thread; it moves (and the sums are rescaled)
+            // only when it grows by more than 8
+            sts32f(xch_mine, cmax);
+            pair_barrier(quarter);
+            cmax = fmaxf(cmax, lds32f(xch_other));
+            pair_barrier(quarter);  // both have read before the next chunk's exchange overwrites
+            const bool need = cmax > m_run + 8.f || (m_run == -INFINITY && cmax > -INFINITY);
+            if (__any_sync(0xffffffffu, need)) {
+                const float f = need ? ex2(m_run - cmax) : 1.f;
+                if (need) {
+                    m_run = cmax;
+                    l_run *= f;
+                }
+                if (n_pv > 0) {  // this thread rescales its 32 of the row's 64 accumulator columns
+                    uint32_t o[32];
+                    tmem_ld32(tm_o, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    tmem_st32(tm_o, o);
+                    tmem_st_wait();
+                }
+            }
+            const float ms = m_run == -INFINITY ? 0.f : m_run;
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float e0 = ex2(x[i] - ms), e1 = ex2(x[i + 1] - ms);
+                l_run += e0 + e1;
+                __nv_bfloat162 v2 = __floats2bfloat162_rn(e0, e1);
+                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&v2);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                sts128(base + L.p + swz(trow, half * 4 + j), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
             cp_async_wait_all();  // the next chunk's K and V have landed
             fence_async_smem();
             fence_before_sync();
@@ -349,31 +390,32 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
         }
         if (aborted) break;
 
-        // ---- the head's result
-        float acc[kHeadDim];
+        // ---- the head's result: each of the row's two threads finishes 32 of the 64 output columns
+        sts32f(xch_mine, l_run);
+        float acc[32];
         if (n_pv > 0) {
             ok = ok && mbar_wait(bar_pv, n_pv_done & 1u);
             ++n_pv_done;
             fence_after_sync();
+            uint32_t o[32];
+            tmem_ld32(tm_o, o);
+            tmem_ld_wait();
 #pragma unroll
-            for (int part = 0; part < 2; ++part) {
-                uint32_t o[32];
-                tmem_ld32(tm_o + part * 32, o);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[part * 32 + i] = __uint_as_float(o[i]);
-            }
+            for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(o[i]);
         } else {
 #pragma unroll
-            for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
+            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
         }
+        pair_barrier(quarter);
+        const float l_row = l_run + lds32f(xch_other);
+        pair_barrier(quarter);
         if (row >= 0 && ok) {
-            const float m_out = m_run + bias_row;
+            const float m_out = m_run + bias_row;  // bias_row is known to the first of the two threads, which writes lse
             if (slot < 0) {
-                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-                uint4 *dst = reinterpret_cast<uint4 *>(p.o + (static_cast<int64_t>(row) * H + h) * kHeadDim);
+                const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+                uint4 *dst = reinterpret_cast<uint4 *>(p.o + (static_cast<int64_t>(row) * H + h) * kHeadDim + half * 32);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < 4; ++j) {
                     uint32_t w[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -382,12 +424,14 @@ __global__ void __launch_bounds__(kRows) attn_forward_tc5_kernel(const Tc5Params
                     }
                     dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                p.lse[static_cast<int64_t>(row) * H + h] = l_run > 0.f ? (m_out + log2f(l_run)) * kLn2 : -INFINITY;
+                if (half == 0)
+                    p.lse[static_cast<int64_t>(row) * H + h] = l_row > 0.f ? (m_out + log2f(l_row)) * kLn2 : -INFINITY;
             } else {
-                float4 *dst = reinterpret_cast<float4 *>(p.part_o + (static_cast<int64_t>(slot) * H + h) * kHeadDim);
+                float4 *dst = reinterpret_cast<float4 *>(p.part_o + (static_cast<int64_t>(slot) * H + h) * kHeadDim + half * 32);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-                *reinterpret_cast<float2 *>(p.part_ml + (static_cast<int64_t>(slot) * H + h) * 2) = make_float2(m_out, l_run);
+                for (int j = 0; j < 8; ++j) dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+                if (half == 0)
+                    *reinterpret_cast<float2 *>(p.part_ml + (static_cast<int64_t>(slot) * H + h) * 2) = make_float2(m_out, l_row);
             }
         }
     }
@@ -426,8 +470,8 @@ extern "C" int bpt_attn_forward_tc5(const bpt_tile_plan_t *tiles, int64_t n_node
     if (tiles->n_groups == 0) return BPT_OK;
     BPT_CHECK_ARG(tiles->groups && tiles->mblocks && q && k && v && o && lse, "attn_forward_tc5: null array");
     BPT_CHECK_ARG(tiles->max_cols_pad == 0 || (tiles->cols && tiles->et), "attn_forward_tc5: null tile plan arrays");
-    BPT_CHECK_ARG(tiles->max_cols_pad % kTileChunk == 0 && tiles->max_cols_pad <= kMaxMaskBits * kMaskCols &&
-                      tiles->t_max % 8 == 0, "attn_forward_tc5: bad tile plan sizes");
+    BPT_CHECK_ARG(tiles->max_cols_pad % kTileChunk == 0 && tiles->max_cols_pad <= 512 && tiles->t_max % 8 == 0,
+                  "attn_forward_tc5: bad tile plan sizes (groups of at most 512 columns)");
     if (tiles->et_bytes != 1 || (ak != nullptr && tiles->t_max > kMaxTypes))
         return fail(BPT_ERR_UNSUPPORTED, "attn_forward_tc5: needs 8-bit cells and at most %d edge types", kMaxTypes);
     BPT_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
@@ -447,7 +491,6 @@ extern "C" int bpt_attn_forward_tc5(const bpt_tile_plan_t *tiles, int64_t n_node
     p.v = static_cast<const __nv_bfloat16 *>(v); p.ak = static_cast<const __nv_bfloat16 *>(ak);
     p.o = static_cast<__nv_bfloat16 *>(o);
     p.lse = lse; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
-    p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = tiles->max_cols_pad;
     const bool bias = ak != nullptr;
     // at least one table column group even when no m-block needs the table, so that the layout is one
     p.tq16 = bias ? ((tiles->t_max > 0 ? tiles->t_max : 8) + 15) / 16 * 16 : 0;
@@ -458,11 +501,11 @@ extern "C" int bpt_attn_forward_tc5(const bpt_tile_plan_t *tiles, int64_t n_node
     if (bias) {
         BPT_CUDA(cudaFuncSetAttribute(attn_forward_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
-        attn_forward_tc5_kernel<true><<<static_cast<unsigned>(tiles->n_groups), kRows, smem, stream>>>(p);
+        attn_forward_tc5_kernel<true><<<static_cast<unsigned>(tiles->n_groups), kThreads, smem, stream>>>(p);
     } else {
         BPT_CUDA(cudaFuncSetAttribute(attn_forward_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
-        attn_forward_tc5_kernel<false><<<static_cast<unsigned>(tiles->n_groups), kRows, smem, stream>>>(p);
+        attn_forward_tc5_kernel<false><<<static_cast<unsigned>(tiles->n_groups), kThreads, smem, stream>>>(p);
     }
     BPT_LAUNCH_CHECK();
     if (tiles->n_split > 0) {

@@ -73,6 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
             : "r"(bar), "r"(parity)
             : "memory");
         if (done) return true;
+        __nanosleep(40);  // waiting warps leave the issue slots to the warps that have work
         if (clock64() - start > limit_cycles) return false;
     }
 }

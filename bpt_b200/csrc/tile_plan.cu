@@ -119,7 +119,7 @@ void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr,
             const size_t base = plan.et.size();
             plan.et.resize(base + static_cast<size_t>(n_chunks) * kTileRows * kTileChunk, kNoEdge);
             plan.cellpos.resize(plan.et.size(), -1);
-            uint32_t mask = 0;
+            uint32_t mask = 0, fine = 0;
             int max_et = -1;
             size_t p = 0;
             for (int r = 0; r < nr; ++r) {
@@ -132,6 +132,7 @@ void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr,
                     plan.et[cell] = static_cast<uint16_t>(e.etype);
                     plan.cellpos[cell] = e.pos;
                     mask |= 1u << (c / kMaskCols);
+                    if (c < 512) fine |= 1u << (c / 16);
                     if (e.etype > max_et) max_et = e.etype;
                     ++cnt;
                     ++p;
@@ -139,6 +140,7 @@ void emit_group(HostTilePlan &plan, const GroupBuild &gb, const int32_t *indptr,
                 if (cnt != indptr[mb.rows[r] + 1] - indptr[mb.rows[r]]) partials.push_back({mb.rows[r], midx, r});
             }
             m[kMbChunkMask] = static_cast<int32_t>(mask);
+            m[kMbFineMask] = ncols_pad <= 512 ? static_cast<int32_t>(fine) : 0;
             m[kMbTq] = (max_et + 1 + 7) / 8 * 8;
             m[kMbQrSlot] = uniform ? -1 : n_qr++;
             if (!uniform && m[kMbTq] > plan.t_max) plan.t_max = m[kMbTq];

@@ -32,6 +32,8 @@ constexpr int kMbRowEtOff = 32;    // [32,48): the row's single edge type when k
 constexpr int kMbEtOff = 48;       // offset (in cells) of the [chunks][16][64] edge-type matrix in `et`
 constexpr int kMbChunkMask = 49;   // bit s set = some row has an edge in columns [32 s, 32 s + 32)
 constexpr int kMbTq = 50;          // edge types [0, tq) occur (multiple of 8)
+constexpr int kMbFineMask = 52;    // bit s set = some row has an edge in columns [16 s, 16 s + 16); meaningful for groups of
+                                   // at most 512 columns (the tcgen05 kernels' plans), 0 beyond
 constexpr int kMbQrSlot = 51;      // >= 0: needs the per-row relative-position table, in this shared-memory
                                    // slot; -1: every row's edges share one type, so the term is a per-row
                                    // constant that cancels in the softmax and only shifts lse

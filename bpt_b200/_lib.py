@@ -49,9 +49,10 @@ SIGNATURES = {
     "bpt_attn_plan_build": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp, _sz, _vp, _vp]),
     "bpt_attn_workspace_bytes": (_sz, [_i64, _i64, _vp, _int, _int, _int]),
     "bpt_attn_forward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
-                                _int, _int, _int, _vp, _sz, _vp]),
+                                _int, _int, _int, _vp, _sz, _vp, _vp]),
     "bpt_attn_backward": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
-                                 _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+                                 _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp, _vp]),
+    "bpt_attn_dropout_mask": (_int, [_vp, _vp, _i64, _int, _vp, _vp, _vp]),
     "bpt_tile_plan_create": (_vp, [_vp, _vp, _vp, _vp, _i64, _i64, _dbl, _int, _int, _int, _int, _int, _int]),
     "bpt_tile_plan_sizes": (_int, [_vp, _vp]),
     "bpt_tile_plan_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
@@ -64,10 +65,10 @@ SIGNATURES = {
     "bpt_attn_forward_tc_workspace_bytes": (_sz, [_i64, _int]),
     "bpt_attn_forward_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp, _vp,
                                    _i64, _i64, _int, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _dbl, _vp,
-                                   _vp, _int, _int, _int, _vp, _sz, _vp]),
+                                   _vp, _int, _int, _int, _vp, _sz, _vp, _vp]),
     "bpt_attn_backward_tc_workspace_bytes": (_sz, [_vp, _vp, _vp, _i64, _i64, _int]),
     "bpt_attn_backward_tc": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp,
-                                    _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
+                                    _vp, _vp, _vp, _vp, _int, _int, _int, _vp, _sz, _vp, _vp]),
     "bpt_attn_forward_tc5_smem_bytes": (_sz, [_int, _int]),
     "bpt_attn_forward_tc5_workspace_bytes": (_sz, [_i64, _int]),
     "bpt_attn_forward_tc5": (_int, [_vp, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
@@ -75,6 +76,22 @@ SIGNATURES = {
     "bpt_attn_forward_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp,
                                        _int, _int, _int, _vp]),
 }
+
+class DropoutStruct(ctypes.Structure):
+    """bpt_dropout_t of include/bpt_b200.h."""
+    _fields_ = [("rate", ctypes.c_double), ("seed", ctypes.c_uint64)]
+
+
+def dropout_arg(dropout):
+    """dropout: None or (rate, seed).  Returns (keep-alive object, pointer value or None) for a bpt_dropout_t*."""
+    if dropout is None or dropout[0] == 0:
+        return None, None
+    rate, seed = float(dropout[0]), int(dropout[1]) & 0xFFFFFFFFFFFFFFFF
+    if not 0.0 <= rate < 1.0:
+        raise RuntimeError("bpt_b200: dropout rate must be in [0, 1)")
+    s = DropoutStruct(rate, seed)
+    return s, ctypes.addressof(s)
+
 
 class TilePlanStruct(ctypes.Structure):
     """bpt_tile_plan_t of include/bpt_b200.h."""

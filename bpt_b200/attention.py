@@ -221,9 +221,10 @@ def tensor_core_eligible(q, embed_ak, plan=None):
     return 0 < need <= MAX_BLOCK_SMEM
 
 
-def attention_forward_tc(plan, q, k, v, embed_ak, scale):
+def attention_forward_tc(plan, q, k, v, embed_ak, scale, dropout=None):
     """Forward through bpt_attn_forward_tc (bf16, head dim 64). Returns (o, lse)."""
     N, h, d = _check_inputs(plan, q, k, v, embed_ak)
+    drop_keep, drop_ptr = _lib.dropout_arg(dropout)
     tp = plan.tile_plan()
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
@@ -235,7 +236,7 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale):
             plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes, plan.n_edges, tp.max_cols_pad,
             tp.t_max, tp.max_mblocks, tp.max_qr_slots, tp.n_etypes, q.data_ptr(), k.data_ptr(), v.data_ptr(),
             _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d, _lib.dtype_code(q.dtype),
-            ws.data_ptr(), ws.numel(), _lib.stream()))
+            ws.data_ptr(), ws.numel(), drop_ptr, _lib.stream()))
     return o, lse
 
 
@@ -289,16 +290,19 @@ def tc5_status(plan, h):
 FORWARD_IMPL = os.environ.get("BPT_FORWARD_IMPL", "tile")
 
 
-def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
+def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None, dropout=None):
     """Returns (o, lse). q, k, v: (N, h, d) contiguous CUDA tensors of one dtype.
-    bf16 with head dim 64 runs on the tensor-core kernel unless tensor_cores=False."""
+    bf16 with head dim 64 runs on the tensor-core kernel unless tensor_cores=False.
+    dropout: None or (rate, seed) -- dropout on the attention weights (modules/attention.py:73); the same
+    pair must be given to attention_backward."""
     N, h, d = _check_inputs(plan, q, k, v, embed_ak)
     if tensor_cores is None:
         tensor_cores = tensor_core_eligible(q, embed_ak, plan)
+    drop_keep, drop_ptr = _lib.dropout_arg(dropout)
     if tensor_cores:
-        if FORWARD_IMPL == "tc5" and tc5_eligible(q, embed_ak, plan):
+        if FORWARD_IMPL == "tc5" and drop_ptr is None and tc5_eligible(q, embed_ak, plan):
             return attention_forward_tc5(plan, q, k, v, embed_ak, scale)
-        return attention_forward_tc(plan, q, k, v, embed_ak, scale)
+        return attention_forward_tc(plan, q, k, v, embed_ak, scale, dropout)
     o = torch.empty_like(q)
     lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
@@ -306,7 +310,7 @@ def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None):
         _lib.check(_lib.lib().bpt_attn_forward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                                _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(),
                                                h, d, _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(),
-                                               _lib.stream()))
+                                               drop_ptr, _lib.stream()))
     return o, lse
 
 
@@ -335,7 +339,7 @@ def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=N
     return o, lse
 
 
-def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_cores=None):
+def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_cores=None, dropout=None):
     """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d).
     bf16 with head dim 64 runs on the tensor-core kernels when the forward's output `o` is given
     (they take delta = <dO, O> from it) unless tensor_cores=False."""
@@ -349,6 +353,7 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
     if tensor_cores is None:
         tensor_cores = o is not None and tensor_core_eligible(q, embed_ak, plan)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    drop_keep, drop_ptr = _lib.dropout_arg(dropout)
     dak = None
     if embed_ak is not None:
         dak = torch.zeros((embed_ak.size(0), d), dtype=torch.float32, device=q.device)
@@ -369,24 +374,25 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
                 ctypes.addressof(dst_tiles), ctypes.addressof(src_tiles), *plan._args(), q.data_ptr(), k.data_ptr(),
                 v.data_ptr(), _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), d_o.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(dak), h, d, _lib.dtype_code(q.dtype),
-                ws.data_ptr(), ws.numel(), _lib.stream()))
+                ws.data_ptr(), ws.numel(), drop_ptr, _lib.stream()))
         else:
             ws = plan.workspace(h, d, True)
             _lib.check(L.bpt_attn_backward(*plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                            _lib.ptr(embed_ak), float(scale), lse.data_ptr(), d_o.data_ptr(),
                                            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.ptr(dak), h, d,
-                                           _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), _lib.stream()))
+                                           _lib.dtype_code(q.dtype), ws.data_ptr(), ws.numel(), drop_ptr,
+                                           _lib.stream()))
     return dq, dk, dv, dak
 
 
 class _BPTAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, plan, q, k, v, embed_ak, scale):
+    def forward(ctx, plan, q, k, v, embed_ak, scale, dropout):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         if embed_ak is not None:
             embed_ak = embed_ak.contiguous()
-        o, lse = attention_forward(plan, q, k, v, embed_ak, scale)
-        ctx.plan, ctx.scale = plan, scale
+        o, lse = attention_forward(plan, q, k, v, embed_ak, scale, dropout=dropout)
+        ctx.plan, ctx.scale, ctx.dropout = plan, scale, dropout
         ctx.has_ak = embed_ak is not None
         ctx.save_for_backward(q, k, v, embed_ak if ctx.has_ak else q.new_empty(0), lse, o)
         return o
@@ -395,13 +401,34 @@ class _BPTAttention(torch.autograd.Function):
     def backward(ctx, d_o):
         q, k, v, ak, lse, o = ctx.saved_tensors
         ak = ak if ctx.has_ak else None
-        dq, dk, dv, dak = attention_backward(ctx.plan, q, k, v, ak, ctx.scale, lse, d_o, o=o)
-        return None, dq, dk, dv, (dak.to(ak.dtype) if dak is not None else None), None
+        dq, dk, dv, dak = attention_backward(ctx.plan, q, k, v, ak, ctx.scale, lse, d_o, o=o, dropout=ctx.dropout)
+        return None, dq, dk, dv, (dak.to(ak.dtype) if dak is not None else None), None, None
 
 
-def bpt_attention(plan, q, k, v, embed_ak=None, scale=None):
-    """o[i,h] = sum over i's incoming edges e of softmax_e(scale * <q[i,h], k[src_e,h] +
-    embed_ak[etype_e]>) * v[src_e,h].  scale defaults to 1/sqrt(d) (modules/attention.py:73)."""
+def bpt_attention(plan, q, k, v, embed_ak=None, scale=None, dropout_p=0.0, seed=None):
+    """o[i,h] = sum over i's incoming edges e of drop(softmax_e(scale * <q[i,h], k[src_e,h] +
+    embed_ak[etype_e]>)) * v[src_e,h].  scale defaults to 1/sqrt(d) (modules/attention.py:73).
+    dropout_p > 0 zeroes each attention weight with that probability and scales the rest by
+    1 / (1 - dropout_p), as the reference's drop_att does between sparse_softmax and vec_spmm; the mask
+    is regenerated in the backward from `seed` (drawn from torch's generator when not given)."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.size(-1))
-    return _BPTAttention.apply(plan, q, k, v, embed_ak, scale)
+    dropout = None
+    if dropout_p:
+        if seed is None:
+            seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+        dropout = (float(dropout_p), int(seed))
+    return _BPTAttention.apply(plan, q, k, v, embed_ak, scale, dropout)
+
+
+def dropout_mask(plan_src, plan_dst, h, dropout_p, seed):
+    """The (E, h) bool mask (True = kept) that bpt_attention(..., dropout_p, seed) applies, for edges given by
+    their int32 source and destination ids in edge-id order."""
+    src, dst = plan_src.to(torch.int32).contiguous(), plan_dst.to(torch.int32).contiguous()
+    _lib.require_cuda(src, dst)
+    out = torch.empty((src.numel(), h), dtype=torch.uint8, device=src.device)
+    keep, ptr_ = _lib.dropout_arg((dropout_p, seed))
+    with torch.cuda.device(src.device):
+        _lib.check(_lib.lib().bpt_attn_dropout_mask(src.data_ptr(), dst.data_ptr(), src.numel(), h, ptr_,
+                                                    out.data_ptr(), _lib.stream()))
+    return out.bool()

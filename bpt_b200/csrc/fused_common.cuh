@@ -8,6 +8,42 @@ namespace bpt {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// Dropout on the attention weights (modules/attention.py:73: drop_att between the edge softmax and the
+// weighted sum).  An edge's weight for one head is kept when a 32-bit hash of (destination, source, head,
+// seed) is at least `threshold` = rate * 2^32, and kept weights are scaled by 1 / (1 - rate).  The mask is a
+// pure function of those four numbers: the forward and every backward kernel regenerate it, nothing is
+// stored.  Parallel edges between one pair of nodes share their bit.  threshold == 0 switches it off.
+struct Dropout {
+    uint32_t seed_lo, seed_hi, threshold;
+    float keep_scale;
+};
+inline Dropout make_dropout(const bpt_dropout_t *d) {
+    Dropout r{0u, 0u, 0u, 1.f};
+    if (d != nullptr && d->rate > 0.0) {
+        const double t = d->rate * 4294967296.0;
+        r.threshold = t >= 4294967295.0 ? 0xFFFFFFFFu : static_cast<uint32_t>(t);
+        r.keep_scale = static_cast<float>(1.0 / (1.0 - d->rate));
+        r.seed_lo = static_cast<uint32_t>(d->seed);
+        r.seed_hi = static_cast<uint32_t>(d->seed >> 32);
+    }
+    return r;
+}
+__host__ __device__ __forceinline__ uint32_t dropout_hash(uint32_t dst, uint32_t src, uint32_t head, uint32_t seed_lo,
+                                                          uint32_t seed_hi) {
+    uint32_t x = (dst * 0x9E3779B1u) ^ ((src + 0x7F4A7C15u) * 0x85EBCA6Bu) ^ ((head + seed_hi) * 0xC2B2AE35u) ^ seed_lo;
+    x ^= x >> 16;
+    x *= 0x7FEB352Du;
+    x ^= x >> 15;
+    x *= 0x846CA68Bu;
+    x ^= x >> 16;
+    return x;
+}
+// The factor an attention weight is multiplied by: 1 / (1 - rate) when kept, 0 when dropped.
+__device__ __forceinline__ float dropout_factor(const Dropout &d, int dst, int src, int head) {
+    return dropout_hash(static_cast<uint32_t>(dst), static_cast<uint32_t>(src), static_cast<uint32_t>(head), d.seed_lo,
+                        d.seed_hi) >= d.threshold ? d.keep_scale : 0.f;
+}
+
 // Head count and head dim of the feature tensors.
 struct Geometry {
     int H, D;
@@ -112,7 +148,7 @@ inline size_t merge_smem_bytes(int H) { return (static_cast<size_t>(kMergeBatch)
 // ({row, begin, end, -1} into the in-CSR arrays); bf16 storage.  Defined in fused_simt.cu.
 int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_src, const int32_t *in_etype,
                               const void *q, const void *k, const void *v, const void *ak, float scale,
-                              void *o, float *lse, int H, int D, cudaStream_t stream);
+                              void *o, float *lse, int H, int D, const Dropout &drop, cudaStream_t stream);
 
 
 struct PlanView;

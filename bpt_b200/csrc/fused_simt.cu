@@ -97,7 +97,7 @@ attn_forward_kernel(const int4 *__restrict__ items, int n_items, const int32_t *
                     const int32_t *__restrict__ in_etype, const T *__restrict__ q,
                     const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ ak,
                     float scale, T *__restrict__ o, float *__restrict__ lse,
-                    float *__restrict__ part_o, float *__restrict__ part_ml, Geometry g) {
+                    float *__restrict__ part_o, float *__restrict__ part_ml, Geometry g, Dropout drop) {
     constexpr int HPW = 32 / LPH;
     __shared__ float s_all[kWarpsPerBlock][kSegEdges * HPW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -167,7 +167,8 @@ attn_forward_kernel(const int4 *__restrict__ items, int n_items, const int32_t *
         #pragma unroll 4
         for (int j = 0; j < n; ++j) {
             const int src = in_src[beg + j];
-            const float p = sc[j * HPW + hl];
+            float p = sc[j * HPW + hl];
+            if (drop.threshold) p *= dropout_factor(drop, row, src, head);  // the sum l keeps every weight
             float vf[16];
             load16<T, kVec>(v + (static_cast<int64_t>(src) * H + head) * D + d0, nvalid, vf);
 #pragma unroll
@@ -209,7 +210,7 @@ attn_backward_dq_kernel(const int4 *__restrict__ items, int n_items, const int32
                         float scale, const float *__restrict__ lse, const T *__restrict__ d_o,
                         float *__restrict__ P, float *__restrict__ dP, float *__restrict__ delta_out,
                         T *__restrict__ dq, float *__restrict__ part_ab, float *__restrict__ part_delta,
-                        Geometry g) {
+                        Geometry g, Dropout drop) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * kWarpsPerBlock + warp;
@@ -262,6 +263,8 @@ attn_backward_dq_kernel(const int4 *__restrict__ items, int n_items, const int32
         s = group_sum<LPH>(s);
         dp = group_sum<LPH>(dp);
         if (active) {
+            // with dropout o = sum p' v, p' = mask * p / (1 - rate): the gradient of p is that of p' times the same factor
+            if (drop.threshold) dp *= dropout_factor(drop, row, src, head);
             const float p = exp2f(s - lse2);
             const float pdp = p * dp;
             delta += pdp;
@@ -323,7 +326,8 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
                          const int32_t *__restrict__ out_inpos, const T *__restrict__ q,
                          const T *__restrict__ d_o, const float *__restrict__ P,
                          const float *__restrict__ dP, const float *__restrict__ delta, float scale,
-                         T *__restrict__ dk, T *__restrict__ dv, float *__restrict__ part_dkv, Geometry g) {
+                         T *__restrict__ dk, T *__restrict__ dv, float *__restrict__ part_dkv, Geometry g,
+                         Dropout drop) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * kWarpsPerBlock + warp;
@@ -347,6 +351,7 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
         const int64_t pos = out_inpos[j];
         const float p = P[pos * H + head];
         const float ds = scale * p * (dP[pos * H + head] - delta[static_cast<int64_t>(dst) * H + head]);
+        const float pv = drop.threshold ? p * dropout_factor(drop, dst, row, head) : p;  // the weight V was summed with
         const int64_t dst_off = (static_cast<int64_t>(dst) * H + head) * D + d0;
         float qf[16], dof[16];
         load16<T, kVec>(q + dst_off, nvalid, qf);
@@ -354,7 +359,7 @@ attn_backward_dkv_kernel(const int4 *__restrict__ items, int n_items, const int3
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             dkf[i] = fmaf(ds, qf[i], dkf[i]);
-            dvf[i] = fmaf(p, dof[i], dvf[i]);
+            dvf[i] = fmaf(pv, dof[i], dvf[i]);
         }
     }
     const int64_t row_off = (static_cast<int64_t>(row) * H + head) * D + d0;
@@ -562,7 +567,7 @@ bool can_vectorise(int D, int lph, const void *a, const void *b, const void *c, 
 template <typename T>
 int forward_impl(const PlanView &p, const int32_t *counts, const void *q_, const void *k_, const void *v_,
                  const void *ak_, float scale, void *o_, float *lse, int H, int D, void *ws_ptr,
-                 size_t ws_bytes, cudaStream_t stream) {
+                 size_t ws_bytes, const Dropout &drop, cudaStream_t stream) {
     const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
     const T *ak = static_cast<const T *>(ak_);
     T *o = static_cast<T *>(o_);
@@ -579,7 +584,7 @@ int forward_impl(const PlanView &p, const int32_t *counts, const void *q_, const
     const int hpw = 32 / lph;
     const dim3 grid((n_items + kWarpsPerBlock - 1) / kWarpsPerBlock, (H + hpw - 1) / hpw);
     BPT_DISPATCH_LPH_VEC(lph, vec, (attn_forward_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-        p.in_work.items, n_items, p.in_src, p.in_etype, q, k, v, ak, scale, o, lse, part_o, part_ml, g)));
+        p.in_work.items, n_items, p.in_src, p.in_etype, q, k, v, ak, scale, o, lse, part_o, part_ml, g, drop)));
     BPT_LAUNCH_CHECK();
     if (n_split > 0) {
         attn_forward_merge_kernel<T><<<n_split, merge_threads(H, D), merge_smem_bytes(H), stream>>>(
@@ -593,7 +598,7 @@ template <typename T>
 int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, const void *k_, const void *v_,
                   const void *ak_, float scale, const float *lse, const void *do_,
                   void *dq_, void *dk_, void *dv_, float *dak, int H, int D, void *ws_ptr, size_t ws_bytes,
-                  cudaStream_t stream) {
+                  const Dropout &drop, cudaStream_t stream) {
     const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
     const T *ak = static_cast<const T *>(ak_), *d_o = static_cast<const T *>(do_);
     T *dq = static_cast<T *>(dq_), *dk = static_cast<T *>(dk_), *dv = static_cast<T *>(dv_);
@@ -616,7 +621,7 @@ int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, cons
         const dim3 grid((counts[0] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
             p.in_work.items, counts[0], p.in_src, p.in_etype, q, k, v, ak, scale, lse, d_o, P, dP, delta, dq,
-            part_ab, part_delta, g)));
+            part_ab, part_delta, g, drop)));
         BPT_LAUNCH_CHECK();
         if (counts[2] > 0) {
             attn_backward_dq_merge_kernel<T><<<counts[2], 256, 0, stream>>>(
@@ -627,7 +632,7 @@ int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, cons
     if (counts[3] > 0 && dk != nullptr && dv != nullptr) {
         const dim3 grid((counts[3] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
         BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dkv_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-            p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dP, delta, scale, dk, dv, part_dkv, g)));
+            p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dP, delta, scale, dk, dv, part_dkv, g, drop)));
         BPT_LAUNCH_CHECK();
         if (counts[5] > 0) {
             sum_merge_kernel<T><<<counts[5], 256, 0, stream>>>(p.out_work.split_rows, counts[5], part_dkv, H * D,
@@ -653,7 +658,7 @@ int backward_impl(const PlanView &p, const int32_t *counts, const void *q_, cons
 
 int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_src, const int32_t *in_etype,
                               const void *q_, const void *k_, const void *v_, const void *ak_, float scale,
-                              void *o_, float *lse, int H, int D, cudaStream_t stream) {
+                              void *o_, float *lse, int H, int D, const Dropout &drop, cudaStream_t stream) {
     using T = __nv_bfloat16;
     if (n_items == 0) return BPT_OK;
     const T *q = static_cast<const T *>(q_), *k = static_cast<const T *>(k_), *v = static_cast<const T *>(v_);
@@ -665,7 +670,7 @@ int launch_forward_items_bf16(const int4 *items, int n_items, const int32_t *in_
     const int hpw = 32 / lph;
     const dim3 grid((n_items + kWarpsPerBlock - 1) / kWarpsPerBlock, (H + hpw - 1) / hpw);
     BPT_DISPATCH_LPH_VEC(lph, vec, (attn_forward_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-        items, n_items, in_src, in_etype, q, k, v, ak, scale, o, lse, nullptr, nullptr, g)));
+        items, n_items, in_src, in_etype, q, k, v, ak, scale, o, lse, nullptr, nullptr, g, drop)));
     BPT_LAUNCH_CHECK();
     return BPT_OK;
 }
@@ -706,6 +711,11 @@ int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, cons
 
 namespace {
 
+int check_dropout(const char *name, const bpt_dropout_t *d) {
+    BPT_CHECK_ARG(d == nullptr || (d->rate >= 0.0 && d->rate < 1.0), "%s: dropout rate must be in [0, 1)", name);
+    return BPT_OK;
+}
+
 int check_attn_args(const char *name, const void *plan, const int32_t *counts, int64_t n_nodes,
                     int64_t n_edges, int n_etypes, int H, int D, int dtype) {
     BPT_CHECK_ARG(plan != nullptr && counts != nullptr, "%s: null plan", name);
@@ -731,14 +741,16 @@ extern "C" size_t bpt_attn_workspace_bytes(int64_t n_nodes, int64_t n_edges, con
 extern "C" int bpt_attn_forward(const void *plan, const int32_t *counts, int64_t n_nodes, int64_t n_edges,
                                 int n_etypes, const void *q, const void *k, const void *v, const void *ak,
                                 double scale, void *o, float *lse, int h, int d, int dtype, void *workspace,
-                                size_t workspace_bytes, bpt_stream_t stream) {
+                                size_t workspace_bytes, const bpt_dropout_t *dropout, bpt_stream_t stream) {
+    if (int rc = check_dropout("attn_forward", dropout)) return rc;
+    const Dropout drop = make_dropout(dropout);
     if (int rc = check_attn_args("attn_forward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
     BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && o && lse), "attn_forward: null tensor");
     const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts[kCountsNSrc], n_edges, n_etypes);
     switch (dtype) {
-        case BPT_F32: return forward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
-        case BPT_BF16: return forward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
-        case BPT_F16: return forward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_F32: return forward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, drop, as_stream(stream));
+        case BPT_BF16: return forward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, drop, as_stream(stream));
+        case BPT_F16: return forward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), o, lse, h, d, workspace, workspace_bytes, drop, as_stream(stream));
         default: return fail(BPT_ERR_UNSUPPORTED, "attn_forward: unknown dtype code %d", dtype);
     }
 }
@@ -747,16 +759,18 @@ extern "C" int bpt_attn_backward(const void *plan, const int32_t *counts, int64_
                                  int n_etypes, const void *q, const void *k, const void *v, const void *ak,
                                  double scale, const float *lse, const void *d_o, void *dq,
                                  void *dk, void *dv, float *dak, int h, int d, int dtype, void *workspace,
-                                 size_t workspace_bytes, bpt_stream_t stream) {
+                                 size_t workspace_bytes, const bpt_dropout_t *dropout, bpt_stream_t stream) {
+    if (int rc = check_dropout("attn_backward", dropout)) return rc;
+    const Dropout drop = make_dropout(dropout);
     if (int rc = check_attn_args("attn_backward", plan, counts, n_nodes, n_edges, n_etypes, h, d, dtype)) return rc;
     BPT_CHECK_ARG(n_nodes == 0 || (q && k && v && lse && d_o && dq), "attn_backward: null tensor");
     BPT_CHECK_ARG((dk == nullptr) == (dv == nullptr), "attn_backward: dk and dv must both be given or both be NULL");
     BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward: ak given without dak");
     const PlanView p = plan_view(const_cast<void *>(plan), n_nodes, counts[kCountsNSrc], n_edges, n_etypes);
     switch (dtype) {
-        case BPT_F32: return backward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
-        case BPT_BF16: return backward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
-        case BPT_F16: return backward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, as_stream(stream));
+        case BPT_F32: return backward_impl<float>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, drop, as_stream(stream));
+        case BPT_BF16: return backward_impl<__nv_bfloat16>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, drop, as_stream(stream));
+        case BPT_F16: return backward_impl<__half>(p, counts, q, k, v, ak, static_cast<float>(scale), lse, d_o, dq, dk, dv, dak, h, d, workspace, workspace_bytes, drop, as_stream(stream));
         default: return fail(BPT_ERR_UNSUPPORTED, "attn_backward: unknown dtype code %d", dtype);
     }
 }
@@ -778,5 +792,31 @@ extern "C" int bpt_attn_forward_static(const void *plan, const int32_t *counts, 
     void *scratch = nullptr;
     if (int rc = static_scratch_address(&scratch)) return rc;
     return bpt_attn_forward(plan, counts, n_nodes, n_edges, n_etypes, q, k, v, ak, scale, o, lse, h, d, dtype,
-                            scratch, kStaticScratchBytes, stream);
+                            scratch, kStaticScratchBytes, nullptr, stream);
+}
+
+namespace bpt {
+namespace {
+__global__ void dropout_mask_kernel(const int32_t *__restrict__ src, const int32_t *__restrict__ dst, int64_t n_edges,
+                                    int H, Dropout drop, uint8_t *__restrict__ mask) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i >= n_edges * H) return;
+    const int64_t e = i / H;
+    const int head = static_cast<int>(i % H);
+    mask[i] = !drop.threshold || dropout_factor(drop, dst[e], src[e], head) != 0.f;
+}
+}  // namespace
+}  // namespace bpt
+
+extern "C" int bpt_attn_dropout_mask(const int32_t *src, const int32_t *dst, int64_t n_edges, int h,
+                                     const bpt_dropout_t *dropout, uint8_t *mask, bpt_stream_t stream) {
+    BPT_CHECK_ARG(n_edges >= 0 && h >= 1, "attn_dropout_mask: bad sizes");
+    if (int rc = check_dropout("attn_dropout_mask", dropout)) return rc;
+    if (n_edges == 0) return BPT_OK;
+    BPT_CHECK_ARG(src && dst && mask, "attn_dropout_mask: null array");
+    const int64_t n = n_edges * h;
+    dropout_mask_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, as_stream(stream)>>>(src, dst, n_edges, h,
+                                                                                            make_dropout(dropout), mask);
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
 }

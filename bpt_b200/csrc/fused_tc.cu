@@ -117,9 +117,10 @@ struct TcParams {
     int n_etypes, H, max_cols_pad, t_max;
     int64_t n_groups;
     float scale;
+    Dropout drop;
 };
 
-template <typename ET, bool kHasBias>
+template <typename ET, bool kHasBias, bool kDrop>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 attn_forward_tile_kernel(const TcParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -372,6 +373,16 @@ attn_forward_tile_kernel(const TcParams p) {
                     l_lo += s[nt][0] + s[nt][1];
                     l_hi += s[nt][2] + s[nt][3];
                 }
+                if (kDrop) {  // the row sums keep every weight; the weights that multiply V are masked and rescaled
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        const int src0 = s_cols[c0 + nt * 8 + 2 * t], src1 = s_cols[c0 + nt * 8 + 2 * t + 1];
+                        s[nt][0] *= dropout_factor(p.drop, row_lo, src0, h);
+                        s[nt][1] *= dropout_factor(p.drop, row_lo, src1, h);
+                        s[nt][2] *= dropout_factor(p.drop, row_hi, src0, h);
+                        s[nt][3] *= dropout_factor(p.drop, row_hi, src1, h);
+                    }
+                }
                 // O += P V
                 cp_async_wait<1>();  // V of this step has landed (the newest group is the next K)
                 __syncwarp();
@@ -440,14 +451,19 @@ size_t tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
            static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2 + static_cast<size_t>(t_max) * kRowBytes;
 }
 
-template <typename ET, bool kHasBias>
-int launch_tile_kernel(const TcParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
-    BPT_CUDA(cudaFuncSetAttribute(attn_forward_tile_kernel<ET, kHasBias>,
+template <typename ET, bool kHasBias, bool kDrop>
+int launch_tile_kernel_d(const TcParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
+    BPT_CUDA(cudaFuncSetAttribute(attn_forward_tile_kernel<ET, kHasBias, kDrop>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attn_forward_tile_kernel<ET, kHasBias><<<static_cast<unsigned>((n_groups + kTilesPerBlock - 1) / kTilesPerBlock),
-                                             kWarps * 32, smem, stream>>>(p);
+    attn_forward_tile_kernel<ET, kHasBias, kDrop><<<static_cast<unsigned>((n_groups + kTilesPerBlock - 1) / kTilesPerBlock),
+                                                    kWarps * 32, smem, stream>>>(p);
     BPT_LAUNCH_CHECK();
     return BPT_OK;
+}
+template <typename ET, bool kHasBias>
+int launch_tile_kernel(const TcParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
+    return p.drop.threshold ? launch_tile_kernel_d<ET, kHasBias, true>(p, n_groups, smem, stream)
+                            : launch_tile_kernel_d<ET, kHasBias, false>(p, n_groups, smem, stream);
 }
 
 }  // namespace
@@ -474,7 +490,10 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
                                    int max_mblocks, int max_qr_slots, int n_etypes, const void *q,
                                    const void *k, const void *v, const void *ak, double scale, void *o,
                                    float *lse, int h, int d, int dtype, void *workspace,
-                                   size_t workspace_bytes, bpt_stream_t stream_) {
+                                   size_t workspace_bytes, const bpt_dropout_t *dropout, bpt_stream_t stream_) {
+    BPT_CHECK_ARG(dropout == nullptr || (dropout->rate >= 0.0 && dropout->rate < 1.0),
+                  "attn_forward_tc: dropout rate must be in [0, 1)");
+    const Dropout drop = make_dropout(dropout);
     BPT_CHECK_ARG(n_groups >= 0 && n_split >= 0 && n_slots >= 0 && n_row_items >= 0 && h >= 1,
                   "attn_forward_tc: bad sizes");
     if (d != kHeadDim || dtype != BPT_BF16)
@@ -503,7 +522,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
         const PlanView pv = plan_view(const_cast<void *>(attn_plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
         if (int rc = launch_forward_items_bf16(reinterpret_cast<const int4 *>(row_items), static_cast<int>(n_row_items),
                                                pv.in_src, pv.in_etype, q, k, v, ak, static_cast<float>(scale), o, lse,
-                                               h, d, stream))
+                                               h, d, drop, stream))
             return rc;
     }
     if (n_groups > 0) {
@@ -518,6 +537,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
         p.t_max = bias ? t_max : 0;
         p.scale = static_cast<float>(scale);
         p.n_groups = n_groups;
+        p.drop = drop;
         if (et_bytes == 1 && p.t_max > kMaxTypes8)
             return fail(BPT_ERR_INVALID, "attn_forward_tc: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
         const size_t smem = tc_smem_bytes(max_cols_pad, p.t_max, et_bytes);

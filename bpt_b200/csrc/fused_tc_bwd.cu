@@ -292,9 +292,10 @@ struct DqParams {
     int n_etypes, H, max_cols_pad, t_max;
     int64_t n_groups;
     float scale;
+    Dropout drop;
 };
 
-template <typename ET, bool kHasBias>
+template <typename ET, bool kHasBias, bool kDrop>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 attn_backward_dq_tile_kernel(const DqParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -552,11 +553,21 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                                           __half2float(s_tab[(g + 8) * tab_stride + i_hi0]),
                                           __half2float(s_tab[(g + 8) * tab_stride + i_hi1])};
                     const int pos[4] = {pos4.x, pos4.y, pos4.z, pos4.w};
+                    float keep[4] = {1.f, 1.f, 1.f, 1.f};
+                    if (kDrop) {  // the factor the forward multiplied this weight by before summing V
+                        const int src0 = s_cols[c], src1 = s_cols[c + 1];
+                        keep[0] = dropout_factor(p.drop, row_lo, src0, h);
+                        keep[1] = dropout_factor(p.drop, row_lo, src1, h);
+                        keep[2] = dropout_factor(p.drop, row_hi, src0, h);
+                        keep[3] = dropout_factor(p.drop, row_hi, src1, h);
+                    }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
-                        s[nt][i] = p.scale * pr * (dp[nt][i] - (i < 2 ? delta_lo : delta_hi));
-                        if (pos[i] >= 0) ps_h[pos[i]] = pack_bf16(pr, s[nt][i]);
+                        // dS = scale * p * (dp - delta) with dp the gradient of p, i.e. keep * <dO, v>; the source
+                        // side needs the weight V was summed with, keep * p
+                        s[nt][i] = p.scale * pr * (dp[nt][i] * keep[i] - (i < 2 ? delta_lo : delta_hi));
+                        if (pos[i] >= 0) ps_h[pos[i]] = pack_bf16(pr * keep[i], s[nt][i]);
                     }
                 }
                 // dQ += dS K
@@ -753,14 +764,19 @@ int run_dkv(const bpt_tile_plan_t *tp, const uint32_t *PS, int64_t n_edges, cons
     return BPT_OK;
 }
 
-template <typename ET, bool kHasBias>
-int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
-    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dq_tile_kernel<ET, kHasBias>,
+template <typename ET, bool kHasBias, bool kDrop>
+int launch_dq_kernel_d(const DqParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
+    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dq_tile_kernel<ET, kHasBias, kDrop>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attn_backward_dq_tile_kernel<ET, kHasBias><<<static_cast<unsigned>((n_groups + kTilesPerBlock - 1) / kTilesPerBlock),
-                                                 kWarps * 32, smem, stream>>>(p);
+    attn_backward_dq_tile_kernel<ET, kHasBias, kDrop><<<static_cast<unsigned>((n_groups + kTilesPerBlock - 1) / kTilesPerBlock),
+                                                        kWarps * 32, smem, stream>>>(p);
     BPT_LAUNCH_CHECK();
     return BPT_OK;
+}
+template <typename ET, bool kHasBias>
+int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
+    return p.drop.threshold ? launch_dq_kernel_d<ET, kHasBias, true>(p, n_groups, smem, stream)
+                            : launch_dq_kernel_d<ET, kHasBias, false>(p, n_groups, smem, stream);
 }
 
 }  // namespace
@@ -790,7 +806,10 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
                                     int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
                                     const void *ak, double scale, const void *o, const float *lse, const void *d_o,
                                     void *dq, void *dk, void *dv, float *dak, int h, int d, int dtype,
-                                    void *workspace, size_t workspace_bytes, bpt_stream_t stream_) {
+                                    void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout,
+                                    bpt_stream_t stream_) {
+    BPT_CHECK_ARG(dropout == nullptr || (dropout->rate >= 0.0 && dropout->rate < 1.0),
+                  "attn_backward_tc: dropout rate must be in [0, 1)");
     if (d != kHeadDim || dtype != BPT_BF16)
         return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: only bf16 with head dim 64 (got dtype %d, d %d)", dtype, d);
     if (int rc = check_tile_plan("attn_backward_tc", dst_tiles, true, true)) return rc;
@@ -832,6 +851,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         p.t_max = bias ? dst_tiles->t_max : 0;
         p.scale = sc;
         p.n_groups = dst_tiles->n_groups;
+        p.drop = make_dropout(dropout);
         if (dst_tiles->et_bytes == 1 && p.t_max > kMaxTypes8)
             return fail(BPT_ERR_INVALID, "attn_backward_tc: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
         const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes +

@@ -86,9 +86,7 @@ class BPTBlock(nn.Module):
 
     def __init__(self, dim_model, h, dim_ff, rel_pos=False, drop_h=0.1, drop_a=0.0, activation="relu"):
         super().__init__()
-        if drop_a != 0.0:
-            raise ValueError("dropout on attention weights is not available in the fused call; "
-                             "use bpt_b200.op (the operator chain) for drop_a > 0")
+        self.drop_a = float(drop_a)  # dropout on the attention weights, inside the fused call (attention.py:73)
         self.dim_model, self.h, self.dim_ff = dim_model, h, dim_ff
         self.d_k = dim_model // h
         self.rel_pos = rel_pos
@@ -115,7 +113,8 @@ class BPTBlock(nn.Module):
         k = self.proj_k(h).view(-1, self.h, self.d_k)
         v = self.proj_v(h).view(-1, self.h, self.d_k)
         ak = self.embed_ak.weight if self.rel_pos else None
-        a = bpt_attention(plan, q, k, v, ak, 1.0 / math.sqrt(self.d_k)).view(-1, self.d_k * self.h)
+        drop_a = self.drop_a if self.training else 0.0
+        a = bpt_attention(plan, q, k, v, ak, 1.0 / math.sqrt(self.d_k), dropout_p=drop_a).view(-1, self.d_k * self.h)
         h = add_layer_norm(h, self.drop_h(self.proj_o(a)), self.norm_in)
         return add_layer_norm(h, self.ffn(h), self.norm_inter)
 
@@ -129,9 +128,7 @@ class BPTMemBlock(nn.Module):
 
     def __init__(self, dim_model, h, dim_ff, rel_pos=False, drop_h=0.1, drop_a=0.0, activation="relu"):
         super().__init__()
-        if drop_a != 0.0:
-            raise ValueError("dropout on attention weights is not available in the fused call; "
-                             "use bpt_b200.op (the operator chain) for drop_a > 0")
+        self.drop_a = float(drop_a)  # dropout on the attention weights, inside the fused call (attention.py:73)
         self.dim_model, self.h, self.dim_ff = dim_model, h, dim_ff
         self.d_k = dim_model // h
         self.rel_pos = rel_pos
@@ -160,11 +157,12 @@ class BPTMemBlock(nn.Module):
         shape = (-1, self.h, self.d_k)
         scale = 1.0 / math.sqrt(self.d_k)
         ak = self.embed_ak.weight if self.rel_pos else None
+        drop_a = self.drop_a if self.training else 0.0
         a = bpt_attention(plan, self.proj_q[0](h).view(shape), self.proj_k[0](h).view(shape),
-                          self.proj_v[0](h).view(shape), ak, scale).view(-1, self.d_k * self.h)
+                          self.proj_v[0](h).view(shape), ak, scale, dropout_p=drop_a).view(-1, self.d_k * self.h)
         h = add_layer_norm(h, self.drop_h[0](self.proj_o[0](a)), self.norm_in[0])  # attention.py:131-141
         a = bpt_attention(plan_inter, self.proj_q[1](h).view(shape), self.proj_k[1](mem).view(shape),
-                          self.proj_v[1](mem).view(shape), None, scale).view(-1, self.d_k * self.h)
+                          self.proj_v[1](mem).view(shape), None, scale, dropout_p=drop_a).view(-1, self.d_k * self.h)
         h = add_layer_norm(h, self.drop_h[1](self.proj_o[1](a)), self.norm_in[1])  # attention.py:151-168
         return add_layer_norm(h, self.ffn(h), self.norm_inter)                     # attention.py:170-171
 

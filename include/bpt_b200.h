@@ -218,6 +218,20 @@ int bpt_vector_spmm_backward(const int64_t *row, const int64_t *indptr, const in
  * sequence attending to gathered K/V have not.
  * ---------------------------------------------------------------------------------- */
 
+/* Dropout on the attention weights, the reference's drop_att between sparse_softmax and vec_spmm
+ * (modules/attention.py:73): with rate r an edge's weight for one head is zeroed with probability r and
+ * the kept ones are scaled by 1 / (1 - r), after the softmax normalisation.  The mask is a hash of
+ * (destination, source, head, seed): the forward and the backward of one layer call must be given the same
+ * seed, nothing is stored between them, and results stay bitwise reproducible for a fixed seed.  Parallel
+ * edges between one pair of nodes share their bit.  A NULL pointer or rate 0 switches dropout off.
+ * bpt_attn_dropout_mask writes the mask (1 = kept) for edges in edge-id order, (n_edges, h) bytes. */
+typedef struct {
+    double rate;   /* in [0, 1) */
+    uint64_t seed;
+} bpt_dropout_t;
+int bpt_attn_dropout_mask(const int32_t *src, const int32_t *dst, int64_t n_edges, int h,
+                          const bpt_dropout_t *dropout, uint8_t *mask, bpt_stream_t stream);
+
 size_t bpt_attn_plan_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes);
 size_t bpt_attn_plan_workspace_bytes(int64_t n_nodes, int64_t n_src, int64_t n_edges, int n_etypes);
 int bpt_attn_plan_build(const int32_t *src, const int32_t *dst, const int32_t *etype,
@@ -236,7 +250,7 @@ size_t bpt_attn_workspace_bytes(int64_t n_nodes, int64_t n_edges, const int32_t 
 int bpt_attn_forward(const void *plan, const int32_t *counts_host, int64_t n_nodes,
                      int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
                      const void *ak, double scale, void *o, float *lse, int h, int d, int dtype,
-                     void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+                     void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout, bpt_stream_t stream);
 
 /* lse: the forward's output; d_o: gradient of o.  dq: (n_nodes, h, d), dk, dv: (n_src, h, d),
  * or both NULL to skip them;
@@ -246,7 +260,8 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
                       int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
                       const void *ak, double scale, const float *lse,
                       const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
-                      int dtype, void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+                      int dtype, void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout,
+                      bpt_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Tensor-core forward (bf16, head dim 64).  Same result as bpt_attn_forward within bf16
@@ -329,7 +344,7 @@ int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, const int32_t *
                         int max_mblocks, int max_qr_slots, int n_etypes, const void *q,
                         const void *k, const void *v, const void *ak, double scale, void *o,
                         float *lse, int h, int d, int dtype, void *workspace,
-                        size_t workspace_bytes, bpt_stream_t stream);
+                        size_t workspace_bytes, const bpt_dropout_t *dropout, bpt_stream_t stream);
 
 /* The whole backward on the tensor-core path (bf16, head dim 64): dst_tiles = the forward's tile
  * plan exported WITH cell_pos and without row items, src_tiles = the transposed tile plan
@@ -350,7 +365,7 @@ int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_tile_plan_t
                          int64_t n_edges, int n_etypes, const void *q, const void *k, const void *v,
                          const void *ak, double scale, const void *o, const float *lse, const void *d_o,
                          void *dq, void *dk, void *dv, float *dak, int h, int d, int dtype,
-                         void *workspace, size_t workspace_bytes, bpt_stream_t stream);
+                         void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout, bpt_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Forward on the 5th-generation tensor cores (tcgen05.mma with accumulators in tensor memory; bf16, head

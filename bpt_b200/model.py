@@ -1,8 +1,9 @@
 """The callers of the attention path, re-hosted on plain tensors (no graph library).
 
 `BPTBlock` keeps the parameters of the reference's block (modules/attention.py:22-52: proj_q/k/v/o
-without bias, embed_ak of MAX_ETYPE rows, post-LN, FFN) under the same names, so a reference
-state dict loads; its forward (attention.py:54-81) takes the node features and an
+without bias, embed_ak of MAX_ETYPE rows, post-LN, FFN) under the same names, and the models keep
+the reference's `embed.lut` / `generator.proj` / `norm` names, so a reference state dict of the
+relative-position configurations with dim_embed == dim_model loads with strict=True; its forward (attention.py:54-81) takes the node features and an
 `AttentionPlan` instead of a DGL graph + CSR tuple and replaces the four-operator chain by
 the fused call.  `BPTMemBlock` (attention.py:84-172) adds attention to an encoder memory over the
 sentence-aligned cross graph; the fused call takes distinct destination and source node sets, so
@@ -176,13 +177,27 @@ class Generator(nn.Module):  # modules/model.py:8-17
         return torch.log_softmax(self.proj(x), dim=-1)
 
 
-class BPTLanguageModel(nn.Module):
-    """modules/model.py:197-280 with rel_pos=True (the character-LM configuration)."""
+class Embedding(nn.Module):
+    """modules/embedding.py:13-21: the token table sits in `.lut`, so its state-dict key is `<name>.lut.weight`
+    as in the reference's checkpoints."""
 
-    def __init__(self, vocab_size, dim_model, dim_ff, h, n_layers, dropout=0.0, activation="relu"):
+    def __init__(self, vocab_size, dim_model):
         super().__init__()
-        self.embed = nn.Embedding(vocab_size, dim_model)
-        self.layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
+        self.lut = nn.Embedding(vocab_size, dim_model)
+        self.dim_model = dim_model
+
+    def forward(self, x):
+        return self.lut(x)
+
+
+class BPTLanguageModel(nn.Module):
+    """modules/model.py:197-280 with rel_pos=True and dim_embed == dim_model (the character-LM
+    configuration): a state dict of that reference model loads as it is."""
+
+    def __init__(self, vocab_size, dim_model, dim_ff, h, n_layers, dropout=0.0, activation="relu", dropout_a=0.0):
+        super().__init__()
+        self.embed = Embedding(vocab_size, dim_model)
+        self.layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout, drop_a=dropout_a,
                                               activation=activation) for _ in range(n_layers)])
         self.generator = Generator(dim_model, vocab_size)
         self.norm = nn.LayerNorm(dim_model)
@@ -206,13 +221,13 @@ class BPTClassifier(nn.Module):
     (text_classification.py:48,77); readout="mean" averages the sequence's leaves."""
 
     def __init__(self, vocab_size, dim_model, dim_ff, h, n_layers, n_classes, dropout=0.0, activation="relu",
-                 readout="root"):
+                 readout="root", dropout_a=0.0):
         super().__init__()
         if readout not in ("root", "mean"):
             raise ValueError("readout must be root or mean")
         self.readout = readout
-        self.embed = nn.Embedding(vocab_size, dim_model)
-        self.layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
+        self.embed = Embedding(vocab_size, dim_model)
+        self.layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout, drop_a=dropout_a,
                                               activation=activation) for _ in range(n_layers)])
         self.generator = Generator(dim_model, n_classes)
         self.norm = nn.LayerNorm(dim_model)
@@ -242,13 +257,14 @@ class BPTEncoderDecoder(nn.Module):
     `n_layers` blocks over the encoder graph, `m_layers` memory blocks over the decoder graph
     reading the encoder's node features, generator on the read-out nodes."""
 
-    def __init__(self, vocab_sizes, dim_model, dim_ff, h, n_layers, m_layers, dropout=0.0, activation="relu"):
+    def __init__(self, vocab_sizes, dim_model, dim_ff, h, n_layers, m_layers, dropout=0.0, activation="relu",
+                 dropout_a=0.0):
         super().__init__()
-        self.embed = nn.ModuleList([nn.Embedding(v, dim_model) for v in vocab_sizes])
-        self.enc_layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
+        self.embed = nn.ModuleList([Embedding(v, dim_model) for v in vocab_sizes])
+        self.enc_layers = nn.ModuleList([BPTBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout, drop_a=dropout_a,
                                                   activation=activation) for _ in range(n_layers)])
         self.dec_layers = nn.ModuleList([BPTMemBlock(dim_model, h, dim_ff, rel_pos=True, drop_h=dropout,
-                                                     activation=activation) for _ in range(m_layers)])
+                                                     drop_a=dropout_a, activation=activation) for _ in range(m_layers)])
         self.generator = Generator(dim_model, vocab_sizes[-1])
         self.norm = nn.LayerNorm(dim_model)
         self.emb_dropout = nn.Dropout(dropout)

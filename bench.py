@@ -50,9 +50,9 @@ def parse():
                          "--seq-len tokens, destination nodes split over the ranks, K/V all-gathered (strong scaling)")
     ap.add_argument("--exchange", default="halo", choices=["halo", "allgather"],
                     help="seqshard mode: send only the remote K/V rows a shard reads (halo) or all-gather K/V")
-    ap.add_argument("--graph", action="store_true",
-                    help="seqshard mode on ONE GPU: capture the step in a CUDA graph and time its replay "
-                         "(with more ranks the step holds NCCL collectives and is timed eagerly)")
+    ap.add_argument("--no-step-graphs", action="store_true",
+                    help="seqshard mode with the halo exchange: issue the pieces between collectives eagerly instead "
+                         "of replaying them from CUDA graphs (collectives are never captured)")
     ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt", "cls", "chain"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
                          "forward, batch 8 x 8192 tokens per rank, tokens/s; mt: 6+6-layer encoder-decoder "
@@ -290,16 +290,16 @@ def measure_seqshard(a, n, k, steps, warmup, min_seconds=1.0):
                      for sg in (0.125, 0.125, 0.125, 1.0)]
     ak = (torch.randn(MAX_ETYPE, D, generator=torch.Generator().manual_seed(1)) * 0.125).to(dtype).to(dev)
     scale = 1.0 / math.sqrt(D)
+    runner = None
     if halo:
-        for t_ in (q, k_, v, ak):
-            t_.requires_grad_(True)
+        # fixed schedule on static buffers: two packed all-to-alls, one all-gather and one all-reduce per step, the
+        # pieces between them replayed from CUDA graphs (the collectives themselves are issued eagerly)
+        runner = sh.HaloRunner(s, plan, H, D, dtype, dev, scale, MAX_ETYPE, graphs=not a.no_step_graphs)
 
     def step():
         if halo:
-            # the autograd function: halo all-to-all, tile kernels, merge of the straddlers' partial rows
-            for t_ in (q, k_, v, ak):
-                t_.grad = None
-            sh.halo_attention(s, plan, q, k_, v, ak, scale).backward(d_o)
+            runner.forward(q, k_, v, ak)
+            runner.backward(d_o)
             return
         if world > 1:
             k_g, v_g = sh.all_gather_rows(s, k_), sh.all_gather_rows(s, v)
@@ -312,19 +312,9 @@ def measure_seqshard(a, n, k, steps, warmup, min_seconds=1.0):
 
     for _ in range(max(warmup, 3)):
         step()
-    run_step, graph_note = step, None
-    if a.graph and world == 1:
-        # One step (tile kernels, GEMMs, index kernels) as a CUDA graph: its launches are issued by one call.
-        # (With more ranks the step holds NCCL collectives and is issued eagerly.)
-        graph = torch.cuda.CUDAGraph()
-        try:
-            with torch.cuda.graph(graph):
-                step()
-            run_step, graph_note = graph.replay, "step replayed from a CUDA graph"
-            for _ in range(3):
-                run_step()
-        except Exception as exc:  # noqa: BLE001 - reported in the record
-            graph_note = "capture failed: %s" % str(exc)[:160]
+    run_step = step
+    graph_note = ("pieces between collectives replayed from CUDA graphs" if halo and runner.graphs
+                  else "eager")
     ms, blocks = timed_blocks(run_step, steps, dev, min_seconds)
     if rank != 0:
         return None
@@ -336,7 +326,8 @@ def measure_seqshard(a, n, k, steps, warmup, min_seconds=1.0):
                        n, k, "halo all-to-all of K/V rows and of their gradients, straddling span nodes merged across ranks"
                        if halo else "K/V all-gather + dK/dV reduce-scatter"),
                    "edges": E, "nodes": g.number_of_nodes, "owned_nodes_rank0": s.n_owned,
-                   "kv_bytes_received_rank0": 2 * (s.n_halo if halo else s.n_gathered) * H * D * q.element_size()}}
+                   "kv_bytes_received_rank0": 2 * (s.n_halo if halo else s.n_gathered) * H * D * q.element_size(),
+                   "collectives_per_step": (4 if world > 1 else 0) if halo else (4 if world > 1 else 0)}}
 
 
 def run_seqshard(a):

@@ -686,6 +686,31 @@ cublasHandle_t cublas_handle() {
     return handles[dev];
 }
 
+// A second stream per device, so that the relative-position step (type table + two GEMMs) and the source-side
+// tile kernel, which both depend only on the destination-side kernel, can run side by side.  The caller's
+// stream forks into it and joins it again inside the call (events), so the call stays stream-ordered.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+SideStream *side_stream() {
+    static std::mutex mu;
+    static SideStream side[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    SideStream &s = side[dev];
+    if (s.stream == nullptr) {
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            s.stream = nullptr;
+            return nullptr;
+        }
+    }
+    return &s;
+}
+
 // Block size of dkv_sum_merge_kernel: one column per thread where that fits.
 inline int sum_merge_threads(int columns) {
     const int t = (columns + 31) / 32 * 32;
@@ -876,6 +901,14 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
             BPT_LAUNCH_CHECK();
         }
     }
+    // 2. and 3. both read the per-edge scratch the destination side has just written and touch disjoint outputs
+    // (2: dQ and d embed_ak, 3: dK and dV), so 2 goes to a second stream that forks from and joins the caller's.
+    SideStream *side = side_stream();
+    if (side == nullptr) return fail(BPT_ERR_CUDA, "attn_backward_tc: could not create the side stream");
+    BPT_CUDA(cudaEventRecord(side->fork, stream));
+    BPT_CUDA(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    cudaStream_t main_stream = stream;
+    stream = side->stream;
     // 2. relative-position part of dQ and the gradient of the type table
     const int tq = dst_tiles->t_max;
     if (ak != nullptr && dak != nullptr)
@@ -907,6 +940,10 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         // many edge types: per-edge CUDA-core kernels
         if (int rc = launch_backward_ak_terms_bf16(pv, counts_host, q, ak, PS, dq, dak, part_dak, h, d, stream)) return rc;
     }
+    stream = main_stream;
+    BPT_CUDA(cudaEventRecord(side->join, side->stream));
     // 3. source side: dK, dV
-    return run_dkv(src_tiles, PS, n_edges, q, d_o, dk, dv, h, part_dkv, stream);
+    const int rc_dkv = run_dkv(src_tiles, PS, n_edges, q, d_o, dk, dv, h, part_dkv, stream);
+    BPT_CUDA(cudaStreamWaitEvent(stream, side->join, 0));
+    return rc_dkv;
 }

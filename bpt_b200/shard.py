@@ -108,6 +108,7 @@ class SequenceShard:
                 0, dst64[span], owner[src64[span]], "amax")
             is_strad = hi > lo                                           # sources on more than one rank
             strad = torch.nonzero(is_strad).squeeze(1)                   # ascending global ids
+            self.strad_ids = strad
             self.n_strad = int(strad.numel())
             # edges this rank computes: into its own non-straddling rows, and from its own sources
             # into any straddler
@@ -401,3 +402,233 @@ def halo_attention(shard, plan, q, k, v, embed_ak=None, scale=None):
     if getattr(shard, "split", False):
         return _StraddleAttention.apply(shard, plan, q, k, v, embed_ak, scale)
     return bpt_attention(plan, q, _HaloKV.apply(shard, k), _HaloKV.apply(shard, v), embed_ak, scale)
+
+
+class HaloRunner:
+    """One attention layer, forward and backward, of a destination-sharded sequence as a fixed schedule with
+    four collectives per step instead of six and everything between them on static buffers:
+
+      forward   pack  -> all-to-all (halo K and V rows + the straddlers' Q rows, owner to everyone)
+                      -> unpack, fused forward, partial (o, lse) of the straddlers
+                      -> all-gather of the partials -> merge
+      backward  all-reduce of the straddlers' dO rows (each owner fills its rows of a zero buffer)
+                      -> fused backward, pack -> all-to-all back (dK, dV of the halo rows + every rank's
+                         share of the straddlers' dQ, to the owner) -> fixed-order sums
+
+    The pieces between collectives are plain tensor programs over precomputed index lists, so on a GPU each
+    of them can be captured once in a CUDA graph (graphs=True) and replayed with one launch; the collectives
+    themselves are issued eagerly between the replays.  shard: a SequenceShard after
+    build_halo(split_straddlers=True); plan: its AttentionPlan.  bf16 / head dim 64 on the GPU (the
+    tensor-core kernels' row term <dO, O> is what lets a rank compute its share of a straddling row).
+    """
+
+    def __init__(self, shard, plan, h, d, dtype, device, scale, ak_rows, graphs=False, group=None):
+        if not getattr(shard, "split", False):
+            raise ValueError("HaloRunner needs shard.build_halo(..., split_straddlers=True)")
+        s = self.shard = shard
+        self.plan, self.h, self.d, self.dtype, self.dev, self.scale, self.group = plan, h, d, dtype, device, scale, group
+        w, rank = s.world, s.rank
+        dev = device
+        i64 = dict(dtype=torch.int64, device=dev)
+        # straddlers: global list (ascending ids), their owners, and which are mine
+        self.n_strad, self.n_ns, self.n_my = s.n_strad, s.n_ns, int(s.s_own_idx.numel())
+        owner_of = (s.to_gathered // s.max_owned)[s.strad_ids].to(dev)       # owner rank of every straddler
+        n_str_of = [int((owner_of == r).sum()) for r in range(w)]
+        pos_of = [torch.nonzero(owner_of == r).squeeze(1) for r in range(w)]   # positions in the straddler list
+        # ---- forward all-to-all: to peer p [halo rows p needs | my straddlers' Q rows]
+        self.f_send_counts = [s.send_counts[p] + self.n_my for p in range(w)]
+        self.f_recv_counts = [s.recv_counts[p] + n_str_of[p] for p in range(w)]
+        sb = [0]
+        for c in self.f_send_counts:
+            sb.append(sb[-1] + c)
+        rb = [0]
+        for c in self.f_recv_counts:
+            rb.append(rb[-1] + c)
+        self.n_fsend, self.n_frecv = sb[-1], rb[-1]
+        self.send_pos_kv = torch.cat([torch.arange(sb[p], sb[p] + s.send_counts[p], **i64) for p in range(w)])
+        self.send_pos_q = torch.cat([torch.arange(sb[p] + s.send_counts[p], sb[p + 1], **i64) for p in range(w)])
+        self.send_src_q = s.s_own_idx.to(dev).repeat(w)
+        self.recv_pos_kv = torch.cat([torch.arange(rb[p], rb[p] + s.recv_counts[p], **i64) for p in range(w)])
+        self.recv_pos_q = torch.cat([torch.arange(rb[p] + s.recv_counts[p], rb[p + 1], **i64) for p in range(w)])
+        self.recv_dst_q = s.n_ns + torch.cat(pos_of) if self.n_strad else torch.zeros(0, **i64)
+        # ---- return all-to-all: to peer p [gradients of the halo rows p sent | my share of dQ of p's straddlers]
+        self.r_send_counts, self.r_recv_counts = self.f_recv_counts, self.f_send_counts
+        self.ret_src_q = self.recv_dst_q                        # rows of dq_loc, in the order of recv_pos_q
+        # received: from peer p [gradients for my rows send_idx[p] | p's share of dQ of my straddlers]
+        self.my_q_parts = self.send_pos_q.view(w, self.n_my) if self.n_my else torch.zeros((w, 0), **i64)
+        self.send_all = s.send_all.to(dev)
+        self.ret_rows, self.ret_mat = s.ret_rows.to(dev), s.ret_mat.to(dev)
+        self.s_own_idx, self.s_own_pos = s.s_own_idx.to(dev), s.s_own_pos.to(dev)
+        self.ns_idx = s.ns_idx.to(dev)
+        # ---- static buffers
+        row = (h, d)
+        mk = lambda n, dt=dtype: torch.zeros((n,) + row, dtype=dt, device=dev)
+        self.q_in, self.k_in, self.v_in, self.do_in = mk(s.n_owned), mk(s.n_owned), mk(s.n_owned), mk(s.n_owned)
+        self.ak_in = None if ak_rows is None else torch.zeros((ak_rows, d), dtype=dtype, device=dev)
+        self.k_e, self.v_e = mk(s.n_ext), mk(s.n_ext)
+        self.q_loc, self.do_loc = mk(s.n_dst_local), mk(s.n_dst_local)
+        self.o_loc = mk(s.n_dst_local)
+        self.lse_loc = torch.zeros((s.n_dst_local, h), dtype=torch.float32, device=dev)
+        self.f_send = torch.zeros((self.n_fsend, 2) + row, dtype=dtype, device=dev)
+        self.f_recv = torch.zeros((self.n_frecv, 2) + row, dtype=dtype, device=dev)
+        self.r_send = torch.zeros((self.n_frecv, 2) + row, dtype=dtype, device=dev)
+        self.r_recv = torch.zeros((self.n_fsend + 1, 2) + row, dtype=dtype, device=dev)   # last row stays zero
+        self.part = torch.zeros((self.n_strad, h * d + h), dtype=torch.float32, device=dev)
+        self.allp = torch.zeros((w * self.n_strad, h * d + h), dtype=torch.float32, device=dev)
+        self.do_strad = mk(self.n_strad)
+        self.o_out, self.dq_out, self.dk_out, self.dv_out = mk(s.n_owned), mk(s.n_owned), mk(s.n_owned), mk(s.n_owned)
+        self.dak_out = None if ak_rows is None else torch.zeros((ak_rows, d), dtype=torch.float32, device=dev)
+        self.graphs = bool(graphs) and device.type == "cuda"
+        self._g = {}
+
+    # ---- the pieces between collectives (no communication inside)
+    def _kernels(self):
+        if _KERNELS is not None:
+            return _KERNELS
+        from .attention import attention_backward, attention_forward
+        return attention_forward, attention_backward
+
+    def _seg_pack(self):
+        s = self.shard
+        self.f_send[self.send_pos_kv, 0] = self.k_in[self.send_all]
+        self.f_send[self.send_pos_kv, 1] = self.v_in[self.send_all]
+        if self.n_my:
+            self.f_send[self.send_pos_q, 0] = self.q_in[self.send_src_q]
+        self.k_e[: s.n_owned] = self.k_in
+        self.v_e[: s.n_owned] = self.v_in
+        self.q_loc[: self.n_ns] = self.q_in[: self.n_ns] if s.ns_prefix else self.q_in[self.ns_idx]
+
+    def _seg_forward(self):
+        s = self.shard
+        self.k_e[s.n_owned:] = self.f_recv[self.recv_pos_kv, 0]
+        self.v_e[s.n_owned:] = self.f_recv[self.recv_pos_kv, 1]
+        if self.n_strad:
+            self.q_loc[self.recv_dst_q] = self.f_recv[self.recv_pos_q, 0]
+        o_loc, lse_loc = self._kernels()[0](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale)
+        self.o_loc.copy_(o_loc)
+        self.lse_loc.copy_(lse_loc)
+        if self.n_strad:
+            n = self.n_strad
+            self.part[:, : self.h * self.d] = o_loc[-n:].float().flatten(1)
+            self.part[:, self.h * self.d:] = lse_loc[-n:]
+
+    def _seg_merge(self):
+        s = self.shard
+        if self.n_strad:
+            # lse = logsumexp_r lse_r, o = sum_r exp(lse_r - lse) o_r over the ranks' partial rows
+            n, w, hd = self.n_strad, s.world, self.h * self.d
+            allp = self.allp.view(w, n, hd + self.h)
+            o_r, lse_r = allp[:, :, :hd].view(w, n, self.h, self.d), allp[:, :, hd:]
+            lse = torch.logsumexp(lse_r, 0)
+            wgt = torch.exp(lse_r - lse.unsqueeze(0)).nan_to_num(0.0)
+            self.o_loc[-n:] = (wgt.unsqueeze(-1) * o_r).sum(0).to(self.dtype)
+            self.lse_loc[-n:] = lse
+        if s.ns_prefix:
+            self.o_out[: self.n_ns] = self.o_loc[: self.n_ns]
+        else:
+            self.o_out[self.ns_idx] = self.o_loc[: self.n_ns]
+        if self.n_my:
+            self.o_out[self.s_own_idx] = self.o_loc[self.n_ns + self.s_own_pos]
+
+    def _seg_dout(self):
+        self.do_strad.zero_()
+        if self.n_my:
+            self.do_strad[self.s_own_pos] = self.do_in[self.s_own_idx]
+
+    def _seg_backward(self):
+        s = self.shard
+        self.do_loc[: self.n_ns] = self.do_in[: self.n_ns] if s.ns_prefix else self.do_in[self.ns_idx]
+        if self.n_strad:
+            self.do_loc[self.n_ns:] = self.do_strad
+        dq_loc, dk_e, dv_e, dak = self._kernels()[1](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale,
+                                                     self.lse_loc, self.do_loc, o=self.o_loc)
+        self._dq_loc, self._dk_e, self._dv_e = dq_loc, dk_e, dv_e
+        if dak is not None:
+            self.dak_out.copy_(dak)
+        self.r_send[self.recv_pos_kv, 0] = dk_e[s.n_owned:].to(self.dtype)
+        self.r_send[self.recv_pos_kv, 1] = dv_e[s.n_owned:].to(self.dtype)
+        if self.n_strad:
+            self.r_send[self.recv_pos_q, 0] = dq_loc[self.ret_src_q].to(self.dtype)
+        # own rows: what the local edges contribute; the peers' shares are added after the exchange
+        self.dk_out.copy_(dk_e[: s.n_owned])
+        self.dv_out.copy_(dv_e[: s.n_owned])
+        if s.ns_prefix:
+            self.dq_out[: self.n_ns] = dq_loc[: self.n_ns]
+        else:
+            self.dq_out[self.ns_idx] = dq_loc[: self.n_ns]
+
+    def _seg_return(self):
+        n_send = self.n_fsend
+        if self.ret_rows.numel():
+            got = self.r_recv[:, :2]
+            # row i of ret_mat lists positions (in peer order) of the halo part that name own row ret_rows[i]
+            halo_part = torch.cat([got[self.send_pos_kv], got[n_send:]], 0)      # + the all-zero padding row
+            total = _wide(halo_part[self.ret_mat]).sum(1)                        # (targets, 2, h, d) in fp32
+            self.dk_out[self.ret_rows] = (_wide(self.dk_out[self.ret_rows]) + total[:, 0]).to(self.dtype)
+            self.dv_out[self.ret_rows] = (_wide(self.dv_out[self.ret_rows]) + total[:, 1]).to(self.dtype)
+        if self.n_my:
+            parts = _wide(self.r_recv[self.my_q_parts, 0])                       # (world, n_my, h, d), rank order
+            self.dq_out[self.s_own_idx] = parts.sum(0).to(self.dtype)
+
+    def _run(self, name, fn):
+        """Runs a piece eagerly, or captures it in a CUDA graph on first use and replays it afterwards."""
+        if not self.graphs:
+            return fn()
+        g = self._g.get(name)
+        if g is None:
+            side = torch.cuda.Stream(device=self.dev)
+            side.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    fn()                                          # warm-up outside the capture (workspaces, handles)
+            torch.cuda.current_stream(self.dev).wait_stream(side)
+            torch.cuda.synchronize(self.dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            self._g[name] = g
+        g.replay()
+
+    # ---- the step
+    def forward(self, q, k, v, embed_ak=None):
+        """q, k, v: (n_owned, h, d) of the nodes this rank owns.  Returns o (n_owned, h, d), a static buffer
+        that the next forward overwrites."""
+        import torch.distributed as dist
+        s = self.shard
+        self.q_in.copy_(q)
+        self.k_in.copy_(k)
+        self.v_in.copy_(v)
+        if self.ak_in is not None:
+            self.ak_in.copy_(embed_ak)
+        self._run("pack", self._seg_pack)
+        if s.world > 1:
+            dist.all_to_all_single(self.f_recv, self.f_send, output_split_sizes=self.f_recv_counts,
+                                   input_split_sizes=self.f_send_counts, group=self.group)
+        else:
+            self.f_recv.copy_(self.f_send)
+        self._run("forward", self._seg_forward)
+        if self.n_strad:
+            if s.world > 1:
+                dist.all_gather_into_tensor(self.allp, self.part, group=self.group)
+            else:
+                self.allp.copy_(self.part)
+        self._run("merge", self._seg_merge)
+        return self.o_out
+
+    def backward(self, d_o):
+        """d_o: gradient of forward()'s result.  Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is this
+        rank's share in fp32.  Static buffers, overwritten by the next backward."""
+        import torch.distributed as dist
+        s = self.shard
+        self.do_in.copy_(d_o)
+        self._run("dout", self._seg_dout)
+        if s.world > 1 and self.n_strad:
+            dist.all_reduce(self.do_strad, group=self.group)      # every row has one owner: a sum with zeros
+        self._run("backward", self._seg_backward)
+        if s.world > 1:
+            dist.all_to_all_single(self.r_recv[: self.n_fsend], self.r_send, output_split_sizes=self.r_recv_counts,
+                                   input_split_sizes=self.r_send_counts, group=self.group)
+        else:
+            self.r_recv[: self.n_fsend].copy_(self.r_send)
+        self._run("return", self._seg_return)
+        return self.dq_out, self.dk_out, self.dv_out, self.dak_out

@@ -155,6 +155,15 @@ def _straddle_worker(rank, world, port, n, k, out):
     errs = [np.abs(o.detach().numpy() - o_ref[own_np]).max(), np.abs(ql.grad.numpy() - ref[0][own_np]).max(),
             np.abs(kl.grad.numpy() - ref[1][own_np]).max(), np.abs(vl.grad.numpy() - ref[2][own_np]).max(),
             np.abs(dak.numpy() - ref[3]).max()]
+    # the same step through the fixed schedule with packed exchanges (HaloRunner), twice on its static buffers
+    runner = sh.HaloRunner(s, plan, H, D, torch.float32, torch.device("cpu"), 0.3, T)
+    for _ in range(2):
+        o_r = runner.forward(q[own], kk[own], v[own], ak).clone()
+        dq_r, dk_r, dv_r, dak_r = [x.clone() for x in runner.backward(d_o[own])]
+    dist.all_reduce(dak_r)
+    errs += [np.abs(o_r.numpy() - o_ref[own_np]).max(), np.abs(dq_r.numpy() - ref[0][own_np]).max(),
+             np.abs(dk_r.numpy() - ref[1][own_np]).max(), np.abs(dv_r.numpy() - ref[2][own_np]).max(),
+             np.abs(dak_r.numpy() - ref[3]).max()]
     info = torch.tensor([s.n_strad, s.n_halo, int(s.eid.numel())])
     gathered = [torch.zeros(3, dtype=torch.int64) for _ in range(world)]
     dist.all_gather(gathered, info)

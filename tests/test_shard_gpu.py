@@ -122,6 +122,20 @@ def _nccl_worker(rank, world, port, out):
     errs_bf16 = [rel(o3.detach().double().cpu().numpy(), o_rb[own_np]), rel(ql3.grad.double().cpu().numpy(), refb[0][own_np]),
                  rel(kl3.grad.double().cpu().numpy(), refb[1][own_np]), rel(vl3.grad.double().cpu().numpy(), refb[2][own_np]),
                  rel(dak3.double().cpu().numpy(), refb[3])]
+    # the same step through the fixed schedule with packed exchanges, eagerly and with the pieces between
+    # collectives replayed from CUDA graphs; results must equal the autograd path bit for bit where the
+    # arithmetic is the same (o, dq) and stay within the bf16 bar everywhere
+    for graphs in (False, True):
+        runner = sh.HaloRunner(s, plan_s, H, D, bf, torch.device("cuda", rank), 0.125, T, graphs=graphs)
+        for _ in range(3):
+            o4 = runner.forward(qb.cuda()[own], kb.cuda()[own], vb.cuda()[own], akb.cuda()).clone()
+            dq4, dk4, dv4, dak4 = [x.clone() for x in runner.backward(dob.cuda()[own])]
+        dak4 = dak4.clone()
+        dist.all_reduce(dak4)
+        errs_bf16 += [rel(o4.double().cpu().numpy(), o_rb[own_np]), rel(dq4.double().cpu().numpy(), refb[0][own_np]),
+                      rel(dk4.double().cpu().numpy(), refb[1][own_np]), rel(dv4.double().cpu().numpy(), refb[2][own_np]),
+                      rel(dak4.double().cpu().numpy(), refb[3])]
+        assert torch.equal(o4, o3.detach()), "runner forward differs from the autograd path"
     out.put((rank, max(errs), max(errs_bf16), s.n_strad, s.n_halo))
     dist.barrier()
     dist.destroy_process_group()

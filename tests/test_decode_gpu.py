@@ -79,3 +79,51 @@ def test_greedy_decoding_is_a_fixed_point_of_the_full_forward():
     top2 = logp.topk(2, -1).values
     clear = (top2[:, 0] - top2[:, 1]) > 1e-3      # positions where the arg-max is not a near tie
     assert bool((logp.argmax(-1)[clear] == want[clear]).all())
+
+
+def test_beam_search_hypotheses_rescore_and_beam_one_is_greedy():
+    """beam_search keeps beam_size hypotheses per sequence on the fused call (modules/beam.py:64-173): with
+    beam 1 it is greedy decoding; with beam 3 its hypotheses come best first, the best is at least as good
+    as the greedy one, and every returned score equals the summed log-probability the full forward gives
+    for that hypothesis' tokens (which checks the cache rows a hypothesis inherits)."""
+    from bpt_b200 import csr as csrmod, graphbuilder
+    from bpt_b200.attention import AttentionPlan
+    from bpt_b200.decode import DecodeSchedule, beam_search, greedy
+    from bpt_b200.model import BPTEncoderDecoder
+    torch.manual_seed(11)
+    enc_len, dec_len, beam = [23, 40], [9, 14], 3
+    enc = csrmod.batch_graphs([graphbuilder.BinaryPartition(n, False, 2, 3) for n in enc_len])
+    model = BPTEncoderDecoder([50, 20], 64, 128, 4, 2, 2).cuda().eval()
+    enc_plan = AttentionPlan.from_batch(enc, n_etypes=1000)
+    enc_tok = torch.randint(0, 50, (sum(enc_len),), device="cuda")
+    first = torch.tensor([1, 2], device="cuda")
+
+    def schedule(copies):
+        lens = [n for n in dec_len for _ in range(copies)]
+        dec = csrmod.batch_graphs([graphbuilder.BinaryPartition(n, True, 2, 3) for n in lens])
+        src_ranges = [(enc.node_offsets[i // copies], enc_len[i // copies]) for i in range(len(lens))]
+        dst_ranges = [(dec.node_offsets[i], lens[i]) for i in range(len(lens))]
+        isrc, idst = csrmod.inter_graph(src_ranges, dst_ranges)
+        return dec, isrc, idst, DecodeSchedule(dec, isrc, idst, enc.n_nodes)
+
+    dec1, isrc1, idst1, sched1 = schedule(1)
+    g_tokens = greedy(model, sched1, enc_tok, enc.leaf_ids(), enc_plan, first)            # (n_steps, 2)
+    b1_tokens, b1_scores = beam_search(model, sched1, 1, enc_tok, enc.leaf_ids(), enc_plan, first)
+    assert torch.equal(b1_tokens[:, :, 0], g_tokens)
+    _, _, _, sched3 = schedule(beam)
+    tokens, scores = beam_search(model, sched3, beam, enc_tok, enc.leaf_ids(), enc_plan, first)
+    assert tokens.shape == (max(dec_len), 2, beam) and scores.shape == (2, beam)
+    assert bool((scores[:, :-1] >= scores[:, 1:]).all())
+    assert bool((scores[:, 0] >= b1_scores[:, 0] - 1e-4).all())
+    # rescore every hypothesis with the one-shot forward over the single-copy decoder batch
+    dec_plan = AttentionPlan.from_batch(dec1, n_etypes=1000)
+    inter_plan = AttentionPlan(isrc1, idst1, None, dec1.n_nodes, n_src=enc.n_nodes)
+    for j in range(beam):
+        inputs = torch.cat([torch.cat([first[b:b + 1], tokens[:n - 1, b, j]]) for b, n in enumerate(dec_len)])
+        with torch.no_grad():
+            logp = model(enc_tok, enc.leaf_ids(), enc_plan, inputs, dec1.leaf_ids(), dec_plan, inter_plan, dec1.leaf_ids())
+        off = 0
+        for b, n in enumerate(dec_len):
+            want = logp[off:off + n].gather(1, tokens[:n, b, j].unsqueeze(1)).sum().item()
+            assert abs(want - scores[b, j].item()) < 1e-3 * max(1.0, abs(want)), (b, j, want, scores[b, j].item())
+            off += n

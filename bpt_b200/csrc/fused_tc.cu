@@ -527,7 +527,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
     }
     if (n_groups > 0) {
         const bool bias = ak != nullptr;
-        TcParams p;
+        TcParams p{};
         p.groups = groups; p.mblocks = mblocks; p.cols = cols; p.et = et;
         p.q = static_cast<const __nv_bfloat16 *>(q); p.k = static_cast<const __nv_bfloat16 *>(k);
         p.v = static_cast<const __nv_bfloat16 *>(v); p.ak = static_cast<const __nv_bfloat16 *>(ak);

@@ -484,13 +484,14 @@ extern "C" int bpt_attn_forward_tc5(const bpt_tile_plan_t *tiles, int64_t n_node
     float *part_ml = ws.take<float>(static_cast<size_t>(tiles->n_slots) * h * 2);
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_forward_tc5: workspace of %zu bytes is too small", workspace_bytes);
 
-    Tc5Params p;
+    Tc5Params p{};
     p.groups = tiles->groups; p.mblocks = tiles->mblocks; p.cols = tiles->cols;
     p.et = static_cast<const uint8_t *>(tiles->et);
     p.q = static_cast<const __nv_bfloat16 *>(q); p.k = static_cast<const __nv_bfloat16 *>(k);
     p.v = static_cast<const __nv_bfloat16 *>(v); p.ak = static_cast<const __nv_bfloat16 *>(ak);
     p.o = static_cast<__nv_bfloat16 *>(o);
     p.lse = lse; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
+    p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = tiles->max_cols_pad;
     const bool bias = ak != nullptr;
     // at least one table column group even when no m-block needs the table, so that the layout is one
     p.tq16 = bias ? ((tiles->t_max > 0 ? tiles->t_max : 8) + 15) / 16 * 16 : 0;

@@ -767,7 +767,7 @@ int check_tile_plan(const char *name, const bpt_tile_plan_t *tp, bool need_et, b
 int run_dkv(const bpt_tile_plan_t *tp, const uint32_t *PS, int64_t n_edges, const void *q, const void *d_o, void *dk, void *dv, int h,
             float *part, cudaStream_t stream) {
     if (tp->n_groups == 0) return BPT_OK;
-    DkvParams p;
+    DkvParams p{};
     p.groups = tp->groups; p.mblocks = tp->mblocks; p.cols = tp->cols; p.cellpos = tp->cell_pos;
     p.PS = PS; p.n_edges = n_edges;
     p.q = static_cast<const __nv_bfloat16 *>(q); p.d_o = static_cast<const __nv_bfloat16 *>(d_o);
@@ -864,7 +864,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
     // 1. destination side: P, dP, delta, K part of dQ
     if (dst_tiles->n_groups > 0) {
         const bool bias = ak != nullptr;
-        DqParams p;
+        DqParams p{};
         p.groups = dst_tiles->groups; p.mblocks = dst_tiles->mblocks; p.cols = dst_tiles->cols;
         p.cellpos = dst_tiles->cell_pos; p.et = dst_tiles->et;
         p.q = static_cast<const __nv_bfloat16 *>(q); p.k = static_cast<const __nv_bfloat16 *>(k);

@@ -295,11 +295,13 @@ def measure_seqshard(a, n, k, steps, warmup, min_seconds=1.0):
         # fixed schedule on static buffers: two packed all-to-alls, one all-gather and one all-reduce per step, the
         # pieces between them replayed from CUDA graphs (the collectives themselves are issued eagerly)
         runner = sh.HaloRunner(s, plan, H, D, dtype, dev, scale, MAX_ETYPE, graphs=not a.no_step_graphs)
+        for buf, x in ((runner.q_in, q), (runner.k_in, k_), (runner.v_in, v), (runner.do_in, d_o), (runner.ak_in, ak)):
+            buf.copy_(x)
 
     def step():
         if halo:
-            runner.forward(q, k_, v, ak)
-            runner.backward(d_o)
+            runner.forward()          # the inputs sit in the runner's buffers, as a layer's projections would
+            runner.backward()
             return
         if world > 1:
             k_g, v_g = sh.all_gather_rows(s, k_), sh.all_gather_rows(s, v)

@@ -460,26 +460,40 @@ class HaloRunner:
         self.ret_rows, self.ret_mat = s.ret_rows.to(dev), s.ret_mat.to(dev)
         self.s_own_idx, self.s_own_pos = s.s_own_idx.to(dev), s.s_own_pos.to(dev)
         self.ns_idx = s.ns_idx.to(dev)
-        # ---- static buffers
+        # ---- static buffers.  The inputs live inside the buffers the kernels read: k_in / v_in are the head of
+        # the extended K / V, q_in / do_in the head of the destination-row buffers (own non-straddlers first,
+        # which is how the owned list is ordered for binary-partition trees), so nothing is copied around the
+        # exchange; a caller can also write its projections straight into them and call forward() / backward()
+        # without arguments.  The straddler rows of q_in / do_in are consumed by the pack step and then reused.
+        if not s.ns_prefix:
+            raise ValueError("HaloRunner expects the straddling nodes last in a rank's owned list")
         row = (h, d)
         mk = lambda n, dt=dtype: torch.zeros((n,) + row, dtype=dt, device=dev)
-        self.q_in, self.k_in, self.v_in, self.do_in = mk(s.n_owned), mk(s.n_owned), mk(s.n_owned), mk(s.n_owned)
-        self.ak_in = None if ak_rows is None else torch.zeros((ak_rows, d), dtype=dtype, device=dev)
+        n_rows = max(s.n_dst_local, s.n_owned)
         self.k_e, self.v_e = mk(s.n_ext), mk(s.n_ext)
-        self.q_loc, self.do_loc = mk(s.n_dst_local), mk(s.n_dst_local)
-        self.o_loc = mk(s.n_dst_local)
-        self.lse_loc = torch.zeros((s.n_dst_local, h), dtype=torch.float32, device=dev)
+        self._q_buf, self._do_buf = mk(n_rows), mk(n_rows)
+        self.q_loc, self.do_loc = self._q_buf[: s.n_dst_local], self._do_buf[: s.n_dst_local]
+        self.k_in, self.v_in = self.k_e[: s.n_owned], self.v_e[: s.n_owned]
+        self.q_in, self.do_in = self._q_buf[: s.n_owned], self._do_buf[: s.n_owned]
+        self.ak_in = None if ak_rows is None else torch.zeros((ak_rows, d), dtype=dtype, device=dev)
+        self.o_loc = self.lse_loc = None                          # the forward kernel's outputs, kept for the backward
         self.f_send = torch.zeros((self.n_fsend, 2) + row, dtype=dtype, device=dev)
         self.f_recv = torch.zeros((self.n_frecv, 2) + row, dtype=dtype, device=dev)
         self.r_send = torch.zeros((self.n_frecv, 2) + row, dtype=dtype, device=dev)
         self.r_recv = torch.zeros((self.n_fsend + 1, 2) + row, dtype=dtype, device=dev)   # last row stays zero
         self.part = torch.zeros((self.n_strad, h * d + h), dtype=torch.float32, device=dev)
         self.allp = torch.zeros((w * self.n_strad, h * d + h), dtype=torch.float32, device=dev)
+        self.q_strad = mk(self.n_my)                              # my straddlers' Q rows, saved by the pack step
         self.do_strad = mk(self.n_strad)
-        self.o_out, self.dq_out, self.dk_out, self.dv_out = mk(s.n_owned), mk(s.n_owned), mk(s.n_owned), mk(s.n_owned)
-        self.dak_out = None if ak_rows is None else torch.zeros((ak_rows, d), dtype=torch.float32, device=dev)
+        self.dq_strad = mk(self.n_my)                             # summed dQ of my straddlers
         self.graphs = bool(graphs) and device.type == "cuda"
         self._g = {}
+
+    def own_rows(self, x_loc, x_strad_own=None):
+        """(n_owned, ...) rows of this rank from a destination-row tensor [own non-straddlers | all straddlers]:
+        the straddlers this rank owns are taken from x_strad_own (n_my rows) when given, else from x_loc."""
+        tail = x_strad_own if x_strad_own is not None else x_loc[self.n_ns + self.s_own_pos]
+        return torch.cat([x_loc[: self.n_ns], tail.to(x_loc.dtype)], 0)
 
     # ---- the pieces between collectives (no communication inside)
     def _kernels(self):
@@ -489,46 +503,33 @@ class HaloRunner:
         return attention_forward, attention_backward
 
     def _seg_pack(self):
-        s = self.shard
         self.f_send[self.send_pos_kv, 0] = self.k_in[self.send_all]
         self.f_send[self.send_pos_kv, 1] = self.v_in[self.send_all]
         if self.n_my:
             self.f_send[self.send_pos_q, 0] = self.q_in[self.send_src_q]
-        self.k_e[: s.n_owned] = self.k_in
-        self.v_e[: s.n_owned] = self.v_in
-        self.q_loc[: self.n_ns] = self.q_in[: self.n_ns] if s.ns_prefix else self.q_in[self.ns_idx]
 
     def _seg_forward(self):
         s = self.shard
         self.k_e[s.n_owned:] = self.f_recv[self.recv_pos_kv, 0]
         self.v_e[s.n_owned:] = self.f_recv[self.recv_pos_kv, 1]
         if self.n_strad:
-            self.q_loc[self.recv_dst_q] = self.f_recv[self.recv_pos_q, 0]
-        o_loc, lse_loc = self._kernels()[0](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale)
-        self.o_loc.copy_(o_loc)
-        self.lse_loc.copy_(lse_loc)
+            self.q_loc[self.recv_dst_q] = self.f_recv[self.recv_pos_q, 0]   # overwrites q_in's straddler rows
+        self.o_loc, self.lse_loc = self._kernels()[0](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale)
         if self.n_strad:
             n = self.n_strad
-            self.part[:, : self.h * self.d] = o_loc[-n:].float().flatten(1)
-            self.part[:, self.h * self.d:] = lse_loc[-n:]
+            self.part[:, : self.h * self.d] = self.o_loc[-n:].float().flatten(1)
+            self.part[:, self.h * self.d:] = self.lse_loc[-n:]
 
     def _seg_merge(self):
-        s = self.shard
         if self.n_strad:
             # lse = logsumexp_r lse_r, o = sum_r exp(lse_r - lse) o_r over the ranks' partial rows
-            n, w, hd = self.n_strad, s.world, self.h * self.d
+            n, w, hd = self.n_strad, self.shard.world, self.h * self.d
             allp = self.allp.view(w, n, hd + self.h)
             o_r, lse_r = allp[:, :, :hd].view(w, n, self.h, self.d), allp[:, :, hd:]
             lse = torch.logsumexp(lse_r, 0)
             wgt = torch.exp(lse_r - lse.unsqueeze(0)).nan_to_num(0.0)
-            self.o_loc[-n:] = (wgt.unsqueeze(-1) * o_r).sum(0).to(self.dtype)
+            self.o_loc[-n:] = (wgt.unsqueeze(-1) * o_r).sum(0).to(self.o_loc.dtype)
             self.lse_loc[-n:] = lse
-        if s.ns_prefix:
-            self.o_out[: self.n_ns] = self.o_loc[: self.n_ns]
-        else:
-            self.o_out[self.ns_idx] = self.o_loc[: self.n_ns]
-        if self.n_my:
-            self.o_out[self.s_own_idx] = self.o_loc[self.n_ns + self.s_own_pos]
 
     def _seg_dout(self):
         self.do_strad.zero_()
@@ -537,25 +538,15 @@ class HaloRunner:
 
     def _seg_backward(self):
         s = self.shard
-        self.do_loc[: self.n_ns] = self.do_in[: self.n_ns] if s.ns_prefix else self.do_in[self.ns_idx]
         if self.n_strad:
-            self.do_loc[self.n_ns:] = self.do_strad
+            self.do_loc[self.n_ns:] = self.do_strad                        # overwrites do_in's straddler rows
         dq_loc, dk_e, dv_e, dak = self._kernels()[1](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale,
                                                      self.lse_loc, self.do_loc, o=self.o_loc)
-        self._dq_loc, self._dk_e, self._dv_e = dq_loc, dk_e, dv_e
-        if dak is not None:
-            self.dak_out.copy_(dak)
+        self.dq_loc, self.dk_e, self.dv_e, self.dak = dq_loc, dk_e, dv_e, dak
         self.r_send[self.recv_pos_kv, 0] = dk_e[s.n_owned:].to(self.dtype)
         self.r_send[self.recv_pos_kv, 1] = dv_e[s.n_owned:].to(self.dtype)
         if self.n_strad:
             self.r_send[self.recv_pos_q, 0] = dq_loc[self.ret_src_q].to(self.dtype)
-        # own rows: what the local edges contribute; the peers' shares are added after the exchange
-        self.dk_out.copy_(dk_e[: s.n_owned])
-        self.dv_out.copy_(dv_e[: s.n_owned])
-        if s.ns_prefix:
-            self.dq_out[: self.n_ns] = dq_loc[: self.n_ns]
-        else:
-            self.dq_out[self.ns_idx] = dq_loc[: self.n_ns]
 
     def _seg_return(self):
         n_send = self.n_fsend
@@ -564,11 +555,11 @@ class HaloRunner:
             # row i of ret_mat lists positions (in peer order) of the halo part that name own row ret_rows[i]
             halo_part = torch.cat([got[self.send_pos_kv], got[n_send:]], 0)      # + the all-zero padding row
             total = _wide(halo_part[self.ret_mat]).sum(1)                        # (targets, 2, h, d) in fp32
-            self.dk_out[self.ret_rows] = (_wide(self.dk_out[self.ret_rows]) + total[:, 0]).to(self.dtype)
-            self.dv_out[self.ret_rows] = (_wide(self.dv_out[self.ret_rows]) + total[:, 1]).to(self.dtype)
+            self.dk_e[self.ret_rows] = (_wide(self.dk_e[self.ret_rows]) + total[:, 0]).to(self.dk_e.dtype)
+            self.dv_e[self.ret_rows] = (_wide(self.dv_e[self.ret_rows]) + total[:, 1]).to(self.dv_e.dtype)
         if self.n_my:
             parts = _wide(self.r_recv[self.my_q_parts, 0])                       # (world, n_my, h, d), rank order
-            self.dq_out[self.s_own_idx] = parts.sum(0).to(self.dtype)
+            self.dq_strad.copy_(parts.sum(0))
 
     def _run(self, name, fn):
         """Runs a piece eagerly, or captures it in a CUDA graph on first use and replays it afterwards."""
@@ -590,16 +581,16 @@ class HaloRunner:
         g.replay()
 
     # ---- the step
-    def forward(self, q, k, v, embed_ak=None):
-        """q, k, v: (n_owned, h, d) of the nodes this rank owns.  Returns o (n_owned, h, d), a static buffer
-        that the next forward overwrites."""
+    def forward(self, q=None, k=None, v=None, embed_ak=None):
+        """q, k, v: (n_owned, h, d) of the nodes this rank owns, embed_ak (rows, d); an argument left out means
+        the caller has already written it into q_in / k_in / v_in / ak_in.  Returns o over this rank's
+        destination rows [own non-straddlers | all straddlers]: own_rows(o) gives the (n_owned, h, d) result.
+        The tensor is reused by the next forward."""
         import torch.distributed as dist
         s = self.shard
-        self.q_in.copy_(q)
-        self.k_in.copy_(k)
-        self.v_in.copy_(v)
-        if self.ak_in is not None:
-            self.ak_in.copy_(embed_ak)
+        for buf, x in ((self.q_in, q), (self.k_in, k), (self.v_in, v), (self.ak_in, embed_ak)):
+            if x is not None and buf is not None:
+                buf.copy_(x)
         self._run("pack", self._seg_pack)
         if s.world > 1:
             dist.all_to_all_single(self.f_recv, self.f_send, output_split_sizes=self.f_recv_counts,
@@ -612,18 +603,22 @@ class HaloRunner:
                 dist.all_gather_into_tensor(self.allp, self.part, group=self.group)
             else:
                 self.allp.copy_(self.part)
-        self._run("merge", self._seg_merge)
-        return self.o_out
+            self._run("merge", self._seg_merge)
+        return self.o_loc
 
-    def backward(self, d_o):
-        """d_o: gradient of forward()'s result.  Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is this
-        rank's share in fp32.  Static buffers, overwritten by the next backward."""
+    def backward(self, d_o=None):
+        """d_o: (n_owned, h, d) gradient of own_rows(forward()), or None when already written into do_in.
+        Returns (dq_loc, dq_strad_own, dk, dv, d_embed_ak): dq over the destination rows with the summed dQ
+        of this rank's straddlers apart -- own_rows(dq_loc, dq_strad_own) is the (n_owned, h, d) gradient --,
+        dk and dv (n_owned, h, d), d_embed_ak this rank's share in fp32 or None.  Reused by the next backward."""
         import torch.distributed as dist
         s = self.shard
-        self.do_in.copy_(d_o)
-        self._run("dout", self._seg_dout)
-        if s.world > 1 and self.n_strad:
-            dist.all_reduce(self.do_strad, group=self.group)      # every row has one owner: a sum with zeros
+        if d_o is not None:
+            self.do_in.copy_(d_o)
+        if self.n_strad:
+            self._run("dout", self._seg_dout)
+            if s.world > 1:
+                dist.all_reduce(self.do_strad, group=self.group)  # every row has one owner: a sum with zeros
         self._run("backward", self._seg_backward)
         if s.world > 1:
             dist.all_to_all_single(self.r_recv[: self.n_fsend], self.r_send, output_split_sizes=self.r_recv_counts,
@@ -631,4 +626,4 @@ class HaloRunner:
         else:
             self.r_recv[: self.n_fsend].copy_(self.r_send)
         self._run("return", self._seg_return)
-        return self.dq_out, self.dk_out, self.dv_out, self.dak_out
+        return self.dq_loc, self.dq_strad, self.dk_e[: s.n_owned], self.dv_e[: s.n_owned], self.dak

@@ -158,8 +158,9 @@ def _straddle_worker(rank, world, port, n, k, out):
     # the same step through the fixed schedule with packed exchanges (HaloRunner), twice on its static buffers
     runner = sh.HaloRunner(s, plan, H, D, torch.float32, torch.device("cpu"), 0.3, T)
     for _ in range(2):
-        o_r = runner.forward(q[own], kk[own], v[own], ak).clone()
-        dq_r, dk_r, dv_r, dak_r = [x.clone() for x in runner.backward(d_o[own])]
+        o_r = runner.own_rows(runner.forward(q[own], kk[own], v[own], ak))
+        dq_l, dq_s, dk_r, dv_r, dak_r = runner.backward(d_o[own])
+        dq_r, dk_r, dv_r, dak_r = runner.own_rows(dq_l, dq_s), dk_r.clone(), dv_r.clone(), dak_r.clone()
     dist.all_reduce(dak_r)
     errs += [np.abs(o_r.numpy() - o_ref[own_np]).max(), np.abs(dq_r.numpy() - ref[0][own_np]).max(),
              np.abs(dk_r.numpy() - ref[1][own_np]).max(), np.abs(dv_r.numpy() - ref[2][own_np]).max(),

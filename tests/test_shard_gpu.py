@@ -128,9 +128,10 @@ def _nccl_worker(rank, world, port, out):
     for graphs in (False, True):
         runner = sh.HaloRunner(s, plan_s, H, D, bf, torch.device("cuda", rank), 0.125, T, graphs=graphs)
         for _ in range(3):
-            o4 = runner.forward(qb.cuda()[own], kb.cuda()[own], vb.cuda()[own], akb.cuda()).clone()
-            dq4, dk4, dv4, dak4 = [x.clone() for x in runner.backward(dob.cuda()[own])]
-        dak4 = dak4.clone()
+            o4 = runner.own_rows(runner.forward(qb.cuda()[own], kb.cuda()[own], vb.cuda()[own], akb.cuda()))
+            dq_l, dq_s, dk4, dv4, dak4 = runner.backward(dob.cuda()[own])
+            dq4, dk4, dv4 = runner.own_rows(dq_l, dq_s), dk4.clone(), dv4.clone()
+        dak4 = dak4.float().clone()
         dist.all_reduce(dak4)
         errs_bf16 += [rel(o4.double().cpu().numpy(), o_rb[own_np]), rel(dq4.double().cpu().numpy(), refb[0][own_np]),
                       rel(dk4.double().cpu().numpy(), refb[1][own_np]), rel(dv4.double().cpu().numpy(), refb[2][own_np]),

@@ -74,6 +74,18 @@ def workload_name(a):
         a.seqs, a.n, a.k, "causal" if a.causal else "bidirectional", H, D, a.dtype)
 
 
+def attention_config(a, seqs, n, k, dtype_name, causal, n_nodes, n_edges):
+    """The `config` of an attention line; both arms (ours and --impl reference) print the same dict."""
+    elem = 2 if dtype_name == "bf16" else 4
+    per_step_mb = 8 * n_nodes * H * D * elem / 1e6
+    return {"workload": "bpt_attention_fwd_bwd %dx(n=%d,k=%d,%s) h=%dx%d %s" % (
+                seqs, n, k, "causal" if causal else "bidirectional", H, D, dtype_name),
+            "nodes_per_gpu": n_nodes, "edges_per_gpu": n_edges,
+            "sharding": "independent graphs per rank, no data-path collective",
+            "l2": ("inputs+outputs %.0f MB per step exceed the 126 MB L2" if per_step_mb > 126
+                   else "inputs+outputs %.0f MB per step fit the 126 MB L2: not flushed between steps") % per_step_mb}
+
+
 def algorithmic_bytes(n_nodes, n_edges, elem_bytes):
     """Bytes a perfect kernel must move: unique Q/K/V/O (and gradient) bytes plus the int32
     CSR (indptr, indices, etype).  Forward reads Q,K,V and writes O; backward reads Q,K,V,dO
@@ -116,7 +128,7 @@ def cpu_reference_run(a, steps, warmup, min_seconds=0.0):
         step()
         done += 1
     dt = time.perf_counter() - t0
-    info = dict(cores=oracle.num_threads(), steps=done, seconds=dt, edges_per_step=E,
+    info = dict(cores=oracle.num_threads(), steps=done, seconds=dt, edges_per_step=E, nodes=N,
                 sample="1 of %d sequences (n=%d,k=%d), fp32, forward+backward, %d repetitions" %
                        (a.seqs, a.n, a.k, done))
     return E * done / dt, info
@@ -126,14 +138,16 @@ def run_reference(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(a.steps, 40))
-    value, info = cpu_reference_run(a, steps, min(a.warmup, 2))
+    steps = max(1, min(a.steps, 60))   # each step is one sequence of the batch, forward + backward, on the host cores
+    value, info = cpu_reference_run(a, steps, a.warmup)
     line = {
         "impl": "reference", "metric": "bpt_attention_edges_per_sec", "value": value, "unit": "edges/s",
-        "n_gpus": a.gpus, "steps": info["steps"], "warmup": min(a.warmup, 2),
+        "n_gpus": a.gpus, "steps": info["steps"], "warmup": a.warmup,
         "ms_per_step": 1e3 * info["seconds"] / info["steps"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(a), "timed_on": "host CPU, one sequence per step"},
+        "timed_on": "host CPU, fp32, one sequence of the batch per step",
+        "config": attention_config(a, a.seqs, a.n, a.k, a.dtype, a.causal, a.seqs * info["nodes"],
+                                   a.seqs * info["edges_per_step"]),
         "cpu_baseline": {"value": value, "unit": "edges/s", "cores": info["cores"], "kind": "port",
                          "sample": info["sample"]},
         "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -752,13 +766,7 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
         "unit": "edges/s", "n_gpus": world, "steps": steps, "blocks": len(blocks), "warmup": max(warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": dtype_name, "data": "synthetic",
-        "config": {"workload": "bpt_attention_fwd_bwd %dx(n=%d,k=%d,%s) h=%dx%d %s" % (
-                       seqs, n, k, "causal" if causal else "bidirectional", H, D, dtype_name),
-                   "nodes_per_gpu": N, "edges_per_gpu": E,
-                   "sharding": "independent graphs per rank, no data-path collective",
-                   "l2": ("inputs+outputs %.0f MB per step exceed the 126 MB L2" if 8 * N * H * D * q.element_size() > 126e6
-                          else "inputs+outputs %.0f MB per step fit the 126 MB L2: not flushed between steps") %
-                         (8 * N * H * D * q.element_size() / 1e6)},
+        "config": attention_config(a, seqs, n, k, dtype_name, causal, N, E),
         "gpu_launches": steps * len(blocks) * (launches_fwd + launches_bwd),
         "forward": {"ms": fwd_ms, "edges_per_sec": world * E / (fwd_ms * 1e-3)},
         "backward": {"ms": bwd_ms, "edges_per_sec": world * E / (bwd_ms * 1e-3)},

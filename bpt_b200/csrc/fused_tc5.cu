@@ -126,8 +126,13 @@ __global__ void __launch_bounds__(kThreads, 2) attn_forward_tc5_kernel(const Tc5
     const uint32_t my_fine = has_mb ? static_cast<uint32_t>(mb[kMbFineMask]) : 0u;  // bit per 16 columns
     const uint32_t warp_fine = my_fine | __shfl_xor_sync(0xffffffffu, my_fine, 16);
     uint32_t group_mask = 0;  // bit per 32 columns
-    for (int i = 0; i < n_mb; ++i)
-        group_mask |= static_cast<uint32_t>(p.mblocks[static_cast<int64_t>(grp[kGroupMbFirst] + i) * kMbInts + kMbChunkMask]);
+    bool group_table = false;  // some m-block of the group needs the relative-position table
+    for (int i = 0; i < n_mb; ++i) {
+        const int32_t *mbi = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + i) * kMbInts;
+        group_mask |= static_cast<uint32_t>(mbi[kMbChunkMask]);
+        group_table = group_table || mbi[kMbQrSlot] >= 0;
+    }
+    group_table = group_table && kHasBias;
     const uint8_t *et_row = p.et + (has_mb ? mb[kMbEtOff] : 0) + r16 * kTileChunk + half * 32;  // + chunk * 16 * 64
     static_assert(kTileChunk == kChunk && kMaskCols * 2 == kChunk, "plan chunking and the kernel's step agree");
 
@@ -197,39 +202,56 @@ __global__ void __launch_bounds__(kThreads, 2) attn_forward_tc5_kernel(const Tc5
     bool ok = true;
     const int c_first = first_chunk_from(0);
 
+    // Q of head h (4 pieces of the row per thread) and the K and V rows of its first chunk -> buffer b
+    auto issue_head = [&](int h, int b) {
+        const __nv_bfloat16 *src = p.q + (static_cast<int64_t>(row < 0 ? 0 : row) * H + h) * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cp_async16(base + L.q + swz(trow, half * 4 + i), src + (half * 4 + i) * 8);
+        if (c_first < n_chunks) issue_kv(h, c_first, b);
+    };
+    // the head's first MMAs: the table Q embed_ak^T and S of the first chunk (one thread)
+    auto issue_head_mma = [&](int b) {
+        if (group_table) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                mma_ss(tmem, desc_kmajor(base + L.q, ks), desc_kmajor(base + L.ak, ks), idesc_tab, ks > 0);
+            mma_commit(bar_tab);
+        }
+        if (c_first < n_chunks) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                mma_ss(tmem + col_s, desc_kmajor(base + L.q, ks), desc_kmajor(base + L.k + b * kTileBytes, ks), kIdescS, ks > 0);
+            mma_commit(bar_s);
+        }
+    };
+    if (!group_table) {  // no table in this group: every row looks up {0, ..., -inf} (entry 0 and the last one)
+        if (half == 0) {
+            asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(tab_addr), "h"(static_cast<unsigned short>(0)) : "memory");
+            asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(tab_addr + none_idx * 2), "h"(static_cast<unsigned short>(0xFC00)) : "memory");
+        }
+    }
+
+    int buf = 0;            // K/V buffer of the chunk being worked on; carried from head to head
+    bool issued_ahead = false;  // the previous head's last step already loaded this head's Q and first chunk and issued its first MMAs
     for (int h = 0; h < H; ++h) {
-        // ---- stage Q of this head (4 pieces of the row per thread) and the first chunk's K and V
-        {
-            const __nv_bfloat16 *src = p.q + (static_cast<int64_t>(row < 0 ? 0 : row) * H + h) * kHeadDim;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) cp_async16(base + L.q + swz(trow, half * 4 + i), src + (half * 4 + i) * 8);
-        }
-        if (c_first < n_chunks) issue_kv(h, c_first, 0);
-        cp_async_commit();
-        cp_async_wait_all();
-        fence_async_smem();
-        fence_before_sync();
-        if (__syncthreads_or(!ok)) break;
-        if (tid == 0) {
-            fence_after_sync();
-            if (kHasBias) {
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ss(tmem, desc_kmajor(base + L.q, ks), desc_kmajor(base + L.ak, ks), idesc_tab, ks > 0);
-                mma_commit(bar_tab);
-            }
-            if (c_first < n_chunks) {
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ss(tmem + col_s, desc_kmajor(base + L.q, ks), desc_kmajor(base + L.k, ks), kIdescS, ks > 0);
-                mma_commit(bar_s);
+        if (!issued_ahead) {
+            issue_head(h, buf);
+            cp_async_commit();
+            cp_async_wait_all();
+            fence_async_smem();
+            fence_before_sync();
+            if (__syncthreads_or(!ok)) break;
+            if (tid == 0) {
+                fence_after_sync();
+                issue_head_mma(buf);
             }
         }
+        issued_ahead = false;
         // ---- the head's table row: scale * log2(e) * <q[row], embed_ak[type]> as fp16 (each of the row's two
         // threads converts half of it); rows whose edges share one type keep zeros: the term is then a
         // per-row constant that cancels in the softmax and is added to lse
         float bias_row = 0.f;
-        if (kHasBias) {
+        if (group_table) {
             ok = ok && mbar_wait(bar_tab, n_tab_done & 1u);
             ++n_tab_done;
             fence_after_sync();
@@ -247,33 +269,31 @@ __global__ void __launch_bounds__(kThreads, 2) attn_forward_tc5_kernel(const Tc5
                 }
             }
             if (half) asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(tab_addr + tq16 * 2), "h"(static_cast<unsigned short>(0xFC00)) : "memory");
-            if (!use_qr && row >= 0 && half == 0) {
-                int type = mb[kMbRowEtOff + r16];
-                type = type < 0 ? 0 : (type < p.n_etypes ? type : p.n_etypes - 1);
-                const uint4 *qa = reinterpret_cast<const uint4 *>(p.q + (static_cast<int64_t>(row) * H + h) * kHeadDim);
-                const uint4 *aa = reinterpret_cast<const uint4 *>(p.ak + static_cast<int64_t>(type) * kHeadDim);
-                float sum = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint4 x = __ldg(qa + i), y = __ldg(aa + i);
-                    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[u]));
-                        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&yw[u]));
-                        sum = fmaf(a.x, b.x, fmaf(a.y, b.y, sum));
-                    }
-                }
-                bias_row = sum * sl2;
-            }
-            pair_barrier(quarter);  // the row's other thread wrote the other half of the table row
-        } else {
-            if (half == 0) asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(tab_addr), "r"(0xFC000000u) : "memory");  // {0, -inf}
-            pair_barrier(quarter);
         }
+        if (kHasBias && !use_qr && row >= 0 && half == 0) {
+            // a row whose edges share one type: <q[row], embed_ak[type]> from the staged Q tile and embed_ak rows
+            int type = mb[kMbRowEtOff + r16];
+            type = type < 0 ? 0 : (type < p.n_etypes ? type : p.n_etypes - 1);
+            float sum = 0.f;
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) {
+                const uint4 x = *reinterpret_cast<const uint4 *>(sm + L.q + swz(trow, piece));
+                const uint4 y = type < tq16 ? *reinterpret_cast<const uint4 *>(sm + L.ak + swz(type, piece))
+                                            : __ldg(reinterpret_cast<const uint4 *>(p.ak + static_cast<int64_t>(type) * kHeadDim) + piece);
+                const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xw[u]));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&yw[u]));
+                    sum = fmaf(a.x, b.x, fmaf(a.y, b.y, sum));
+                }
+            }
+            bias_row = sum * sl2;
+        }
+        pair_barrier(quarter);  // the row's other thread wrote the other half of the table row
 
         float m_run = -INFINITY, l_run = 0.f;  // m_run is shared by the row's two threads, l_run is this thread's part
-        int n_pv = 0, buf = 0;
+        int n_pv = 0;
         int c = c_first;
         bool aborted = false;
         while (c < n_chunks) {
@@ -298,6 +318,13 @@ __global__ void __launch_bounds__(kThreads, 2) attn_forward_tc5_kernel(const Tc5
             ok = ok && mbar_wait(bar_s, n_s_done & 1u);
             ++n_s_done;
             fence_after_sync();
+            // last step of the head: S, the last MMA that reads Q, is done, so the next head's Q and first chunk
+            // travel while this step's softmax runs
+            const bool ahead = nc >= n_chunks && h + 1 < H;
+            if (ahead) {
+                issue_head(h + 1, buf ^ 1);
+                cp_async_commit();
+            }
 
             // scores of the two 16-column units of this thread, in the log2 domain, mask applied
             const uint32_t act = (warp_fine >> (4 * c + 2 * half)) & 3u;  // uniform over the warp
@@ -382,8 +409,11 @@ __global__ void __launch_bounds__(kThreads, 2) attn_forward_tc5_kernel(const Tc5
                         mma_ss(tmem + col_s, desc_kmajor(base + L.q, ks), desc_kmajor(base + L.k + (buf ^ 1) * kTileBytes, ks),
                                kIdescS, ks > 0);
                     mma_commit(bar_s);
+                } else if (ahead) {
+                    issue_head_mma(buf ^ 1);
                 }
             }
+            issued_ahead = ahead;
             ++n_pv;
             c = nc;
             buf ^= 1;

@@ -6,6 +6,15 @@
 namespace bpt {
 
 constexpr float kLog2e = 1.4426950408889634f;
+
+// 2^x in one instruction of the special-function unit (about 2 ulp; denormal results flush to zero;
+// ex2(-inf) = 0).  The bf16 tensor-core kernels use it for softmax weights, whose rounding to bf16
+// is 2^-9 relative; the fp32 kernels keep exp2f.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 constexpr float kLn2 = 0.6931471805599453f;
 
 // Dropout on the attention weights (modules/attention.py:73: drop_att between the edge softmax and the

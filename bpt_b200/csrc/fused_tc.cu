@@ -136,7 +136,7 @@ attn_forward_tile_kernel(const TcParams p) {
                                            kTilesPerBlock * p.max_cols_pad);
     ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
-    const int tab_stride = p.t_max + 8;  // t_max types + the -inf entry, padded; >= 8
+    const int tab_stride = p.t_max + 10;  // t_max types + the -inf entry, padded to an odd number of words (rows spread over the banks)
     // embed_ak rows [0, t_max), staged once per block (16-byte aligned: every region before it is)
     const uint32_t s_ak_addr = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
@@ -173,15 +173,20 @@ attn_forward_tile_kernel(const TcParams p) {
         for (int i = tid; i < ncols_pad; i += kTileThreads) s_cols[i] = gc[i];
     }
 
-    // 32 rows of K or V of head h for step j -> the warp's buffer (16-byte pieces, piece index XOR (row & 7))
+    // 32 rows of K or V of head h for step j -> the warp's buffer (16-byte pieces, piece index XOR (row & 7)).
+    // Lane l copies piece (l & 7) of rows (l >> 3) + 4 i: the swizzled offset takes two values per lane
+    // (i even / odd) plus 1024 bytes per pair of i, and a row's address is one widening multiply-add.
+    const int copy_row = lane >> 3, copy_piece = lane & 7;
+    const uint32_t copy_even = copy_row * kRowBytes + ((copy_piece ^ copy_row) << 4);
+    const uint32_t copy_odd = (copy_row + 4) * kRowBytes + ((copy_piece ^ (copy_row + 4)) << 4);
+    const uint32_t row_pitch = static_cast<uint32_t>(H) * kRowBytes;  // bytes between consecutive nodes
     auto issue_rows = [&](uint32_t dst, const __nv_bfloat16 *__restrict__ base, int h, int j) {
+        const char *src = reinterpret_cast<const char *>(base) + (h * kRowBytes + copy_piece * 16);
+        const int32_t *cj = s_cols + j * kStep + copy_row;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int id = i * 32 + lane;
-            const int r = id >> 3, piece = id & 7;
-            cp_async16(dst + r * kRowBytes + ((piece ^ (r & 7)) << 4),
-                       base + (static_cast<int64_t>(s_cols[j * kStep + r]) * H + h) * kHeadDim + piece * 8);
-        }
+        for (int i = 0; i < 8; ++i)
+            cp_async16(dst + (i >> 1) * (8 * kRowBytes) + ((i & 1) ? copy_odd : copy_even),
+                       src + static_cast<uint64_t>(static_cast<uint32_t>(cj[4 * i])) * row_pitch);
     };
 
     for (int mbi = 0; mbi < n_mblocks; ++mbi) {
@@ -242,7 +247,10 @@ attn_forward_tile_kernel(const TcParams p) {
                 load_row_frag(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim, t, q_lo);
                 load_row_frag(p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim, t, q_hi);
             }
-            float bias_lo = 0.f, bias_hi = 0.f;  // per-row constant of m-blocks without a table (log2 domain)
+            // per-row constant of m-blocks without a table (log2 domain), parked in the unused table entries
+            // [2, 4) of the row until the epilogue
+            float *s_bias_lo = reinterpret_cast<float *>(s_tab + g * tab_stride + 2);
+            float *s_bias_hi = reinterpret_cast<float *>(s_tab + (g + 8) * tab_stride + 2);
             if (use_qr) {
                 // table[row][type] = scale * log2(e) * <q[row], ak[type]> for the types of this m-block
                 for (int nt = 0; nt < tq; nt += 8) {
@@ -287,8 +295,11 @@ attn_forward_tile_kernel(const TcParams p) {
                         }
                         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                        (half ? bias_hi : bias_lo) = sum * sl2;
+                        if (t == 0) *(half ? s_bias_hi : s_bias_lo) = sum * sl2;
                     }
+                } else if (t == 0) {
+                    *s_bias_lo = 0.f;
+                    *s_bias_hi = 0.f;
                 }
             }
             __syncwarp();
@@ -353,7 +364,7 @@ attn_forward_tile_kernel(const TcParams p) {
                 const float mn_lo = fmaxf(m_lo, cmax_lo), mn_hi = fmaxf(m_hi, cmax_hi);
                 const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
                 if (__any_sync(0xffffffffu, mn_lo != m_lo || mn_hi != m_hi)) {  // some row's maximum moved
-                    const float corr_lo = exp2f(m_lo - ms_lo), corr_hi = exp2f(m_hi - ms_hi);
+                    const float corr_lo = ex2(m_lo - ms_lo), corr_hi = ex2(m_hi - ms_hi);
                     l_lo *= corr_lo;
                     l_hi *= corr_hi;
 #pragma unroll
@@ -366,10 +377,10 @@ attn_forward_tile_kernel(const TcParams p) {
                 }
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
-                    s[nt][0] = exp2f(s[nt][0] - ms_lo);
-                    s[nt][1] = exp2f(s[nt][1] - ms_lo);
-                    s[nt][2] = exp2f(s[nt][2] - ms_hi);
-                    s[nt][3] = exp2f(s[nt][3] - ms_hi);
+                    s[nt][0] = ex2(s[nt][0] - ms_lo);
+                    s[nt][1] = ex2(s[nt][1] - ms_lo);
+                    s[nt][2] = ex2(s[nt][2] - ms_hi);
+                    s[nt][3] = ex2(s[nt][3] - ms_hi);
                     l_lo += s[nt][0] + s[nt][1];
                     l_hi += s[nt][2] + s[nt][3];
                 }
@@ -416,10 +427,10 @@ attn_forward_tile_kernel(const TcParams p) {
             l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int row = half ? row_hi : row_lo;
+                const int row = kDrop ? (half ? row_hi : row_lo) : mb[kMbRowOff + g + 8 * half];
                 if (row < 0) continue;
                 const int slot = mb[kMbSlotOff + g + 8 * half];
-                const float m = (half ? m_hi : m_lo) + (half ? bias_hi : bias_lo);
+                const float m = (half ? m_hi : m_lo) + (use_qr ? 0.f : *(half ? s_bias_hi : s_bias_lo));
                 const float l = half ? l_hi : l_lo;
                 if (slot < 0) {
                     const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -448,7 +459,7 @@ attn_forward_tile_kernel(const TcParams p) {
 size_t tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
     return static_cast<size_t>(kWarps) * kKvStageBytes + static_cast<size_t>(kTilesPerBlock) * max_cols_pad * 4 +
            static_cast<size_t>(kTilesPerBlock) * kTileRows * (max_cols_pad + kEtPad) * et_bytes +
-           static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2 + static_cast<size_t>(t_max) * kRowBytes;
+           static_cast<size_t>(kWarps) * kTileRows * (t_max + 10) * 2 + static_cast<size_t>(t_max) * kRowBytes;
 }
 
 template <typename ET, bool kHasBias, bool kDrop>

@@ -69,11 +69,6 @@ __host__ __device__ inline Tc5Smem tc5_smem_layout(int max_cols_pad, int tq16) {
     return s;
 }
 
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
 __device__ __forceinline__ float lds_half(uint32_t addr) {
     unsigned short v;
     asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));

@@ -86,15 +86,21 @@ attn_backward_dkv_tile_kernel(const DkvParams p) {
     }
     const int n_steps = ncols_pad / kDkvStep;
     // dO and Q rows of head h for the 16 destinations of step j -> buffer b of the warp
+    // Lane l copies piece (l & 7) of rows (l >> 3) + 4 i: two swizzled offsets per lane (i even / odd)
+    // plus 1024 bytes per pair of i; a row's offset in dO and Q is one widening multiply-add.
+    const int copy_row = lane >> 3, copy_piece = lane & 7;
+    const uint32_t copy_even = copy_row * kRowBytes + ((copy_piece ^ copy_row) << 4);
+    const uint32_t copy_odd = (copy_row + 4) * kRowBytes + ((copy_piece ^ (copy_row + 4)) << 4);
+    const uint32_t row_pitch = static_cast<uint32_t>(H) * kRowBytes;  // bytes between consecutive nodes
     auto issue_rows = [&](int h, int j, int b) {
+        const uint64_t head_off = static_cast<uint64_t>(h * kRowBytes + copy_piece * 16);
+        const int32_t *cj = s_cols + j * kDkvStep + copy_row;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int id = i * 32 + lane;
-            const int r = id >> 3, piece = id & 7;
-            const int64_t off = (static_cast<int64_t>(s_cols[j * kDkvStep + r]) * H + h) * kHeadDim + piece * 8;
-            const uint32_t dst = b * kDkvBufBytes + r * kRowBytes + ((piece ^ (r & 7)) << 4);
-            cp_async16(s_do + dst, p.d_o + off);
-            cp_async16(s_do + kDkvBufBytes / 2 + dst, p.q + off);
+            const uint64_t off = static_cast<uint64_t>(static_cast<uint32_t>(cj[4 * i])) * row_pitch + head_off;
+            const uint32_t dst = s_do + b * kDkvBufBytes + (i >> 1) * (8 * kRowBytes) + ((i & 1) ? copy_odd : copy_even);
+            cp_async16(dst, reinterpret_cast<const char *>(p.d_o) + off);
+            cp_async16(dst + kDkvBufBytes / 2, reinterpret_cast<const char *>(p.q) + off);
         }
     };
     for (int mbi = 0; mbi < grp[kGroupMbCount]; ++mbi) {
@@ -311,7 +317,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                                            kTilesPerBlock * p.max_cols_pad);
     ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
-    const int tab_stride = p.t_max + 8;
+    const int tab_stride = p.t_max + 10;  // an odd number of words: the 16 rows spread over the banks
     const uint32_t s_ak = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
     if (kHasBias) {
@@ -343,15 +349,21 @@ attn_backward_dq_tile_kernel(const DqParams p) {
     }
     const int n_steps = ncols_pad / kDqStep;
     // K and V rows of head h for the 16 columns of step j -> buffer b of the warp (K rows, then V rows)
+    // Lane l copies piece (l & 7) of rows (l >> 3) + 4 i: two swizzled offsets per lane (i even / odd)
+    // plus 1024 bytes per pair of i; a row's offset in K and V is one widening multiply-add.
+    const int copy_row = lane >> 3, copy_piece = lane & 7;
+    const uint32_t copy_even = copy_row * kRowBytes + ((copy_piece ^ copy_row) << 4);
+    const uint32_t copy_odd = (copy_row + 4) * kRowBytes + ((copy_piece ^ (copy_row + 4)) << 4);
+    const uint32_t row_pitch = static_cast<uint32_t>(H) * kRowBytes;  // bytes between consecutive nodes
     auto issue_kv = [&](int h, int j, int b) {
+        const uint64_t head_off = static_cast<uint64_t>(h * kRowBytes + copy_piece * 16);
+        const int32_t *cj = s_cols + j * kDqStep + copy_row;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int id = i * 32 + lane;
-            const int r = id >> 3, piece = id & 7;
-            const int64_t off = (static_cast<int64_t>(s_cols[j * kDqStep + r]) * H + h) * kHeadDim + piece * 8;
-            const uint32_t dst = s_k + b * kDqBufBytes + r * kRowBytes + ((piece ^ (r & 7)) << 4);
-            cp_async16(dst, p.k + off);
-            cp_async16(dst + kDqBufBytes / 2, p.v + off);
+            const uint64_t off = static_cast<uint64_t>(static_cast<uint32_t>(cj[4 * i])) * row_pitch + head_off;
+            const uint32_t dst = s_k + b * kDqBufBytes + (i >> 1) * (8 * kRowBytes) + ((i & 1) ? copy_odd : copy_even);
+            cp_async16(dst, reinterpret_cast<const char *>(p.k) + off);
+            cp_async16(dst + kDqBufBytes / 2, reinterpret_cast<const char *>(p.v) + off);
         }
     };
     for (int mbi = 0; mbi < n_mblocks; ++mbi) {
@@ -498,7 +510,8 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             }
             primed_step = -1;
             int buf = 0;
-            // cell positions in lane order (cell_pos_index), fetched one step ahead: column groups 2j, 2j+1
+            // cell positions in lane order (cell_pos_index) of column groups 2j, 2j+1; the next step's are
+            // fetched as soon as this step's have been used
             const int4 *pos_base = reinterpret_cast<const int4 *>(cell_pos) + lane;
             int4 pos_cur[2] = {make_int4(-1, -1, -1, -1), make_int4(-1, -1, -1, -1)};
             if (j < n_steps) {
@@ -507,12 +520,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
             }
             while (j < n_steps) {
                 const int nj = next_step(j);
-                int4 pos_next[2] = {pos_cur[0], pos_cur[1]};
-                if (nj < n_steps) {
-                    issue_kv(h, nj, buf ^ 1);
-                    pos_next[0] = __ldg(pos_base + (nj * 2) * 32);
-                    pos_next[1] = __ldg(pos_base + (nj * 2 + 1) * 32);
-                }
+                if (nj < n_steps) issue_kv(h, nj, buf ^ 1);
                 cp_async_commit();
                 cp_async_wait_one();  // this step's rows have landed; the newest group is the next step's
                 __syncwarp();
@@ -539,10 +547,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                     mma_bf16(s[nt], q_lo[2], q_hi[2], q_lo[3], q_hi[3], b0[2], b0[3]);
                     mma_bf16(s[nt], q_lo[4], q_hi[4], q_lo[5], q_hi[5], b1[0], b1[1]);
                     mma_bf16(s[nt], q_lo[6], q_hi[6], q_lo[7], q_hi[7], b1[2], b1[3]);
-                }
-                // probabilities, per-edge scratch, dS (kept in s)
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+                    // probabilities, per-edge scratch, dS (kept in s)
                     const int c = j * kDqStep + nt * 8 + 2 * t;
                     uint32_t i_lo0, i_lo1, i_hi0, i_hi1;
                     load_idx_pair(s_idx + g * idx_stride + c, i_lo0, i_lo1);
@@ -563,12 +568,17 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
+                        const float pr = ex2(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
                         // dS = scale * p * (dp - delta) with dp the gradient of p, i.e. keep * <dO, v>; the source
                         // side needs the weight V was summed with, keep * p
                         s[nt][i] = p.scale * pr * (dp[nt][i] * keep[i] - (i < 2 ? delta_lo : delta_hi));
                         if (pos[i] >= 0) ps_h[pos[i]] = pack_bf16(pr * keep[i], s[nt][i]);
                     }
+                }
+                // the next step's cell positions travel during dQ += dS K and the next step's first products
+                if (nj < n_steps) {
+                    pos_cur[0] = __ldg(pos_base + (nj * 2) * 32);
+                    pos_cur[1] = __ldg(pos_base + (nj * 2 + 1) * 32);
                 }
                 // dQ += dS K
                 {
@@ -585,8 +595,6 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                     }
                 }
                 __syncwarp();  // these buffers are refilled by the step after next
-                pos_cur[0] = pos_next[0];
-                pos_cur[1] = pos_next[1];
                 j = nj;
                 buf ^= 1;
             }
@@ -882,7 +890,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes +
                             static_cast<size_t>(kTilesPerBlock) * p.max_cols_pad * 4 +
                             static_cast<size_t>(kTilesPerBlock) * kTileRows * (p.max_cols_pad + kIdxPad) * dst_tiles->et_bytes +
-                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2 +
+                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 10) * 2 +
                             static_cast<size_t>(p.t_max) * kRowBytes;
         if (smem > 227 * 1024)
             return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: tile plan needs %zu bytes of shared memory", smem);

@@ -57,6 +57,10 @@ SIGNATURES = {
     "bpt_tile_plan_sizes": (_int, [_vp, _vp]),
     "bpt_tile_plan_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "bpt_tile_plan_destroy": (None, [_vp]),
+    "bpt_tile_plan_create_device": (_vp, [_vp, _vp, _i64, _i64, _int, _int, _dbl, _int, _int, _int, _int, _vp]),
+    "bpt_tile_plan_device_sizes": (_int, [_vp, _vp]),
+    "bpt_tile_plan_device_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
+    "bpt_tile_plan_device_destroy": (None, [_vp]),
     "bpt_add_layer_norm": (_int, [_vp, _vp, _vp, _vp, _dbl, _vp, _i64, _int, _int, _vp]),
     "bpt_dense_blocks_fill": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "bpt_export_in_csr": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),

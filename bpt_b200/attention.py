@@ -114,7 +114,61 @@ class TilePlan:
     carry the edge's position in the in-CSR (source side of bpt_attn_backward_tc)."""
 
     def __init__(self, plan, transposed=False, min_density=0.25, max_cols=384, group_rows=16, col_block=128,
-                 simt_max_degree=0, max_mblocks=1, join_dense=False):
+                 simt_max_degree=0, max_mblocks=1, join_dense=False, planner=None):
+        """planner: "device" (the default; BPT_TILE_PLANNER overrides it) plans with CUDA kernels from the CSR
+        arrays where the plan keeps them; "host" exports the CSR, plans in C++ on the host and uploads.  Both
+        give the same arrays; simt_max_degree and join_dense exist on the host planner only."""
+        planner = planner or TILE_PLANNER
+        if planner not in ("device", "host"):
+            raise ValueError("TilePlan: planner must be 'device' or 'host'")
+        if simt_max_degree or join_dense:
+            planner = "host"
+        self.planner = planner
+        self.n_etypes = plan.n_etypes
+        self.transposed = transposed
+        self._ws = {}
+        if planner == "device":
+            self._plan_on_device(plan, transposed, min_density, max_cols, group_rows, col_block, max_mblocks)
+        else:
+            self._plan_on_host(plan, transposed, min_density, max_cols, group_rows, col_block, simt_max_degree,
+                               max_mblocks, join_dense)
+
+    def _plan_on_device(self, plan, transposed, min_density, max_cols, group_rows, col_block, max_mblocks):
+        L = _lib.lib()
+        dev = plan.device
+        with torch.cuda.device(dev):
+            handle = L.bpt_tile_plan_create_device(plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes,
+                                                   plan.n_edges, plan.n_etypes, int(bool(transposed)),
+                                                   float(min_density), int(max_cols), int(group_rows), int(col_block),
+                                                   int(max_mblocks), _lib.stream())
+            if not handle:
+                _lib.check(1)
+            try:
+                sizes = (ctypes.c_int64 * 13)()
+                _lib.check(L.bpt_tile_plan_device_sizes(handle, ctypes.addressof(sizes)))
+                (self.n_groups, self.n_mblocks, n_cols, self.n_cells, self.n_split, self.n_slots, self.t_max,
+                 self.max_cols_pad, self.max_mblocks, self.max_qr_slots, self.n_row_items,
+                 self.n_dense_groups, max_et) = [int(x) for x in sizes]
+                self.n_cols = n_cols
+                self.et_bytes = 1 if transposed or max_et < 248 else 2
+                i32 = dict(dtype=torch.int32, device=dev)
+                self.groups = torch.empty(max(self.n_groups * 8, 1), **i32)
+                self.mblocks = torch.empty(max(self.n_mblocks * 56, 1), **i32)
+                self.cols = torch.empty(max(n_cols, 1), **i32)
+                self.et = None if transposed else torch.empty(max(self.n_cells, 1) * self.et_bytes, dtype=torch.uint8,
+                                                              device=dev)
+                self.cellpos = torch.empty(max(self.n_cells, 1), **i32)
+                self.split = torch.empty(max(self.n_split * 4, 1), **i32)
+                self.items = torch.empty(1, **i32)
+                _lib.check(L.bpt_tile_plan_device_export(
+                    handle, self.groups.data_ptr(), self.mblocks.data_ptr(), self.cols.data_ptr(),
+                    None if self.et is None else self.et.data_ptr(), self.et_bytes, self.cellpos.data_ptr(),
+                    self.split.data_ptr(), _lib.stream()))
+            finally:
+                L.bpt_tile_plan_device_destroy(handle)
+
+    def _plan_on_host(self, plan, transposed, min_density, max_cols, group_rows, col_block, simt_max_degree,
+                      max_mblocks, join_dense):
         L = _lib.lib()
         E, T = plan.n_edges, plan.n_etypes
         n_rows = plan.n_src if transposed else plan.n_nodes
@@ -137,6 +191,7 @@ class TilePlan:
             (self.n_groups, self.n_mblocks, n_cols, self.n_cells, self.n_split, self.n_slots, self.t_max,
              self.max_cols_pad, self.max_mblocks, self.max_qr_slots, self.n_row_items,
              self.n_dense_groups) = [int(x) for x in sizes]
+            self.n_cols = n_cols
             max_et = 0 if transposed or not E else int(extra[:E].max())
             self.et_bytes = 1 if max_et < 248 else 2  # 8-bit cells: types and the "no edge" table index fit a byte
             groups = np.empty(max(self.n_groups * 8, 1), np.int32)
@@ -160,9 +215,6 @@ class TilePlan:
         self.cellpos = torch.from_numpy(cellpos).to(dev)
         self.split = torch.from_numpy(split).to(dev)
         self.items = torch.from_numpy(items).to(dev)
-        self.n_etypes = T
-        self.transposed = transposed
-        self._ws = {}
 
     def struct(self):
         """The bpt_tile_plan_t view of the device arrays."""
@@ -185,6 +237,7 @@ class TilePlan:
         return ws
 
 
+TILE_PLANNER = os.environ.get("BPT_TILE_PLANNER", "device")
 MAX_BLOCK_SMEM = 227 * 1024  # shared memory one thread block can have on this GPU
 
 

@@ -304,6 +304,27 @@ int bpt_tile_plan_sizes(const void *handle, int64_t *sizes);
 int bpt_tile_plan_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols, void *et,
                          int et_bytes, int32_t *cell_pos, int32_t *split_rows, int32_t *row_items);
 void bpt_tile_plan_destroy(void *handle);
+
+/* The same planner on the device (replaces, for a batch shape not seen before, the per-batch host work
+ * of graph/base.py:71-86 plus the export, host planning and upload of the calls above).  Reads the
+ * in-CSR (transposed = 0: rows = destinations, cells carry edge types) or the out-CSR (transposed = 1:
+ * rows = sources, cells carry positions in the in-CSR) of a bpt_attn_plan_build plan where it lies and
+ * produces, array for array, what bpt_tile_plan_create + bpt_tile_plan_export produce for the same
+ * parameters with simt_max_degree = 0 and join_dense = 0.  It allocates its own device memory
+ * (temporaries are freed before it returns, the plan's arrays by bpt_tile_plan_device_destroy) and
+ * waits for the stream three times to learn array sizes.  bpt_tile_plan_device_sizes fills sizes[13]:
+ * the twelve of bpt_tile_plan_sizes and the largest edge type (-1 without edges).
+ * bpt_tile_plan_device_export copies into DEVICE arrays of those sizes (any of them may be NULL) and
+ * waits for the stream. */
+void *bpt_tile_plan_create_device(const void *attn_plan, const int32_t *counts_host, int64_t n_nodes,
+                                  int64_t n_edges, int n_etypes, int transposed, double min_density,
+                                  int max_cols, int group_rows, int col_block, int max_mblocks,
+                                  bpt_stream_t stream);
+int bpt_tile_plan_device_sizes(const void *handle, int64_t *sizes);
+int bpt_tile_plan_device_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols,
+                                void *et, int et_bytes, int32_t *cell_pos, int32_t *split_rows,
+                                bpt_stream_t stream);
+void bpt_tile_plan_device_destroy(void *handle);
 int bpt_export_in_csr(const void *plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
                       int n_etypes, int32_t *in_indptr_host, int32_t *in_src_host, int32_t *in_etype_host,
                       bpt_stream_t stream);

@@ -607,7 +607,7 @@ def run_chain(a):
 # (bidirectional, bf16): bytes per edge, keyed by the kernel that was captured.  A kernel without an entry
 # (or another shape) reports traffic = null rather than a stale figure.
 FORWARD_TRAFFIC_PER_EDGE = {
-    "attn_forward_tile_kernel": {"bytes_per_edge": 151.35e6 / 1491572,
+    "attn_forward_tile_kernel": {"bytes_per_edge": (123.61e6 + 18.83e6) / 1491572,
                                  "source": "ncu dram__bytes, 2 x (n=8192,k=4), profiles/attn_tile_kernels_bf16_n8192_k4.md"},
     "attn_forward_tc5_kernel": {"bytes_per_edge": (112.53e6 + 20.41e6) / 1491572,
                                 "source": "ncu dram__bytes, 2 x (n=8192,k=4), profiles/attn_forward_tc5_bf16_n8192_k4.md"},

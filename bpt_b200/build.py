@@ -65,5 +65,41 @@ def build(force=False, verbose=False):
     return LIB_PATH
 
 
+EXT_SRC = os.path.join(PKG_DIR, "csrc_torch", "graphop_ext.cpp")
+EXT_NAME = "_graphop_ext"
+
+
+def ext_path():
+    import sysconfig
+    return os.path.join(PKG_DIR, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_torch_ext(force=False):
+    """Compile the thin torch C++ extension (csrc_torch/graphop_ext.cpp) in-tree with g++ against the
+    installed torch and link it to libbpt_b200.so (found through $ORIGIN at run time)."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension
+    out = ext_path()
+    deps = [EXT_SRC, os.path.join(os.path.dirname(PKG_DIR), "include", "bpt_b200.h"), os.path.abspath(__file__)]
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= max(os.path.getmtime(p) for p in deps):
+        return out
+    build()  # the library the extension links to
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-w", EXT_SRC,
+           "-DTORCH_EXTENSION_NAME=" + EXT_NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    for inc in cpp_extension.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include"]:
+        cmd += ["-I", inc]
+    cmd += ["-L", torch_lib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+            "-L", PKG_DIR, "-l:libbpt_b200.so", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+    tmp = out + ".tmp%d" % os.getpid()
+    subprocess.check_call(cmd + ["-o", tmp])
+    os.replace(tmp, out)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--no-torch-ext" not in sys.argv:
+        print(build_torch_ext(force="--force" in sys.argv))

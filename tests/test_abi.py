@@ -71,3 +71,26 @@ def test_tile_kernel_shared_memory_query():
     assert 0 < L.bpt_attn_tc_smem_bytes(384, 72, 1) <= 113 * 1024
     assert L.bpt_attn_tc_smem_bytes(384, 904, 2) > 227 * 1024
     assert L.bpt_attn_tc_smem_bytes(384, 72, 3) == 0 and L.bpt_attn_tc_smem_bytes(-64, 72, 1) == 0
+
+
+def test_torch_extension_exports_the_reference_module_surface():
+    """bpt_b200._graphop_ext (csrc_torch/graphop_ext.cpp) carries the eight names the reference's module
+    exports at graph_kernel/graphop.cpp:216-225 and refuses CPU tensors with a RuntimeError, as CHECK_INPUT
+    does (graphop.cpp:4-6).  No kernel is launched."""
+    import torch
+    import bpt_b200
+    import bpt_b200.graphop
+    from bpt_b200 import build as lib_build
+    lib_build.build_torch_ext()
+    ext = bpt_b200.graphop_extension()
+    names = ["maskedmm_csr_forward", "maskedmm_csr_backward", "node_mul_edge_forward", "node_mul_edge_backward",
+             "sparse_softmax_forward", "sparse_softmax_backward", "vector_spmm_forward", "vector_spmm_backward"]
+    assert sorted(n for n in dir(ext) if not n.startswith("_")) == sorted(names)
+    assert sorted(names) == sorted(bpt_b200.graphop.__all__)
+    idx = torch.zeros(2, dtype=torch.long)
+    with pytest.raises(RuntimeError):
+        ext.sparse_softmax_forward(idx, idx, idx, torch.zeros(2))
+    installed = bpt_b200.install_dropin("extension")[0]
+    import graphop
+    assert graphop is installed is ext
+    assert bpt_b200.install_dropin("ctypes")[0] is bpt_b200.graphop

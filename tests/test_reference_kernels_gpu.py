@@ -166,20 +166,26 @@ def test_chained_layer_and_fused_call_match_reference_kernels(oracle_lib, ref_gr
             assert rel_err(a.float().cpu(), b.cpu()) < tol
 
 
-def test_reference_block_runs_unchanged_on_this_library(oracle_lib, ref_graphop):
+@pytest.mark.parametrize("binding", ["extension", "ctypes"])
+def test_reference_block_runs_unchanged_on_this_library(oracle_lib, ref_graphop, binding):
     """modules/attention.py:54-81 -- the reference's BPTBlock.forward(g, csr), its file unchanged --
-    with `graphop` resolved to this library (bpt_b200.install_dropin), against the same block on the
-    reference's own kernels and against the re-hosted bpt_b200.model.BPTBlock with the same weights."""
+    with `graphop` resolved to this library (bpt_b200.install_dropin: the torch C++ extension or the
+    ctypes module), against the same block on the reference's own kernels and against the re-hosted
+    bpt_b200.model.BPTBlock with the same weights."""
     import bpt_b200
+    import bpt_b200.graphop
     from bpt_b200 import csr as csrmod, graphbuilder
     from bpt_b200.attention import AttentionPlan
     from bpt_b200.model import BPTBlock
-    ours = build_ref_graphop.load_modules(bpt_b200.install_dropin()[0], REF_ROOT)
+    installed = bpt_b200.install_dropin(binding)[0]
+    assert sys.modules["graphop"] is installed
+    assert installed is (bpt_b200.graphop_extension() if binding == "extension" else bpt_b200.graphop)
+    ours = build_ref_graphop.load_modules(installed, REF_ROOT)
     theirs = build_ref_graphop.load_modules(ref_graphop, REF_ROOT)
     if ours is None:
         pytest.skip("the reference's modules/attention.py is neither mounted nor compiled")
     # the module objects really are bound to different graphop implementations
-    assert ours[0].sparse_softmax_forward is bpt_b200.graphop.sparse_softmax_forward
+    assert ours[0].sparse_softmax_forward is installed.sparse_softmax_forward
     assert theirs[0].sparse_softmax_forward is ref_graphop.sparse_softmax_forward
     torch.manual_seed(0)
     graphs = [graphbuilder.BinaryPartition(n, False, 4, 10) for n in (512, 300, 513)]
@@ -214,4 +220,4 @@ def test_reference_block_runs_unchanged_on_this_library(oracle_lib, ref_graphop)
     assert rel_err(out.detach().cpu(), outs[1].cpu()) < 1e-5
     for a, b in zip([h_in.grad] + [p.grad for p in mine.parameters()], grads[1]):
         assert rel_err(a.cpu(), b.cpu()) < 1e-4
-    assert "graphop" in sys.modules and sys.modules["graphop"] is bpt_b200.graphop
+    assert "graphop" in sys.modules and sys.modules["graphop"] is installed

@@ -6,6 +6,9 @@
 // row, every output element has one writer and a fixed summation order, and blocks of the
 // row's other chunks return at once.  Per-edge outputs (the SDDMM-type operators) have no
 // cross-chunk reduction and keep one block per chunk.
+#include <algorithm>
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace bpt {
@@ -132,6 +135,252 @@ row_sum_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indp
 }
 static_assert(kRowWarps * 32 == 32 * kRowCols, "one thread per column of a pass in the final sum");
 
+// The same row sums for fp32 rows of 128, 256, 384 or 512 columns (head width a multiple of 4), the shapes
+// of the attention layers.  One block per SM-sized share of the chunk list; its 16 warps take the rows
+// that start in that share round-robin, so at any time the block works on ~16 neighbouring rows, whose
+// gathered rows overlap heavily on binary-partition graphs and are then served by the L1 instead of the
+// L2 (the generic kernel gives every row its own block, and neighbouring rows land on different SMs).
+// A warp owns a whole row: lane l holds columns 4 l + 128 u as float4 accumulators (kVec = columns / 128
+// of them), every gathered row is read with 16-byte loads, two entries are in flight per step, and
+// nothing is combined across warps.  One writer per output element; a row's entries are added in CSR
+// order, even and odd entries in two partial sums.
+constexpr int kWideWarps = 16;
+constexpr int kWideLongRow = 256;  // rows with more entries are summed by the whole block
+
+// acc0/acc1 += W[e] * X-row for the entries [beg, end) taken `step` apart (two in flight)
+template <int kVec, bool kEdgeX>
+__device__ __forceinline__ void wide_accumulate(const int64_t *__restrict__ eid, const int64_t *__restrict__ indices,
+                                                int64_t beg, int64_t end, const float *__restrict__ W,
+                                                const float *__restrict__ X, int h, int d, int hd,
+                                                const int (&head)[kVec], const int (&xpiece)[kVec],
+                                                float4 (&acc0)[kVec], float4 (&acc1)[kVec]) {
+    int64_t k = beg;
+    for (; k + 1 < end; k += 2) {
+        const int64_t e0 = eid[k], e1 = eid[k + 1];
+        const float4 *x0 = reinterpret_cast<const float4 *>(kEdgeX ? X + e0 * d : X + indices[k] * hd);
+        const float4 *x1 = reinterpret_cast<const float4 *>(kEdgeX ? X + e1 * d : X + indices[k + 1] * hd);
+        float4 v0[kVec], v1[kVec];
+        float w0[kVec], w1[kVec];
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) {
+            v0[u] = __ldg(x0 + xpiece[u]);
+            v1[u] = __ldg(x1 + xpiece[u]);
+            w0[u] = __ldg(W + e0 * h + head[u]);
+            w1[u] = __ldg(W + e1 * h + head[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) {
+            acc0[u].x = fmaf(w0[u], v0[u].x, acc0[u].x); acc0[u].y = fmaf(w0[u], v0[u].y, acc0[u].y);
+            acc0[u].z = fmaf(w0[u], v0[u].z, acc0[u].z); acc0[u].w = fmaf(w0[u], v0[u].w, acc0[u].w);
+            acc1[u].x = fmaf(w1[u], v1[u].x, acc1[u].x); acc1[u].y = fmaf(w1[u], v1[u].y, acc1[u].y);
+            acc1[u].z = fmaf(w1[u], v1[u].z, acc1[u].z); acc1[u].w = fmaf(w1[u], v1[u].w, acc1[u].w);
+        }
+    }
+    if (k < end) {
+        const int64_t e0 = eid[k];
+        const float4 *x0 = reinterpret_cast<const float4 *>(kEdgeX ? X + e0 * d : X + indices[k] * hd);
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) {
+            const float4 v = __ldg(x0 + xpiece[u]);
+            const float w = __ldg(W + e0 * h + head[u]);
+            acc0[u].x = fmaf(w, v.x, acc0[u].x); acc0[u].y = fmaf(w, v.y, acc0[u].y);
+            acc0[u].z = fmaf(w, v.z, acc0[u].z); acc0[u].w = fmaf(w, v.w, acc0[u].w);
+        }
+    }
+}
+
+template <int kVec, bool kEdgeX>
+__global__ void __launch_bounds__(kWideWarps * 32)
+row_sum_wide_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indptr,
+                    const int64_t *__restrict__ eid, const int64_t *__restrict__ indices, int64_t n_chunks,
+                    const float *__restrict__ W, const float *__restrict__ X, float *__restrict__ out, int h,
+                    int d) {
+    __shared__ float4 s_part[kWideWarps][32 * kVec];  // partial sums of a long row, one slice per warp
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hd = h * d;
+    const int64_t c0 = n_chunks * blockIdx.x / gridDim.x, c1 = n_chunks * (blockIdx.x + 1) / gridDim.x;
+    int head[kVec], xpiece[kVec];  // head of this lane's u-th column group; its float4 inside a gathered row
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) {
+        const int col = lane * 4 + 128 * u;
+        head[u] = col / d;
+        xpiece[u] = kEdgeX ? (col % d) / 4 : col / 4;
+    }
+    int ordinal = 0;  // short rows that started in this block's share so far (the same count in every warp)
+    for (int64_t base = c0; base < c1; base += 32) {
+        const int64_t cl = base + lane;
+        const bool starts = cl < c1 && (cl == 0 || row[cl - 1] != row[cl]);
+        unsigned mask = __ballot_sync(0xffffffffu, starts);
+        while (mask) {
+            const int bit = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const int64_t c = base + bit;
+            const int64_t r = row[c];
+            // a short row ends within a few chunks; every warp walks them (the block agrees on long / short)
+            int64_t ce = c + 1;
+            while (ce < n_chunks && row[ce] == r) ++ce;
+            const int64_t beg = indptr[c], end = indptr[ce];
+            const bool is_long = end - beg > kWideLongRow;
+            if (!is_long && ordinal++ % kWideWarps != warp) continue;
+            float4 acc0[kVec], acc1[kVec];
+#pragma unroll
+            for (int u = 0; u < kVec; ++u) {
+                acc0[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                acc1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float4 *o = reinterpret_cast<float4 *>(out + r * hd);
+            if (!is_long) {
+                wide_accumulate<kVec, kEdgeX>(eid, indices, beg, end, W, X, h, d, hd, head, xpiece, acc0, acc1);
+#pragma unroll
+                for (int u = 0; u < kVec; ++u)
+                    o[lane + 32 * u] = make_float4(acc0[u].x + acc1[u].x, acc0[u].y + acc1[u].y,
+                                                   acc0[u].z + acc1[u].z, acc0[u].w + acc1[u].w);
+                continue;
+            }
+            // long row: warp w sums its contiguous sixteenth of the entries, the slices meet in warp order
+            const int64_t len = end - beg;
+            wide_accumulate<kVec, kEdgeX>(eid, indices, beg + len * warp / kWideWarps,
+                                          beg + len * (warp + 1) / kWideWarps, W, X, h, d, hd, head, xpiece, acc0, acc1);
+#pragma unroll
+            for (int u = 0; u < kVec; ++u)
+                s_part[warp][lane + 32 * u] = make_float4(acc0[u].x + acc1[u].x, acc0[u].y + acc1[u].y,
+                                                          acc0[u].z + acc1[u].z, acc0[u].w + acc1[u].w);
+            __syncthreads();
+            for (int i = threadIdx.x; i < 32 * kVec; i += blockDim.x) {
+                float4 sum = s_part[0][i];
+#pragma unroll
+                for (int w = 1; w < kWideWarps; ++w) {
+                    const float4 p = s_part[w][i];
+                    sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+                }
+                o[i] = sum;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Per-edge dot products and the per-edge gradient of node_mul_edge for the same fp32 shapes (rows of 128..512
+// columns, head width 16, 32, 64 or 128).  One block per SM-sized share of the chunk list, its warps take
+// the chunks round-robin (16 neighbouring chunks in flight per block, so gathered rows are shared through
+// the L1); a warp keeps the chunk's A row in registers (lane l: columns 4 l + 128 u), reads every gathered
+// row with 16-byte loads, two entries in flight, and reduces inside the d / 4 lanes that hold one head.
+template <int kVec, bool kPerHead>
+__global__ void __launch_bounds__(kWideWarps * 32)
+edge_dot_wide_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indptr,
+                     const int64_t *__restrict__ eid, const int64_t *__restrict__ indices, int64_t n_chunks,
+                     const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ y, int h, int d) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hd = h * d, lanes_per_head = d / 4;
+    const int64_t c0 = n_chunks * blockIdx.x / gridDim.x, c1 = n_chunks * (blockIdx.x + 1) / gridDim.x;
+    int head[kVec];
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) head[u] = (lane * 4 + 128 * u) / d;
+    const int bpiece = (lane * 4 % d) / 4;  // !kPerHead: this lane's float4 of the shared d-wide row
+    const bool writer = lane % lanes_per_head == 0;
+    for (int64_t c = c0 + warp; c < c1; c += kWideWarps) {
+        const float4 *a_row = reinterpret_cast<const float4 *>(A + row[c] * hd);
+        float4 a[kVec];
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) a[u] = __ldg(a_row + lane + 32 * u);
+        const int64_t beg = indptr[c], end = indptr[c + 1];
+        for (int64_t k = beg; k < end; k += 2) {
+            const bool two = k + 1 < end;
+            const int64_t e0 = eid[k], e1 = two ? eid[k + 1] : e0;
+            const float4 *b0 = reinterpret_cast<const float4 *>(kPerHead ? B + indices[k] * hd : B + e0 * d);
+            const float4 *b1 = reinterpret_cast<const float4 *>(kPerHead ? B + indices[two ? k + 1 : k] * hd : B + e1 * d);
+            float p0[kVec], p1[kVec];
+            if (kPerHead) {
+                float4 v0[kVec], v1[kVec];
+#pragma unroll
+                for (int u = 0; u < kVec; ++u) {
+                    v0[u] = __ldg(b0 + lane + 32 * u);
+                    v1[u] = __ldg(b1 + lane + 32 * u);
+                }
+#pragma unroll
+                for (int u = 0; u < kVec; ++u) {
+                    p0[u] = fmaf(a[u].x, v0[u].x, fmaf(a[u].y, v0[u].y, fmaf(a[u].z, v0[u].z, a[u].w * v0[u].w)));
+                    p1[u] = fmaf(a[u].x, v1[u].x, fmaf(a[u].y, v1[u].y, fmaf(a[u].z, v1[u].z, a[u].w * v1[u].w)));
+                }
+            } else {
+                const float4 v0 = __ldg(b0 + bpiece), v1 = __ldg(b1 + bpiece);
+#pragma unroll
+                for (int u = 0; u < kVec; ++u) {
+                    p0[u] = fmaf(a[u].x, v0.x, fmaf(a[u].y, v0.y, fmaf(a[u].z, v0.z, a[u].w * v0.w)));
+                    p1[u] = fmaf(a[u].x, v1.x, fmaf(a[u].y, v1.y, fmaf(a[u].z, v1.z, a[u].w * v1.w)));
+                }
+            }
+            for (int off = lanes_per_head >> 1; off > 0; off >>= 1) {
+#pragma unroll
+                for (int u = 0; u < kVec; ++u) {
+                    p0[u] += __shfl_xor_sync(0xffffffffu, p0[u], off);
+                    p1[u] += __shfl_xor_sync(0xffffffffu, p1[u], off);
+                }
+            }
+            if (writer) {
+#pragma unroll
+                for (int u = 0; u < kVec; ++u) {
+                    y[e0 * h + head[u]] = p0[u];
+                    if (two) y[e1 * h + head[u]] = p1[u];
+                }
+            }
+        }
+    }
+}
+
+template <int kVec>
+__global__ void __launch_bounds__(kWideWarps * 32)
+nme_backward_edge_wide_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indptr,
+                              const int64_t *__restrict__ eid, int64_t n_chunks, const float *__restrict__ A,
+                              const float *__restrict__ dy, float *__restrict__ dB, int h, int d) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hd = h * d, lanes_per_head = d / 4;
+    const int64_t c0 = n_chunks * blockIdx.x / gridDim.x, c1 = n_chunks * (blockIdx.x + 1) / gridDim.x;
+    int head[kVec];
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) head[u] = (lane * 4 + 128 * u) / d;
+    for (int64_t c = c0 + warp; c < c1; c += kWideWarps) {
+        const float4 *a_row = reinterpret_cast<const float4 *>(A + row[c] * hd);
+        float4 a[kVec];
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) a[u] = __ldg(a_row + lane + 32 * u);
+        const int64_t beg = indptr[c], end = indptr[c + 1];
+        for (int64_t k = beg; k < end; ++k) {
+            const int64_t e = eid[k];
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);  // heads in ascending order within the lane, then across lanes
+#pragma unroll
+            for (int u = 0; u < kVec; ++u) {
+                const float g = __ldg(dy + e * h + head[u]);
+                t.x = fmaf(g, a[u].x, t.x); t.y = fmaf(g, a[u].y, t.y);
+                t.z = fmaf(g, a[u].z, t.z); t.w = fmaf(g, a[u].w, t.w);
+            }
+            for (int off = lanes_per_head; off < 32; off <<= 1) {
+                t.x += __shfl_xor_sync(0xffffffffu, t.x, off); t.y += __shfl_xor_sync(0xffffffffu, t.y, off);
+                t.z += __shfl_xor_sync(0xffffffffu, t.z, off); t.w += __shfl_xor_sync(0xffffffffu, t.w, off);
+            }
+            if (lane < lanes_per_head) reinterpret_cast<float4 *>(dB + e * d)[lane] = t;
+        }
+    }
+}
+
+// True when the fp32 wide kernels apply: rows of 128, 256, 384 or 512 columns, 16-byte aligned.
+inline bool wide_shape(int h, int d, bool need_head_pow2, const void *p0, const void *p1, const void *p2) {
+    const int hd = h * d;
+    if (hd % 128 != 0 || hd > 512 || d % 4 != 0) return false;
+    if (need_head_pow2 && d != 16 && d != 32 && d != 64 && d != 128) return false;
+    return reinterpret_cast<uintptr_t>(p0) % 16 == 0 && reinterpret_cast<uintptr_t>(p1) % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(p2) % 16 == 0;
+}
+// blocks_per_sm: 1 for the kernels whose gathered rows fill the registers and the L1, more for the ones that
+// move little per entry and wait on chains of dependent loads instead.
+inline int wide_grid(int64_t n_chunks, unsigned &grid, int blocks_per_sm = 1) {
+    int dev = 0, sms = 0;
+    BPT_CUDA(cudaGetDevice(&dev));
+    BPT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    grid = static_cast<unsigned>(std::min<int64_t>(n_chunks, static_cast<int64_t>(sms) * blocks_per_sm));
+    return BPT_OK;
+}
+
 // node_mul_edge backward, dB[eid[k], dd] = sum_hh dy[eid[k], hh] * A[row, hh, dd]
 template <typename T>
 __global__ void nme_backward_edge_kernel(const int64_t *__restrict__ row, const int64_t *__restrict__ indptr,
@@ -236,6 +485,20 @@ int launch_edge_dot(const int64_t *row, const int64_t *indptr, const int64_t *ei
                     int64_t n_chunks, const void *A, const void *B, void *y, int h, int d,
                     cudaStream_t stream) {
     if (n_chunks == 0) return BPT_OK;
+    if (std::is_same<T, float>::value && wide_shape(h, d, true, A, B, A)) {
+        unsigned grid = 1;
+        if (int rc = wide_grid(n_chunks, grid, kPerHead ? 1 : 3)) return rc;
+        const float *a = static_cast<const float *>(A), *b = static_cast<const float *>(B);
+        float *o = static_cast<float *>(y);
+        switch (h * d / 128) {
+            case 1: edge_dot_wide_kernel<1, kPerHead><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, a, b, o, h, d); break;
+            case 2: edge_dot_wide_kernel<2, kPerHead><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, a, b, o, h, d); break;
+            case 3: edge_dot_wide_kernel<3, kPerHead><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, a, b, o, h, d); break;
+            default: edge_dot_wide_kernel<4, kPerHead><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, a, b, o, h, d); break;
+        }
+        BPT_LAUNCH_CHECK();
+        return BPT_OK;
+    }
     const int warps = 4;
     const unsigned blocks = static_cast<unsigned>((n_chunks + warps - 1) / warps);
     edge_dot_kernel<T, kPerHead><<<blocks, warps * 32, 0, stream>>>(
@@ -251,6 +514,21 @@ int launch_row_sum(const int64_t *row, const int64_t *indptr, const int64_t *eid
                    int d, cudaStream_t stream) {
     BPT_CUDA(cudaMemsetAsync(out, 0, sizeof(T) * static_cast<size_t>(n_rows_out) * h * d, stream));
     if (n_chunks == 0) return BPT_OK;
+    const int hd = h * d;
+    if (std::is_same<T, float>::value && wide_shape(h, d, false, X, out, X)) {
+        unsigned grid = 1;
+        if (int rc = wide_grid(n_chunks, grid)) return rc;
+        const float *w = static_cast<const float *>(W), *x = static_cast<const float *>(X);
+        float *o = static_cast<float *>(out);
+        switch (hd / 128) {
+            case 1: row_sum_wide_kernel<1, kEdgeX><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, w, x, o, h, d); break;
+            case 2: row_sum_wide_kernel<2, kEdgeX><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, w, x, o, h, d); break;
+            case 3: row_sum_wide_kernel<3, kEdgeX><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, w, x, o, h, d); break;
+            default: row_sum_wide_kernel<4, kEdgeX><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, indices, n_chunks, w, x, o, h, d); break;
+        }
+        BPT_LAUNCH_CHECK();
+        return BPT_OK;
+    }
     row_sum_kernel<T, kEdgeX><<<static_cast<unsigned>(n_chunks), kRowWarps * 32, 0, stream>>>(
         row, indptr, eid, indices, n_chunks, static_cast<const T *>(W), static_cast<const T *>(X),
         static_cast<T *>(out), h, d);
@@ -319,7 +597,19 @@ extern "C" int bpt_node_mul_edge_backward(const int64_t *row, const int64_t *ind
         if (int rc = launch_row_sum<scalar_t, true>(row, indptr, eid, nullptr, n_chunks, dy, B, dA, n_rows_a,
                                                     h, d, stream))
             return rc;
-        if (n_chunks > 0) {
+        if (n_chunks > 0 && std::is_same<scalar_t, float>::value && wide_shape(h, d, true, A, dB, A)) {
+            unsigned grid = 1;
+            if (int rc = wide_grid(n_chunks, grid, 3)) return rc;
+            const float *a = static_cast<const float *>(A), *g = static_cast<const float *>(dy);
+            float *o = static_cast<float *>(dB);
+            switch (h * d / 128) {
+                case 1: nme_backward_edge_wide_kernel<1><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, n_chunks, a, g, o, h, d); break;
+                case 2: nme_backward_edge_wide_kernel<2><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, n_chunks, a, g, o, h, d); break;
+                case 3: nme_backward_edge_wide_kernel<3><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, n_chunks, a, g, o, h, d); break;
+                default: nme_backward_edge_wide_kernel<4><<<grid, kWideWarps * 32, 0, stream>>>(row, indptr, eid, n_chunks, a, g, o, h, d); break;
+            }
+            BPT_LAUNCH_CHECK();
+        } else if (n_chunks > 0) {
             nme_backward_edge_kernel<scalar_t><<<static_cast<unsigned>(n_chunks), 128, 0, stream>>>(
                 row, indptr, eid, n_chunks, static_cast<const scalar_t *>(A),
                 static_cast<const scalar_t *>(dy), static_cast<scalar_t *>(dB), h, d);

@@ -53,14 +53,14 @@ def parse():
     ap.add_argument("--no-step-graphs", action="store_true",
                     help="seqshard mode with the halo exchange: issue the pieces between collectives eagerly instead "
                          "of replaying them from CUDA graphs (collectives are never captured)")
-    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt", "cls", "chain"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "lm", "mt", "cls", "chain", "sweep"],
                     help="attention: the fused layer forward+backward (headline); lm: 12-layer character LM "
                          "forward, batch 8 x 8192 tokens per rank, tokens/s; mt: 6+6-layer encoder-decoder "
                          "forward over 16 documents of 64 sentences per rank, target tokens/s; cls: 5-layer fp32 "
                          "classifier (d_model 300, 6 x 50) over 32 variable-length sequences per rank, forward + "
                          "backward with the graph, CSRs and plans rebuilt every step, sequences/s; chain: the same "
                          "layer as `attention` through the reference's four separate operators (modules/op.py), "
-                         "forward + backward")
+                         "forward + backward; sweep: one sequence per rank for n in {8192..65536} x k in {1, 2, 4, 8}")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -812,6 +812,26 @@ def run_ours(a):
         print(json.dumps(line), flush=True)
 
 
+def run_sweep(a):
+    """One attention layer forward + backward on ONE sequence per rank for n in {8192, 16384, 32768, 65536}
+    and k in {1, 2, 4, 8} (8 x 64, bf16 unless --dtype says otherwise): one JSON line with a cell per (n, k)."""
+    world, rank, dev = dist_context()
+    cells = []
+    for n in (8192, 16384, 32768, 65536):
+        for k in (1, 2, 4, 8):
+            rec = measure_attention(a, 1, n, k, a.dtype, a.causal, max(5, min(a.steps, 20)), 3, False, False, 0.25)
+            if rank == 0:
+                cells.append({"n": n, "k": k, "nodes": rec["config"]["nodes_per_gpu"], "edges": rec["config"]["edges_per_gpu"],
+                              "ms_per_step": rec["ms_per_step"], "forward_ms": rec["forward"]["ms"],
+                              "backward_ms": rec["backward"]["ms"], "edges_per_sec": rec["value"] / world,
+                              "forward_kernel": rec["roofline"]["kernel"], "forward_frac": rec["roofline"]["frac"],
+                              "backward_frac": rec["roofline_backward"]["frac"]})
+    if rank == 0:
+        print(json.dumps({"metric": "bpt_attention_edges_per_sec", "unit": "edges/s", "n_gpus": world, "dtype": a.dtype,
+                          "data": "synthetic", "config": {"workload": "sweep: 1 x (n, k) per rank, h=8x64, fwd+bwd"},
+                          "cells": cells}), flush=True)
+
+
 def main():
     a = parse()
     if a.impl == "reference":
@@ -834,6 +854,8 @@ def dispatch(a):
         run_cls(a)
     elif a.workload == "chain":
         run_chain(a)
+    elif a.workload == "sweep":
+        run_sweep(a)
     elif a.mode == "seqshard":
         run_seqshard(a)
     else:

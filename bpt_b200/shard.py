@@ -575,7 +575,9 @@ class HaloRunner:
             torch.cuda.current_stream(self.dev).wait_stream(side)
             torch.cuda.synchronize(self.dev)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            # thread_local: other threads of the process (the collective library's watchdog queries events
+            # while ranks wait for each other) may keep calling the CUDA runtime during the capture
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 fn()
             self._g[name] = g
         g.replay()

@@ -293,7 +293,8 @@ __global__ void left_col_kernel(const int32_t *__restrict__ gidx2, const int32_t
 // ---- stage 3: emitted groups ----
 struct GroupArrays {
     int32_t *ncols, *pad, *mbc, *cells;       // per emitted group (+1 closing element for the scans)
-    int32_t *col_off, *mb_first, *cells_off;  // exclusive sums of pad, mbc, cells
+    int32_t *col_off, *mb_first;              // exclusive sums of pad, mbc
+    int64_t *cells_off;                       // exclusive sum of cells (64-bit: the total is checked against 2^31)
 };
 __device__ __forceinline__ void set_group(const GroupArrays &g, int64_t gr, int ncols, int mbc) {
     const int pad = (ncols + kTileChunk - 1) / kTileChunk * kTileChunk;
@@ -382,7 +383,7 @@ __global__ void write_groups_kernel(GroupArrays g, int64_t n_emitted, int n_dens
             mb[kMbRowEtOff + i] = row >= 0 ? runi[row] : 0;
             if (row >= 0 && runi[row] < 0) uniform = false;
         }
-        mb[kMbEtOff] = g.cells_off[gr] + k * chunk_cells;
+        mb[kMbEtOff] = static_cast<int32_t>(g.cells_off[gr]) + k * chunk_cells;
         mb[kMbChunkMask] = 0;
         mb[kMbTq] = -1;  // holds the largest edge type until finish_mblocks_kernel
         mb[kMbQrSlot] = uniform ? -1 : n_qr++;
@@ -614,11 +615,12 @@ struct Sorter {
         PLAN_CUDA(cub::DeviceScan::InclusiveSum(buf, need, in, out, n, s));
         return true;
     }
-    bool exclusive_sum(const int32_t *in, int32_t *out, int64_t n, cudaStream_t s) {
+    template <typename Out>
+    bool exclusive_sum(const int32_t *in, Out *out, int64_t n, cudaStream_t s) {
         size_t need = 0;
-        PLAN_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, in, out, n, s));
+        PLAN_CUDA(cub::DeviceScan::ExclusiveScan(nullptr, need, in, out, cub::Sum(), Out(0), n, s));
         if (!reserve(need)) return false;
-        PLAN_CUDA(cub::DeviceScan::ExclusiveSum(buf, need, in, out, n, s));
+        PLAN_CUDA(cub::DeviceScan::ExclusiveScan(buf, need, in, out, cub::Sum(), Out(0), n, s));
         return true;
     }
     bool select_flagged(const int32_t *in, const int32_t *flags, int32_t *out, int *n_out, int64_t n, cudaStream_t s) {
@@ -727,7 +729,7 @@ bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, cons
     g.ncols = tmp.take<int32_t>(n_emitted + 1); g.pad = tmp.take<int32_t>(n_emitted + 1);
     g.mbc = tmp.take<int32_t>(n_emitted + 1); g.cells = tmp.take<int32_t>(n_emitted + 1);
     g.col_off = tmp.take<int32_t>(n_emitted + 1); g.mb_first = tmp.take<int32_t>(n_emitted + 1);
-    g.cells_off = tmp.take<int32_t>(n_emitted + 1);
+    g.cells_off = tmp.take<int64_t>(n_emitted + 1);
     int32_t *dense_gi = tmp.take<int32_t>(n_dense), *copy_bucket = tmp.take<int32_t>(n_copies);
     if (!tmp.ok) { fail(BPT_ERR_CUDA, "tile_plan_device: out of device memory"); return false; }
     emit_groups_kernel<<<blocks_for(nG + h.n_buckets + n_zero_groups + 1), kThreads, 0, stream>>>(
@@ -739,13 +741,14 @@ bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, cons
     if (!sorter.exclusive_sum(g.mbc, g.mb_first, n_emitted + 1, stream)) return false;
     if (!sorter.exclusive_sum(g.cells, g.cells_off, n_emitted + 1, stream)) return false;
     // second crossing: array sizes.  Cell offsets are 32-bit in the m-block records; check the 64-bit total.
-    int totals[3] = {0, 0, 0};
+    int totals[2] = {0, 0};
+    int64_t total_cells = 0;
     PLAN_CUDA(cudaMemcpyAsync(&totals[0], g.col_off + n_emitted, sizeof(int), cudaMemcpyDeviceToHost, stream));
     PLAN_CUDA(cudaMemcpyAsync(&totals[1], g.mb_first + n_emitted, sizeof(int), cudaMemcpyDeviceToHost, stream));
-    PLAN_CUDA(cudaMemcpyAsync(&totals[2], g.cells_off + n_emitted, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    PLAN_CUDA(cudaMemcpyAsync(&total_cells, g.cells_off + n_emitted, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
     PLAN_CUDA(cudaStreamSynchronize(stream));
-    const int64_t n_cols = totals[0], n_mblocks = totals[1], n_cells = totals[2];
-    if (n_cols < 0 || n_cells < 0 || n_mblocks < 0) {
+    const int64_t n_cols = totals[0], n_mblocks = totals[1], n_cells = total_cells;
+    if (n_cols < 0 || n_mblocks < 0 || n_cells >= (1ll << 31)) {
         fail(BPT_ERR_UNSUPPORTED, "tile_plan_create: the plan has more than 2^31 cells");
         return false;
     }

@@ -43,10 +43,14 @@ def graphop_so_path():
     return hits[0] if hits else None
 
 
+MODULE_NAMES = ("op", "attention", "embedding", "model")  # modules/*.py, in import order
+
+
 def modules_so_paths():
-    """{'op': path, 'attention': path} of the compiled reference modules, or None."""
+    """{'op': path, 'attention': path, 'embedding': path, 'model': path} of the compiled reference modules,
+    or None when one is missing."""
     out = {}
-    for name in ("op", "attention"):
+    for name in MODULE_NAMES:
         hits = sorted(glob.glob(os.path.join(OUT, MODULES_PKG, name + "*.so")))
         if not hits:
             return None
@@ -95,7 +99,7 @@ def build_modules(ref_root, quiet=True):
     sink = dict(stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) if quiet else {}
     ext = sysconfig.get_config_var("EXT_SUFFIX")
     with tempfile.TemporaryDirectory(prefix="bpt_ref_modules_") as tmp:
-        for name in ("op", "attention"):
+        for name in MODULE_NAMES:
             py = os.path.join(ref_root, "modules", name + ".py")
             if not os.path.isfile(py):
                 raise FileNotFoundError(py)
@@ -127,12 +131,53 @@ def load_graphop():
 
 
 class FakeGraph:
-    """What BPTBlock.forward touches of a DGLGraph: dict-like node and edge frames
-    (modules/attention.py:55-57,62-64,81)."""
+    """What the reference's blocks and models touch of a DGLGraph: dict-like node and edge frames
+    (modules/attention.py:55-57,62-64,81), `g.nodes[ids].data[key]` read and assignment over a subset of the
+    nodes (modules/model.py:249-262,275; rows never assigned are zero, as in a DGL frame), local_var() and
+    number_of_nodes() (modules/model.py:89-93, modules/attention.py:163-164)."""
 
-    def __init__(self, ndata=None, edata=None):
+    def __init__(self, ndata=None, edata=None, n_nodes=None):
         self.ndata = dict(ndata or {})
         self.edata = dict(edata or {})
+        self.n_nodes = n_nodes
+        self.nodes = _NodeIndexer(self)
+
+    def local_var(self):
+        return self
+
+    def number_of_nodes(self):
+        return self.n_nodes
+
+
+class _NodeIndexer:
+    def __init__(self, graph):
+        self.graph = graph
+
+    def __getitem__(self, ids):
+        return _NodeSubset(self.graph, ids)
+
+
+class _NodeSubset:
+    def __init__(self, graph, ids):
+        self.data = _NodeSubsetData(graph, ids)
+
+
+class _NodeSubsetData:
+    def __init__(self, graph, ids):
+        self.graph, self.ids = graph, ids
+
+    def __getitem__(self, key):
+        return self.graph.ndata[key][self.ids]
+
+    def __setitem__(self, key, value):
+        import torch
+        g = self.graph
+        old = g.ndata.get(key)
+        if old is None or old.shape[1:] != value.shape[1:] or old.dtype != value.dtype:
+            old = torch.zeros((g.n_nodes,) + tuple(value.shape[1:]), dtype=value.dtype, device=value.device)
+        new = old.clone()          # out of place: autograd keeps the previous version
+        new[self.ids] = value
+        g.ndata[key] = new
 
 
 def _stub_dgl():
@@ -160,13 +205,14 @@ def _remove_temp_dirs():
 
 
 def load_modules(graphop_module, ref_root=None):
-    """The reference's modules/op.py and modules/attention.py bound to `graphop_module` (what their
-    `from graphop import *`, modules/op.py:2, resolves to).  Taken from the checkout's .py files
+    """The reference's modules/op.py, attention.py, embedding.py and model.py bound to `graphop_module`
+    (what `from graphop import *`, modules/op.py:2, resolves to).  Taken from the checkout's .py files
     when ref_root holds them, else from the compiled copies in oracle/_ref/.  Returns
-    (op_module, attention_module) or None when neither is available.  sys.modules is left as found."""
+    (op, attention, embedding, model) module objects, or None when neither source is available.
+    sys.modules is left as found."""
     src = None
     if ref_root and os.path.isfile(os.path.join(ref_root, "modules", "attention.py")):
-        src = {n: os.path.join(ref_root, "modules", n + ".py") for n in ("op", "attention")}
+        src = {n: os.path.join(ref_root, "modules", n + ".py") for n in MODULE_NAMES}
     else:
         src = modules_so_paths()
         if src is not None:
@@ -177,7 +223,7 @@ def load_modules(graphop_module, ref_root=None):
             src = {n: shutil.copy2(path, os.path.join(tmp, os.path.basename(path))) for n, path in src.items()}
     if src is None:
         return None
-    saved = {k: sys.modules.get(k) for k in ("graphop", MODULES_PKG, MODULES_PKG + ".op", MODULES_PKG + ".attention")}
+    saved = {k: sys.modules.get(k) for k in ("graphop", MODULES_PKG) + tuple(MODULES_PKG + "." + n for n in MODULE_NAMES)}
     stubs = _stub_dgl()
     try:
         sys.modules["graphop"] = graphop_module
@@ -185,7 +231,7 @@ def load_modules(graphop_module, ref_root=None):
         pkg.__path__ = []
         sys.modules[MODULES_PKG] = pkg
         mods = []
-        for name in ("op", "attention"):
+        for name in MODULE_NAMES:
             full = MODULES_PKG + "." + name
             if src[name].endswith(".py"):
                 spec = importlib.util.spec_from_file_location(full, src[name])

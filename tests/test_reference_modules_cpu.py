@@ -56,7 +56,7 @@ def test_reference_block_forward_equals_oracle_chain(oracle_lib, source):
     if source == "compiled" and build_ref_graphop.modules_so_paths() is None:
         pytest.skip("compiled reference modules absent (python oracle/build_ref_graphop.py)")
     stand_in = _cpu_graphop()
-    op_mod, att_mod = build_ref_graphop.load_modules(stand_in, root)
+    op_mod, att_mod = build_ref_graphop.load_modules(stand_in, root)[:2]
     assert op_mod.maskedmm_csr_forward is stand_in.maskedmm_csr_forward
     g = oracle_lib.batch_graphs([oracle_lib.binary_partition(40, False, 2, 10), oracle_lib.binary_partition(33, True, 3, 4)])
     N = g["n_nodes"]
@@ -85,3 +85,54 @@ def test_reference_block_forward_equals_oracle_chain(oracle_lib, source):
     for x, y in zip(g1, g2):
         assert torch.allclose(x, y, rtol=1e-8, atol=1e-10)
     assert np.isfinite(out.detach().numpy()).all()
+
+
+@pytest.mark.parametrize("source", ["checkout", "compiled"])
+def test_reference_language_model_forward_equals_blocks_spelled_out(oracle_lib, source):
+    """modules/model.py:197-280 (BinaryPartitionTransformer, rel_pos=True, dim_embed == dim_model) on the CPU
+    stand-in: the graph object's `g.nodes[ids].data[key]` read / assignment behaves like a DGL frame (rows
+    never assigned are zero), and the model equals embedding -> norm -> its blocks (each spelled with the
+    oracle's chain) -> generator on the leaves."""
+    root = REF_ROOT if source == "checkout" else None
+    if source == "checkout" and not os.path.isfile(os.path.join(REF_ROOT, "modules", "model.py")):
+        pytest.skip("reference checkout not mounted")
+    if source == "compiled" and build_ref_graphop.modules_so_paths() is None:
+        pytest.skip("compiled reference modules absent (python oracle/build_ref_graphop.py)")
+    mods = build_ref_graphop.load_modules(_cpu_graphop(), root)
+    model_mod = mods[3]
+    g = oracle_lib.batch_graphs([oracle_lib.binary_partition(40, True, 2, 10), oracle_lib.binary_partition(21, True, 3, 4)])
+    N = g["n_nodes"]
+    csr_np = oracle_lib.get_csrs(g["src"], g["dst"], N)
+    f = torch.from_numpy
+    csr = ([f(a) for a in csr_np[0]], [f(a) for a in csr_np[1]], f(csr_np[2]), f(csr_np[3]), f(csr_np[4]), f(csr_np[5]))
+    torch.manual_seed(0)
+    vocab, dim, heads, layers = 17, 32, 4, 2
+    lm = model_mod.make_model(vocab, dim, dim, 64, heads, vocab, layers, dropouti=0.0, dropouth=0.0, dropouta=0.0,
+                              dropoutc=0.0, rel_pos=True).double()
+    # leaves are the first n nodes of every sequence (graph_builder/builder.pyx:29-62)
+    n0 = oracle_lib.binary_partition(40, True, 2, 10)["n_nodes"]
+    leaf_ids = torch.cat([torch.arange(0, 40), torch.arange(n0, n0 + 21)])
+    tokens = torch.randint(0, vocab, (leaf_ids.numel(),))
+    x = torch.zeros(N, dtype=torch.long)
+    x[leaf_ids] = tokens
+    etype = f(g["etype"])
+    graph = build_ref_graphop.FakeGraph(ndata={"x": x}, edata={"etype": etype}, n_nodes=N)
+    batch = types.SimpleNamespace(g=graph, leaf_ids=leaf_ids, g_csr=csr, readout_ids=leaf_ids)
+    out = lm(batch)
+    h = torch.zeros(N, dim, dtype=torch.float64)
+    h = h.index_put((leaf_ids,), lm.norm(lm.embed(tokens)))
+    for blk in lm.layers:
+        q, k, v = [p(h).view(-1, heads, dim // heads) for p in (blk.proj_q, blk.proj_k, blk.proj_v)]
+        a = ops_torch.attention_chain(csr, etype, q, k, v, blk.embed_ak.weight, dim // heads).reshape(N, dim)
+        hh = blk.norm_in(h + blk.proj_o(a))
+        h = blk.norm_inter(hh + blk.ffn(hh))
+    want = lm.generator(h[leaf_ids])
+    assert out.shape == (leaf_ids.numel(), vocab)
+    assert torch.allclose(out, want, rtol=1e-9, atol=1e-11)
+    w_loss = torch.randn_like(out)
+    g1 = torch.autograd.grad((out * w_loss).sum(), list(lm.parameters()), retain_graph=True, allow_unused=True)
+    g2 = torch.autograd.grad((want * w_loss).sum(), list(lm.parameters()), allow_unused=True)
+    for a_, b_ in zip(g1, g2):
+        assert (a_ is None) == (b_ is None)
+        if a_ is not None:
+            assert torch.allclose(a_, b_, rtol=1e-7, atol=1e-9)

@@ -82,9 +82,10 @@ class AttentionPlan:
         return ws
 
     def tile_plan(self):
-        """The tile plan of the tensor-core forward (built once, on the host, then uploaded)."""
+        """The tile plan of the tensor-core forward and of the destination side of the backward (built once
+        per graph)."""
         if self.tiles is None:
-            self.tiles = TilePlan(self)
+            self.tiles = TilePlan(self, max_cols=TILE_MAX_COLS)
         return self.tiles
 
     def tile_plan5(self):
@@ -238,6 +239,8 @@ class TilePlan:
 
 
 TILE_PLANNER = os.environ.get("BPT_TILE_PLANNER", "device")
+# Widest column list of a 16-row tile; rows that would need more are cut by blocks of 128 source columns.
+TILE_MAX_COLS = int(os.environ.get("BPT_TILE_MAX_COLS", "384"))
 MAX_BLOCK_SMEM = 227 * 1024  # shared memory one thread block can have on this GPU
 
 

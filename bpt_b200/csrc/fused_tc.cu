@@ -136,7 +136,7 @@ attn_forward_tile_kernel(const TcParams p) {
                                            kTilesPerBlock * p.max_cols_pad);
     ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
-    const int tab_stride = p.t_max + 10;  // t_max types + the -inf entry, padded to an odd number of words (rows spread over the banks)
+    const int tab_stride = p.t_max + 8;  // t_max types + the -inf entry, padded; >= 8.  (Two more would spread the rows over the banks, but the 512 bytes cost the second block per SM on plans with 192 columns.)
     // embed_ak rows [0, t_max), staged once per block (16-byte aligned: every region before it is)
     const uint32_t s_ak_addr = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
@@ -459,7 +459,7 @@ attn_forward_tile_kernel(const TcParams p) {
 size_t tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
     return static_cast<size_t>(kWarps) * kKvStageBytes + static_cast<size_t>(kTilesPerBlock) * max_cols_pad * 4 +
            static_cast<size_t>(kTilesPerBlock) * kTileRows * (max_cols_pad + kEtPad) * et_bytes +
-           static_cast<size_t>(kWarps) * kTileRows * (t_max + 10) * 2 + static_cast<size_t>(t_max) * kRowBytes;
+           static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2 + static_cast<size_t>(t_max) * kRowBytes;
 }
 
 template <typename ET, bool kHasBias, bool kDrop>

@@ -317,7 +317,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                                            kTilesPerBlock * p.max_cols_pad);
     ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
-    const int tab_stride = p.t_max + 10;  // an odd number of words: the 16 rows spread over the banks
+    const int tab_stride = p.t_max + 8;
     const uint32_t s_ak = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
     if (kHasBias) {
@@ -890,7 +890,7 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes +
                             static_cast<size_t>(kTilesPerBlock) * p.max_cols_pad * 4 +
                             static_cast<size_t>(kTilesPerBlock) * kTileRows * (p.max_cols_pad + kIdxPad) * dst_tiles->et_bytes +
-                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 10) * 2 +
+                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2 +
                             static_cast<size_t>(p.t_max) * kRowBytes;
         if (smem > 227 * 1024)
             return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: tile plan needs %zu bytes of shared memory", smem);

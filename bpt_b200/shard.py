@@ -577,8 +577,12 @@ class HaloRunner:
             g = torch.cuda.CUDAGraph()
             # thread_local: other threads of the process (the collective library's watchdog queries events
             # while ranks wait for each other) may keep calling the CUDA runtime during the capture
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                fn()
+            import warnings
+            with warnings.catch_warnings():
+                # a piece that has nothing to do on this rank (no straddlers, no peers) captures an empty graph
+                warnings.filterwarnings("ignore", message="The CUDA Graph is empty")
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    fn()
             self._g[name] = g
         g.replay()
 

@@ -114,7 +114,7 @@ struct TcParams {
     const __nv_bfloat16 *q, *k, *v, *ak;
     __nv_bfloat16 *o;
     float *lse, *part_o, *part_ml;
-    int n_etypes, H, max_cols_pad, t_max;
+    int n_etypes, H, max_cols_pad, t_max, tab_stride;
     int64_t n_groups;
     float scale;
     Dropout drop;
@@ -136,7 +136,7 @@ attn_forward_tile_kernel(const TcParams p) {
                                            kTilesPerBlock * p.max_cols_pad);
     ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
-    const int tab_stride = p.t_max + 8;  // t_max types + the -inf entry, padded; >= 8.  (Two more would spread the rows over the banks, but the 512 bytes cost the second block per SM on plans with 192 columns.)
+    const int tab_stride = p.tab_stride;  // t_max types + the -inf entry, padded (table_stride(): >= 8, even)
     // embed_ak rows [0, t_max), staged once per block (16-byte aligned: every region before it is)
     const uint32_t s_ak_addr = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
@@ -456,10 +456,18 @@ attn_forward_tile_kernel(const TcParams p) {
     }
 }
 
-size_t tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
+// Shared memory of a block without the score tables, the tables' row stride, and the total.
+size_t tc_other_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
     return static_cast<size_t>(kWarps) * kKvStageBytes + static_cast<size_t>(kTilesPerBlock) * max_cols_pad * 4 +
            static_cast<size_t>(kTilesPerBlock) * kTileRows * (max_cols_pad + kEtPad) * et_bytes +
-           static_cast<size_t>(kWarps) * kTileRows * (t_max + 8) * 2 + static_cast<size_t>(t_max) * kRowBytes;
+           static_cast<size_t>(t_max) * kRowBytes;
+}
+int tc_table_stride(int max_cols_pad, int t_max, int et_bytes) {
+    return table_stride(tc_other_smem_bytes(max_cols_pad, t_max, et_bytes), t_max, kWarps);
+}
+size_t tc_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
+    return tc_other_smem_bytes(max_cols_pad, t_max, et_bytes) +
+           static_cast<size_t>(kWarps) * kTileRows * tc_table_stride(max_cols_pad, t_max, et_bytes) * 2;
 }
 
 template <typename ET, bool kHasBias, bool kDrop>
@@ -551,6 +559,7 @@ extern "C" int bpt_attn_forward_tc(const int32_t *groups, int64_t n_groups, cons
         p.drop = drop;
         if (et_bytes == 1 && p.t_max > kMaxTypes8)
             return fail(BPT_ERR_INVALID, "attn_forward_tc: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
+        p.tab_stride = tc_table_stride(max_cols_pad, p.t_max, et_bytes);
         const size_t smem = tc_smem_bytes(max_cols_pad, p.t_max, et_bytes);
         if (smem > 227 * 1024)
             return fail(BPT_ERR_UNSUPPORTED, "attn_forward_tc: tile plan needs %zu bytes of shared memory", smem);

@@ -295,7 +295,7 @@ struct DqParams {
     int64_t n_edges;
     float *part_dq;
     __nv_bfloat16 *dq;
-    int n_etypes, H, max_cols_pad, t_max;
+    int n_etypes, H, max_cols_pad, t_max, tab_stride;
     int64_t n_groups;
     float scale;
     Dropout drop;
@@ -317,7 +317,7 @@ attn_backward_dq_tile_kernel(const DqParams p) {
                                            kTilesPerBlock * p.max_cols_pad);
     ET *s_idx = s_idx_all + tib * kTileRows * idx_stride;
     __half *s_tab_all = reinterpret_cast<__half *>(s_idx_all + kTilesPerBlock * kTileRows * idx_stride);
-    const int tab_stride = p.t_max + 8;
+    const int tab_stride = p.tab_stride;
     const uint32_t s_ak = static_cast<uint32_t>(
         __cvta_generic_to_shared(s_tab_all + static_cast<int64_t>(kWarps) * kTileRows * tab_stride));
     if (kHasBias) {
@@ -887,11 +887,12 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         p.drop = make_dropout(dropout);
         if (dst_tiles->et_bytes == 1 && p.t_max > kMaxTypes8)
             return fail(BPT_ERR_INVALID, "attn_backward_tc: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
-        const size_t smem = static_cast<size_t>(kWarps) * kKStageBytes +
-                            static_cast<size_t>(kTilesPerBlock) * p.max_cols_pad * 4 +
-                            static_cast<size_t>(kTilesPerBlock) * kTileRows * (p.max_cols_pad + kIdxPad) * dst_tiles->et_bytes +
-                            static_cast<size_t>(kWarps) * kTileRows * (p.t_max + 8) * 2 +
-                            static_cast<size_t>(p.t_max) * kRowBytes;
+        const size_t other = static_cast<size_t>(kWarps) * kKStageBytes +
+                             static_cast<size_t>(kTilesPerBlock) * p.max_cols_pad * 4 +
+                             static_cast<size_t>(kTilesPerBlock) * kTileRows * (p.max_cols_pad + kIdxPad) * dst_tiles->et_bytes +
+                             static_cast<size_t>(p.t_max) * kRowBytes;
+        p.tab_stride = table_stride(other, p.t_max, kWarps);
+        const size_t smem = other + static_cast<size_t>(kWarps) * kTileRows * p.tab_stride * 2;
         if (smem > 227 * 1024)
             return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc: tile plan needs %zu bytes of shared memory", smem);
         int rc;

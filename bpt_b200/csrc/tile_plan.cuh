@@ -45,6 +45,17 @@ constexpr int kMbQrSlot = 51;      // >= 0: needs the per-row relative-position 
 __host__ __device__ constexpr int cell_pos_index(int r, int c) {
     return (((c / 32) * 4 + (c % 32) / 8) * 32 + (r % 8) * 4 + (c % 8) / 2) * 4 + (r / 8) * 2 + (c & 1);
 }
+// Row stride (in 16-bit entries) of the per-warp score tables of the tile kernels: t_max types and the -inf
+// entry, padded.  t_max + 10 is an odd number of 32-bit words, which spreads a table's 16 rows over the
+// shared-memory banks (worth ~15 % of the forward on narrow tiles); t_max + 8 saves 512 bytes per block and
+// is taken when exactly those bytes would stop a second block per SM (plans whose widest tile has 192
+// columns).  other_bytes = the block's shared memory without the tables; n_tables = warps per block.
+inline int table_stride(size_t other_bytes, int t_max, int n_tables) {
+    constexpr size_t kTwoBlocksPerSm = (228 * 1024 - 2 * 1024) / 2;  // per block, with the 1 KB the system reserves
+    const size_t wide = other_bytes + static_cast<size_t>(n_tables) * kTileRows * (t_max + 10) * 2;
+    const size_t narrow = other_bytes + static_cast<size_t>(n_tables) * kTileRows * (t_max + 8) * 2;
+    return wide > kTwoBlocksPerSm && narrow <= kTwoBlocksPerSm ? t_max + 8 : t_max + 10;
+}
 constexpr uint16_t kNoEdge = 0xFFFF;
 constexpr uint8_t kNoEdge8 = 0xFF;
 

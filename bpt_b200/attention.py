@@ -109,7 +109,7 @@ class AttentionPlan:
 
 class TilePlan:
     """Groups of columns shared by m-blocks of <= 16 rows, for the tensor-core kernels.
-    Planned on the host from a CSR of the plan (integer work, once per graph), kept on the
+    Planned once per graph from a CSR of the plan (integer work; on the device by default), kept on the
     device.  transposed=False: rows are destinations, columns sources, cells carry edge types
     (bpt_attn_forward_tc).  transposed=True: rows are sources, columns destinations, cells
     carry the edge's position in the in-CSR (source side of bpt_attn_backward_tc)."""

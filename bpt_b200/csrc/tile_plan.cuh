@@ -1,4 +1,4 @@
-// Record layout of the tensor-core path's tile plan, shared by the host planner and the kernel.
+// Record layout of the tensor-core path's tile plan, shared by the planners (host and device) and the kernels.
 //
 // A *group* is a sorted list of source columns (padded to a multiple of 64) plus up to
 // kMaxMBlocks *m-blocks*; an m-block is <=16 destination rows with a dense matrix of edge

@@ -268,7 +268,8 @@ int bpt_attn_backward(const void *plan, const int32_t *counts_host, int64_t n_no
  * tolerance; the graph is given as a tile plan.  No counterpart in the reference beyond the
  * operator chain named at bpt_attn_forward.
  *
- * The planner runs on the host (pure integer code, no GPU needed).  It takes the in-CSR as
+ * bpt_tile_plan_create is the planner on the host (pure integer code, no GPU needed;
+ * bpt_tile_plan_create_device below makes the same plan on the device).  It takes the in-CSR as
  * host int32 arrays (in_indptr[n_nodes+1], in_src[n_edges], in_etype[n_edges] or NULL) and
  * covers the attention matrix with groups: a sorted list of source columns shared by up to
  * 8 m-blocks of <= 16 destination rows, each m-block holding a dense matrix of edge types

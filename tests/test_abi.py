@@ -94,3 +94,18 @@ def test_torch_extension_exports_the_reference_module_surface():
     import graphop
     assert graphop is installed is ext
     assert bpt_b200.install_dropin("ctypes")[0] is bpt_b200.graphop
+
+
+def test_tile_kernel_shared_memory_keeps_two_blocks_per_sm_where_it_can():
+    """bpt_attn_tc_smem_bytes (host arithmetic only): the per-warp score tables take the odd-word row stride
+    (t_max + 10 entries) unless exactly those 512 bytes would push a block past (228 KB - 2 KB) / 2, the most
+    that lets two blocks share an SM -- the case of plans whose widest tile has 192 columns."""
+    from bpt_b200 import _lib
+    L = _lib.lib()
+    other = lambda cols, t: 8 * 8192 + 2 * cols * 4 + 2 * 16 * (cols + 8) + t * 128
+    two_blocks = (228 * 1024 - 2 * 1024) // 2
+    assert L.bpt_attn_tc_smem_bytes(128, 104, 1) == other(128, 104) + 128 * 114 * 2 <= two_blocks
+    assert L.bpt_attn_tc_smem_bytes(192, 104, 1) == other(192, 104) + 128 * 112 * 2 <= two_blocks
+    assert other(192, 104) + 128 * 114 * 2 > two_blocks
+    assert L.bpt_attn_tc_smem_bytes(384, 104, 1) == other(384, 104) + 128 * 114 * 2 > two_blocks
+    assert L.bpt_attn_tc_smem_bytes(128, 0, 1) == other(128, 0) + 128 * 10 * 2

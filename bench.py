@@ -61,6 +61,9 @@ def parse():
                          "backward with the graph, CSRs and plans rebuilt every step, sequences/s; chain: the same "
                          "layer as `attention` through the reference's four separate operators (modules/op.py), "
                          "forward + backward; sweep: one sequence per rank for n in {8192..65536} x k in {1, 2, 4, 8}")
+    ap.add_argument("--attn-dropout", type=float, default=0.0,
+                    help="dropout rate on the attention weights inside the fused call (attention workload; the "
+                         "reference's training configurations use 0.1-0.3, the headline measures 0)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -656,9 +659,11 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
         launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
         bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"
 
+    drop = (float(a.attn_dropout), 20240607) if getattr(a, "attn_dropout", 0.0) > 0.0 else None
+
     def step():
-        o, lse = attention_forward(plan, q, k_, v, ak, scale)
-        return o, attention_backward(plan, q, k_, v, ak, scale, lse, d_o, o=o)
+        o, lse = attention_forward(plan, q, k_, v, ak, scale, dropout=drop)
+        return o, attention_backward(plan, q, k_, v, ak, scale, lse, d_o, o=o, dropout=drop)
 
     for _ in range(max(warmup, 3)):
         step()
@@ -677,9 +682,9 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
         start.record()
         for i in range(steps):
             ev[i][0].record()
-            o, lse = attention_forward(plan, q, k_, v, ak, scale)
+            o, lse = attention_forward(plan, q, k_, v, ak, scale, dropout=drop)
             ev[i][1].record()
-            attention_backward(plan, q, k_, v, ak, scale, lse, d_o, o=o)
+            attention_backward(plan, q, k_, v, ak, scale, lse, d_o, o=o, dropout=drop)
             ev[i][2].record()
         stop.record()
         barrier()
@@ -724,8 +729,8 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
                 s_main.wait_event(ev_in[b])
                 s_main.wait_event(ev_out[b])         # the previous results of this set have left the device
                 q_, kk_, v_, do_ = dev_in[b]
-                o, lse = attention_forward(plan, q_, kk_, v_, ak, scale)
-                grads = attention_backward(plan, q_, kk_, v_, ak, scale, lse, do_, o=o)
+                o, lse = attention_forward(plan, q_, kk_, v_, ak, scale, dropout=drop)
+                grads = attention_backward(plan, q_, kk_, v_, ak, scale, lse, do_, o=o, dropout=drop)
                 results[b] = (o, grads[0], grads[1], grads[2])
                 ev_done[b].record(s_main)
                 with torch.cuda.stream(s_out):
@@ -769,7 +774,8 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
         "unit": "edges/s", "n_gpus": world, "steps": steps, "blocks": len(blocks), "warmup": max(warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": dtype_name, "data": "synthetic",
-        "config": attention_config(a, seqs, n, k, dtype_name, causal, N, E),
+        "config": dict(attention_config(a, seqs, n, k, dtype_name, causal, N, E),
+                       **({"attention_dropout": drop[0]} if drop else {})),
         "gpu_launches": steps * len(blocks) * (launches_fwd + launches_bwd),
         "forward": {"ms": fwd_ms, "edges_per_sec": world * E / (fwd_ms * 1e-3)},
         "backward": {"ms": bwd_ms, "edges_per_sec": world * E / (bwd_ms * 1e-3)},

@@ -654,8 +654,9 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
         launches_bwd = 3 + (tpd.n_split > 0) + (tpt.n_split > 0)
         bwd_kernels = "attn_backward_dq_tile_kernel + build_type_table_kernel + 2 cuBLAS GEMMs + attn_backward_dkv_tile_kernel"
     else:
-        launches_fwd = 1 + (plan.counts[2] > 0)
-        fwd_kernel = "attn_forward_kernel"
+        tc32 = dtype == torch.float32 and att.FP32_FORWARD == "tc32" and att.tc32_eligible(q, ak, plan)
+        launches_fwd = 1 + ((plan.tile_plan().n_split > 0) if tc32 else (plan.counts[2] > 0))
+        fwd_kernel = "attn_forward_tile32_kernel" if tc32 else "attn_forward_kernel"
         launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
         bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"
 

@@ -238,6 +238,8 @@ class TilePlan:
         return ws
 
 
+# fp32 with head dim 64: "tc32" = forward on the tile plan with 3xTF32 products, "simt" = CUDA-core kernel
+FP32_FORWARD = os.environ.get("BPT_FP32_FORWARD", "tc32")
 TILE_PLANNER = os.environ.get("BPT_TILE_PLANNER", "device")
 # Widest column list of a 16-row tile; rows that would need more are cut by blocks of 128 source columns.
 TILE_MAX_COLS = int(os.environ.get("BPT_TILE_MAX_COLS", "384"))
@@ -293,6 +295,36 @@ def attention_forward_tc(plan, q, k, v, embed_ak, scale, dropout=None):
             tp.t_max, tp.max_mblocks, tp.max_qr_slots, tp.n_etypes, q.data_ptr(), k.data_ptr(), v.data_ptr(),
             _lib.ptr(embed_ak), float(scale), o.data_ptr(), lse.data_ptr(), h, d, _lib.dtype_code(q.dtype),
             ws.data_ptr(), ws.numel(), drop_ptr, _lib.stream()))
+    return o, lse
+
+
+def tc32_eligible(q, embed_ak, plan):
+    """fp32 with head dim 64 and a tile plan that the 3xTF32 tile kernel takes: no CUDA-core row items and
+    tables that fit in shared memory."""
+    if not (q.dtype == torch.float32 and q.size(-1) == 64):
+        return False
+    tp = plan.tile_plan()
+    if tp.n_row_items:
+        return False
+    need = _lib.lib().bpt_attn_forward_tc32_smem_bytes(tp.max_cols_pad, tp.t_max if embed_ak is not None else 0,
+                                                       tp.et_bytes)
+    return 0 < need <= MAX_BLOCK_SMEM
+
+
+def attention_forward_tc32(plan, q, k, v, embed_ak, scale, dropout=None):
+    """fp32 forward through bpt_attn_forward_tc32 (tile plan, every product as three TF32 products; within
+    the fp32 tolerance of the CUDA-core kernel).  Returns (o, lse)."""
+    N, h, d = _check_inputs(plan, q, k, v, embed_ak)
+    drop_keep, drop_ptr = _lib.dropout_arg(dropout)
+    tp = plan.tile_plan()
+    o = torch.empty_like(q)
+    lse = torch.empty((N, h), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        ws = tp.workspace(h, q.device)
+        s = tp.struct()
+        _lib.check(_lib.lib().bpt_attn_forward_tc32(
+            ctypes.addressof(s), N, tp.n_etypes, q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(embed_ak),
+            float(scale), o.data_ptr(), lse.data_ptr(), h, d, ws.data_ptr(), ws.numel(), drop_ptr, _lib.stream()))
     return o, lse
 
 
@@ -353,9 +385,12 @@ def attention_forward(plan, q, k, v, embed_ak, scale, tensor_cores=None, dropout
     pair must be given to attention_backward."""
     N, h, d = _check_inputs(plan, q, k, v, embed_ak)
     if tensor_cores is None:
-        tensor_cores = tensor_core_eligible(q, embed_ak, plan)
+        tensor_cores = tensor_core_eligible(q, embed_ak, plan) or (FP32_FORWARD == "tc32" and
+                                                                   tc32_eligible(q, embed_ak, plan))
     drop_keep, drop_ptr = _lib.dropout_arg(dropout)
     if tensor_cores:
+        if q.dtype == torch.float32:
+            return attention_forward_tc32(plan, q, k, v, embed_ak, scale, dropout)
         if FORWARD_IMPL == "tc5" and drop_ptr is None and tc5_eligible(q, embed_ak, plan):
             return attention_forward_tc5(plan, q, k, v, embed_ak, scale)
         return attention_forward_tc(plan, q, k, v, embed_ak, scale, dropout)

@@ -407,6 +407,21 @@ int bpt_attn_forward_tc5(const bpt_tile_plan_t *tiles, int64_t n_nodes, int n_et
                          void *workspace, size_t workspace_bytes, bpt_stream_t stream);
 int bpt_attn_forward_tc5_status(const void *workspace, int32_t *status_host, bpt_stream_t stream);
 
+/* ------------------------------------------------------------------------------------
+ * Forward for fp32 tensors on tensor cores (head dim 64), same result as bpt_attn_forward within its
+ * fp32 tolerance and the same operator chain of the reference (modules/attention.py:66-77): the tile
+ * plan of bpt_attn_forward_tc (exported without row items; 8- or 16-bit cells), every product run as
+ * three TF32 products on operands split into a TF32 head and an fp32 remainder.  q, o: (n_nodes, h, 64),
+ * k, v: (n_src, h, 64), ak: (n_etypes, 64) or NULL, all fp32 and 16-byte aligned; lse fp32 (n_nodes, h).
+ * The workspace is that of bpt_attn_forward_tc_workspace_bytes.
+ * bpt_attn_forward_tc32_smem_bytes: shared memory per block for a plan with these sizes (host only).
+ * ---------------------------------------------------------------------------------- */
+size_t bpt_attn_forward_tc32_smem_bytes(int max_cols_pad, int t_max, int et_bytes);
+int bpt_attn_forward_tc32(const bpt_tile_plan_t *tiles, int64_t n_nodes, int n_etypes, const void *q, const void *k,
+                          const void *v, const void *ak, double scale, void *o, float *lse, int h, int d,
+                          void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout,
+                          bpt_stream_t stream);
+
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

@@ -657,8 +657,19 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
         tc32 = dtype == torch.float32 and att.FP32_FORWARD == "tc32" and att.tc32_eligible(q, ak, plan)
         launches_fwd = 1 + ((plan.tile_plan().n_split > 0) if tc32 else (plan.counts[2] > 0))
         fwd_kernel = "attn_forward_tile32_kernel" if tc32 else "attn_forward_kernel"
-        launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
-        bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"
+        if tc32 and att.FP32_BACKWARD == "tc32":
+            # destination-side tiles, relative-position part of dQ, source-side tiles (or the CUDA-core
+            # kernel), d embed_ak (+ merges)
+            tiles_t = att.FP32_BACKWARD_SOURCE_SIDE == "tc32"
+            tpd = plan.tile_plan()
+            n_split_src = plan.tile_plan_t().n_split if tiles_t else plan.counts[5]
+            launches_bwd = 4 + (tpd.n_split > 0) + (n_split_src > 0) + (plan.counts[8] > 0)
+            bwd_kernels = ("attn_backward_dq_tile32_kernel + attn_backward_dq_ak_kernel + " +
+                           ("attn_backward_dkv_tile32_kernel" if tiles_t else "attn_backward_dkv_kernel") +
+                           " + attn_backward_dak_kernel")
+        else:
+            launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
+            bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"
 
     drop = (float(a.attn_dropout), 20240607) if getattr(a, "attn_dropout", 0.0) > 0.0 else None
 

@@ -68,6 +68,9 @@ SIGNATURES = {
     "bpt_attn_tc_smem_bytes": (_sz, [_int, _int, _int]),
     "bpt_attn_forward_tc32_smem_bytes": (_sz, [_int, _int, _int]),
     "bpt_attn_forward_tc32": (_int, [_vp, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _int, _int, _vp, _sz, _vp, _vp]),
+    "bpt_attn_backward_tc32_workspace_bytes": (_sz, [_vp, _vp, _vp, _i64, _i64, _int]),
+    "bpt_attn_backward_tc32": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _dbl, _vp, _vp, _vp, _vp,
+                                      _vp, _vp, _vp, _int, _int, _vp, _sz, _vp, _vp]),
     "bpt_attn_forward_tc_workspace_bytes": (_sz, [_i64, _int]),
     "bpt_attn_forward_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp, _vp,
                                    _i64, _i64, _int, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _dbl, _vp,

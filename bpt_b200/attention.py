@@ -240,6 +240,10 @@ class TilePlan:
 
 # fp32 with head dim 64: "tc32" = forward on the tile plan with 3xTF32 products, "simt" = CUDA-core kernel
 FP32_FORWARD = os.environ.get("BPT_FP32_FORWARD", "tc32")
+# fp32 backward: "tc32" = destination side (p, dp, K part of dQ) on the tile plan with 3xTF32 products, the
+# source-side and embed_ak passes on the CUDA-core kernels; "simt" = all CUDA-core
+FP32_BACKWARD = os.environ.get("BPT_FP32_BACKWARD", "tc32")
+FP32_BACKWARD_SOURCE_SIDE = os.environ.get("BPT_FP32_BACKWARD_SOURCE_SIDE", "tc32")  # with FP32_BACKWARD = "tc32"
 TILE_PLANNER = os.environ.get("BPT_TILE_PLANNER", "device")
 # Widest column list of a 16-row tile; rows that would need more are cut by blocks of 128 source columns.
 TILE_MAX_COLS = int(os.environ.get("BPT_TILE_MAX_COLS", "384"))
@@ -441,6 +445,8 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
         raise RuntimeError("bpt_attention: d_o must have the shape and dtype of q")
     if lse.shape != (N, h) or lse.dtype != torch.float32:
         raise RuntimeError("bpt_attention: lse must be float32 (n_nodes, h)")
+    tile32 = tensor_cores is not False and o is not None and FP32_BACKWARD == "tc32" and \
+        tc32_eligible(q, embed_ak, plan) and plan.tile_plan().cellpos is not None
     if tensor_cores is None:
         tensor_cores = o is not None and tensor_core_eligible(q, embed_ak, plan)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -449,6 +455,23 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
     if embed_ak is not None:
         dak = torch.zeros((embed_ak.size(0), d), dtype=torch.float32, device=q.device)
     L = _lib.lib()
+    if tile32:
+        _lib.require_cuda(o)
+        tiles = plan.tile_plan().struct()
+        src_tiles = plan.tile_plan_t().struct() if FP32_BACKWARD_SOURCE_SIDE == "tc32" else None
+        src_ptr = None if src_tiles is None else ctypes.addressof(src_tiles)
+        with torch.cuda.device(q.device):
+            ws = plan._ws.get(("tc32_bwd", h))
+            if ws is None:
+                ws = _lib.workspace(L.bpt_attn_backward_tc32_workspace_bytes(
+                    ctypes.addressof(tiles), src_ptr, ctypes.addressof(plan._counts), plan.n_nodes, plan.n_edges, h),
+                    q.device)
+                plan._ws[("tc32_bwd", h)] = ws
+            _lib.check(L.bpt_attn_backward_tc32(
+                ctypes.addressof(tiles), src_ptr, *plan._args(), q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(embed_ak),
+                float(scale), o.data_ptr(), lse.data_ptr(), d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                dv.data_ptr(), _lib.ptr(dak), h, d, ws.data_ptr(), ws.numel(), drop_ptr, _lib.stream()))
+        return dq, dk, dv, dak
     with torch.cuda.device(q.device):
         if tensor_cores:
             if o is None:

@@ -168,4 +168,16 @@ int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, cons
                                   const uint32_t *PS, void *dq, float *dak, float *part_dak, int H, int D,
                                   cudaStream_t stream);
 
+// Defined in fused_simt.cu: what the fp32 tile backward keeps of the CUDA-core backward, from the fp32 scratch
+// (P, dP in [in-CSR position][head] order, delta per (row, head)): dq += relative-position part, dK and dV,
+// d embed_ak.  part_dkv: counts[4] * 2 * H * D floats, part_dak: counts[7] * D floats.
+int launch_backward_rest_f32(const PlanView &p, const int32_t *counts, const float *q, const float *ak,
+                             const float *d_o, const float *P, const float *dP, const float *delta, float scale,
+                             float *dq, float *dk, float *dv, float *dak, float *part_dkv, float *part_dak, int H,
+                             int D, const Dropout &drop, cudaStream_t stream);
+// out[row, :] = sum over the row's slots ({row, first, count, .} records), in slot order, of fp32 partial rows;
+// with out1 a slot holds two rows side by side (out | out1).
+int launch_sum_merge_f32(const int4 *split_rows, int n_split, const float *part, int width, float *out,
+                         cudaStream_t stream, float *out1 = nullptr);
+
 }  // namespace bpt

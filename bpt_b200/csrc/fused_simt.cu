@@ -435,11 +435,15 @@ attn_backward_dak_kernel(const int4 *__restrict__ items, int n_items, const int3
 // whose destination-side kernel only does the K part and leaves {bf16 p, bf16 dS} per (edge, head).  One warp per
 // destination row (whole row, fixed edge order); rows whose edges share one type are skipped:
 // their sum of dS is zero.
-template <typename T, int LPH, bool kVec>
+// kPacked = false: the scratch is fp32 P, dP in [in-CSR position][head] order and delta per (row, head),
+// dS = scale * p * (dp - delta).
+template <typename T, int LPH, bool kVec, bool kPacked = true>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
                            const int32_t *__restrict__ row_uniform, int n_rows, const T *__restrict__ ak,
-                           const uint32_t *__restrict__ PS, int64_t ps_edges, T *__restrict__ dq, Geometry g) {
+                           const uint32_t *__restrict__ PS, int64_t ps_edges, T *__restrict__ dq, Geometry g,
+                           const float *__restrict__ P = nullptr, const float *__restrict__ dP = nullptr,
+                           const float *__restrict__ delta = nullptr, float scale = 1.f) {
     constexpr int HPW = 32 / LPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerBlock + warp;
@@ -456,8 +460,13 @@ attn_backward_dq_ak_kernel(const int32_t *__restrict__ in_indptr, const int32_t 
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
     const int beg = in_indptr[row], end = in_indptr[row + 1];
 #pragma unroll 4
+    const float dl = kPacked ? 0.f : delta[static_cast<int64_t>(row) * H + head];
     for (int j = beg; j < end; ++j) {
-        const float ds = __uint_as_float(PS[head * ps_edges + j] & 0xffff0000u);
+        float ds;
+        if (kPacked)
+            ds = __uint_as_float(PS[head * ps_edges + j] & 0xffff0000u);
+        else
+            ds = scale * P[static_cast<int64_t>(j) * H + head] * (dP[static_cast<int64_t>(j) * H + head] - dl);
         float af[16];
         load16<T, kVec>(ak + static_cast<int64_t>(in_etype[j]) * D + d0, nvalid, af);
 #pragma unroll
@@ -706,6 +715,59 @@ int launch_backward_ak_terms_bf16(const PlanView &p, const int32_t *counts, cons
             BPT_LAUNCH_CHECK();
         }
     }
+    return BPT_OK;
+}
+
+// The passes of the CUDA-core backward that the fp32 tile backward keeps, all from the fp32 scratch (P, dP in
+// [in-CSR position][head] order, delta per (row, head)) that its destination-side kernel leaves: the
+// relative-position part of dQ (added to dq), dK and dV over the out-CSR, d embed_ak over the type buckets.
+int launch_backward_rest_f32(const PlanView &p, const int32_t *counts, const float *q, const float *ak,
+                             const float *d_o, const float *P, const float *dP, const float *delta, float scale,
+                             float *dq, float *dk, float *dv, float *dak, float *part_dkv, float *part_dak, int H,
+                             int D, const Dropout &drop, cudaStream_t stream) {
+    using T = float;
+    const int lph = pick_lph(D);
+    const bool vec = can_vectorise<T>(D, lph, q, ak, d_o, dq, dk, dv);
+    const Geometry g{H, D};
+    const int hpw = 32 / lph;
+    const unsigned gy = (H + hpw - 1) / hpw;
+    if (ak != nullptr && p.n_nodes > 0) {
+        const dim3 grid(static_cast<unsigned>((p.n_nodes + kWarpsPerBlock - 1) / kWarpsPerBlock), gy);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dq_ak_kernel<T, LPH, VEC, false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.in_indptr, p.in_etype, p.row_uniform, static_cast<int>(p.n_nodes), ak, nullptr, 0, dq, g, P, dP, delta, scale)));
+        BPT_LAUNCH_CHECK();
+    }
+    if (counts[3] > 0 && dk != nullptr && dv != nullptr) {
+        const dim3 grid((counts[3] + kWarpsPerBlock - 1) / kWarpsPerBlock, gy);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dkv_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.out_work.items, counts[3], p.out_dst, p.out_inpos, q, d_o, P, dP, delta, scale, dk, dv, part_dkv, g, drop)));
+        BPT_LAUNCH_CHECK();
+        if (counts[5] > 0) {
+            sum_merge_kernel<T><<<counts[5], 256, 0, stream>>>(p.out_work.split_rows, counts[5], part_dkv, H * D, 2, dk, dv);
+            BPT_LAUNCH_CHECK();
+        }
+    }
+    if (ak != nullptr && dak != nullptr && counts[6] > 0) {
+        const dim3 grid((counts[6] + kWarpsPerBlock - 1) / kWarpsPerBlock, 1);
+        BPT_DISPATCH_LPH_VEC(lph, vec, (attn_backward_dak_kernel<T, LPH, VEC><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            p.et_work.items, counts[6], p.et_dst, p.et_inpos, q, P, dP, delta, scale, dak, part_dak, g)));
+        BPT_LAUNCH_CHECK();
+        if (counts[8] > 0) {
+            sum_merge_kernel<float><<<counts[8], 128, 0, stream>>>(p.et_work.split_rows, counts[8], part_dak, D, 1, dak, dak);
+            BPT_LAUNCH_CHECK();
+        }
+    }
+    return BPT_OK;
+}
+
+// out[row, :] = sum over the row's slots, in slot order, of fp32 partial rows of `width` columns; with out1 a
+// slot holds two such rows side by side (out | out1).
+int launch_sum_merge_f32(const int4 *split_rows, int n_split, const float *part, int width, float *out,
+                         cudaStream_t stream, float *out1) {
+    if (n_split <= 0) return BPT_OK;
+    sum_merge_kernel<float><<<n_split, 256, 0, stream>>>(split_rows, n_split, part, width, out1 ? 2 : 1, out,
+                                                         out1 ? out1 : out);
+    BPT_LAUNCH_CHECK();
     return BPT_OK;
 }
 

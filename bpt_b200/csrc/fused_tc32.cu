@@ -115,6 +115,79 @@ __device__ __forceinline__ void load_q_frags(const float *__restrict__ row_lo, c
     }
 }
 
+// The per-head score table of an m-block, in the log2 domain: with a table (use_qr) entry [row][type] =
+// scale * log2(e) * <q[row], ak[type]> for the tq types of the m-block and entry tq = -inf (the cell of a
+// missing edge); without one entry 0 = 0, entry 1 = -inf, and when every row has one edge type its
+// <q[row], ak[type]> comes back as the row's constant (bias_lo for row g, bias_hi for row g + 8).
+// Four groups of eight types per pass share the splits of Q.
+template <bool kHasBias>
+__device__ __forceinline__ void build_score_table(const float (&qa)[8][4], const float *__restrict__ ak, int n_etypes,
+                                                  bool use_qr, int tq, const int32_t *__restrict__ mb, float *s_tab,
+                                                  int tab_stride, float sl2, int g, int t, float &bias_lo,
+                                                  float &bias_hi) {
+    if (use_qr) {
+        for (int nt0 = 0; nt0 < tq; nt0 += 32) {
+            float c[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { c[u][0] = 0.f; c[u][1] = 0.f; c[u][2] = 0.f; c[u][3] = 0.f; }
+            const float *ak_row[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                int type = nt0 + 8 * u + g;
+                type = type < n_etypes ? type : n_etypes - 1;
+                ak_row[u] = ak + static_cast<int64_t>(type) * kHeadDim + t;
+            }
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                float a_hi[4], a_lo[4];
+                split4(qa[s], a_hi, a_lo);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (nt0 + 8 * u < tq)
+                        mma_3xtf32(c[u], a_hi, a_lo, __ldg(ak_row[u] + 8 * s), __ldg(ak_row[u] + 8 * s + 4));
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int nt = nt0 + 8 * u;
+                if (nt < tq) {
+                    s_tab[g * tab_stride + nt + 2 * t] = c[u][0] * sl2;
+                    s_tab[g * tab_stride + nt + 2 * t + 1] = c[u][1] * sl2;
+                    s_tab[(g + 8) * tab_stride + nt + 2 * t] = c[u][2] * sl2;
+                    s_tab[(g + 8) * tab_stride + nt + 2 * t + 1] = c[u][3] * sl2;
+                }
+            }
+        }
+        if (t == 0) {
+            s_tab[g * tab_stride + tq] = -INFINITY;
+            s_tab[(g + 8) * tab_stride + tq] = -INFINITY;
+        }
+    } else {
+        if (t == 0) {
+            s_tab[g * tab_stride] = 0.f;
+            s_tab[g * tab_stride + 1] = -INFINITY;
+            s_tab[(g + 8) * tab_stride] = 0.f;
+            s_tab[(g + 8) * tab_stride + 1] = -INFINITY;
+        }
+        if (kHasBias) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                int type = mb[kMbRowEtOff + g + 8 * half];
+                type = type < 0 ? 0 : (type < n_etypes ? type : n_etypes - 1);
+                const float *a = ak + static_cast<int64_t>(type) * kHeadDim + t;
+                float sum = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    sum = fmaf(qa[s][half], __ldg(a + 8 * s), sum);
+                    sum = fmaf(qa[s][2 + half], __ldg(a + 8 * s + 4), sum);
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                (half ? bias_hi : bias_lo) = sum * sl2;
+            }
+        }
+    }
+}
+
 template <typename ET, bool kHasBias, bool kDrop>
 __global__ void __launch_bounds__(kWarps * 32, 3)
 attn_forward_tile32_kernel(const Tc32Params p) {
@@ -216,70 +289,7 @@ attn_forward_tile32_kernel(const Tc32Params p) {
             load_q_frags(p.q + (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim,
                          p.q + (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim, t, qa);
             float bias_lo = 0.f, bias_hi = 0.f;  // per-row constant of m-blocks without a table (log2 domain)
-            if (use_qr) {
-                // table[row][type] = scale * log2(e) * <q[row], ak[type]> for the types of this m-block, four
-                // groups of eight types per pass (the splits of Q are shared by the four)
-                for (int nt0 = 0; nt0 < tq; nt0 += 32) {
-                    float c[4][4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) { c[u][0] = 0.f; c[u][1] = 0.f; c[u][2] = 0.f; c[u][3] = 0.f; }
-                    const float *ak_row[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        int type = nt0 + 8 * u + g;
-                        type = type < p.n_etypes ? type : p.n_etypes - 1;
-                        ak_row[u] = p.ak + static_cast<int64_t>(type) * kHeadDim + t;
-                    }
-#pragma unroll
-                    for (int s = 0; s < 8; ++s) {
-                        float a_hi[4], a_lo[4];
-                        split4(qa[s], a_hi, a_lo);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (nt0 + 8 * u < tq)
-                                mma_3xtf32(c[u], a_hi, a_lo, __ldg(ak_row[u] + 8 * s), __ldg(ak_row[u] + 8 * s + 4));
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int nt = nt0 + 8 * u;
-                        if (nt < tq) {
-                            s_tab[g * tab_stride + nt + 2 * t] = c[u][0] * sl2;
-                            s_tab[g * tab_stride + nt + 2 * t + 1] = c[u][1] * sl2;
-                            s_tab[(g + 8) * tab_stride + nt + 2 * t] = c[u][2] * sl2;
-                            s_tab[(g + 8) * tab_stride + nt + 2 * t + 1] = c[u][3] * sl2;
-                        }
-                    }
-                }
-                if (t == 0) {
-                    s_tab[g * tab_stride + tq] = -INFINITY;
-                    s_tab[(g + 8) * tab_stride + tq] = -INFINITY;
-                }
-            } else {
-                if (t == 0) {
-                    s_tab[g * tab_stride] = 0.f;
-                    s_tab[g * tab_stride + 1] = -INFINITY;
-                    s_tab[(g + 8) * tab_stride] = 0.f;
-                    s_tab[(g + 8) * tab_stride + 1] = -INFINITY;
-                }
-                if (kHasBias) {
-                    // every row has one edge type: <q[row], ak[type]> shifts all its scores alike
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        int type = mb[kMbRowEtOff + g + 8 * half];
-                        type = type < 0 ? 0 : (type < p.n_etypes ? type : p.n_etypes - 1);
-                        const float *a = p.ak + static_cast<int64_t>(type) * kHeadDim + t;
-                        float sum = 0.f;
-#pragma unroll
-                        for (int s = 0; s < 8; ++s) {
-                            sum = fmaf(qa[s][half], __ldg(a + 8 * s), sum);
-                            sum = fmaf(qa[s][2 + half], __ldg(a + 8 * s + 4), sum);
-                        }
-                        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                        (half ? bias_hi : bias_lo) = sum * sl2;
-                    }
-                }
-            }
+            build_score_table<kHasBias>(qa, p.ak, p.n_etypes, use_qr, tq, mb, s_tab, tab_stride, sl2, g, t, bias_lo, bias_hi);
             __syncwarp();
 
             float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
@@ -454,6 +464,481 @@ int launch_tile32_kernel(const Tc32Params &p, int64_t n_groups, size_t smem, cud
     return BPT_OK;
 }
 
+
+// ------------------------------------------------------------------ backward, destination side
+//
+// For every (edge, head): p = exp2(s - lse), dp = <dO[dst], v[src]> (times the dropout factor), written to the
+// fp32 scratch of the CUDA-core backward (P, dP in [in-CSR position][head] order) with delta = <dO, O> per
+// (row, head), so that the source-side and type-bucket passes of that backward run unchanged on it; and the K
+// part of dQ, dQ[row] += sum_e dS_e k[src_e] with dS = scale * p * (dp - delta).  The relative-position part
+// (sum_e dS_e ak[type_e]) is added afterwards from the scratch.
+//
+// Same tiles, tables and three-product TF32 scheme as the forward.  Per step of 16 columns a warp holds the K
+// rows and the V rows in a swizzled 4 KB tile each, in one of two buffers (the next step's rows travel while
+// this step's products run): dP = dO V^T (ldmatrix on V), S = Q K^T (ldmatrix on K), the per-cell work,
+// dQ += dS K (K read with plain 4-byte loads: row 8 ks + 2 t (+1), element 8 dn + g of the swizzled tile is
+// bank-conflict-free).  Q, dO and the dQ accumulators take 96 registers: two blocks of four warps per SM.
+struct Dq32Params {
+    const int32_t *groups, *mblocks, *cols, *cellpos;
+    const void *et;
+    const float *q, *k, *v, *ak, *o, *d_o, *lse;
+    float *P, *dP, *delta, *part_dq, *dq;
+    int n_etypes, H, max_cols_pad, t_max, tab_stride;
+    int64_t n_groups;
+    float scale;
+    Dropout drop;
+};
+
+constexpr int kDqBufBytes = 2 * kKBytes;       // K rows, V rows of one step
+constexpr int kDqStageBytes = 2 * kDqBufBytes;  // per warp: two such buffers
+#ifndef BPT_DQ32_MIN_BLOCKS
+#define BPT_DQ32_MIN_BLOCKS 2
+#endif
+constexpr int kDqMinBlocks = BPT_DQ32_MIN_BLOCKS;
+
+template <typename ET, bool kHasBias, bool kDrop>
+__global__ void __launch_bounds__(kWarps * 32, kDqMinBlocks)
+attn_backward_dq_tile32_kernel(const Dq32Params p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    // layout: per warp 2 x {K tile 4 KB, V tile 4 KB} | column ids | table indices of the m-block | tables (fp32, per warp)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int idx_stride = p.max_cols_pad + kEtPad;
+    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kWarps * kDqStageBytes);
+    ET *s_idx = reinterpret_cast<ET *>(s_cols + p.max_cols_pad);
+    const int tab_stride = p.tab_stride;
+    float *s_tab_all = reinterpret_cast<float *>(smem + kWarps * kDqStageBytes + p.max_cols_pad * 4 +
+                                                 (kTileRows * idx_stride * static_cast<int>(sizeof(ET)) + 15) / 16 * 16);
+    const int64_t tile = blockIdx.x;
+    const int32_t *grp = p.groups + tile * kGroupInts;
+    const int n_mblocks = grp[kGroupMbCount];
+    if (n_mblocks == 0) return;
+    const int ncols_pad = grp[kGroupNcolsPad];
+    const int g = lane >> 2, t = lane & 3;
+    const int H = p.H;
+    const uint32_t s_kv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kDqStageBytes));
+    const int n_steps = ncols_pad / kStep;
+    float *s_tab = s_tab_all + static_cast<int64_t>(warp) * kTileRows * tab_stride;
+    const uint32_t s_tab_lo = static_cast<uint32_t>(__cvta_generic_to_shared(s_tab + g * tab_stride));
+    const uint32_t s_tab_hi = static_cast<uint32_t>(__cvta_generic_to_shared(s_tab + (g + 8) * tab_stride));
+    const float sl2 = p.scale * kLog2e;
+    const ET *et_base = static_cast<const ET *>(p.et);
+    {
+        const int32_t *gc = p.cols + grp[kGroupColOff];
+        for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
+    }
+    // Row copies: lane l copies piece (l & 15) of rows (l >> 4) + 2 i, pieces swizzled on their low three bits.
+    const int copy_row = lane >> 4, copy_piece = lane & 15;
+    const uint32_t row_pitch = static_cast<uint32_t>(H) * kRowBytes;
+    auto issue_kv = [&](int h, int j, int b) {
+        const uint64_t head_off = static_cast<uint64_t>(h * kRowBytes + copy_piece * 16);
+        const int32_t *cj = s_cols + j * kStep + copy_row;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = copy_row + 2 * i;
+            const uint64_t off = static_cast<uint64_t>(static_cast<uint32_t>(cj[2 * i])) * row_pitch + head_off;
+            const uint32_t dst = s_kv_addr + b * kDqBufBytes + r * kRowBytes + (((copy_piece & 8) | ((copy_piece ^ r) & 7)) << 4);
+            cp_async16(dst, reinterpret_cast<const char *>(p.k) + off);
+            cp_async16(dst + kKBytes, reinterpret_cast<const char *>(p.v) + off);
+        }
+    };
+    // dQ += dS K reads element 8 dn + g of rows 8 ks + 2 t and 8 ks + 2 t + 1: piece 2 dn + (g >> 2), whose low
+    // three bits are swizzled with the row's
+    const uint32_t kb_lo = (2 * t) * kRowBytes + (g & 3) * 4;
+    const uint32_t kx_lo = static_cast<uint32_t>((g >> 2) ^ (2 * t)), kx_hi = kx_lo ^ 1u;
+
+    for (int mbi = 0; mbi < n_mblocks; ++mbi) {
+        const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
+        const bool use_qr = kHasBias && mb[kMbQrSlot] >= 0;
+        const int tq = use_qr ? mb[kMbTq] : 0;
+        const uint32_t none_idx = use_qr ? tq : 1;
+        const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
+        const int4 *pos_base = reinterpret_cast<const int4 *>(p.cellpos + mb[kMbEtOff]) + lane;
+        auto next_step = [&](int j) {
+            ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 1)) & 1u)) ++j;
+            return j;
+        };
+        __syncthreads();  // previous m-block's indices are no longer read; s_cols is visible
+        int primed_step = -1;
+        if (warp < H) primed_step = next_step(-1);
+        if (primed_step >= 0 && primed_step < n_steps) issue_kv(warp, primed_step, 0);
+        cp_async_commit();
+        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
+        {
+            constexpr int kCellsPerPiece = 16 / static_cast<int>(sizeof(ET));
+            const uint4 *ge = reinterpret_cast<const uint4 *>(et_base + mb[kMbEtOff]);
+            const int pieces = kTileRows * ncols_pad / kCellsPerPiece;
+            for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+                const int cell = i * kCellsPerPiece;
+                const int chunk = cell / (kTileRows * kTileChunk), rem = cell % (kTileRows * kTileChunk);
+                const int r = rem / kTileChunk, c = rem % kTileChunk;
+                const uint4 raw = __ldg(ge + i);
+                const ET *e = reinterpret_cast<const ET *>(&raw);
+                ET *dst = s_idx + r * idx_stride + chunk * kTileChunk + c;
+#pragma unroll
+                for (int u = 0; u < kCellsPerPiece; ++u)
+                    dst[u] = static_cast<ET>(e[u] == EtTraits<ET>::kNone ? none_idx : (use_qr ? e[u] : 0u));
+            }
+        }
+        __syncthreads();
+
+        for (int h = warp; h < H; h += kWarps) {
+            const int64_t off_lo = (static_cast<int64_t>(row_lo < 0 ? 0 : row_lo) * H + h) * kHeadDim;
+            const int64_t off_hi = (static_cast<int64_t>(row_hi < 0 ? 0 : row_hi) * H + h) * kHeadDim;
+            float qa[8][4], da[8][4];
+            load_q_frags(p.q + off_lo, p.q + off_hi, t, qa);
+            load_q_frags(p.d_o + off_lo, p.d_o + off_hi, t, da);
+            float delta_lo = 0.f, delta_hi = 0.f;
+            {
+                const float *o_lo = p.o + off_lo + t, *o_hi = p.o + off_hi + t;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    delta_lo = fmaf(da[s][0], __ldg(o_lo + 8 * s), fmaf(da[s][2], __ldg(o_lo + 8 * s + 4), delta_lo));
+                    delta_hi = fmaf(da[s][1], __ldg(o_hi + 8 * s), fmaf(da[s][3], __ldg(o_hi + 8 * s + 4), delta_hi));
+                }
+                delta_lo += __shfl_xor_sync(0xffffffffu, delta_lo, 1);
+                delta_lo += __shfl_xor_sync(0xffffffffu, delta_lo, 2);
+                delta_hi += __shfl_xor_sync(0xffffffffu, delta_hi, 1);
+                delta_hi += __shfl_xor_sync(0xffffffffu, delta_hi, 2);
+            }
+            float lse2_lo = row_lo < 0 ? 0.f : p.lse[static_cast<int64_t>(row_lo) * H + h];
+            float lse2_hi = row_hi < 0 ? 0.f : p.lse[static_cast<int64_t>(row_hi) * H + h];
+            lse2_lo = lse2_lo == -INFINITY ? 0.f : lse2_lo * kLog2e;
+            lse2_hi = lse2_hi == -INFINITY ? 0.f : lse2_hi * kLog2e;
+            if (t == 0) {
+                if (row_lo >= 0) p.delta[static_cast<int64_t>(row_lo) * H + h] = delta_lo;
+                if (row_hi >= 0) p.delta[static_cast<int64_t>(row_hi) * H + h] = delta_hi;
+            }
+            {
+                // rows with one edge type: the forward folded scale * <q, ak[type]> into lse; take it out again
+                float bias_lo = 0.f, bias_hi = 0.f;
+                build_score_table<kHasBias>(qa, p.ak, p.n_etypes, use_qr, tq, mb, s_tab, tab_stride, sl2, g, t, bias_lo, bias_hi);
+                lse2_lo -= bias_lo;
+                lse2_hi -= bias_hi;
+            }
+            __syncwarp();
+
+            float acc[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { acc[i][0] = 0.f; acc[i][1] = 0.f; acc[i][2] = 0.f; acc[i][3] = 0.f; }
+            float *__restrict__ P_h = p.P + h;
+            float *__restrict__ dP_h = p.dP + h;
+
+            int j = primed_step;
+            if (j < 0) {
+                j = next_step(-1);
+                if (j < n_steps) issue_kv(h, j, 0);
+                cp_async_commit();
+            }
+            primed_step = -1;
+            int buf = 0;
+            while (j < n_steps) {
+                const int nj = next_step(j);
+                const int c0 = j * kStep;
+                if (nj < n_steps) issue_kv(h, nj, buf ^ 1);
+                cp_async_commit();
+                const uint32_t s_k_addr = s_kv_addr + buf * kDqBufBytes, s_v_addr = s_k_addr + kKBytes;
+                // the cells' in-CSR positions, in fragment order (cell_pos_index): column groups 2 j and 2 j + 1
+                const int4 pos4[2] = {__ldg(pos_base + (j * 2) * 32), __ldg(pos_base + (j * 2 + 1) * 32)};
+                cp_async_wait<1>();  // this step's rows have landed; the newest group is the next step's
+                __syncwarp();
+                float dp[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) { dp[nt][0] = 0.f; dp[nt][1] = 0.f; dp[nt][2] = 0.f; dp[nt][3] = 0.f; }
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) {
+                    float a_hi[2][4], a_lo[2][4];
+                    split4(da[2 * sp], a_hi[0], a_lo[0]);
+                    split4(da[2 * sp + 1], a_hi[1], a_lo[1]);
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int r = nt * 8 + (lane & 7), piece = sp * 4 + (lane >> 3);
+                        uint32_t b[4];
+                        ldmatrix_x4(b, s_v_addr + r * kRowBytes + (((piece & 8) | ((piece ^ r) & 7)) << 4));
+                        mma_3xtf32(dp[nt], a_hi[0], a_lo[0], __uint_as_float(b[0]), __uint_as_float(b[1]));
+                        mma_3xtf32(dp[nt], a_hi[1], a_lo[1], __uint_as_float(b[2]), __uint_as_float(b[3]));
+                    }
+                }
+                float s[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) { s[nt][0] = 0.f; s[nt][1] = 0.f; s[nt][2] = 0.f; s[nt][3] = 0.f; }
+#pragma unroll
+                for (int sp = 0; sp < 4; ++sp) {
+                    float a_hi[2][4], a_lo[2][4];
+                    split4(qa[2 * sp], a_hi[0], a_lo[0]);
+                    split4(qa[2 * sp + 1], a_hi[1], a_lo[1]);
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int r = nt * 8 + (lane & 7), piece = sp * 4 + (lane >> 3);
+                        uint32_t b[4];
+                        ldmatrix_x4(b, s_k_addr + r * kRowBytes + (((piece & 8) | ((piece ^ r) & 7)) << 4));
+                        mma_3xtf32(s[nt], a_hi[0], a_lo[0], __uint_as_float(b[0]), __uint_as_float(b[1]));
+                        mma_3xtf32(s[nt], a_hi[1], a_lo[1], __uint_as_float(b[2]), __uint_as_float(b[3]));
+                    }
+                }
+                // probabilities, the per-edge scratch, dS (kept in s)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int c = c0 + nt * 8 + 2 * t;
+                    uint32_t i_lo0, i_lo1, i_hi0, i_hi1;
+                    load_idx_pair(s_idx + g * idx_stride + c, i_lo0, i_lo1);
+                    load_idx_pair(s_idx + (g + 8) * idx_stride + c, i_hi0, i_hi1);
+                    const float tab[4] = {lds_f32(s_tab_lo + 4 * i_lo0), lds_f32(s_tab_lo + 4 * i_lo1),
+                                          lds_f32(s_tab_hi + 4 * i_hi0), lds_f32(s_tab_hi + 4 * i_hi1)};
+                    const int pos[4] = {pos4[nt].x, pos4[nt].y, pos4[nt].z, pos4[nt].w};
+                    float keep[4] = {1.f, 1.f, 1.f, 1.f};
+                    if (kDrop) {  // the factor the forward multiplied this weight by before summing V
+                        const int src0 = s_cols[c], src1 = s_cols[c + 1];
+                        keep[0] = dropout_factor(p.drop, row_lo, src0, h);
+                        keep[1] = dropout_factor(p.drop, row_lo, src1, h);
+                        keep[2] = dropout_factor(p.drop, row_hi, src0, h);
+                        keep[3] = dropout_factor(p.drop, row_hi, src1, h);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float pr = exp2f(fmaf(s[nt][i], sl2, tab[i]) - (i < 2 ? lse2_lo : lse2_hi));
+                        const float dpk = dp[nt][i] * keep[i];
+                        if (pos[i] >= 0) {
+                            P_h[static_cast<int64_t>(pos[i]) * H] = pr;
+                            dP_h[static_cast<int64_t>(pos[i]) * H] = dpk;
+                        }
+                        s[nt][i] = p.scale * pr * (dpk - (i < 2 ? delta_lo : delta_hi));
+                    }
+                }
+                // dQ += dS K.  k index kk of the product stands for column 8 ks + 2 (kk mod 4) + kk / 4 of the step,
+                // so that the accumulators of S are the A fragments as they are.
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) {
+                    const float pa[4] = {s[ks][0], s[ks][2], s[ks][1], s[ks][3]};
+                    float p_hi[4], p_lo[4];
+                    split4(pa, p_hi, p_lo);
+                    const uint32_t k0 = s_k_addr + kb_lo + ks * 8 * kRowBytes;
+#pragma unroll
+                    for (int dn = 0; dn < 8; ++dn) {
+                        const uint32_t piece_off = (dn >> 2) * 128;
+                        mma_3xtf32(acc[dn], p_hi, p_lo,
+                                   lds_f32(k0 + piece_off + (((2u * (dn & 3)) ^ kx_lo) << 4)),
+                                   lds_f32(k0 + kRowBytes + piece_off + (((2u * (dn & 3)) ^ kx_hi) << 4)));
+                    }
+                }
+                __syncwarp();  // these buffers are refilled by the step after next
+                j = nj;
+                buf ^= 1;
+            }
+            cp_async_wait<0>();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = half ? row_hi : row_lo;
+                if (row < 0) continue;
+                const int slot = mb[kMbSlotOff + g + 8 * half];
+                float *dst = (slot < 0 ? p.dq + (static_cast<int64_t>(row) * H + h) * kHeadDim
+                                       : p.part_dq + (static_cast<int64_t>(slot) * H + h) * kHeadDim) + 2 * t;
+#pragma unroll
+                for (int dn = 0; dn < 8; ++dn)
+                    *reinterpret_cast<float2 *>(dst + dn * 8) = make_float2(acc[dn][2 * half], acc[dn][2 * half + 1]);
+            }
+            __syncwarp();  // the table is rewritten for the next head
+        }
+    }
+}
+
+size_t dq32_smem_bytes(int max_cols_pad, int t_max, int et_bytes) {
+    return static_cast<size_t>(kWarps) * kDqStageBytes + static_cast<size_t>(max_cols_pad) * 4 +
+           align_up(static_cast<size_t>(kTileRows) * (max_cols_pad + kEtPad) * et_bytes, 16) +
+           static_cast<size_t>(kWarps) * kTileRows * tab_stride32(t_max) * 4;
+}
+
+template <typename ET, bool kHasBias>
+int launch_dq32_kernel(const Dq32Params &p, int64_t n_groups, size_t smem, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>(n_groups);
+    if (p.drop.threshold) {
+        BPT_CUDA(cudaFuncSetAttribute(attn_backward_dq_tile32_kernel<ET, kHasBias, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attn_backward_dq_tile32_kernel<ET, kHasBias, true><<<grid, kWarps * 32, smem, stream>>>(p);
+    } else {
+        BPT_CUDA(cudaFuncSetAttribute(attn_backward_dq_tile32_kernel<ET, kHasBias, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attn_backward_dq_tile32_kernel<ET, kHasBias, false><<<grid, kWarps * 32, smem, stream>>>(p);
+    }
+    BPT_LAUNCH_CHECK();
+    return BPT_OK;
+}
+
+
+// ------------------------------------------------------------------ backward, source side
+//
+// dV[src] = sum_dst p' dO[dst] and dK[src] = sum_dst dS q[dst] on the transposed tile plan (an m-block is <= 16
+// source rows, its columns are the destinations that attend to them, every cell knows its edge's in-CSR
+// position), from the fp32 scratch the destination side left: p' = p * dropout factor, dS = scale * p *
+// (dp - delta[dst]).  One block per tile, a warp takes heads w, w + kDkvWarps, ...; per 16 destinations the
+// warp stages their dO and Q rows (272-byte pitch, plain 4-byte loads for the B fragments) while it holds the
+// step's 8 + 8 weights per lane, gathered a step ahead; the cell positions come in fragment order, so a lane's
+// four cells of a column group are the A fragment of m16n8k8 under the k <-> column permutation of the
+// forward.  Rows spread over several m-blocks write fp32 partials that are summed in slot order.
+struct Dkv32Params {
+    const int32_t *groups, *mblocks, *cols, *cellpos;
+    const float *P, *dP, *delta, *q, *d_o;
+    float *dk, *dv, *part;
+    int H, max_cols_pad;
+    float scale;
+    Dropout drop;
+};
+constexpr int kDkvWarps = 4;                         // three blocks per SM at 168 registers
+constexpr int kDkvTileBytes = kStep * kVPitch;        // 16 rows, 272 bytes apart
+constexpr int kDkvStageBytes = 2 * kDkvTileBytes;     // per warp: dO rows, Q rows of one step
+
+template <bool kDrop>
+__global__ void __launch_bounds__(kDkvWarps * 32, 3)
+attn_backward_dkv_tile32_kernel(const Dkv32Params p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    // layout: per warp {dO tile, Q tile} | destination ids
+    int32_t *s_cols = reinterpret_cast<int32_t *>(smem + kDkvWarps * kDkvStageBytes);
+    const int32_t *grp = p.groups + static_cast<int64_t>(blockIdx.x) * kGroupInts;
+    const int n_mblocks = grp[kGroupMbCount];
+    if (n_mblocks == 0) return;
+    const int ncols_pad = grp[kGroupNcolsPad];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int H = p.H;
+    const uint32_t s_do = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kDkvStageBytes));
+    {
+        const int32_t *gc = p.cols + grp[kGroupColOff];
+        for (int i = threadIdx.x; i < ncols_pad; i += blockDim.x) s_cols[i] = gc[i];
+    }
+    __syncthreads();
+    const int n_steps = ncols_pad / kStep;
+    const int copy_row = lane >> 4, copy_piece = lane & 15;
+    const uint32_t row_pitch = static_cast<uint32_t>(H) * kRowBytes;
+    auto issue_rows = [&](int h, int j) {
+        const uint64_t head_off = static_cast<uint64_t>(h * kRowBytes + copy_piece * 16);
+        const int32_t *cj = s_cols + j * kStep + copy_row;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint64_t off = static_cast<uint64_t>(static_cast<uint32_t>(cj[2 * i])) * row_pitch + head_off;
+            const uint32_t dst = s_do + (copy_row + 2 * i) * kVPitch + copy_piece * 16;
+            cp_async16(dst, reinterpret_cast<const char *>(p.d_o) + off);
+            cp_async16(dst + kDkvTileBytes, reinterpret_cast<const char *>(p.q) + off);
+        }
+    };
+    for (int mbi = 0; mbi < n_mblocks; ++mbi) {
+        const int32_t *mb = p.mblocks + static_cast<int64_t>(grp[kGroupMbFirst] + mbi) * kMbInts;
+        const uint32_t chunk_mask = static_cast<uint32_t>(mb[kMbChunkMask]);
+        static_assert(kMaskCols == 2 * kStep, "two pipeline steps per mask bit");
+        auto next_step = [&](int j) {
+            ++j;
+            while (j < n_steps && !((chunk_mask >> (j >> 1)) & 1u)) ++j;
+            return j;
+        };
+        const int4 *pos_base = reinterpret_cast<const int4 *>(p.cellpos + mb[kMbEtOff]) + lane;
+        const int row_lo = mb[kMbRowOff + g], row_hi = mb[kMbRowOff + g + 8];
+        // this lane's 8 cells of step j (rows g / g + 8, destinations 8 nt + 2 t, + 1): p and dp, and delta of its
+        // four destinations
+        auto gather_weights = [&](int h, int j, float (&wp)[8], float (&wd)[8], float (&dl)[4]) {
+            const float *__restrict__ P_h = p.P + h;
+            const float *__restrict__ dP_h = p.dP + h;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int4 pos4 = __ldg(pos_base + (j * 2 + nt) * 32);
+                const int pos[4] = {pos4.x, pos4.y, pos4.z, pos4.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const bool on = pos[i] >= 0;
+                    wp[4 * nt + i] = on ? __ldg(P_h + static_cast<int64_t>(pos[i]) * H) : 0.f;
+                    wd[4 * nt + i] = on ? __ldg(dP_h + static_cast<int64_t>(pos[i]) * H) : 0.f;
+                }
+                const int c = j * kStep + nt * 8 + 2 * t;
+                dl[2 * nt] = __ldg(p.delta + static_cast<int64_t>(s_cols[c]) * H + h);
+                dl[2 * nt + 1] = __ldg(p.delta + static_cast<int64_t>(s_cols[c + 1]) * H + h);
+            }
+        };
+        for (int h = warp; h < H; h += kDkvWarps) {
+            float dk[8][4], dv[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { dk[i][u] = 0.f; dv[i][u] = 0.f; }
+            int j = next_step(-1);
+            if (j < n_steps) issue_rows(h, j);
+            cp_async_commit();
+            float wp[8], wd[8], dl[4];
+            if (j < n_steps) gather_weights(h, j, wp, wd, dl);
+            while (j < n_steps) {
+                const int nj = next_step(j);
+                // p' (the weight V was summed with) and dS of this step's cells
+                float pw[8], ds[8];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    float keep[4] = {1.f, 1.f, 1.f, 1.f};
+                    if (kDrop) {
+                        const int c = j * kStep + nt * 8 + 2 * t;
+                        const int dst0 = s_cols[c], dst1 = s_cols[c + 1];
+                        keep[0] = dropout_factor(p.drop, dst0, row_lo, h);
+                        keep[1] = dropout_factor(p.drop, dst1, row_lo, h);
+                        keep[2] = dropout_factor(p.drop, dst0, row_hi, h);
+                        keep[3] = dropout_factor(p.drop, dst1, row_hi, h);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float pr = wp[4 * nt + i];
+                        pw[4 * nt + i] = pr * keep[i];
+                        ds[4 * nt + i] = p.scale * pr * (wd[4 * nt + i] - dl[2 * nt + (i & 1)]);
+                    }
+                }
+                // the next step's weights travel during this step's products
+                if (nj < n_steps) gather_weights(h, nj, wp, wd, dl);
+                cp_async_wait<0>();  // this step's rows have landed
+                __syncwarp();
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    // cells {(g, c), (g, c + 1), (g + 8, c), (g + 8, c + 1)} -> A fragment {a0, a2, a1, a3}
+                    const float ap[4] = {pw[4 * nt], pw[4 * nt + 2], pw[4 * nt + 1], pw[4 * nt + 3]};
+                    const float as[4] = {ds[4 * nt], ds[4 * nt + 2], ds[4 * nt + 1], ds[4 * nt + 3]};
+                    float p_hi[4], p_lo[4], s_hi[4], s_lo[4];
+                    split4(ap, p_hi, p_lo);
+                    split4(as, s_hi, s_lo);
+                    const uint32_t r0 = s_do + (8 * nt + 2 * t) * kVPitch + g * 4;
+#pragma unroll
+                    for (int dn = 0; dn < 8; ++dn) {
+                        mma_3xtf32(dv[dn], p_hi, p_lo, lds_f32(r0 + dn * 32), lds_f32(r0 + kVPitch + dn * 32));
+                        mma_3xtf32(dk[dn], s_hi, s_lo, lds_f32(r0 + kDkvTileBytes + dn * 32),
+                                   lds_f32(r0 + kDkvTileBytes + kVPitch + dn * 32));
+                    }
+                }
+                __syncwarp();  // every lane has read the tiles: they may be refilled
+                if (nj < n_steps) issue_rows(h, nj);
+                cp_async_commit();
+                j = nj;
+            }
+            cp_async_wait<0>();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = half ? row_hi : row_lo;
+                if (row < 0) continue;
+                const int slot = mb[kMbSlotOff + g + 8 * half];
+                float *out_k, *out_v;
+                if (slot < 0) {
+                    const int64_t off = (static_cast<int64_t>(row) * H + h) * kHeadDim + 2 * t;
+                    out_k = p.dk + off;
+                    out_v = p.dv + off;
+                } else {
+                    // partial layout of the sum-merge kernel: [slot][dK (H*64) | dV (H*64)]
+                    out_k = p.part + static_cast<int64_t>(slot) * 2 * H * kHeadDim + h * kHeadDim + 2 * t;
+                    out_v = out_k + H * kHeadDim;
+                }
+#pragma unroll
+                for (int dn = 0; dn < 8; ++dn) {
+                    *reinterpret_cast<float2 *>(out_k + dn * 8) = make_float2(dk[dn][2 * half], dk[dn][2 * half + 1]);
+                    *reinterpret_cast<float2 *>(out_v + dn * 8) = make_float2(dv[dn][2 * half], dv[dn][2 * half + 1]);
+                }
+            }
+        }
+    }
+}
+
+size_t dkv32_smem_bytes(int max_cols_pad) {
+    return static_cast<size_t>(kDkvWarps) * kDkvStageBytes + static_cast<size_t>(max_cols_pad) * 4;
+}
+
 }  // namespace
 }  // namespace bpt
 
@@ -526,4 +1011,154 @@ extern "C" int bpt_attn_forward_tc32(const bpt_tile_plan_t *tiles, int64_t n_nod
         BPT_LAUNCH_CHECK();
     }
     return BPT_OK;
+}
+
+namespace {
+size_t dkv_slots(const bpt_tile_plan_t *src_tiles, const int32_t *counts_host) {
+    const size_t a = static_cast<size_t>(counts_host[4]);
+    const size_t b = src_tiles ? static_cast<size_t>(src_tiles->n_slots) : 0;
+    return a > b ? a : b;
+}
+}  // namespace
+
+extern "C" size_t bpt_attn_backward_tc32_workspace_bytes(const bpt_tile_plan_t *tiles, const bpt_tile_plan_t *src_tiles,
+                                                         const int32_t *counts_host, int64_t n_nodes, int64_t n_edges,
+                                                         int h) {
+    if (!tiles || !counts_host || n_nodes < 0 || n_edges < 0 || h < 1) return 0;
+    const size_t e = static_cast<size_t>(n_edges);
+    return 2 * align_up(e * h * 4, 256) + align_up(static_cast<size_t>(n_nodes) * h * 4, 256) +
+           align_up(static_cast<size_t>(tiles->n_slots) * h * kHeadDim * 4, 256) +
+           align_up(dkv_slots(src_tiles, counts_host) * 2 * h * kHeadDim * 4, 256) +
+           align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) + 2048;
+}
+
+extern "C" int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_tile_plan_t *src_tiles,
+                                      const void *attn_plan, const int32_t *counts_host, int64_t n_nodes, int64_t n_edges, int n_etypes, const void *q, const void *k,
+                                      const void *v, const void *ak, double scale, const void *o, const float *lse,
+                                      const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
+                                      void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout,
+                                      bpt_stream_t stream_) {
+    BPT_CHECK_ARG(tiles != nullptr && attn_plan != nullptr && counts_host != nullptr, "attn_backward_tc32: null plan");
+    BPT_CHECK_ARG(dropout == nullptr || (dropout->rate >= 0.0 && dropout->rate < 1.0),
+                  "attn_backward_tc32: dropout rate must be in [0, 1)");
+    BPT_CHECK_ARG(tiles->n_groups >= 0 && tiles->n_split >= 0 && tiles->n_slots >= 0 && h >= 1 && h <= 40 &&
+                      n_nodes >= 0 && n_edges >= 0 && n_etypes >= 1,
+                  "attn_backward_tc32: bad sizes");
+    if (d != kHeadDim) return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc32: head dim 64 only (got %d)", d);
+    if (tiles->n_row_items != 0)
+        return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc32: tile plans with CUDA-core row items are not supported");
+    if (n_nodes == 0) return BPT_OK;
+    BPT_CHECK_ARG(q && k && v && o && lse && d_o && dq, "attn_backward_tc32: null tensor");
+    BPT_CHECK_ARG((dk == nullptr) == (dv == nullptr), "attn_backward_tc32: dk and dv must both be given or both be NULL");
+    BPT_CHECK_ARG(ak == nullptr || dak != nullptr, "attn_backward_tc32: ak given without dak");
+    BPT_CHECK_ARG(tiles->n_groups == 0 || (tiles->groups && tiles->mblocks), "attn_backward_tc32: null plan arrays");
+    BPT_CHECK_ARG(tiles->max_cols_pad == 0 || (tiles->cols && tiles->et && tiles->cell_pos),
+                  "attn_backward_tc32: the tile plan must carry cell types and cell positions");
+    BPT_CHECK_ARG(tiles->et_bytes == 1 || tiles->et_bytes == 2, "attn_backward_tc32: et_bytes must be 1 or 2");
+    BPT_CHECK_ARG(tiles->max_cols_pad % kTileChunk == 0 && tiles->t_max % 8 == 0 && tiles->n_groups < (int64_t(1) << 31),
+                  "attn_backward_tc32: bad plan sizes");
+    BPT_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                    reinterpret_cast<uintptr_t>(ak) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o) |
+                    reinterpret_cast<uintptr_t>(dq)) & 15) == 0,
+                  "attn_backward_tc32: tensors must be 16-byte aligned");
+    cudaStream_t stream = as_stream(stream_);
+    const PlanView pv = plan_view(const_cast<void *>(attn_plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
+    Workspace ws(workspace, workspace_bytes);
+    const size_t e = static_cast<size_t>(n_edges);
+    float *P = ws.take<float>(e * h);
+    float *dP = ws.take<float>(e * h);
+    float *delta = ws.take<float>(static_cast<size_t>(n_nodes) * h);
+    float *part_dq = ws.take<float>(static_cast<size_t>(tiles->n_slots) * h * kHeadDim);
+    float *part_dkv = ws.take<float>(dkv_slots(src_tiles, counts_host) * 2 * h * kHeadDim);
+    float *part_dak = ws.take<float>(static_cast<size_t>(counts_host[7]) * kHeadDim);
+    if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_tc32: workspace of %zu bytes is too small", workspace_bytes);
+    const float sc = static_cast<float>(scale);
+    const Dropout drop = make_dropout(dropout);
+    // rows without a tile (no incoming edge) get no dQ and no delta from the tile kernel
+    BPT_CUDA(cudaMemsetAsync(dq, 0, static_cast<size_t>(n_nodes) * h * kHeadDim * sizeof(float), stream));
+    BPT_CUDA(cudaMemsetAsync(delta, 0, static_cast<size_t>(n_nodes) * h * sizeof(float), stream));
+    if (tiles->n_groups > 0) {
+        const bool bias = ak != nullptr;
+        Dq32Params p{};
+        p.groups = tiles->groups; p.mblocks = tiles->mblocks; p.cols = tiles->cols; p.cellpos = tiles->cell_pos;
+        p.et = tiles->et;
+        p.q = static_cast<const float *>(q); p.k = static_cast<const float *>(k); p.v = static_cast<const float *>(v);
+        p.ak = static_cast<const float *>(ak); p.o = static_cast<const float *>(o);
+        p.d_o = static_cast<const float *>(d_o); p.lse = lse;
+        p.P = P; p.dP = dP; p.delta = delta; p.part_dq = part_dq; p.dq = static_cast<float *>(dq);
+        p.n_etypes = n_etypes; p.H = h; p.max_cols_pad = tiles->max_cols_pad;
+        p.t_max = bias ? tiles->t_max : 0;
+        p.tab_stride = tab_stride32(p.t_max);
+        p.scale = sc;
+        p.n_groups = tiles->n_groups;
+        p.drop = drop;
+        if (tiles->et_bytes == 1 && p.t_max > kMaxTypes8)
+            return fail(BPT_ERR_INVALID, "attn_backward_tc32: 8-bit cells need t_max <= %d (got %d)", kMaxTypes8, p.t_max);
+        const size_t smem = dq32_smem_bytes(tiles->max_cols_pad, p.t_max, tiles->et_bytes);
+        if (smem > 227 * 1024)
+            return fail(BPT_ERR_UNSUPPORTED, "attn_backward_tc32: tile plan needs %zu bytes of shared memory", smem);
+        int rc;
+        if (tiles->et_bytes == 1)
+            rc = bias ? launch_dq32_kernel<uint8_t, true>(p, tiles->n_groups, smem, stream)
+                      : launch_dq32_kernel<uint8_t, false>(p, tiles->n_groups, smem, stream);
+        else
+            rc = bias ? launch_dq32_kernel<uint16_t, true>(p, tiles->n_groups, smem, stream)
+                      : launch_dq32_kernel<uint16_t, false>(p, tiles->n_groups, smem, stream);
+        if (rc) return rc;
+        if (int rc2 = launch_sum_merge_f32(reinterpret_cast<const int4 *>(tiles->split_rows),
+                                           static_cast<int>(tiles->n_split), part_dq, h * kHeadDim,
+                                           static_cast<float *>(dq), stream))
+            return rc2;
+    }
+    // source side on the transposed tile plan when one is given (else on the CUDA-core kernel below)
+    bool dkv_done = false;
+    if (src_tiles != nullptr && dk != nullptr && dv != nullptr) {
+        BPT_CHECK_ARG(src_tiles->n_groups >= 0 && src_tiles->n_groups < (int64_t(1) << 31) && src_tiles->n_split >= 0 &&
+                          src_tiles->n_slots >= 0 && src_tiles->max_cols_pad % kTileChunk == 0,
+                      "attn_backward_tc32: bad transposed tile plan sizes");
+        BPT_CHECK_ARG(src_tiles->n_groups == 0 || (src_tiles->groups && src_tiles->mblocks),
+                      "attn_backward_tc32: null transposed plan arrays");
+        BPT_CHECK_ARG(src_tiles->max_cols_pad == 0 || (src_tiles->cols && src_tiles->cell_pos),
+                      "attn_backward_tc32: the transposed tile plan must carry cell positions");
+        BPT_CHECK_ARG(src_tiles->n_split == 0 || src_tiles->split_rows, "attn_backward_tc32: null split rows");
+        BPT_CHECK_ARG(((reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15) == 0,
+                      "attn_backward_tc32: tensors must be 16-byte aligned");
+        const size_t smem = dkv32_smem_bytes(src_tiles->max_cols_pad);
+        if (smem <= 227 * 1024) {
+            // sources without a tile (no outgoing edge) get no gradient from the tile kernel
+            const size_t kv_bytes = static_cast<size_t>(counts_host[kCountsNSrc]) * h * kHeadDim * sizeof(float);
+            BPT_CUDA(cudaMemsetAsync(dk, 0, kv_bytes, stream));
+            BPT_CUDA(cudaMemsetAsync(dv, 0, kv_bytes, stream));
+            if (src_tiles->n_groups > 0) {
+                Dkv32Params kp{};
+                kp.groups = src_tiles->groups; kp.mblocks = src_tiles->mblocks; kp.cols = src_tiles->cols;
+                kp.cellpos = src_tiles->cell_pos;
+                kp.P = P; kp.dP = dP; kp.delta = delta;
+                kp.q = static_cast<const float *>(q); kp.d_o = static_cast<const float *>(d_o);
+                kp.dk = static_cast<float *>(dk); kp.dv = static_cast<float *>(dv); kp.part = part_dkv;
+                kp.H = h; kp.max_cols_pad = src_tiles->max_cols_pad; kp.scale = sc; kp.drop = drop;
+                const unsigned grid = static_cast<unsigned>(src_tiles->n_groups);
+                if (drop.threshold) {
+                    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dkv_tile32_kernel<true>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                    attn_backward_dkv_tile32_kernel<true><<<grid, kDkvWarps * 32, smem, stream>>>(kp);
+                } else {
+                    BPT_CUDA(cudaFuncSetAttribute(attn_backward_dkv_tile32_kernel<false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                    attn_backward_dkv_tile32_kernel<false><<<grid, kDkvWarps * 32, smem, stream>>>(kp);
+                }
+                BPT_LAUNCH_CHECK();
+                if (int rc3 = launch_sum_merge_f32(reinterpret_cast<const int4 *>(src_tiles->split_rows),
+                                                   static_cast<int>(src_tiles->n_split), part_dkv, h * kHeadDim,
+                                                   static_cast<float *>(dk), stream, static_cast<float *>(dv)))
+                    return rc3;
+            }
+            dkv_done = true;
+        }
+    }
+    return launch_backward_rest_f32(pv, counts_host, static_cast<const float *>(q), static_cast<const float *>(ak),
+                                    static_cast<const float *>(d_o), P, dP, delta, sc, static_cast<float *>(dq),
+                                    dkv_done ? nullptr : static_cast<float *>(dk),
+                                    dkv_done ? nullptr : static_cast<float *>(dv), dak, part_dkv, part_dak, h, d,
+                                    drop, stream);
 }

@@ -422,6 +422,24 @@ int bpt_attn_forward_tc32(const bpt_tile_plan_t *tiles, int64_t n_nodes, int n_e
                           void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout,
                           bpt_stream_t stream);
 
+/* Backward for fp32 tensors with the destination side on tensor cores (head dim 64), same gradients as
+ * bpt_attn_backward within its fp32 tolerance (the backward of the operator chain of
+ * modules/attention.py:66-77, graphop.py:42-47, 84-92, 130-137).  `tiles` is the forward's tile plan with
+ * cell positions, `src_tiles` the transposed tile plan (with cell positions) or NULL; attn_plan /
+ * counts_host the bpt_attn_plan_build plan of the same graph (its type buckets drive the embed_ak
+ * passes, which stay on the CUDA-core kernels, as does the source side when src_tiles is NULL).  The
+ * destination-side tile kernel recomputes p and dp = <dO, v> per edge with three TF32 products per
+ * product, takes delta = <dO, O> from the forward's output o, and accumulates the K part of dQ; the
+ * source-side tile kernel accumulates dK and dV from the per-edge scratch.  dk and dv may both be NULL; dak is required when ak is given and must be zeroed by the caller. */
+size_t bpt_attn_backward_tc32_workspace_bytes(const bpt_tile_plan_t *tiles, const bpt_tile_plan_t *src_tiles,
+                                              const int32_t *counts_host, int64_t n_nodes, int64_t n_edges, int h);
+int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_tile_plan_t *src_tiles, const void *attn_plan,
+                           const int32_t *counts_host, int64_t n_nodes, int64_t n_edges, int n_etypes, const void *q, const void *k,
+                           const void *v, const void *ak, double scale, const void *o, const float *lse,
+                           const void *d_o, void *dq, void *dk, void *dv, float *dak, int h, int d,
+                           void *workspace, size_t workspace_bytes, const bpt_dropout_t *dropout,
+                           bpt_stream_t stream);
+
 /* Bytes of device memory built into the library as scratch for bpt_attn_forward_static. */
 #define BPT_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
 

@@ -92,3 +92,75 @@ def test_tc32_forward_with_dropout_equals_cuda_core_forward(oracle_lib):
     assert rel_err(lse[finite].cpu(), lse_s[finite].cpu()) < 1e-5
     o_plain, _, _, _ = _forward(g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, 0.125)
     assert rel_err(o.cpu(), o_plain.cpu()) > 1e-3  # the mask really was applied
+
+
+# ---------------------------------------------------------------- backward, destination side on tensor cores
+
+def _backward(monkeypatch, src, dst, etype, N, T, q, k, v, ak, d_o, scale, dropout=None):
+    """Gradients of the fp32 tile backward (bpt_attn_backward_tc32) and of the CUDA-core backward."""
+    from bpt_b200 import attention as A
+    dev = "cuda"
+    plan = A.AttentionPlan(torch.from_numpy(src).to(dev), torch.from_numpy(dst).to(dev),
+                           None if etype is None else torch.from_numpy(etype).to(dev), N, n_etypes=T)
+    qg, kg, vg, dog = [t.to(dev) for t in (q, k, v, d_o)]
+    akg = None if ak is None else ak.to(dev)
+    o, lse = A.attention_forward_tc32(plan, qg, kg, vg, akg, scale, dropout)
+    monkeypatch.setattr(A, "FP32_BACKWARD", "tc32")
+    got = A.attention_backward(plan, qg, kg, vg, akg, scale, lse, dog, o=o, dropout=dropout)
+    again = A.attention_backward(plan, qg, kg, vg, akg, scale, lse, dog, o=o, dropout=dropout)
+    for a, b in zip(got, again):
+        assert (a is None and b is None) or torch.equal(a, b), "the fp32 tile backward is not bitwise reproducible"
+    assert ("tc32_bwd", qg.size(1)) in plan._ws, "the fp32 tile backward did not run"
+    monkeypatch.setattr(A, "FP32_BACKWARD", "simt")
+    ref = A.attention_backward(plan, qg, kg, vg, akg, scale, lse, dog, o=o, dropout=dropout)
+    return got, ref
+
+
+@pytest.mark.parametrize("graph", list(GRAPHS))
+@pytest.mark.parametrize("heads", [8, 3])
+def test_tc32_backward_matches_oracle(oracle_lib, monkeypatch, graph, heads):
+    g = GRAPHS[graph](oracle_lib)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = _inputs(N, heads, 64, T, torch.float32, 10)
+    want = _oracle(oracle_lib, g["src"], g["dst"], g["etype"], N, q, k, v, ak, d_o, 0.125)
+    got, ref = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
+    for name, a, b, c in zip(("dq", "dk", "dv", "dak"), got, want[2:], ref):
+        assert rel_err(a.cpu(), b) < 1e-5, name
+        assert rel_err(a.cpu(), c.cpu()) < 1e-5, name
+
+
+def test_tc32_backward_without_relative_term_and_with_empty_rows(oracle_lib, monkeypatch):
+    src, dst, N0 = fully_connected_blocks(5, 30)
+    N = N0 + 7
+    q, k, v, _, d_o = _inputs(N, 8, 64, 1, torch.float32, 11, sigma=0.5)
+    want = _oracle(oracle_lib, src, dst, None, N, q, k, v, None, d_o, 0.125)
+    got, _ = _backward(monkeypatch, src, dst, None, N, 1, q, k, v, None, d_o, 0.125)
+    for name, a, b in zip(("dq", "dk", "dv"), got, want[2:5]):
+        assert rel_err(a.cpu(), b) < 1e-5, name
+    assert got[3] is None
+    assert torch.all(got[0][N0:] == 0)
+
+
+def test_tc32_backward_headline_size_and_dropout(oracle_lib, monkeypatch):
+    g = oracle_lib.binary_partition(8192, False, 4, 10)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = _inputs(N, 8, 64, T, torch.float32, 12, sigma=0.125)
+    got, ref = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
+    for name, a, c in zip(("dq", "dk", "dv", "dak"), got, ref):
+        assert rel_err(a.cpu(), c.cpu()) < 1e-5, name
+    got, ref = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125, dropout=(0.3, 7))
+    for name, a, c in zip(("dq", "dk", "dv", "dak"), got, ref):
+        assert rel_err(a.cpu(), c.cpu()) < 1e-5, name
+
+
+def test_tc32_backward_with_cuda_core_source_side(oracle_lib, monkeypatch):
+    """The destination-side tile kernel alone (src_tiles = NULL): dK and dV from the CUDA-core kernel on its scratch."""
+    from bpt_b200 import attention as A
+    monkeypatch.setattr(A, "FP32_BACKWARD_SOURCE_SIDE", "simt")
+    g = GRAPHS["bpt_batch"](oracle_lib)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = _inputs(N, 8, 64, T, torch.float32, 13)
+    want = _oracle(oracle_lib, g["src"], g["dst"], g["etype"], N, q, k, v, ak, d_o, 0.125)
+    got, _ = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
+    for name, a, b in zip(("dq", "dk", "dv", "dak"), got, want[2:]):
+        assert rel_err(a.cpu(), b) < 1e-5, name

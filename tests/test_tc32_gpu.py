@@ -164,3 +164,18 @@ def test_tc32_backward_with_cuda_core_source_side(oracle_lib, monkeypatch):
     got, _ = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
     for name, a, b in zip(("dq", "dk", "dv", "dak"), got, want[2:]):
         assert rel_err(a.cpu(), b) < 1e-5, name
+
+
+def test_tc32_backward_sixteen_bit_cells(oracle_lib, monkeypatch):
+    g = oracle_lib.binary_partition(700, False, 64, 10)  # > 255 edge types
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    q, k, v, ak, d_o = _inputs(N, 2, 64, T, torch.float32, 14)
+    from bpt_b200.attention import AttentionPlan, tc32_eligible
+    plan = AttentionPlan(torch.from_numpy(g["src"]).cuda(), torch.from_numpy(g["dst"]).cuda(),
+                         torch.from_numpy(g["etype"]).cuda(), N, n_etypes=T)
+    if not tc32_eligible(q.cuda(), ak.cuda(), plan):
+        pytest.skip("the tables of this many edge types do not fit in shared memory")
+    want = _oracle(oracle_lib, g["src"], g["dst"], g["etype"], N, q, k, v, ak, d_o, 0.125)
+    got, _ = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
+    for name, a, b in zip(("dq", "dk", "dv", "dak"), got, want[2:]):
+        assert rel_err(a.cpu(), b) < 1e-5, name

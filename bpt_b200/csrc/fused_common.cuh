@@ -175,6 +175,13 @@ int launch_backward_rest_f32(const PlanView &p, const int32_t *counts, const flo
                              const float *d_o, const float *P, const float *dP, const float *delta, float scale,
                              float *dq, float *dk, float *dv, float *dak, float *part_dkv, float *part_dak, int H,
                              int D, const Dropout &drop, cudaStream_t stream);
+// Defined in fused_tc_bwd.cu: the relative-position gradients of the fp32 backward through a dense per-row type
+// table G (fp32, n_nodes * H x tq, made from the fp32 scratch) and two fp32 library GEMMs: dq += G . ak,
+// dak = G^T . q.  type_table_f32_elems: floats of G, or 0 when the table does not apply.
+size_t type_table_f32_elems(int tq, int64_t n_nodes, int h);
+int launch_type_table_terms_f32(const PlanView &pv, int tq, int n_etypes, const float *q, const float *ak,
+                                const float *P, const float *dP, const float *delta, float scale, float *dq,
+                                float *dak, float *G, int h, cudaStream_t stream);
 // out[row, :] = sum over the row's slots ({row, first, count, .} records), in slot order, of fp32 partial rows;
 // with out1 a slot holds two rows side by side (out | out1).
 int launch_sum_merge_f32(const int4 *split_rows, int n_split, const float *part, int width, float *out,

@@ -1029,7 +1029,8 @@ extern "C" size_t bpt_attn_backward_tc32_workspace_bytes(const bpt_tile_plan_t *
     return 2 * align_up(e * h * 4, 256) + align_up(static_cast<size_t>(n_nodes) * h * 4, 256) +
            align_up(static_cast<size_t>(tiles->n_slots) * h * kHeadDim * 4, 256) +
            align_up(dkv_slots(src_tiles, counts_host) * 2 * h * kHeadDim * 4, 256) +
-           align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) + 2048;
+           align_up(static_cast<size_t>(counts_host[7]) * kHeadDim * 4, 256) +
+           align_up(type_table_f32_elems(tiles->t_max, n_nodes, h) * 4, 256) + 2048;
 }
 
 extern "C" int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_tile_plan_t *src_tiles,
@@ -1071,6 +1072,8 @@ extern "C" int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_ti
     float *part_dq = ws.take<float>(static_cast<size_t>(tiles->n_slots) * h * kHeadDim);
     float *part_dkv = ws.take<float>(dkv_slots(src_tiles, counts_host) * 2 * h * kHeadDim);
     float *part_dak = ws.take<float>(static_cast<size_t>(counts_host[7]) * kHeadDim);
+    const size_t table_elems = ak != nullptr ? type_table_f32_elems(tiles->t_max, n_nodes, h) : 0;
+    float *G = ws.take<float>(table_elems);
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_tc32: workspace of %zu bytes is too small", workspace_bytes);
     const float sc = static_cast<float>(scale);
     const Dropout drop = make_dropout(dropout);
@@ -1156,6 +1159,18 @@ extern "C" int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_ti
             dkv_done = true;
         }
     }
+    // relative-position gradients: per-row type table and two fp32 GEMMs where the table applies, else the
+    // per-edge CUDA-core kernels below
+    bool ak_done = false;
+    if (table_elems > 0) {
+        if (int rc4 = launch_type_table_terms_f32(pv, tiles->t_max, n_etypes, static_cast<const float *>(q),
+                                                  static_cast<const float *>(ak), P, dP, delta, sc,
+                                                  static_cast<float *>(dq), dak, G, h, stream))
+            return rc4;
+        ak_done = true;
+    }
+    if (ak_done && dkv_done) return BPT_OK;
+    if (ak_done) ak = nullptr;
     return launch_backward_rest_f32(pv, counts_host, static_cast<const float *>(q), static_cast<const float *>(ak),
                                     static_cast<const float *>(d_o), P, dP, delta, sc, static_cast<float *>(dq),
                                     dkv_done ? nullptr : static_cast<float *>(dk),

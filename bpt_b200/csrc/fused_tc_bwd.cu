@@ -629,20 +629,38 @@ attn_backward_dq_tile_kernel(const DqParams p) {
 // 32 types differ (the usual case: a leaf's edges all differ in level or offset) the lanes add
 // into their own bins at once; otherwise they add one after the other in lane order.  Either
 // way every bin sees its edges in CSR order, so the sums have a fixed order.
-// G is bf16, (n_nodes * H, tq); PS is [head][in-CSR position].
+// G is (n_nodes * H, tq).  kPacked: G is bf16 and PS is [head][in-CSR position] words {bf16 p, bf16 dS};
+// otherwise G is fp32 and dS = scale * p * (dp - delta) comes from the fp32 scratch of the CUDA-core backward
+// (P, dP in [in-CSR position][head] order, delta per (row, head)).
+template <bool kPacked>
+struct TableScratch {
+    const uint32_t *PS;
+    int64_t n_edges;
+    const float *P, *dP, *delta;
+    float scale;
+};
+__device__ __forceinline__ void store_table_pair(__nv_bfloat16 *out, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162 *>(out) = __floats2bfloat162_rn(a, b);
+}
+__device__ __forceinline__ void store_table_pair(float *out, float a, float b) {
+    *reinterpret_cast<float2 *>(out) = make_float2(a, b);
+}
+template <bool kPacked, typename GT>
 __global__ void __launch_bounds__(128)
 build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__restrict__ in_etype,
-                        const int32_t *__restrict__ row_uniform, int n_rows, const uint32_t *__restrict__ PS,
-                        int64_t n_edges, __nv_bfloat16 *__restrict__ G, int H, int tq) {
+                        const int32_t *__restrict__ row_uniform, int n_rows, const TableScratch<kPacked> sc,
+                        GT *__restrict__ G, int H, int tq) {
+    const uint32_t *__restrict__ PS = sc.PS;
+    const int64_t n_edges = sc.n_edges;
     extern __shared__ float s_g[];  // [4 warps][H][tq]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;
     if (row >= n_rows) return;
     float *g = s_g + static_cast<int64_t>(warp) * H * tq;
-    __nv_bfloat16 *out = G + static_cast<int64_t>(row) * H * tq;
+    GT *out = G + static_cast<int64_t>(row) * H * tq;
     const int cells = H * tq;
     if (row_uniform[row]) {
-        for (int i = lane * 2; i < cells; i += 64) *reinterpret_cast<uint32_t *>(out + i) = 0u;
+        for (int i = lane * 2; i < cells; i += 64) store_table_pair(out + i, 0.f, 0.f);
         return;
     }
     for (int i = lane; i < cells; i += 32) g[i] = 0.f;
@@ -656,10 +674,20 @@ build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__
         for (int h0 = 0; h0 < H; h0 += 8) {
             float ds[8];  // the loads of eight heads travel together
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-                ds[u] = valid && h0 + u < H
-                            ? __uint_as_float(__ldg(PS + static_cast<int64_t>(h0 + u) * n_edges + j) & 0xffff0000u)
-                            : 0.f;
+            for (int u = 0; u < 8; ++u) {
+                if (kPacked) {
+                    ds[u] = valid && h0 + u < H
+                                ? __uint_as_float(__ldg(PS + static_cast<int64_t>(h0 + u) * n_edges + j) & 0xffff0000u)
+                                : 0.f;
+                } else {
+                    ds[u] = 0.f;
+                    if (valid && h0 + u < H) {
+                        const int64_t at = static_cast<int64_t>(j) * H + h0 + u;
+                        ds[u] = sc.scale * __ldg(sc.P + at) *
+                                (__ldg(sc.dP + at) - __ldg(sc.delta + static_cast<int64_t>(row) * H + h0 + u));
+                    }
+                }
+            }
             if (distinct) {
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
@@ -677,10 +705,7 @@ build_type_table_kernel(const int32_t *__restrict__ in_indptr, const int32_t *__
         }
         __syncwarp();
     }
-    for (int i = lane * 2; i < cells; i += 64) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(g[i], g[i + 1]);
-        *reinterpret_cast<__nv_bfloat162 *>(out + i) = v;
-    }
+    for (int i = lane * 2; i < cells; i += 64) store_table_pair(out + i, g[i], g[i + 1]);
 }
 
 // One cuBLAS handle per device, created on first use.
@@ -751,7 +776,47 @@ __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_
     }
 }
 
+constexpr int kMaxTableTypes = 256;  // beyond this the dense per-row type table is not used
 }  // namespace
+
+// The relative-position gradients of the fp32 backward through the dense per-row type table: G (fp32,
+// n_nodes * H x tq) from the fp32 scratch, then dQ += G . embed_ak and d embed_ak = G^T . Q as fp32 library
+// GEMMs (no tensor-core math: the 1e-5 bar).  type_table_f32_elems: floats of G, 0 when the table does not apply
+// (no types, too many types for the kernel's shared memory) and the caller keeps its per-edge kernels.
+size_t type_table_f32_elems(int tq, int64_t n_nodes, int h) {
+    if (tq <= 0 || tq > kMaxTableTypes || static_cast<size_t>(4) * h * tq * sizeof(float) > 48 * 1024) return 0;
+    return static_cast<size_t>(n_nodes) * h * tq;
+}
+int launch_type_table_terms_f32(const PlanView &pv, int tq, int n_etypes, const float *q, const float *ak,
+                                const float *P, const float *dP, const float *delta, float scale, float *dq,
+                                float *dak, float *G, int h, cudaStream_t stream) {
+    const int64_t n_nodes = pv.n_nodes;
+    if (n_nodes == 0) return BPT_OK;
+    const long long nh = static_cast<long long>(n_nodes) * h;
+    BPT_CHECK_ARG(nh < (1ll << 31), "attn_backward_tc32: n_nodes * h exceeds the GEMM index range");
+    const int kk = tq < n_etypes ? tq : n_etypes;
+    const size_t smem_g = static_cast<size_t>(4) * h * tq * sizeof(float);
+    const TableScratch<false> scratch{nullptr, pv.n_edges, P, dP, delta, scale};
+    build_type_table_kernel<false, float><<<static_cast<unsigned>((n_nodes + 3) / 4), 128, smem_g, stream>>>(
+        pv.in_indptr, pv.in_etype, pv.row_uniform, static_cast<int>(n_nodes), scratch, G, h, tq);
+    BPT_LAUNCH_CHECK();
+    cublasHandle_t handle = cublas_handle();
+    if (handle == nullptr) return fail(BPT_ERR_CUDA, "attn_backward_tc32: cuBLAS handle could not be created");
+    if (cublasSetStream(handle, stream) != CUBLAS_STATUS_SUCCESS) return fail(BPT_ERR_CUDA, "attn_backward_tc32: cublasSetStream failed");
+    const float one = 1.f, zero = 0.f;
+    // row-major dQ (nh x 64) += G (nh x tq) . ak (tq x 64)   ==   column-major dQ^T = ak^T . G^T
+    cublasStatus_t st = cublasGemmEx(handle, CUBLAS_OP_N, CUBLAS_OP_N, kHeadDim, static_cast<int>(nh), kk, &one, ak,
+                                     CUDA_R_32F, kHeadDim, G, CUDA_R_32F, tq, &one, dq, CUDA_R_32F, kHeadDim,
+                                     CUBLAS_COMPUTE_32F_PEDANTIC, CUBLAS_GEMM_DEFAULT);
+    if (st != CUBLAS_STATUS_SUCCESS) return fail(BPT_ERR_CUDA, "attn_backward_tc32: cublasGemmEx (dQ) failed with %d", int(st));
+    // row-major d ak (kk x 64) = G^T (kk x nh) . Q (nh x 64)   ==   column-major (d ak)^T = Q^T . G
+    st = cublasGemmEx(handle, CUBLAS_OP_N, CUBLAS_OP_T, kHeadDim, kk, static_cast<int>(nh), &one, q, CUDA_R_32F,
+                      kHeadDim, G, CUDA_R_32F, tq, &zero, dak, CUDA_R_32F, kHeadDim, CUBLAS_COMPUTE_32F_PEDANTIC,
+                      CUBLAS_GEMM_DEFAULT);
+    if (st != CUBLAS_STATUS_SUCCESS) return fail(BPT_ERR_CUDA, "attn_backward_tc32: cublasGemmEx (d ak) failed with %d", int(st));
+    return BPT_OK;
+}
+
 }  // namespace bpt
 
 using namespace bpt;
@@ -815,7 +880,6 @@ int launch_dq_kernel(const DqParams &p, int64_t n_groups, size_t smem, cudaStrea
 }  // namespace
 
 namespace {
-constexpr int kMaxTableTypes = 256;  // beyond this the dense per-row type table is not used
 size_t type_table_elems(const bpt_tile_plan_t *dst_tiles, int64_t n_nodes, int h) {
     const int tq = dst_tiles->t_max;
     return tq > 0 && tq <= kMaxTableTypes ? static_cast<size_t>(n_nodes) * h * tq : 1;
@@ -926,8 +990,9 @@ extern "C" int bpt_attn_backward_tc(const bpt_tile_plan_t *dst_tiles, const bpt_
         // dense per-row type table, then two library GEMMs
         const int kk = tq < n_etypes ? tq : n_etypes;
         const size_t smem_g = static_cast<size_t>(4) * h * tq * sizeof(float);
-        build_type_table_kernel<<<static_cast<unsigned>((n_nodes + 3) / 4), 128, smem_g, stream>>>(
-            pv.in_indptr, pv.in_etype, pv.row_uniform, static_cast<int>(n_nodes), PS, n_edges, G, h, tq);
+        const TableScratch<true> scratch{PS, n_edges, nullptr, nullptr, nullptr, 1.f};
+        build_type_table_kernel<true, __nv_bfloat16><<<static_cast<unsigned>((n_nodes + 3) / 4), 128, smem_g, stream>>>(
+            pv.in_indptr, pv.in_etype, pv.row_uniform, static_cast<int>(n_nodes), scratch, G, h, tq);
         BPT_LAUNCH_CHECK();
         cublasHandle_t handle = cublas_handle();
         if (handle == nullptr) return fail(BPT_ERR_CUDA, "attn_backward_tc: cuBLAS handle could not be created");

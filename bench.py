@@ -663,10 +663,16 @@ def measure_attention(a, seqs, n, k, dtype_name, causal, steps, warmup, with_e2e
             tiles_t = att.FP32_BACKWARD_SOURCE_SIDE == "tc32"
             tpd = plan.tile_plan()
             n_split_src = plan.tile_plan_t().n_split if tiles_t else plan.counts[5]
-            launches_bwd = 4 + (tpd.n_split > 0) + (n_split_src > 0) + (plan.counts[8] > 0)
-            bwd_kernels = ("attn_backward_dq_tile32_kernel + attn_backward_dq_ak_kernel + " +
-                           ("attn_backward_dkv_tile32_kernel" if tiles_t else "attn_backward_dkv_kernel") +
-                           " + attn_backward_dak_kernel")
+            dkv_name = "attn_backward_dkv_tile32_kernel" if tiles_t else "attn_backward_dkv_kernel"
+            if 0 < tpd.t_max <= 256 and 4 * H * tpd.t_max * 4 <= 48 * 1024:
+                # per-row type table; its two fp32 GEMMs are cuBLAS launches and not counted
+                launches_bwd = 3 + (tpd.n_split > 0) + (n_split_src > 0)
+                bwd_kernels = ("attn_backward_dq_tile32_kernel + build_type_table_kernel + 2 cuBLAS fp32 GEMMs + " +
+                               dkv_name)
+            else:
+                launches_bwd = 4 + (tpd.n_split > 0) + (n_split_src > 0) + (plan.counts[8] > 0)
+                bwd_kernels = ("attn_backward_dq_tile32_kernel + attn_backward_dq_ak_kernel + " + dkv_name +
+                               " + attn_backward_dak_kernel")
         else:
             launches_bwd = 3 + (plan.counts[2] > 0) + (plan.counts[5] > 0) + (plan.counts[8] > 0)
             bwd_kernels = "attn_backward_{dq,dkv,dak}_kernel"

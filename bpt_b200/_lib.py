@@ -58,6 +58,8 @@ SIGNATURES = {
     "bpt_tile_plan_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "bpt_tile_plan_destroy": (None, [_vp]),
     "bpt_tile_plan_create_device": (_vp, [_vp, _vp, _i64, _i64, _int, _int, _dbl, _int, _int, _int, _int, _vp]),
+    "bpt_tile_plan_create_device_aligned": (_vp, [_vp, _vp, _i64, _i64, _int, _int, _vp, _int, _dbl, _int, _int, _int,
+                                                  _int, _vp]),
     "bpt_tile_plan_device_sizes": (_int, [_vp, _vp]),
     "bpt_tile_plan_device_export": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "bpt_tile_plan_device_destroy": (None, [_vp]),

@@ -63,11 +63,17 @@ class AttentionPlan:
         self.tiles = None    # TilePlan of the tensor-core forward, built on first use
         self.tiles_t = None  # transposed TilePlan of the tensor-core dK/dV kernel
         self.tiles5 = None   # 128-row TilePlan of the tcgen05 forward
+        self.segments = None  # node offsets of the graphs of a block-diagonal batch (from_batch), for the tile plans
 
     @classmethod
     def from_batch(cls, batch, n_etypes=None):
-        """From a csr.BatchedGraph."""
-        return cls(batch.src, batch.dst, batch.etype, batch.n_nodes, n_etypes)
+        """From a csr.BatchedGraph.  The tile plans count their blocks of source columns from each graph's first
+        node, so a graph is cut into tiles where it is cut when it is planned alone."""
+        plan = cls(batch.src, batch.dst, batch.etype, batch.n_nodes, n_etypes)
+        offsets = [int(x) for x in batch.node_offsets]
+        if TILE_ALIGN_GRAPHS and len(offsets) > 2:
+            plan.segments = offsets
+        return plan
 
     def workspace(self, h, d, backward):
         """Scratch for one call; cached per (h, d, direction) and reused by later calls on
@@ -85,7 +91,7 @@ class AttentionPlan:
         """The tile plan of the tensor-core forward and of the destination side of the backward (built once
         per graph)."""
         if self.tiles is None:
-            self.tiles = TilePlan(self, max_cols=TILE_MAX_COLS)
+            self.tiles = TilePlan(self, max_cols=TILE_MAX_COLS, col_segments=self.segments)
         return self.tiles
 
     def tile_plan5(self):
@@ -94,13 +100,14 @@ class AttentionPlan:
         block of 128 consecutive sources."""
         if self.tiles5 is None:
             self.tiles5 = TilePlan(self, min_density=0.05, max_cols=512, group_rows=128, col_block=128,
-                                   max_mblocks=8)
+                                   max_mblocks=8, col_segments=self.segments)
         return self.tiles5
 
     def tile_plan_t(self):
         """The transposed tile plan (rows = sources) of the tensor-core dK/dV kernel."""
         if self.tiles_t is None:
-            self.tiles_t = TilePlan(self, transposed=True, min_density=0.15, simt_max_degree=0)
+            self.tiles_t = TilePlan(self, transposed=True, min_density=0.15, simt_max_degree=0,
+                                    col_segments=self.segments)
         return self.tiles_t
 
     def _args(self):
@@ -115,10 +122,19 @@ class TilePlan:
     carry the edge's position in the in-CSR (source side of bpt_attn_backward_tc)."""
 
     def __init__(self, plan, transposed=False, min_density=0.25, max_cols=384, group_rows=16, col_block=128,
-                 simt_max_degree=0, max_mblocks=1, join_dense=False, planner=None):
+                 simt_max_degree=0, max_mblocks=1, join_dense=False, planner=None, col_segments=None):
         """planner: "device" (the default; BPT_TILE_PLANNER overrides it) plans with CUDA kernels from the CSR
         arrays where the plan keeps them; "host" exports the CSR, plans in C++ on the host and uploads.  Both
-        give the same arrays; simt_max_degree and join_dense exist on the host planner only."""
+        give the same arrays; simt_max_degree and join_dense exist on the host planner only.
+        col_segments: ascending offsets [0, ..., number of columns] of the graphs of a block-diagonal batch;
+        blocks of col_block columns are then counted from each graph's first column."""
+        if col_segments is not None:
+            col_segments = [int(x) for x in col_segments]
+            n_col_space = plan.n_nodes if transposed else plan.n_src
+            if len(col_segments) < 2 or col_segments[0] != 0 or col_segments[-1] != n_col_space or \
+                    any(b < a for a, b in zip(col_segments, col_segments[1:])):
+                raise ValueError("TilePlan: col_segments must ascend from 0 to the number of columns")
+        self.col_segments = col_segments
         planner = planner or TILE_PLANNER
         if planner not in ("device", "host"):
             raise ValueError("TilePlan: planner must be 'device' or 'host'")
@@ -129,19 +145,23 @@ class TilePlan:
         self.transposed = transposed
         self._ws = {}
         if planner == "device":
-            self._plan_on_device(plan, transposed, min_density, max_cols, group_rows, col_block, max_mblocks)
+            self._plan_on_device(plan, transposed, min_density, max_cols, group_rows, col_block, max_mblocks,
+                                 col_segments)
         else:
             self._plan_on_host(plan, transposed, min_density, max_cols, group_rows, col_block, simt_max_degree,
-                               max_mblocks, join_dense)
+                               max_mblocks, join_dense, col_segments)
 
-    def _plan_on_device(self, plan, transposed, min_density, max_cols, group_rows, col_block, max_mblocks):
+    def _plan_on_device(self, plan, transposed, min_density, max_cols, group_rows, col_block, max_mblocks,
+                        col_segments=None):
         L = _lib.lib()
         dev = plan.device
+        n_segs = 0 if col_segments is None else len(col_segments) - 1
+        segs = (ctypes.c_int64 * (n_segs + 1))(*col_segments) if n_segs else None
         with torch.cuda.device(dev):
-            handle = L.bpt_tile_plan_create_device(plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes,
-                                                   plan.n_edges, plan.n_etypes, int(bool(transposed)),
-                                                   float(min_density), int(max_cols), int(group_rows), int(col_block),
-                                                   int(max_mblocks), _lib.stream())
+            handle = L.bpt_tile_plan_create_device_aligned(
+                plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes, plan.n_edges, plan.n_etypes,
+                int(bool(transposed)), None if segs is None else ctypes.addressof(segs), n_segs, float(min_density),
+                int(max_cols), int(group_rows), int(col_block), int(max_mblocks), _lib.stream())
             if not handle:
                 _lib.check(1)
             try:
@@ -169,7 +189,7 @@ class TilePlan:
                 L.bpt_tile_plan_device_destroy(handle)
 
     def _plan_on_host(self, plan, transposed, min_density, max_cols, group_rows, col_block, simt_max_degree,
-                      max_mblocks, join_dense):
+                      max_mblocks, join_dense, col_segments=None):
         L = _lib.lib()
         E, T = plan.n_edges, plan.n_etypes
         n_rows = plan.n_src if transposed else plan.n_nodes
@@ -180,6 +200,16 @@ class TilePlan:
         with torch.cuda.device(plan.device):
             _lib.check(export(plan.blob.data_ptr(), ctypes.addressof(plan._counts), plan.n_nodes, E, T,
                               indptr.ctypes.data, other.ctypes.data, extra.ctypes.data, _lib.stream()))
+        seg_start = seg_shift = None
+        if col_segments is not None and len(col_segments) > 1:
+            # every graph's columns start at a multiple of col_block for the planner; shifted back below
+            seg_start = np.asarray(col_segments[:-1], np.int64)
+            sizes_seg = np.diff(np.asarray(col_segments, np.int64))
+            padded = (sizes_seg + col_block - 1) // col_block * col_block
+            vstart = np.concatenate([[0], np.cumsum(padded)[:-1]])
+            seg_shift = vstart - seg_start
+            seg = np.searchsorted(seg_start, other[:E], side="right") - 1
+            other[:E] = (other[:E] + seg_shift[seg]).astype(np.int32)
         etype_ptr, payload_ptr = (None, extra.ctypes.data) if transposed else (extra.ctypes.data, None)
         handle = L.bpt_tile_plan_create(indptr.ctypes.data, other.ctypes.data, etype_ptr, payload_ptr, n_rows, E,
                                         float(min_density), int(max_cols), int(group_rows), int(col_block),
@@ -208,6 +238,9 @@ class TilePlan:
                                               items.ctypes.data))
         finally:
             L.bpt_tile_plan_destroy(handle)
+        if seg_start is not None and n_cols > 0:
+            seg = np.searchsorted(seg_start + seg_shift, cols[:n_cols], side="right") - 1
+            cols[:n_cols] = (cols[:n_cols] - seg_shift[seg]).astype(np.int32)
         dev = plan.device
         self.groups = torch.from_numpy(groups).to(dev)
         self.mblocks = torch.from_numpy(mblocks).to(dev)
@@ -245,6 +278,8 @@ FP32_FORWARD = os.environ.get("BPT_FP32_FORWARD", "tc32")
 FP32_BACKWARD = os.environ.get("BPT_FP32_BACKWARD", "tc32")
 FP32_BACKWARD_SOURCE_SIDE = os.environ.get("BPT_FP32_BACKWARD_SOURCE_SIDE", "tc32")  # with FP32_BACKWARD = "tc32"
 TILE_PLANNER = os.environ.get("BPT_TILE_PLANNER", "device")
+# Tile plans of a batch count their column blocks from each graph's first node (AttentionPlan.from_batch)
+TILE_ALIGN_GRAPHS = os.environ.get("BPT_TILE_ALIGN_GRAPHS", "1") != "0"
 # Widest column list of a 16-row tile; rows that would need more are cut by blocks of 128 source columns.
 TILE_MAX_COLS = int(os.environ.get("BPT_TILE_MAX_COLS", "384"))
 MAX_BLOCK_SMEM = 227 * 1024  # shared memory one thread block can have on this GPU

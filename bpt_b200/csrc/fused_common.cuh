@@ -126,7 +126,14 @@ __global__ void attn_forward_merge_kernel(const int4 *__restrict__ split_rows, i
 #pragma unroll
                 for (int v = 0; v < 16; ++v) a = fmaf(x[v], s_w[(s + v) * H + head], a);
             }
-            for (; s < nb; ++s) a = fmaf(src[static_cast<int64_t>(s) * HD], s_w[s * H + head], a);
+            if (s < nb) {  // the last, partial batch: its loads travel together too
+                float x[16];
+#pragma unroll
+                for (int v = 0; v < 16; ++v) x[v] = s + v < nb ? src[static_cast<int64_t>(s + v) * HD] : 0.f;
+#pragma unroll
+                for (int v = 0; v < 16; ++v)
+                    if (s + v < nb) a = fmaf(x[v], s_w[(s + v) * H + head], a);
+            }
             acc[u] = a;
         }
     }

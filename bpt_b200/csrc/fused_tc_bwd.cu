@@ -752,7 +752,7 @@ inline int sum_merge_threads(int columns) {
 
 // out0[row] | out1[row] = sum over the row's slots, in slot order, of the slot's two halves.
 // (out1 == nullptr: a slot holds one array of `width` values.)
-__global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_split, const float *__restrict__ part,
+__global__ void __launch_bounds__(1024, 2) dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_split, const float *__restrict__ part,
                                      int width, __nv_bfloat16 *__restrict__ out0, __nv_bfloat16 *__restrict__ out1) {
     const int sr = blockIdx.x;
     if (sr >= n_split) return;
@@ -770,7 +770,14 @@ __global__ void dkv_sum_merge_kernel(const int4 *__restrict__ split_rows, int n_
 #pragma unroll
             for (int u = 0; u < 16; ++u) acc += x[u];
         }
-        for (; s < count; ++s) acc += src[static_cast<int64_t>(s) * stride];
+        if (s < count) {  // the last, partial batch: its loads travel together too
+            float x[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) x[u] = s + u < count ? src[static_cast<int64_t>(s + u) * stride] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                if (s + u < count) acc += x[u];
+        }
         if (c < width) out0[static_cast<int64_t>(row) * width + c] = __float2bfloat16_rn(acc);
         else out1[static_cast<int64_t>(row) * width + (c - width)] = __float2bfloat16_rn(acc);
     }

@@ -75,15 +75,44 @@ __global__ void row_col_key_kernel(const int32_t *__restrict__ erow, const int32
     key[j] = (static_cast<uint64_t>(static_cast<uint32_t>(erow[j])) << 32) | static_cast<uint32_t>(col[j]);
     iota[j] = static_cast<int32_t>(j);
 }
+// Column segments (the graphs of a block-diagonal batch): segment s holds the columns [start[s], start[s + 1])
+// and is planned as if it began at start[s] + shift[s], a multiple of the column block, so that the blocks of
+// `col_block` consecutive columns fall in every graph where they fall when it is planned alone.  n_segs == 0:
+// no shift.  The plan's column lists are shifted back once they are written.
+struct ColSegments {
+    const int32_t *start;  // n_segs + 1 ascending real column ids (the last one past the end)
+    const int32_t *shift;  // n_segs non-decreasing shifts
+    int n_segs;
+};
+__device__ __forceinline__ int32_t shifted_col(const ColSegments &cs, int32_t c) {
+    if (cs.n_segs == 0) return c;
+    int lo = 0, hi = cs.n_segs - 1;  // last segment whose start is <= c
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (cs.start[mid] <= c) lo = mid; else hi = mid - 1;
+    }
+    return c + cs.shift[lo];
+}
+__global__ void unshift_cols_kernel(int32_t *__restrict__ cols, int64_t n, ColSegments cs) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i >= n) return;
+    const int32_t v = cols[i];
+    int lo = 0, hi = cs.n_segs - 1;  // last segment whose shifted start is <= v
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (cs.start[mid] + cs.shift[mid] <= v) lo = mid; else hi = mid - 1;
+    }
+    cols[i] = v - cs.shift[lo];
+}
 // perm == nullptr: entry i is CSR entry i.
 __global__ void gather_entries_kernel(const int32_t *__restrict__ perm, const int32_t *__restrict__ col,
                                       const int32_t *__restrict__ etype, const int32_t *__restrict__ payload,
                                       int64_t n_entries, int32_t *__restrict__ scol, int32_t *__restrict__ set,
-                                      int32_t *__restrict__ spos, Counts *__restrict__ counts) {
+                                      int32_t *__restrict__ spos, Counts *__restrict__ counts, ColSegments cs) {
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (i >= n_entries) return;
     const int32_t j = perm ? perm[i] : static_cast<int32_t>(i);
-    scol[i] = col[j];
+    scol[i] = shifted_col(cs, col[j]);
     const int32_t e = etype ? etype[j] : 0;
     if (e < 0 || e >= kNoEdge) atomicOr(&counts->err_etype, 1);
     set[i] = e;
@@ -634,7 +663,8 @@ struct Sorter {
 
 bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, const int32_t *etype,
            const int32_t *payload, int64_t R, int64_t E, bool rows_sorted, double min_density, int max_cols,
-           int group_rows, int col_block, int max_mblocks, cudaStream_t stream) {
+           int group_rows, int col_block, int max_mblocks, const int64_t *seg_starts_host, int n_segs,
+           cudaStream_t stream) {
     Arena tmp;
     Sorter sorter(tmp);
     const int64_t nG = (R + group_rows - 1) / group_rows;
@@ -656,6 +686,23 @@ bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, cons
     int32_t *accept = tmp.take<int32_t>(nG + 1), *dpos = tmp.take<int32_t>(nG + 1), *ncols_g = tmp.take<int32_t>(nG + 1);
     int32_t *ecol = tmp.take<int32_t>(E);
     if (!tmp.ok) { fail(BPT_ERR_CUDA, "tile_plan_device: out of device memory"); return false; }
+    ColSegments cs{nullptr, nullptr, 0};
+    std::vector<int32_t> seg_host;  // starts, then shifts; read by the copy below before this function returns
+    if (n_segs > 0) {
+        seg_host.resize(2 * static_cast<size_t>(n_segs) + 1);
+        int64_t vstart = 0;
+        for (int i = 0; i < n_segs; ++i) {
+            seg_host[i] = static_cast<int32_t>(seg_starts_host[i]);
+            seg_host[n_segs + 1 + i] = static_cast<int32_t>(vstart - seg_starts_host[i]);
+            vstart = (vstart + (seg_starts_host[i + 1] - seg_starts_host[i]) + col_block - 1) / col_block * col_block;
+        }
+        seg_host[n_segs] = static_cast<int32_t>(seg_starts_host[n_segs]);
+        int32_t *seg_dev = tmp.take<int32_t>(static_cast<int64_t>(seg_host.size()));
+        if (!tmp.ok) { fail(BPT_ERR_CUDA, "tile_plan_device: out of device memory"); return false; }
+        PLAN_CUDA(cudaMemcpyAsync(seg_dev, seg_host.data(), sizeof(int32_t) * seg_host.size(), cudaMemcpyHostToDevice, stream));
+        PLAN_CUDA(cudaStreamSynchronize(stream));
+        cs = ColSegments{seg_dev, seg_dev + n_segs + 1, n_segs};
+    }
     if (E > 0) {
         entry_rows_kernel<<<blocks_for(E), kThreads, 0, stream>>>(indptr, R, E, erow);
         const int32_t *perm = nullptr;
@@ -666,7 +713,7 @@ bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, cons
             PLAN_CUDA(cudaMemcpyAsync(iota2, gidx, sizeof(int32_t) * E, cudaMemcpyDeviceToDevice, stream));
             perm = iota2;
         }
-        gather_entries_kernel<<<blocks_for(E), kThreads, 0, stream>>>(perm, col, etype, payload, E, scol, set, spos, counts);
+        gather_entries_kernel<<<blocks_for(E), kThreads, 0, stream>>>(perm, col, etype, payload, E, scol, set, spos, counts, cs);
     }
     if (E > 0) {
         rank_key_kernel<<<blocks_for(E), kThreads, 0, stream>>>(indptr, erow, scol, set, E, group_rows, gkey, iota, counts);
@@ -772,6 +819,7 @@ bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, cons
         write_dense_cols_kernel<<<blocks_for(E), kThreads, 0, stream>>>(gk_sorted, uflag, ucnt, indptr, E, group_rows, accept, dpos, g, plan.cols);
         write_bucket_cols_kernel<<<blocks_for(E), kThreads, 0, stream>>>(bk_sorted, uflag2, ucnt2, bscan, bstart, E, counts, n_dense, cbase, ncopies_b, g, plan.cols);
         scatter_entries_kernel<<<blocks_for(E), kThreads, 0, stream>>>(erow, ecol, set, spos, E, group_rows, accept, dpos, n_dense, e_bucket, e_ord, cbase, max_mblocks, g, plan.mblocks, plan.et, plan.cellpos);
+        if (cs.n_segs > 0 && n_cols > 0) unshift_cols_kernel<<<blocks_for(n_cols), kThreads, 0, stream>>>(plan.cols, n_cols, cs);
     }
     finish_mblocks_kernel<<<blocks_for(n_mblocks), kThreads, 0, stream>>>(n_mblocks, mb_group, g, plan.mblocks, counts);
     if (h.n_partial > 0) {
@@ -806,10 +854,11 @@ bool build(DeviceTilePlan &plan, const int32_t *indptr, const int32_t *col, cons
 
 using namespace bpt;
 
-extern "C" void *bpt_tile_plan_create_device(const void *attn_plan, const int32_t *counts_host, int64_t n_nodes,
-                                             int64_t n_edges, int n_etypes, int transposed, double min_density,
-                                             int max_cols, int group_rows, int col_block, int max_mblocks,
-                                             bpt_stream_t stream_) {
+extern "C" void *bpt_tile_plan_create_device_aligned(const void *attn_plan, const int32_t *counts_host,
+                                                     int64_t n_nodes, int64_t n_edges, int n_etypes, int transposed,
+                                                     const int64_t *col_seg_starts_host, int n_segs,
+                                                     double min_density, int max_cols, int group_rows, int col_block,
+                                                     int max_mblocks, bpt_stream_t stream_) {
     if (!attn_plan || !counts_host || n_nodes < 0 || n_edges < 0 || n_edges > INT_MAX || max_cols < kTileChunk ||
         max_cols > kMaxMaskBits * kMaskCols || col_block < 1 || group_rows < kTileRows ||
         group_rows % kTileRows != 0 || max_mblocks < 1 || max_mblocks > kMaxMBlocks ||
@@ -819,7 +868,26 @@ extern "C" void *bpt_tile_plan_create_device(const void *attn_plan, const int32_
     }
     const PlanView p = plan_view(const_cast<void *>(attn_plan), n_nodes, counts_host[kCountsNSrc], n_edges, n_etypes);
     const int64_t n_rows = transposed ? p.n_src : p.n_nodes;
-    const int64_t n_col_space = transposed ? p.n_nodes : p.n_src;
+    int64_t n_col_space = transposed ? p.n_nodes : p.n_src;
+    if (n_segs < 0 || (n_segs > 0 && !col_seg_starts_host)) {
+        fail(BPT_ERR_INVALID, "tile_plan_create_device: bad column segments");
+        return nullptr;
+    }
+    if (n_segs > 0) {
+        // segments must tile [0, columns) in ascending order; the planner then sees every segment start at a
+        // multiple of col_block
+        int64_t vend = 0;
+        bool ok_segs = col_seg_starts_host[0] == 0 && col_seg_starts_host[n_segs] == n_col_space;
+        for (int i = 0; i < n_segs && ok_segs; ++i) {
+            ok_segs = col_seg_starts_host[i + 1] >= col_seg_starts_host[i];
+            vend = (vend + (col_seg_starts_host[i + 1] - col_seg_starts_host[i]) + col_block - 1) / col_block * col_block;
+        }
+        if (!ok_segs) {
+            fail(BPT_ERR_INVALID, "tile_plan_create_device: column segments must ascend from 0 to the number of columns");
+            return nullptr;
+        }
+        n_col_space = vend;
+    }
     if ((n_rows + group_rows - 1) / group_rows >= (1ll << 22) || n_rows >= (1ll << 31) - 1 ||
         n_col_space / col_block >= (1ll << 22) || n_col_space >= (1ll << 31) - 1) {
         fail(BPT_ERR_UNSUPPORTED, "tile_plan_create_device: too many rows or column blocks for the composite sort keys");
@@ -828,15 +896,25 @@ extern "C" void *bpt_tile_plan_create_device(const void *attn_plan, const int32_
     DeviceTilePlan *plan = new DeviceTilePlan();
     const bool ok = transposed
                         ? build(*plan, p.out_indptr, p.out_dst, nullptr, p.out_inpos, n_rows, n_edges, false, min_density,
-                                max_cols, group_rows, col_block, max_mblocks, as_stream(stream_))
+                                max_cols, group_rows, col_block, max_mblocks, col_seg_starts_host, n_segs,
+                                as_stream(stream_))
                         : build(*plan, p.in_indptr, p.in_src, p.in_etype, nullptr, n_rows, n_edges, true, min_density,
-                                max_cols, group_rows, col_block, max_mblocks, as_stream(stream_));
+                                max_cols, group_rows, col_block, max_mblocks, col_seg_starts_host, n_segs,
+                                as_stream(stream_));
     if (!ok) {
         cudaStreamSynchronize(as_stream(stream_));
         delete plan;
         return nullptr;
     }
     return plan;
+}
+
+extern "C" void *bpt_tile_plan_create_device(const void *attn_plan, const int32_t *counts_host, int64_t n_nodes,
+                                             int64_t n_edges, int n_etypes, int transposed, double min_density,
+                                             int max_cols, int group_rows, int col_block, int max_mblocks,
+                                             bpt_stream_t stream_) {
+    return bpt_tile_plan_create_device_aligned(attn_plan, counts_host, n_nodes, n_edges, n_etypes, transposed, nullptr, 0,
+                                               min_density, max_cols, group_rows, col_block, max_mblocks, stream_);
 }
 
 extern "C" int bpt_tile_plan_device_sizes(const void *handle, int64_t *sizes) {

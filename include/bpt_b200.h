@@ -321,6 +321,18 @@ void *bpt_tile_plan_create_device(const void *attn_plan, const int32_t *counts_h
                                   int64_t n_edges, int n_etypes, int transposed, double min_density,
                                   int max_cols, int group_rows, int col_block, int max_mblocks,
                                   bpt_stream_t stream);
+/* The same with the column space given as `n_segs` segments (col_seg_starts_host: n_segs + 1 ascending HOST
+ * values from 0 to the number of columns: the node offsets of the graphs of a block-diagonal batch,
+ * graph/lm.py:59-98).  Blocks of `col_block` consecutive columns are then counted from each segment's start,
+ * so every graph of the batch is cut where it is cut when planned alone (a 64-leaf span of the second
+ * sequence no longer straddles two blocks because the first sequence has an odd number of nodes): fewer
+ * rows spread over several tiles.  n_segs = 0 is bpt_tile_plan_create_device.  The host planner gives the
+ * same plan when its column ids are shifted the same way and the exported column lists shifted back. */
+void *bpt_tile_plan_create_device_aligned(const void *attn_plan, const int32_t *counts_host, int64_t n_nodes,
+                                          int64_t n_edges, int n_etypes, int transposed,
+                                          const int64_t *col_seg_starts_host, int n_segs, double min_density,
+                                          int max_cols, int group_rows, int col_block, int max_mblocks,
+                                          bpt_stream_t stream);
 int bpt_tile_plan_device_sizes(const void *handle, int64_t *sizes);
 int bpt_tile_plan_device_export(const void *handle, int32_t *groups, int32_t *mblocks, int32_t *cols,
                                 void *et, int et_bytes, int32_t *cell_pos, int32_t *split_rows,

@@ -105,3 +105,56 @@ def test_device_planner_headline_graph_and_attention_result(oracle_lib):
         outs.append((o, lse) + tuple(grads))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+def _batch_with_offsets(oracle_lib, specs):
+    parts = [oracle_lib.binary_partition(*s) for s in specs]
+    g = oracle_lib.batch_graphs(parts)
+    offsets = np.concatenate([[0], np.cumsum([p["n_nodes"] for p in parts])]).tolist()
+    return g, offsets
+
+
+@pytest.mark.parametrize("params", ["forward16", "rows128", "buckets"])
+@pytest.mark.parametrize("transposed", [False, True])
+def test_device_planner_equals_host_planner_with_column_segments(oracle_lib, params, transposed):
+    """Column blocks counted from each graph's first node (the graphs of a block-diagonal batch)."""
+    from bpt_b200.attention import TilePlan
+    g, offsets = _batch_with_offsets(oracle_lib, [(513, False, 4, 10), (100, True, 2, 3), (2048, False, 4, 10), (37, False, 1, 2)])
+    plan = _plan(g["src"], g["dst"], g["etype"], g["n_nodes"], int(g["etype"].max()) + 1)
+    host = TilePlan(plan, transposed=transposed, planner="host", col_segments=offsets, **PARAMS[params])
+    dev = TilePlan(plan, transposed=transposed, planner="device", col_segments=offsets, **PARAMS[params])
+    for f in FIELDS:
+        assert getattr(dev, f) == getattr(host, f), (f, getattr(dev, f), getattr(host, f))
+    for name, n in dict(groups=host.n_groups * 8, mblocks=host.n_mblocks * 56, cols=host.n_cols, cellpos=host.n_cells,
+                        split=host.n_split * 4).items():
+        a, b = getattr(dev, name).cpu().numpy().ravel()[:n], getattr(host, name).cpu().numpy().ravel()[:n]
+        assert np.array_equal(a, b), name
+    cols = dev.cols.cpu().numpy()[:dev.n_cols]
+    assert cols.min() >= 0 and cols.max() < g["n_nodes"]
+
+
+def test_column_segments_keep_a_batch_cut_like_its_graphs_and_the_result(oracle_lib):
+    """Two sequences of the headline size: with the graphs' offsets the forward plan spreads as many rows over
+    several tiles as two single-sequence plans do (63 each); attention results match the unaligned plan's at the
+    dtype's tolerance and the oracle's (fp32)."""
+    from bpt_b200 import attention as A
+    from helpers import rel_err
+    g, offsets = _batch_with_offsets(oracle_lib, [(8192, False, 4, 10)] * 2)
+    N, T = g["n_nodes"], int(g["etype"].max()) + 1
+    plain = _plan(g["src"], g["dst"], g["etype"], N, T)
+    aligned = _plan(g["src"], g["dst"], g["etype"], N, T)
+    aligned.segments = offsets
+    assert plain.tile_plan().n_split > 4 * 63
+    assert aligned.tile_plan().n_split <= 2 * 63 + 16
+    gen = torch.Generator().manual_seed(9)
+    q, k, v, d_o = [(torch.randn(N, 8, 64, generator=gen) * 0.125) for _ in range(4)]
+    ak = torch.randn(T, 64, generator=gen) * 0.125
+    for dtype, tol in ((torch.bfloat16, 2e-2), (torch.float32, 1e-5)):
+        args = [t.to(dtype).cuda() for t in (q, k, v, ak)]
+        outs = []
+        for p in (plain, aligned):
+            o, lse = A.attention_forward(p, args[0], args[1], args[2], args[3], 0.125)
+            grads = A.attention_backward(p, args[0], args[1], args[2], args[3], 0.125, lse, d_o.to(dtype).cuda(), o=o)
+            outs.append((o, lse) + tuple(grads))
+        for a, b in zip(*outs):
+            assert rel_err(a.float().cpu(), b.float().cpu()) < tol

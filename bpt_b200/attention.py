@@ -107,7 +107,7 @@ class AttentionPlan:
         """The transposed tile plan (rows = sources) of the tensor-core dK/dV kernel."""
         if self.tiles_t is None:
             self.tiles_t = TilePlan(self, transposed=True, min_density=0.15, simt_max_degree=0,
-                                    col_segments=self.segments)
+                                    max_cols=TILE_T_MAX_COLS, col_block=TILE_T_COL_BLOCK, col_segments=self.segments)
         return self.tiles_t
 
     def _args(self):
@@ -282,6 +282,10 @@ TILE_PLANNER = os.environ.get("BPT_TILE_PLANNER", "device")
 TILE_ALIGN_GRAPHS = os.environ.get("BPT_TILE_ALIGN_GRAPHS", "1") != "0"
 # Widest column list of a 16-row tile; rows that would need more are cut by blocks of 128 source columns.
 TILE_MAX_COLS = int(os.environ.get("BPT_TILE_MAX_COLS", "384"))
+# The transposed plan (rows = sources): widest destination list of a tile, and the block of destinations by which
+# sources with longer lists are cut (each block a source falls into is one partial dK/dV row to merge)
+TILE_T_MAX_COLS = int(os.environ.get("BPT_TILE_T_MAX_COLS", "384"))
+TILE_T_COL_BLOCK = int(os.environ.get("BPT_TILE_T_COL_BLOCK", "128"))
 MAX_BLOCK_SMEM = 227 * 1024  # shared memory one thread block can have on this GPU
 
 

@@ -1077,9 +1077,12 @@ extern "C" int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_ti
     if (!ws.ok()) return fail(BPT_ERR_WORKSPACE, "attn_backward_tc32: workspace of %zu bytes is too small", workspace_bytes);
     const float sc = static_cast<float>(scale);
     const Dropout drop = make_dropout(dropout);
-    // rows without a tile (no incoming edge) get no dQ and no delta from the tile kernel
-    BPT_CUDA(cudaMemsetAsync(dq, 0, static_cast<size_t>(n_nodes) * h * kHeadDim * sizeof(float), stream));
+    // Every row is in some m-block of the tile plan (rows without edges form m-blocks without columns), so the
+    // tile kernels write every row of dQ, dK and dV; delta is cleared because only the tile kernel's lanes of
+    // real rows write it.
     BPT_CUDA(cudaMemsetAsync(delta, 0, static_cast<size_t>(n_nodes) * h * sizeof(float), stream));
+    if (tiles->n_groups == 0)  // a plan without a single m-block writes nothing
+        BPT_CUDA(cudaMemsetAsync(dq, 0, static_cast<size_t>(n_nodes) * h * kHeadDim * sizeof(float), stream));
     if (tiles->n_groups > 0) {
         const bool bias = ak != nullptr;
         Dq32Params p{};
@@ -1128,10 +1131,11 @@ extern "C" int bpt_attn_backward_tc32(const bpt_tile_plan_t *tiles, const bpt_ti
                       "attn_backward_tc32: tensors must be 16-byte aligned");
         const size_t smem = dkv32_smem_bytes(src_tiles->max_cols_pad);
         if (smem <= 227 * 1024) {
-            // sources without a tile (no outgoing edge) get no gradient from the tile kernel
-            const size_t kv_bytes = static_cast<size_t>(counts_host[kCountsNSrc]) * h * kHeadDim * sizeof(float);
-            BPT_CUDA(cudaMemsetAsync(dk, 0, kv_bytes, stream));
-            BPT_CUDA(cudaMemsetAsync(dv, 0, kv_bytes, stream));
+            if (src_tiles->n_groups == 0) {
+                const size_t kv_bytes = static_cast<size_t>(counts_host[kCountsNSrc]) * h * kHeadDim * sizeof(float);
+                BPT_CUDA(cudaMemsetAsync(dk, 0, kv_bytes, stream));
+                BPT_CUDA(cudaMemsetAsync(dv, 0, kv_bytes, stream));
+            }
             if (src_tiles->n_groups > 0) {
                 Dkv32Params kp{};
                 kp.groups = src_tiles->groups; kp.mblocks = src_tiles->mblocks; kp.cols = src_tiles->cols;

@@ -179,3 +179,21 @@ def test_tc32_backward_sixteen_bit_cells(oracle_lib, monkeypatch):
     got, _ = _backward(monkeypatch, g["src"], g["dst"], g["etype"], N, T, q, k, v, ak, d_o, 0.125)
     for name, a, b in zip(("dq", "dk", "dv", "dak"), got, want[2:]):
         assert rel_err(a.cpu(), b) < 1e-5, name
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_graph_without_edges_gives_zero_output_and_gradients(dtype):
+    """A plan with nodes and no edge at all: o = 0, lse = -inf, every gradient zero, on the tile kernels of
+    either dtype (outputs are allocated uninitialised, so every row must be written)."""
+    from bpt_b200 import attention as A
+    N, T = 40, 3
+    z = torch.zeros(0, dtype=torch.int32, device="cuda")
+    plan = A.AttentionPlan(z, z, z, N, n_etypes=T)
+    gen = torch.Generator().manual_seed(3)
+    q, k, v, d_o = [torch.randn(N, 8, 64, generator=gen).to(dtype).cuda() for _ in range(4)]
+    ak = torch.randn(T, 64, generator=gen).to(dtype).cuda()
+    o, lse = A.attention_forward(plan, q, k, v, ak, 0.125)
+    assert torch.all(o == 0) and torch.all(torch.isinf(lse) & (lse < 0))
+    dq, dk, dv, dak = A.attention_backward(plan, q, k, v, ak, 0.125, lse, d_o, o=o)
+    for g in (dq, dk, dv, dak):
+        assert torch.all(g == 0)

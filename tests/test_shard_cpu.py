@@ -173,7 +173,7 @@ def _straddle_worker(rank, world, port, n, k, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,n,k", [(2, 128, 2), (4, 256, 4)])
+@pytest.mark.parametrize("world,n,k", [(2, 128, 2), (4, 256, 4), (8, 512, 4)])
 def test_split_straddlers_match_unsharded(world, n, k):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()

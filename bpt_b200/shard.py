@@ -411,7 +411,8 @@ class HaloRunner:
       forward   pack  -> all-to-all (halo K and V rows + the straddlers' Q rows, owner to everyone)
                       -> unpack, fused forward, partial (o, lse) of the straddlers
                       -> all-gather of the partials -> merge
-      backward  all-reduce of the straddlers' dO rows (each owner fills its rows of a zero buffer)
+      backward  all-gather of the straddlers' dO rows (each owner contributes its rows, padded to the largest
+                         share; an all-reduce of a zero-filled buffer took twice as long on eight ranks)
                       -> fused backward, pack -> all-to-all back (dK, dV of the halo rows + every rank's
                          share of the straddlers' dQ, to the owner) -> fixed-order sums
 
@@ -485,6 +486,15 @@ class HaloRunner:
         self.allp = torch.zeros((w * self.n_strad, h * d + h), dtype=torch.float32, device=dev)
         self.q_strad = mk(self.n_my)                              # my straddlers' Q rows, saved by the pack step
         self.do_strad = mk(self.n_strad)
+        # dO rows of the straddlers travel by all-gather: every rank sends max_my rows (its own straddlers first),
+        # straddler j is row do_pick[j] of the gathered buffer
+        self.max_my = max(n_str_of) if n_str_of else 0
+        self.do_mine = mk(self.max_my)
+        self.do_all = mk(w * self.max_my)
+        pick = torch.zeros(self.n_strad, **i64)
+        for r in range(w):
+            pick[pos_of[r]] = r * self.max_my + torch.arange(n_str_of[r], **i64)
+        self.do_pick = pick
         self.dq_strad = mk(self.n_my)                             # summed dQ of my straddlers
         self.graphs = bool(graphs) and device.type == "cuda"
         self._g = {}
@@ -532,9 +542,11 @@ class HaloRunner:
             self.lse_loc[-n:] = lse
 
     def _seg_dout(self):
-        self.do_strad.zero_()
         if self.n_my:
-            self.do_strad[self.s_own_pos] = self.do_in[self.s_own_idx]
+            self.do_mine[: self.n_my] = self.do_in[self.s_own_idx]
+
+    def _seg_dout_pick(self):
+        self.do_strad.copy_(self.do_all[self.do_pick])
 
     def _seg_backward(self):
         s = self.shard
@@ -624,7 +636,10 @@ class HaloRunner:
         if self.n_strad:
             self._run("dout", self._seg_dout)
             if s.world > 1:
-                dist.all_reduce(self.do_strad, group=self.group)  # every row has one owner: a sum with zeros
+                dist.all_gather_into_tensor(self.do_all, self.do_mine, group=self.group)
+            else:
+                self.do_all.copy_(self.do_mine)
+            self._run("dout_pick", self._seg_dout_pick)
         self._run("backward", self._seg_backward)
         if s.world > 1:
             dist.all_to_all_single(self.r_recv[: self.n_fsend], self.r_send, output_split_sizes=self.r_recv_counts,

@@ -473,10 +473,11 @@ def attention_forward_static(plan, q, k, v, embed_ak, scale, out=None, lse_out=N
     return o, lse
 
 
-def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_cores=None, dropout=None):
+def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_cores=None, dropout=None, out=None):
     """Returns (dq, dk, dv, d_embed_ak or None); d_embed_ak is fp32 (rows of embed_ak, d).
     bf16 with head dim 64 runs on the tensor-core kernels when the forward's output `o` is given
-    (they take delta = <dO, O> from it) unless tensor_cores=False."""
+    (they take delta = <dO, O> from it) unless tensor_cores=False.  out: optional (dq, dk, dv) tensors of the
+    shapes and dtype of q, k, v (contiguous, on their device) that receive the gradients instead of new ones."""
     d_o = d_o.contiguous()
     N, h, d = _check_inputs(plan, q, k, v, embed_ak)
     _lib.require_cuda(lse, d_o)
@@ -488,7 +489,14 @@ def attention_backward(plan, q, k, v, embed_ak, scale, lse, d_o, o=None, tensor_
         tc32_eligible(q, embed_ak, plan) and plan.tile_plan().cellpos is not None
     if tensor_cores is None:
         tensor_cores = o is not None and tensor_core_eligible(q, embed_ak, plan)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if out is None:
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    else:
+        dq, dk, dv = out
+        for name, t, like in (("dq", dq, q), ("dk", dk, k), ("dv", dv, v)):
+            if t.shape != like.shape or t.dtype != like.dtype or t.device != like.device or not t.is_contiguous():
+                raise RuntimeError("bpt_attention: out[%s] must be a contiguous tensor of the shape, dtype and device "
+                                   "of its input" % name)
     drop_keep, drop_ptr = _lib.dropout_arg(dropout)
     dak = None
     if embed_ak is not None:

@@ -471,8 +471,18 @@ class HaloRunner:
         row = (h, d)
         mk = lambda n, dt=dtype: torch.zeros((n,) + row, dtype=dt, device=dev)
         n_rows = max(s.n_dst_local, s.n_owned)
-        self.k_e, self.v_e = mk(s.n_ext), mk(s.n_ext)
-        self._q_buf, self._do_buf = mk(n_rows), mk(n_rows)
+        # K, V and Q rows live in one tensor [K (n_ext) | V (n_ext) | Q (n_rows) | zero row | dump row], so that the
+        # pack step is one gather of rows into the send buffer and the unpack step one scatter of the received rows
+        self._big = mk(2 * s.n_ext + n_rows + 2)
+        self.k_e, self.v_e = self._big[: s.n_ext], self._big[s.n_ext: 2 * s.n_ext]
+        self._q_buf, self._do_buf = self._big[2 * s.n_ext: 2 * s.n_ext + n_rows], mk(n_rows)
+        q0, zero_row, dump_row = 2 * s.n_ext, 2 * s.n_ext + n_rows, 2 * s.n_ext + n_rows + 1
+        # the gradients likewise: [dQ (n_dst_local) | dK (n_ext) | dV (n_ext) | zero row]
+        self._gbig = mk(s.n_dst_local + 2 * s.n_ext + 1)
+        self._dq_out = self._gbig[: s.n_dst_local]
+        self._dk_out = self._gbig[s.n_dst_local: s.n_dst_local + s.n_ext]
+        self._dv_out = self._gbig[s.n_dst_local + s.n_ext: s.n_dst_local + 2 * s.n_ext]
+        g_dk0, g_dv0, g_zero = s.n_dst_local, s.n_dst_local + s.n_ext, s.n_dst_local + 2 * s.n_ext
         self.q_loc, self.do_loc = self._q_buf[: s.n_dst_local], self._do_buf[: s.n_dst_local]
         self.k_in, self.v_in = self.k_e[: s.n_owned], self.v_e[: s.n_owned]
         self.q_in, self.do_in = self._q_buf[: s.n_owned], self._do_buf[: s.n_owned]
@@ -484,7 +494,6 @@ class HaloRunner:
         self.r_recv = torch.zeros((self.n_fsend + 1, 2) + row, dtype=dtype, device=dev)   # last row stays zero
         self.part = torch.zeros((self.n_strad, h * d + h), dtype=torch.float32, device=dev)
         self.allp = torch.zeros((w * self.n_strad, h * d + h), dtype=torch.float32, device=dev)
-        self.q_strad = mk(self.n_my)                              # my straddlers' Q rows, saved by the pack step
         self.do_strad = mk(self.n_strad)
         # dO rows of the straddlers travel by all-gather: every rank sends max_my rows (its own straddlers first),
         # straddler j is row do_pick[j] of the gathered buffer
@@ -496,6 +505,33 @@ class HaloRunner:
             pick[pos_of[r]] = r * self.max_my + torch.arange(n_str_of[r], **i64)
         self.do_pick = pick
         self.dq_strad = mk(self.n_my)                             # summed dQ of my straddlers
+        # row lists of the exchanges over those tensors; a send or receive buffer is (rows, 2, h, d), its flat row
+        # 2 p + c is slot c of position p
+        send_all = s.send_all.to(dev).to(torch.int64)
+        pack = torch.full((2 * self.n_fsend,), zero_row, **i64)
+        pack[2 * self.send_pos_kv] = send_all
+        pack[2 * self.send_pos_kv + 1] = s.n_ext + send_all
+        if self.n_my:
+            pack[2 * self.send_pos_q] = q0 + self.send_src_q.to(torch.int64)
+        self.pack_rows = pack
+        unpack = torch.full((2 * self.n_frecv,), dump_row, **i64)
+        n_kv_recv = int(self.recv_pos_kv.numel())
+        unpack[2 * self.recv_pos_kv] = s.n_owned + torch.arange(n_kv_recv, **i64)
+        unpack[2 * self.recv_pos_kv + 1] = s.n_ext + s.n_owned + torch.arange(n_kv_recv, **i64)
+        if self.n_strad:
+            unpack[2 * self.recv_pos_q] = q0 + self.recv_dst_q.to(torch.int64)
+        self.unpack_rows = unpack
+        ret = torch.full((2 * self.n_frecv,), g_zero, **i64)
+        ret[2 * self.recv_pos_kv] = g_dk0 + s.n_owned + torch.arange(n_kv_recv, **i64)
+        ret[2 * self.recv_pos_kv + 1] = g_dv0 + s.n_owned + torch.arange(n_kv_recv, **i64)
+        if self.n_strad:
+            ret[2 * self.recv_pos_q] = self.ret_src_q.to(torch.int64)
+        self.ret_pack_rows = ret
+        # returned halo gradients: ret_mat lists, per own row, positions among [kv part of the received buffer |
+        # the all-zero last row]; as positions of the received buffer itself
+        halo_pos = torch.cat([self.send_pos_kv, torch.tensor([self.n_fsend], **i64)])
+        self.ret_mat_recv = halo_pos[self.ret_mat] if self.ret_rows.numel() else self.ret_mat
+        self.ret_rows_kv = torch.cat([g_dk0 + self.ret_rows.to(torch.int64), g_dv0 + self.ret_rows.to(torch.int64)])
         self.graphs = bool(graphs) and device.type == "cuda"
         self._g = {}
 
@@ -513,17 +549,14 @@ class HaloRunner:
         return attention_forward, attention_backward
 
     def _seg_pack(self):
-        self.f_send[self.send_pos_kv, 0] = self.k_in[self.send_all]
-        self.f_send[self.send_pos_kv, 1] = self.v_in[self.send_all]
-        if self.n_my:
-            self.f_send[self.send_pos_q, 0] = self.q_in[self.send_src_q]
+        if self.n_fsend:
+            torch.index_select(self._big, 0, self.pack_rows, out=self.f_send.view((-1,) + self._big.shape[1:]))
 
     def _seg_forward(self):
         s = self.shard
-        self.k_e[s.n_owned:] = self.f_recv[self.recv_pos_kv, 0]
-        self.v_e[s.n_owned:] = self.f_recv[self.recv_pos_kv, 1]
-        if self.n_strad:
-            self.q_loc[self.recv_dst_q] = self.f_recv[self.recv_pos_q, 0]   # overwrites q_in's straddler rows
+        if self.n_frecv:
+            # halo K and V rows behind the own ones, the straddlers' Q rows over q_in's straddler rows
+            self._big.index_copy_(0, self.unpack_rows, self.f_recv.view((-1,) + self._big.shape[1:]))
         self.o_loc, self.lse_loc = self._kernels()[0](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale)
         if self.n_strad:
             n = self.n_strad
@@ -552,23 +585,29 @@ class HaloRunner:
         s = self.shard
         if self.n_strad:
             self.do_loc[self.n_ns:] = self.do_strad                        # overwrites do_in's straddler rows
-        dq_loc, dk_e, dv_e, dak = self._kernels()[1](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale,
-                                                     self.lse_loc, self.do_loc, o=self.o_loc)
-        self.dq_loc, self.dk_e, self.dv_e, self.dak = dq_loc, dk_e, dv_e, dak
-        self.r_send[self.recv_pos_kv, 0] = dk_e[s.n_owned:].to(self.dtype)
-        self.r_send[self.recv_pos_kv, 1] = dv_e[s.n_owned:].to(self.dtype)
-        if self.n_strad:
-            self.r_send[self.recv_pos_q, 0] = dq_loc[self.ret_src_q].to(self.dtype)
+        if _KERNELS is None:
+            # the library's kernels write straight into the gradient tensor the return step gathers from
+            _, _, _, dak = self._kernels()[1](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale,
+                                              self.lse_loc, self.do_loc, o=self.o_loc,
+                                              out=(self._dq_out, self._dk_out, self._dv_out))
+        else:
+            dq_loc, dk_e, dv_e, dak = self._kernels()[1](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in,
+                                                         self.scale, self.lse_loc, self.do_loc, o=self.o_loc)
+            self._dq_out.copy_(dq_loc)
+            self._dk_out.copy_(dk_e)
+            self._dv_out.copy_(dv_e)
+        self.dq_loc, self.dk_e, self.dv_e, self.dak = self._dq_out, self._dk_out, self._dv_out, dak
+        if self.n_frecv:
+            torch.index_select(self._gbig, 0, self.ret_pack_rows, out=self.r_send.view((-1,) + self._gbig.shape[1:]))
 
     def _seg_return(self):
         n_send = self.n_fsend
         if self.ret_rows.numel():
-            got = self.r_recv[:, :2]
-            # row i of ret_mat lists positions (in peer order) of the halo part that name own row ret_rows[i]
-            halo_part = torch.cat([got[self.send_pos_kv], got[n_send:]], 0)      # + the all-zero padding row
-            total = _wide(halo_part[self.ret_mat]).sum(1)                        # (targets, 2, h, d) in fp32
-            self.dk_e[self.ret_rows] = (_wide(self.dk_e[self.ret_rows]) + total[:, 0]).to(self.dk_e.dtype)
-            self.dv_e[self.ret_rows] = (_wide(self.dv_e[self.ret_rows]) + total[:, 1]).to(self.dv_e.dtype)
+            # row i of ret_mat_recv lists the positions of the received buffer that name own row ret_rows[i]
+            # (padded with the all-zero last row); dK and dV rows are updated together
+            total = _wide(self.r_recv[self.ret_mat_recv]).sum(1)                 # (targets, 2, h, d) in fp32
+            both = torch.cat([total[:, 0], total[:, 1]], 0)
+            self._gbig[self.ret_rows_kv] = (_wide(self._gbig[self.ret_rows_kv]) + both).to(self._gbig.dtype)
         if self.n_my:
             parts = _wide(self.r_recv[self.my_q_parts, 0])                       # (world, n_my, h, d), rank order
             self.dq_strad.copy_(parts.sum(0))

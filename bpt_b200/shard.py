@@ -531,7 +531,7 @@ class HaloRunner:
         # the all-zero last row]; as positions of the received buffer itself
         halo_pos = torch.cat([self.send_pos_kv, torch.tensor([self.n_fsend], **i64)])
         self.ret_mat_recv = halo_pos[self.ret_mat] if self.ret_rows.numel() else self.ret_mat
-        self.ret_rows_kv = torch.cat([g_dk0 + self.ret_rows.to(torch.int64), g_dv0 + self.ret_rows.to(torch.int64)])
+        self.ret_rows_kv = torch.stack([g_dk0 + self.ret_rows.to(torch.int64), g_dv0 + self.ret_rows.to(torch.int64)], 1)
         self.graphs = bool(graphs) and device.type == "cuda"
         self._g = {}
 
@@ -560,7 +560,7 @@ class HaloRunner:
         self.o_loc, self.lse_loc = self._kernels()[0](self.plan, self.q_loc, self.k_e, self.v_e, self.ak_in, self.scale)
         if self.n_strad:
             n = self.n_strad
-            self.part[:, : self.h * self.d] = self.o_loc[-n:].float().flatten(1)
+            self.part[:, : self.h * self.d].copy_(self.o_loc[-n:].flatten(1))   # widened by the copy
             self.part[:, self.h * self.d:] = self.lse_loc[-n:]
 
     def _seg_merge(self):
@@ -569,10 +569,10 @@ class HaloRunner:
             n, w, hd = self.n_strad, self.shard.world, self.h * self.d
             allp = self.allp.view(w, n, hd + self.h)
             o_r, lse_r = allp[:, :, :hd].view(w, n, self.h, self.d), allp[:, :, hd:]
-            lse = torch.logsumexp(lse_r, 0)
-            wgt = torch.exp(lse_r - lse.unsqueeze(0)).nan_to_num(0.0)
+            # weights exp(lse_r - lse) are the softmax of the ranks' lse (rows no rank has an edge for: all -inf)
+            wgt = torch.softmax(lse_r, 0).nan_to_num_(0.0)
             self.o_loc[-n:] = (wgt.unsqueeze(-1) * o_r).sum(0).to(self.o_loc.dtype)
-            self.lse_loc[-n:] = lse
+            torch.logsumexp(lse_r, 0, out=self.lse_loc[-n:])
 
     def _seg_dout(self):
         if self.n_my:
@@ -605,12 +605,11 @@ class HaloRunner:
         if self.ret_rows.numel():
             # row i of ret_mat_recv lists the positions of the received buffer that name own row ret_rows[i]
             # (padded with the all-zero last row); dK and dV rows are updated together
-            total = _wide(self.r_recv[self.ret_mat_recv]).sum(1)                 # (targets, 2, h, d) in fp32
-            both = torch.cat([total[:, 0], total[:, 1]], 0)
-            self._gbig[self.ret_rows_kv] = (_wide(self._gbig[self.ret_rows_kv]) + both).to(self._gbig.dtype)
+            total = self.r_recv[self.ret_mat_recv].sum(1, dtype=torch.float32)   # (targets, 2, h, d) in fp32
+            self._gbig[self.ret_rows_kv] = (total + self._gbig[self.ret_rows_kv]).to(self._gbig.dtype)
         if self.n_my:
-            parts = _wide(self.r_recv[self.my_q_parts, 0])                       # (world, n_my, h, d), rank order
-            self.dq_strad.copy_(parts.sum(0))
+            parts = self.r_recv[self.my_q_parts, 0]                              # (world, n_my, h, d), rank order
+            self.dq_strad.copy_(parts.sum(0, dtype=torch.float32))
 
     def _run(self, name, fn):
         """Runs a piece eagerly, or captures it in a CUDA graph on first use and replays it afterwards."""
